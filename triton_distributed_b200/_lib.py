@@ -1,0 +1,110 @@
+"""ctypes binding of ``libtdist.so`` (the C ABI is declared in ``csrc/include/tdist.h``).
+
+The library is built in-tree by :mod:`triton_distributed_b200._build`. On a machine with a GPU
+a missing or unloadable library is an error, never a silent fallback: ops that need native code
+call :func:`lib` and raise.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+import threading
+from pathlib import Path
+
+MAX_RANKS = 8
+
+_LIB = None
+_LOCK = threading.Lock()
+
+
+class TdistError(RuntimeError):
+    """A native entry point returned a non-zero code."""
+
+
+class TdistTimeoutError(TdistError):
+    """A bounded device-side wait gave up; the status block says which."""
+
+
+class Status(C.Structure):
+    _fields_ = [
+        ("abort_flag", C.c_int), ("code", C.c_int), ("kernel_id", C.c_int), ("rank", C.c_int),
+        ("peer", C.c_int), ("index", C.c_int), ("expected", C.c_longlong), ("seen", C.c_longlong),
+        ("block", C.c_int), ("where", C.c_int), ("reserved", C.c_int * 4),
+    ]
+
+
+class GemmArgs(C.Structure):
+    _fields_ = [
+        ("a", C.c_void_p),
+        ("a_ws", C.c_void_p),
+        ("a_ws_peer", C.c_void_p * MAX_RANKS),
+        ("b", C.c_void_p),
+        ("c", C.c_void_p),
+        ("c_stage_peer", C.c_void_p * MAX_RANKS),
+        ("rs_out", C.c_void_p),
+        ("flags", C.c_void_p),
+        ("flags_peer", C.c_void_p * MAX_RANKS),
+        ("m_per_rank", C.c_int), ("n", C.c_int), ("k", C.c_int),
+        ("world", C.c_int), ("rank", C.c_int),
+        ("mode", C.c_int), ("dtype", C.c_int),
+        ("epoch", C.c_uint32),
+        ("num_sms", C.c_int), ("num_comm_sms", C.c_int), ("debug_delay_ns", C.c_int),
+        ("status", C.c_void_p),
+        ("timeout_ns", C.c_uint64),
+        ("stream", C.c_void_p),
+    ]
+
+
+GEMM_PLAIN, GEMM_AG, GEMM_RS = 0, 1, 2
+DT_BF16, DT_F16 = 0, 1
+
+
+def lib_path() -> Path:
+    return Path(__file__).resolve().parent / "_C" / "libtdist.so"
+
+
+def available() -> bool:
+    return lib_path().exists()
+
+
+def _declare(lib):
+    lib.tdist_last_error.restype = C.c_char_p
+    lib.tdist_last_error.argtypes = []
+    lib.tdist_status_create.argtypes = [C.POINTER(C.POINTER(Status)), C.POINTER(C.c_void_p)]
+    lib.tdist_status_destroy.argtypes = [C.POINTER(Status)]
+    lib.tdist_gemm_run.argtypes = [C.POINTER(GemmArgs)]
+    lib.tdist_gemm_grid.argtypes = [C.POINTER(GemmArgs)]
+
+
+def lib():
+    """Load (once) and return the native library; build it first if sources are newer."""
+    global _LIB
+    if _LIB is not None:
+        return _LIB
+    with _LOCK:
+        if _LIB is not None:
+            return _LIB
+        path = lib_path()
+        if not path.exists() or os.environ.get("TDIST_REBUILD") == "1":
+            from . import _build
+            _build.build()
+        if not path.exists():
+            raise TdistError(f"native library missing: {path} (run python -m triton_distributed_b200._build)")
+        handle = C.CDLL(str(path), mode=C.RTLD_GLOBAL)
+        _declare(handle)
+        _LIB = handle
+    return _LIB
+
+
+def check(code: int, what: str = "") -> None:
+    if code == 0:
+        return
+    msg = lib().tdist_last_error().decode(errors="replace")
+    raise TdistError(f"{what or 'native call'} failed with code {code}: {msg}")
+
+
+def ptr_array(values) -> "C.Array":
+    arr = (C.c_void_p * MAX_RANKS)()
+    for i, v in enumerate(values):
+        arr[i] = int(v) if v else None
+    return arr

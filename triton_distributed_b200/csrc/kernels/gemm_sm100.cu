@@ -1,0 +1,555 @@
+// Persistent warp-specialised tcgen05 GEMM for sm_100a and its two fused forms.
+//
+//   PLAIN  C[M,N] = A[M,K] * B[N,K]^T
+//   AG     AllGather-GEMM (tensor-parallel column-parallel linear). Each rank holds a row shard
+//          of A; dedicated pusher CTAs of the SAME kernel copy the shard into every peer's
+//          gather workspace 128 rows at a time (bulk-async copies over NVLink) and publish one
+//          flag per 128-row block; the MMA side consumes its own rows first, then the peers'
+//          blocks in arrival order, waiting per block. Plays the role of the reference's
+//          `ag_gemm_intra_node` (python/triton_dist/kernels/nvidia/allgather_gemm.py:131-252,
+//          835-882), where the gather is a copy-engine stream and the wait is per rank.
+//   RS     GEMM-ReduceScatter (row-parallel linear). The epilogue TMA-stores each partial tile
+//          straight into the owning rank's staging slot over NVLink and raises that tile's flag;
+//          once a CTA has finished its GEMM tiles it reduces the tiles this rank owns in fp32 as
+//          their eight partials land. Plays the role of the reference's `gemm_rs`
+//          (python/triton_dist/kernels/nvidia/gemm_reduce_scatter.py:104-232,482-538 and
+//          reduce_scatter.py:527-685), where scatter and reduction are separate streams.
+//
+// Tile 128 x 256 x 64, 4 TMA stages, fp32 accumulators double-buffered in TMEM (2 x 256
+// columns) so the epilogue of tile i overlaps the main loop of tile i+1.
+// Warp roles (192 threads): warp 0 = TMA producer, warp 1 = MMA issuer and TMEM owner,
+// warps 2..5 = epilogue (TMEM -> registers -> swizzled smem -> TMA store).
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+
+#include <string>
+
+#include "../device/ptx.cuh"
+#include "../device/signal.cuh"
+#include "../include/tdist.h"
+#include "../runtime/host_common.h"
+
+namespace tdist {
+
+constexpr int BM = 128;
+constexpr int BN = 256;
+constexpr int BK = 64;
+constexpr int STAGES = 4;
+constexpr int UMMA_K = 16;
+constexpr int A_BYTES = BM * BK * 2;
+constexpr int B_BYTES = BN * BK * 2;
+constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+constexpr int EPI_COLS = 64;                    // columns per epilogue store
+constexpr int EPI_BYTES = BM * EPI_COLS * 2;    // 16 KB
+constexpr int SMEM_TILES = STAGES * STAGE_BYTES + 2 * EPI_BYTES;
+constexpr int SMEM_BYTES = SMEM_TILES + 1024 /*alignment slack*/ + 256 /*barriers*/;
+constexpr int THREADS = 192;
+constexpr int TMEM_COLS = 512;
+constexpr int GROUP_M = 8;
+
+// Pusher pipeline (AG): PUSH_STAGES buffers of PUSH_CHUNK bytes, loads run PUSH_AHEAD chunks
+// ahead of the stores.
+constexpr int PUSH_CHUNK = 32768;
+constexpr int PUSH_STAGES = 7;
+constexpr int PUSH_AHEAD = 5;
+static_assert(PUSH_STAGES * PUSH_CHUNK <= SMEM_TILES, "pusher buffers must fit the tile area");
+
+constexpr int kKernelGemm = 1;
+
+struct GemmParams {
+    CUtensorMap tm_a;       // PLAIN/RS: A as {K, m_per_rank, world}; AG: the gather workspace
+    CUtensorMap tm_a_own;   // AG: this rank's shard as {K, m_per_rank, 1}
+    CUtensorMap tm_b;       // {K, N, 1}
+    CUtensorMap tm_c[kMaxRanks];  // PLAIN/AG: [0] = C as {N, m_per_rank, world}; RS: per owner
+    const char* a_own;            // AG pusher source
+    char* a_ws_peer[kMaxRanks];
+    const char* stage_local;      // RS reduce source [world][m_per_rank][N]
+    void* rs_out;
+    uint32_t* flags;
+    uint32_t* flags_peer[kMaxRanks];
+    int m_per_rank, n, k;
+    int world, rank;
+    int seg_m_tiles, n_tiles, k_blocks;
+    int num_tiles;
+    int num_comm;
+    int is_f16;
+    uint32_t epoch;
+    int debug_delay_ns;
+    WaitCtx wctx;
+};
+
+struct TileCoord {
+    int seg, m_in_seg, n_tile;
+};
+
+// Tiles are ordered segment by segment (a segment = the rows one rank owns), starting at
+// `first_seg`; inside a segment, groups of GROUP_M row-tiles sweep all column-tiles so that
+// concurrently running CTAs share A rows and B columns in L2.
+__device__ __forceinline__ TileCoord decode_tile(int t, int first_seg, int world, int seg_m_tiles,
+                                                 int n_tiles) {
+    const int per_seg = seg_m_tiles * n_tiles;
+    const int si = t / per_seg;
+    int r = t - si * per_seg;
+    TileCoord c;
+    c.seg = first_seg + si;
+    if (c.seg >= world) c.seg -= world;
+    const int group_span = GROUP_M * n_tiles;
+    const int g = r / group_span;
+    r -= g * group_span;
+    const int first_m = g * GROUP_M;
+    const int gsize = min(GROUP_M, seg_m_tiles - first_m);
+    c.n_tile = r / gsize;
+    c.m_in_seg = first_m + (r - c.n_tile * gsize);
+    return c;
+}
+
+// ------------------------------------------------------------------------------------------
+// AG pusher: one thread per pusher CTA streams this rank's shard to the peers.
+// Work items are (destination, 128-row block) pairs ordered by how soon the destination's
+// MMA side reaches this rank's rows (rank-1 first), dealt round-robin to the pusher CTAs.
+// ------------------------------------------------------------------------------------------
+__device__ void ag_pusher(const GemmParams& p, uint8_t* smem, uint64_t* bars) {
+    if (threadIdx.x != 0) return;
+    const int nitems = (p.world - 1) * p.seg_m_tiles;
+    const size_t row_bytes = static_cast<size_t>(p.k) * 2;
+    uint32_t full[PUSH_STAGES];
+    for (int s = 0; s < PUSH_STAGES; ++s) full[s] = smem_u32(&bars[s]);
+    uint32_t it_load = 0, it_store = 0;  // running chunk counters (stage = counter % PUSH_STAGES)
+
+    for (int item = static_cast<int>(blockIdx.x); item < nitems; item += p.num_comm) {
+        const int hop = item / p.seg_m_tiles + 1;
+        const int mb = item - (hop - 1) * p.seg_m_tiles;
+        int dst = p.rank - hop;
+        if (dst < 0) dst += p.world;
+        const int rows = min(BM, p.m_per_rank - mb * BM);
+        const size_t bytes = static_cast<size_t>(rows) * row_bytes;
+        const char* src = p.a_own + static_cast<size_t>(mb) * BM * row_bytes;
+        char* out = p.a_ws_peer[dst] +
+                    (static_cast<size_t>(p.rank) * p.m_per_rank + static_cast<size_t>(mb) * BM) * row_bytes;
+        const int nchunks = static_cast<int>((bytes + PUSH_CHUNK - 1) / PUSH_CHUNK);
+        if (p.debug_delay_ns > 0) __nanosleep(p.debug_delay_ns);
+
+        for (int c = 0; c < nchunks + PUSH_AHEAD; ++c) {
+            if (c < nchunks) {
+                const uint32_t s = it_load % PUSH_STAGES;
+                // The store that last used this buffer was issued PUSH_STAGES chunks ago; at most
+                // PUSH_STAGES - PUSH_AHEAD - 1 younger stores may still be reading smem.
+                if (it_load >= PUSH_STAGES) bulk_wait_read<PUSH_STAGES - PUSH_AHEAD - 1>();
+                const size_t off = static_cast<size_t>(c) * PUSH_CHUNK;
+                const uint32_t sz = static_cast<uint32_t>(min(static_cast<size_t>(PUSH_CHUNK), bytes - off));
+                mbar_expect_tx(full[s], sz);
+                bulk_load(smem_u32(smem + s * PUSH_CHUNK), src + off, sz, full[s]);
+                ++it_load;
+            }
+            if (c >= PUSH_AHEAD) {
+                const int cs = c - PUSH_AHEAD;
+                const uint32_t s = it_store % PUSH_STAGES;
+                mbar_wait(full[s], (it_store / PUSH_STAGES) & 1u, p.wctx, 10);
+                const size_t off = static_cast<size_t>(cs) * PUSH_CHUNK;
+                const uint32_t sz = static_cast<uint32_t>(min(static_cast<size_t>(PUSH_CHUNK), bytes - off));
+                bulk_store(out + off, smem_u32(smem + s * PUSH_CHUNK), sz);
+                bulk_commit();
+                ++it_store;
+            }
+        }
+        // Block complete at the destination before its flag: wait for the writes themselves,
+        // then order them (async proxy) before the system-scope release store (generic proxy).
+        bulk_wait<0>();
+        fence_proxy_async();
+        fence_acq_rel_sys();
+        st_release_sys_u32(p.flags_peer[dst] + p.rank * p.seg_m_tiles + mb, p.epoch);
+    }
+}
+
+// ------------------------------------------------------------------------------------------
+// RS reduce: sum the `world` partial copies of one owned tile in fp32, write bf16/f16.
+// ------------------------------------------------------------------------------------------
+__device__ __forceinline__ void rs_reduce_tile(const GemmParams& p, int m_in_seg, int n_tile) {
+    const int row0 = m_in_seg * BM;
+    const int col0 = n_tile * BN;
+    const int rows = min(BM, p.m_per_rank - row0);
+    const int cols = min(BN, p.n - col0);
+    const int vec_per_row = cols / 8;  // N % 8 == 0 is checked on the host
+    const int nvec = rows * vec_per_row;
+    const size_t slot = static_cast<size_t>(p.m_per_rank) * p.n;  // elements per source slot
+    for (int v = static_cast<int>(threadIdx.x); v < nvec; v += THREADS) {
+        const int r = v / vec_per_row;
+        const int cv = v - r * vec_per_row;
+        const size_t off = static_cast<size_t>(row0 + r) * p.n + col0 + cv * 8;
+        float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+        for (int s = 0; s < p.world; ++s) {
+            const uint4 q = *reinterpret_cast<const uint4*>(p.stage_local + (s * slot + off) * 2);
+            const uint32_t w[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                if (p.is_f16) {
+                    const __half2 h = *reinterpret_cast<const __half2*>(&w[i]);
+                    const float2 f = __half22float2(h);
+                    acc[2 * i] += f.x;
+                    acc[2 * i + 1] += f.y;
+                } else {
+                    acc[2 * i] += __uint_as_float(w[i] << 16);
+                    acc[2 * i + 1] += __uint_as_float(w[i] & 0xffff0000u);
+                }
+            }
+        }
+        uint4 o;
+        uint32_t* ow = reinterpret_cast<uint32_t*>(&o);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            if (p.is_f16) {
+                const __half2 h = __floats2half2_rn(acc[2 * i], acc[2 * i + 1]);
+                ow[i] = *reinterpret_cast<const uint32_t*>(&h);
+            } else {
+                ow[i] = pack_bf16x2(acc[2 * i], acc[2 * i + 1]);
+            }
+        }
+        *reinterpret_cast<uint4*>(static_cast<char*>(p.rs_out) + off * 2) = o;
+    }
+}
+
+template <int MODE>
+__global__ void __launch_bounds__(THREADS, 1) gemm_sm100_kernel(const __grid_constant__ GemmParams p) {
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + SMEM_TILES);
+    // barrier slots: [0,S) full, [S,2S) empty, [2S,2S+2) tmem_full, [2S+2,2S+4) tmem_empty
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 4);
+
+    const int warp = static_cast<int>(threadIdx.x) >> 5;
+    const int lane = static_cast<int>(threadIdx.x) & 31;
+
+    // ---------------- pusher CTAs (AG only) ----------------
+    if (MODE == TDIST_GEMM_AG && static_cast<int>(blockIdx.x) < p.num_comm) {
+        if (threadIdx.x == 0) {
+            for (int s = 0; s < PUSH_STAGES; ++s) mbar_init(smem_u32(&bars[s]), 1);
+            fence_mbar_init();
+        }
+        __syncthreads();
+        ag_pusher(p, smem, bars);
+        return;
+    }
+
+    const int cta = static_cast<int>(blockIdx.x) - p.num_comm;
+    const int num_cta = static_cast<int>(gridDim.x) - p.num_comm;
+    const int first_seg = (MODE == TDIST_GEMM_RS) ? (p.rank + 1) % p.world : p.rank;
+
+    if (threadIdx.x == 0) {
+        prefetch_tensormap(&p.tm_a);
+        prefetch_tensormap(&p.tm_b);
+        if (MODE == TDIST_GEMM_AG) prefetch_tensormap(&p.tm_a_own);
+        for (int s = 0; s < STAGES; ++s) {
+            mbar_init(smem_u32(&bars[s]), 1);
+            mbar_init(smem_u32(&bars[STAGES + s]), 1);
+        }
+        for (int b = 0; b < 2; ++b) {
+            mbar_init(smem_u32(&bars[2 * STAGES + b]), 1);
+            mbar_init(smem_u32(&bars[2 * STAGES + 2 + b]), 128);
+        }
+        fence_mbar_init();
+    }
+    if (warp == 1) {
+        tmem_alloc<1>(smem_u32(tmem_slot), TMEM_COLS);
+        tmem_relinquish<1>();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(tmem_slot);
+
+    if (warp == 0) {
+        // ===================== TMA producer =====================
+        if (lane == 0) {
+            uint32_t it = 0;
+            for (int t = cta; t < p.num_tiles; t += num_cta) {
+                const TileCoord tc = decode_tile(t, first_seg, p.world, p.seg_m_tiles, p.n_tiles);
+                const CUtensorMap* am = &p.tm_a;
+                int az = tc.seg;
+                if (MODE == TDIST_GEMM_AG) {
+                    if (tc.seg == p.rank) {
+                        am = &p.tm_a_own;
+                        az = 0;
+                    } else {
+                        wait_flag_ge_sys(p.flags + tc.seg * p.seg_m_tiles + tc.m_in_seg, p.epoch, p.wctx,
+                                         tc.seg, tc.m_in_seg, 1);
+                        fence_proxy_async();
+                    }
+                }
+                const int row = tc.m_in_seg * BM;
+                const int col = tc.n_tile * BN;
+                for (int kb = 0; kb < p.k_blocks; ++kb, ++it) {
+                    const uint32_t s = it % STAGES;
+                    mbar_wait(smem_u32(&bars[STAGES + s]), ((it / STAGES) & 1u) ^ 1u, p.wctx, 2);
+                    const uint32_t full = smem_u32(&bars[s]);
+                    mbar_expect_tx(full, STAGE_BYTES);
+                    const uint32_t sa = smem_u32(smem + s * STAGE_BYTES);
+                    tma_load_3d(sa, am, full, kb * BK, row, az);
+                    tma_load_3d(sa + A_BYTES, &p.tm_b, full, kb * BK, col, 0);
+                }
+            }
+        }
+        __syncwarp();
+    } else if (warp == 1) {
+        // ===================== MMA issuer =====================
+        if (lane == 0) {
+            const uint32_t idesc = umma_idesc(p.is_f16 ? 0u : 1u, p.is_f16 ? 0u : 1u, BM, BN);
+            uint32_t it = 0;
+            uint32_t local_tile = 0;
+            for (int t = cta; t < p.num_tiles; t += num_cta, ++local_tile) {
+                const uint32_t buf = local_tile & 1u;
+                mbar_wait(smem_u32(&bars[2 * STAGES + 2 + buf]), ((local_tile >> 1) & 1u) ^ 1u, p.wctx, 3);
+                tc_fence_after();
+                const uint32_t d_tmem = tmem_base + buf * BN;
+                for (int kb = 0; kb < p.k_blocks; ++kb, ++it) {
+                    const uint32_t s = it % STAGES;
+                    mbar_wait(smem_u32(&bars[s]), (it / STAGES) & 1u, p.wctx, 4);
+                    tc_fence_after();
+                    const uint32_t sa = smem_u32(smem + s * STAGE_BYTES);
+                    const uint64_t adesc = umma_desc_k_sw128(sa);
+                    const uint64_t bdesc = umma_desc_k_sw128(sa + A_BYTES);
+#pragma unroll
+                    for (int k = 0; k < BK / UMMA_K; ++k) {
+                        // 16 elements of K = 32 bytes = 2 descriptor address units
+                        umma_bf16<1>(d_tmem, adesc + 2 * k, bdesc + 2 * k, idesc, (kb | k) != 0 ? 1u : 0u);
+                    }
+                    umma_commit(smem_u32(&bars[STAGES + s]));  // frees the smem stage when the MMAs retire
+                }
+                umma_commit(smem_u32(&bars[2 * STAGES + buf]));  // accumulator ready
+            }
+        }
+        __syncwarp();
+    } else {
+        // ===================== epilogue (warps 2..5) =====================
+        const int q = warp & 3;                 // TMEM lane quadrant this warp may read
+        const int row_in_tile = q * 32 + lane;
+        const bool issuer = (warp == 2 && lane == 0);
+        uint8_t* cstage = smem + STAGES * STAGE_BYTES;
+        uint32_t local_tile = 0;
+        for (int t = cta; t < p.num_tiles; t += num_cta, ++local_tile) {
+            const TileCoord tc = decode_tile(t, first_seg, p.world, p.seg_m_tiles, p.n_tiles);
+            const uint32_t buf = local_tile & 1u;
+            mbar_wait(smem_u32(&bars[2 * STAGES + buf]), (local_tile >> 1) & 1u, p.wctx, 5);
+            tc_fence_after();
+            const CUtensorMap* cm = (MODE == TDIST_GEMM_RS) ? &p.tm_c[tc.seg] : &p.tm_c[0];
+            const int cz = (MODE == TDIST_GEMM_RS) ? p.rank : tc.seg;
+            const int row = tc.m_in_seg * BM;
+            const int col = tc.n_tile * BN;
+#pragma unroll 1
+            for (int c = 0; c < BN / EPI_COLS; ++c) {
+                uint32_t r0[32], r1[32];
+                const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + buf * BN + c * EPI_COLS;
+                tmem_ld_32x32(taddr, r0);
+                tmem_ld_32x32(taddr + 32, r1);
+                tmem_ld_wait();
+                if (c == BN / EPI_COLS - 1) {
+                    // accumulator fully read: hand the TMEM buffer back to the MMA warp
+                    tc_fence_before();
+                    mbar_arrive(smem_u32(&bars[2 * STAGES + 2 + buf]));
+                }
+                uint8_t* cs = cstage + (c & 1) * EPI_BYTES;
+                named_barrier(1, 128);  // the store that last read this buffer has drained
+                uint8_t* rowp = cs + row_in_tile * 128;
+                const int sw = row_in_tile & 7;
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    uint4 v0, v1;
+                    if (p.is_f16) {
+                        __half2 h;
+                        h = __floats2half2_rn(__uint_as_float(r0[8 * j + 0]), __uint_as_float(r0[8 * j + 1])); v0.x = *reinterpret_cast<uint32_t*>(&h);
+                        h = __floats2half2_rn(__uint_as_float(r0[8 * j + 2]), __uint_as_float(r0[8 * j + 3])); v0.y = *reinterpret_cast<uint32_t*>(&h);
+                        h = __floats2half2_rn(__uint_as_float(r0[8 * j + 4]), __uint_as_float(r0[8 * j + 5])); v0.z = *reinterpret_cast<uint32_t*>(&h);
+                        h = __floats2half2_rn(__uint_as_float(r0[8 * j + 6]), __uint_as_float(r0[8 * j + 7])); v0.w = *reinterpret_cast<uint32_t*>(&h);
+                        h = __floats2half2_rn(__uint_as_float(r1[8 * j + 0]), __uint_as_float(r1[8 * j + 1])); v1.x = *reinterpret_cast<uint32_t*>(&h);
+                        h = __floats2half2_rn(__uint_as_float(r1[8 * j + 2]), __uint_as_float(r1[8 * j + 3])); v1.y = *reinterpret_cast<uint32_t*>(&h);
+                        h = __floats2half2_rn(__uint_as_float(r1[8 * j + 4]), __uint_as_float(r1[8 * j + 5])); v1.z = *reinterpret_cast<uint32_t*>(&h);
+                        h = __floats2half2_rn(__uint_as_float(r1[8 * j + 6]), __uint_as_float(r1[8 * j + 7])); v1.w = *reinterpret_cast<uint32_t*>(&h);
+                    } else {
+                        v0.x = pack_bf16x2(__uint_as_float(r0[8 * j + 0]), __uint_as_float(r0[8 * j + 1]));
+                        v0.y = pack_bf16x2(__uint_as_float(r0[8 * j + 2]), __uint_as_float(r0[8 * j + 3]));
+                        v0.z = pack_bf16x2(__uint_as_float(r0[8 * j + 4]), __uint_as_float(r0[8 * j + 5]));
+                        v0.w = pack_bf16x2(__uint_as_float(r0[8 * j + 6]), __uint_as_float(r0[8 * j + 7]));
+                        v1.x = pack_bf16x2(__uint_as_float(r1[8 * j + 0]), __uint_as_float(r1[8 * j + 1]));
+                        v1.y = pack_bf16x2(__uint_as_float(r1[8 * j + 2]), __uint_as_float(r1[8 * j + 3]));
+                        v1.z = pack_bf16x2(__uint_as_float(r1[8 * j + 4]), __uint_as_float(r1[8 * j + 5]));
+                        v1.w = pack_bf16x2(__uint_as_float(r1[8 * j + 6]), __uint_as_float(r1[8 * j + 7]));
+                    }
+                    // 16-byte chunk index inside the 128-byte row, XOR-swizzled with the row
+                    *reinterpret_cast<uint4*>(rowp + ((j ^ sw) << 4)) = v0;
+                    *reinterpret_cast<uint4*>(rowp + (((4 + j) ^ sw) << 4)) = v1;
+                }
+                fence_proxy_async_smem();
+                named_barrier(1, 128);  // the staging buffer is complete
+                if (issuer) {
+                    if (col + c * EPI_COLS < p.n) {
+                        tma_store_3d(cm, smem_u32(cs), col + c * EPI_COLS, row, cz);
+                        bulk_commit();
+                    }
+                    bulk_wait_read<1>();
+                }
+            }
+            if (MODE == TDIST_GEMM_RS && issuer) {
+                // The partial tile has to be complete at its owner before the flag is.
+                bulk_wait<0>();
+                fence_proxy_async();
+                fence_acq_rel_sys();
+                const int tile_in_seg = tc.m_in_seg * p.n_tiles + tc.n_tile;
+                st_release_sys_u32(p.flags_peer[tc.seg] + tile_in_seg * p.world + p.rank, p.epoch);
+            }
+        }
+        if (issuer) bulk_wait<0>();
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) tmem_dealloc<1>(tmem_base, TMEM_COLS);
+
+    if (MODE == TDIST_GEMM_RS) {
+        // ===================== reduce the tiles this rank owns =====================
+        const int own_tiles = p.seg_m_tiles * p.n_tiles;
+        for (int ti = cta; ti < own_tiles; ti += num_cta) {
+            if (warp == 0) {
+                if (lane < p.world)
+                    wait_flag_ge_sys(p.flags + ti * p.world + lane, p.epoch, p.wctx, lane, ti, 6);
+            }
+            __syncthreads();
+            rs_reduce_tile(p, ti / p.n_tiles, ti % p.n_tiles);
+        }
+    }
+}
+
+}  // namespace tdist
+
+// ============================================================================================
+// host side
+// ============================================================================================
+using namespace tdist;
+using tdist_host::fail;
+
+static int plan_grid(const TdistGemmArgs* a, int* num_comm_out, int* num_tiles_out) {
+    const int seg_m_tiles = (a->m_per_rank + BM - 1) / BM;
+    const int n_tiles = (a->n + BN - 1) / BN;
+    const int num_tiles = seg_m_tiles * n_tiles * a->world;
+    int sms = a->num_sms > 0 ? a->num_sms : tdist_host::sm_count();
+    int num_comm = 0;
+    if (a->mode == TDIST_GEMM_AG && a->world > 1) {
+        num_comm = a->num_comm_sms > 0 ? a->num_comm_sms : 8;
+        if (num_comm > sms - 1) num_comm = sms - 1;
+    }
+    int gemm_ctas = sms - num_comm;
+    if (gemm_ctas > num_tiles) gemm_ctas = num_tiles;
+    if (gemm_ctas < 1) gemm_ctas = 1;
+    if (num_comm_out) *num_comm_out = num_comm;
+    if (num_tiles_out) *num_tiles_out = num_tiles;
+    return gemm_ctas + num_comm;
+}
+
+extern "C" int tdist_gemm_grid(const TdistGemmArgs* a) { return plan_grid(a, nullptr, nullptr); }
+
+extern "C" int tdist_gemm_run(const TdistGemmArgs* a) {
+    if (a == nullptr) return fail(TDIST_EINVAL, "null args");
+    if (a->world < 1 || a->world > TDIST_MAX_RANKS || a->rank < 0 || a->rank >= a->world)
+        return fail(TDIST_EINVAL, "world/rank out of range (at most 8 ranks)");
+    if (a->m_per_rank < 1 || a->n < 1 || a->k < 1) return fail(TDIST_EINVAL, "empty problem");
+    if (a->k % 8 != 0 || a->n % 8 != 0)
+        return fail(TDIST_EINVAL, "K and N must be multiples of 8 (16-byte rows for TMA)");
+    if (a->mode < TDIST_GEMM_PLAIN || a->mode > TDIST_GEMM_RS) return fail(TDIST_EINVAL, "bad mode");
+
+    GemmParams p;
+    memset(&p, 0, sizeof(p));
+    const CUtensorMapDataType dt = a->dtype == TDIST_F16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
+    const uint64_t K = a->k, N = a->n, MPR = a->m_per_rank, W = a->world;
+    int rc;
+    {
+        // A (or the gather workspace): {K, m_per_rank, world}
+        const void* base = a->mode == TDIST_GEMM_AG ? a->a_ws : a->a;
+        if (a->mode == TDIST_GEMM_AG && a->world == 1) base = a->a;
+        if (base == nullptr) return fail(TDIST_EINVAL, "A / workspace pointer is null");
+        uint64_t dims[3] = {K, MPR, W};
+        uint64_t strides[2] = {K * 2, MPR * K * 2};
+        uint32_t box[3] = {BK, BM, 1};
+        if ((rc = tdist_host::encode_tmap(&p.tm_a, dt, 2, 3, base, dims, strides, box, tdist_host::Swizzle::B128))) return rc;
+    }
+    if (a->mode == TDIST_GEMM_AG) {
+        uint64_t dims[3] = {K, MPR, 1};
+        uint64_t strides[2] = {K * 2, MPR * K * 2};
+        uint32_t box[3] = {BK, BM, 1};
+        if ((rc = tdist_host::encode_tmap(&p.tm_a_own, dt, 2, 3, a->a, dims, strides, box, tdist_host::Swizzle::B128))) return rc;
+    }
+    {
+        uint64_t dims[3] = {K, N, 1};
+        uint64_t strides[2] = {K * 2, N * K * 2};
+        uint32_t box[3] = {BK, BN, 1};
+        if ((rc = tdist_host::encode_tmap(&p.tm_b, dt, 2, 3, a->b, dims, strides, box, tdist_host::Swizzle::B128))) return rc;
+    }
+    {
+        uint64_t dims[3] = {N, MPR, W};
+        uint64_t strides[2] = {N * 2, MPR * N * 2};
+        uint32_t box[3] = {EPI_COLS, BM, 1};
+        if (a->mode == TDIST_GEMM_RS) {
+            for (int r = 0; r < a->world; ++r) {
+                if (a->c_stage_peer[r] == nullptr) return fail(TDIST_EINVAL, "RS staging pointer is null");
+                if ((rc = tdist_host::encode_tmap(&p.tm_c[r], dt, 2, 3, a->c_stage_peer[r], dims, strides, box, tdist_host::Swizzle::B128))) return rc;
+            }
+        } else {
+            if (a->c == nullptr) return fail(TDIST_EINVAL, "C pointer is null");
+            if ((rc = tdist_host::encode_tmap(&p.tm_c[0], dt, 2, 3, a->c, dims, strides, box, tdist_host::Swizzle::B128))) return rc;
+        }
+    }
+    p.a_own = static_cast<const char*>(a->a);
+    for (int r = 0; r < a->world; ++r) {
+        p.a_ws_peer[r] = static_cast<char*>(a->a_ws_peer[r]);
+        p.flags_peer[r] = a->flags_peer[r];
+    }
+    p.stage_local = static_cast<const char*>(a->c_stage_peer[a->rank]);
+    p.rs_out = a->rs_out;
+    p.flags = a->flags;
+    p.m_per_rank = a->m_per_rank;
+    p.n = a->n;
+    p.k = a->k;
+    p.world = a->world;
+    p.rank = a->rank;
+    p.seg_m_tiles = (a->m_per_rank + BM - 1) / BM;
+    p.n_tiles = (a->n + BN - 1) / BN;
+    p.k_blocks = (a->k + BK - 1) / BK;
+    p.is_f16 = a->dtype == TDIST_F16;
+    p.epoch = a->epoch;
+    p.debug_delay_ns = a->debug_delay_ns;
+    p.wctx.status = static_cast<Status*>(a->status);
+    p.wctx.timeout_ns = a->timeout_ns;
+    p.wctx.kernel_id = kKernelGemm;
+    p.wctx.rank = a->rank;
+    const int grid = plan_grid(a, &p.num_comm, &p.num_tiles);
+
+    if (a->mode == TDIST_GEMM_AG && a->world > 1) {
+        if (a->flags == nullptr) return fail(TDIST_EINVAL, "AG needs flags");
+        for (int r = 0; r < a->world; ++r)
+            if (a->a_ws_peer[r] == nullptr || a->flags_peer[r] == nullptr)
+                return fail(TDIST_EINVAL, "AG needs the workspace and flags of every rank");
+    }
+    if (a->mode == TDIST_GEMM_RS) {
+        if (a->flags == nullptr || a->rs_out == nullptr) return fail(TDIST_EINVAL, "RS needs flags and rs_out");
+        for (int r = 0; r < a->world; ++r)
+            if (a->flags_peer[r] == nullptr) return fail(TDIST_EINVAL, "RS needs the flags of every rank");
+    }
+
+    cudaStream_t stream = static_cast<cudaStream_t>(a->stream);
+    static bool attr_set[64][3] = {};
+    int dev = 0;
+    TDIST_CUDA_OK(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= 64) return fail(TDIST_EINVAL, "device ordinal out of range");
+    const void* fn = nullptr;
+    switch (a->mode) {
+        case TDIST_GEMM_PLAIN: fn = reinterpret_cast<const void*>(&gemm_sm100_kernel<TDIST_GEMM_PLAIN>); break;
+        case TDIST_GEMM_AG: fn = reinterpret_cast<const void*>(&gemm_sm100_kernel<TDIST_GEMM_AG>); break;
+        default: fn = reinterpret_cast<const void*>(&gemm_sm100_kernel<TDIST_GEMM_RS>); break;
+    }
+    if (!attr_set[dev][a->mode]) {
+        TDIST_CUDA_OK(cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
+        attr_set[dev][a->mode] = true;
+    }
+    void* kargs[] = {&p};
+    TDIST_CUDA_OK(cudaLaunchKernel(fn, dim3(grid), dim3(THREADS), kargs, SMEM_BYTES, stream));
+    return 0;
+}
