@@ -1,0 +1,121 @@
+"""tcgen05 GEMM family on one GPU: plain GEMM numerics, and the fused AG / RS kernels of one
+emulated rank at a time against peer buffers prepared by the host (LocalWorld).
+
+Oracle: plain PyTorch fp32 matmul of the same operands. Mirrors the reference's
+test_ag_gemm_intra_node.py / test_gemm_rs.py checks (non-tile-aligned M, stale workspace poisoning)
+without needing several GPUs.
+"""
+import pytest
+import torch
+
+from triton_distributed_b200 import _lib
+from triton_distributed_b200.ops import gemm as G
+from triton_distributed_b200.runtime import LocalWorld, check_status, global_status
+
+pytestmark = pytest.mark.gpu
+
+
+def _rand(shape, dtype, dev, scale=1.0):
+    return (torch.randn(shape, device=dev, dtype=torch.float32) * scale).to(dtype)
+
+
+@pytest.mark.parametrize("M,N,K", [(128, 256, 64), (256, 512, 512), (300, 264, 136), (1000, 1000, 992), (4096, 768, 2048)])
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+def test_plain_gemm_matches_fp32_reference(cuda_device, M, N, K, dtype):
+    torch.manual_seed(M + N + K)
+    a = _rand((M, K), dtype, cuda_device)
+    b = _rand((N, K), dtype, cuda_device, K ** -0.5)
+    c = G.gemm_persistent(a, b)
+    check_status()
+    ref = a.float() @ b.float().t()
+    tol = 2e-2 if dtype == torch.bfloat16 else 4e-3
+    assert torch.isfinite(c).all()
+    torch.testing.assert_close(c.float(), ref, atol=tol, rtol=tol)
+
+
+@pytest.mark.parametrize("world,mpr,N,K", [(2, 128, 256, 128), (4, 250, 520, 264), (8, 96, 256, 512), (4, 999, 768, 1024)])
+def test_ag_gemm_single_rank_kernels_against_prepared_peers(cuda_device, world, mpr, N, K):
+    """Each emulated rank's fused kernel runs alone: blocks of lower ranks were really pushed by
+    their kernels, blocks of higher ranks are written by the host together with their flags."""
+    torch.manual_seed(world * 1000 + mpr)
+    dtype = torch.bfloat16
+    lw = LocalWorld(world, cuda_device)
+    A = [_rand((mpr, K), dtype, cuda_device) for _ in range(world)]
+    B = [_rand((N, K), dtype, cuda_device, K ** -0.5) for _ in range(world)]
+    ctxs = [G.create_ag_gemm_intra_node_context(A[r], B[r], r, world, max_M=world * mpr + 64, heap=lw.heap(r))
+            for r in range(world)]
+    full = torch.cat(A).float()
+    mt = (mpr + 127) // 128
+    for r in range(world):
+        ctx = ctxs[r]
+        half = (ctx.epoch + 1) & 1
+        ws = ctx.workspace.local[half][: world * mpr * K].view(world, mpr, K)
+        flags = ctx.flags.local[half][: world * mt].view(world, mt)
+        # poison what no kernel has written yet, then stand in for the ranks that have not run
+        for s in range(r + 1, world):
+            ws[s].copy_(A[s])
+            flags[s].fill_(ctx.epoch + 1)
+        ws[r].fill_(float("nan"))  # own slot is never read from the workspace
+        c = G.ag_gemm_intra_node(A[r], B[r], ctx)
+        check_status()
+        ref = full @ B[r].float().t()
+        torch.testing.assert_close(c.float(), ref, atol=2e-2, rtol=2e-2)
+    # every rank's shard was pushed to every other rank, with its flags
+    for r in range(world):
+        ws = ctxs[r].workspace.local[1][: world * mpr * K].view(world, mpr, K)
+        flags = ctxs[r].flags.local[1][: world * mt].view(world, mt)
+        for s in range(world):
+            if s == r:
+                continue
+            assert torch.equal(ws[s], A[s]), f"rank {r} workspace slot {s}"
+            assert (flags[s] == 1).all()
+
+
+@pytest.mark.parametrize("world,mpr,N,K", [(2, 128, 256, 128), (4, 250, 520, 264), (8, 96, 512, 256), (4, 512, 1024, 512)])
+def test_gemm_rs_single_rank_kernels_against_prepared_peers(cuda_device, world, mpr, N, K):
+    torch.manual_seed(world * 77 + mpr)
+    dtype = torch.bfloat16
+    lw = LocalWorld(world, cuda_device)
+    M = world * mpr
+    A = [_rand((M, K), dtype, cuda_device) for _ in range(world)]
+    B = [_rand((N, K), dtype, cuda_device, (K * world) ** -0.5) for _ in range(world)]
+    partial = [(A[s].float() @ B[s].float().t()) for s in range(world)]
+    total = sum(partial)
+    ctxs = [G.create_gemm_rs_context(M + 8, N, r, world, heap=lw.heap(r), device=cuda_device) for r in range(world)]
+    tiles = ((mpr + 127) // 128) * ((N + 255) // 256)
+    for r in range(world):
+        ctx = ctxs[r]
+        half = (ctx.epoch + 1) & 1
+        stage = ctx.staging.local[half][: world * mpr * N].view(world, mpr, N)
+        flags = ctx.flags.local[half][: tiles * world].view(tiles, world)
+        for s in range(r + 1, world):
+            stage[s].copy_(partial[s][r * mpr:(r + 1) * mpr].to(dtype))
+            flags[:, s].fill_(ctx.epoch + 1)
+        out = G.gemm_rs(A[r], B[r], ctx)
+        check_status()
+        ref = total[r * mpr:(r + 1) * mpr]
+        torch.testing.assert_close(out.float(), ref, atol=3e-2, rtol=3e-2)
+
+
+def test_abandoned_wait_reports_timeout_and_leaves_the_context_usable(cuda_device, monkeypatch):
+    """A flag that nothing sets: the kernel must give up after its limit, report which flag it was
+    waiting for, and return, and the next launch must work."""
+    monkeypatch.setenv("TDIST_WAIT_TIMEOUT_MS", "50")
+    dtype = torch.bfloat16
+    lw = LocalWorld(2, cuda_device)
+    a = _rand((128, 128), dtype, cuda_device)
+    b = _rand((256, 128), dtype, cuda_device)
+    ctx = G.create_ag_gemm_intra_node_context(a, b, 0, 2, max_M=256, heap=lw.heap(0))
+    G.create_ag_gemm_intra_node_context(a, b, 1, 2, max_M=256, heap=lw.heap(1))
+    G.ag_gemm_intra_node(a, b, ctx)
+    torch.cuda.synchronize()
+    st = global_status()
+    assert st.aborted()
+    rec = st.record
+    assert rec.code == 1 and rec.peer == 1 and rec.expected == 1
+    with pytest.raises(_lib.TdistTimeoutError):
+        check_status()
+    # the context is still usable
+    c = G.gemm_persistent(a, b)
+    check_status()
+    torch.testing.assert_close(c.float(), a.float() @ b.float().t(), atol=2e-2, rtol=2e-2)
