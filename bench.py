@@ -1,0 +1,249 @@
+"""Headline benchmark: tensor-parallel AllGather-GEMM on the BASELINE shape.
+
+    python bench.py --gpus N --steps K --warmup W           (N=1)
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 \
+        --master-port P bench.py --gpus N --steps K --warmup W
+
+Problem (fixed as N grows = strong scaling): A [8192, 12288] row-sharded over the N ranks,
+B [12288, 49152] column-sharded (held as [49152/N, 12288], K contiguous), bf16 with fp32
+accumulation, C = allgather(A) @ B_shard^T -> [8192, 49152/N] per rank. `value` is the aggregate
+TFLOP/s of the whole job: 2*8192*49152*12288 FLOP / (max-over-ranks device time of one step).
+
+One step = one call of the public op `ag_gemm_intra_node` = ONE fused kernel launch (the gather
+is done inside the kernel over NVLink). Timing: CUDA events on the launching stream around K
+back-to-back steps, barrier + synchronize on both sides, max over ranks. The operands of a step
+(B shard >= 151 MB, plus A and C) exceed the 126 MB L2, so no explicit flush is needed.
+
+Extra keys: `e2e` repeats the measurement with, every step, the host->device copy of the step's
+A shard from pinned memory and a device->host read of a slice of the result; `torch_baseline` is
+the non-overlapped NCCL all_gather + cuBLAS matmul on the same box; `extra` holds GEMM-RS.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+M_TOTAL, N_TOTAL, K_TOTAL = 8192, 49152, 12288
+REFERENCE_PUBLISHED_SPEEDUP = 1.36  # AG-GEMM m8192 n49152 k12288 vs PyTorch+NCCL, 16xH800 (reference README.md:155-156)
+
+
+class ClockSampler:
+    """Samples SM clock and throttle reasons of one GPU with nvidia-smi while a region runs."""
+
+    QUERY = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+             "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+             "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index = index
+        self.proc = None
+        self.lines = []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits", "-lms", "100"],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            threading.Thread(target=self._pump, daemon=True).start()
+        except OSError:
+            self.proc = None
+
+    def _pump(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self) -> dict:
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, mx, pw, reasons = [], [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in self.lines:
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) < 7:
+                continue
+            try:
+                sm.append(float(parts[0]))
+                mx.append(float(parts[1]))
+                pw.append(float(parts[2]))
+            except ValueError:
+                continue
+            for name, val in zip(names, parts[3:7]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        busy = [s for s, p in zip(sm, pw) if p > 300] or sm
+        return {"sm_mhz": statistics.median(busy) if busy else None, "sm_max_mhz": max(mx) if mx else None,
+                "power_w_max": max(pw) if pw else None, "samples": len(sm), "reasons": sorted(reasons)}
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--no-extra", action="store_true", help="skip the GEMM-RS / torch-baseline side measurements")
+    args = ap.parse_args()
+
+    if args.impl == "reference":
+        print(json.dumps({"impl": "reference",
+                          "unavailable": "reference cannot be installed offline: its setup downloads Triton/LLVM and needs "
+                                         "NVSHMEM sources (pip install of /root/reference fails at metadata generation, no network)"}))
+        return 0
+
+    import torch
+    import torch.distributed as dist
+
+    from triton_distributed_b200.ops import gemm as G
+    from triton_distributed_b200.runtime import check_status, finalize_distributed, initialize_distributed
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    if world != args.gpus:
+        if world == 1 and args.gpus > 1:
+            # convenience: re-launch under torchrun
+            cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={args.gpus}",
+                   "--master-addr", "127.0.0.1", "--master-port", "29533", os.path.abspath(__file__), *sys.argv[1:]]
+            return subprocess.call(cmd)
+        raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}")
+    W = max(3, args.warmup)
+    K_STEPS = max(1, args.steps)
+
+    group = initialize_distributed(seed=0)
+    rank = dist.get_rank()
+    dev = torch.device("cuda", torch.cuda.current_device())
+    mpr, npr = M_TOTAL // world, N_TOTAL // world
+    gen = torch.Generator(device=dev).manual_seed(rank)
+    a = torch.randn(mpr, K_TOTAL, device=dev, dtype=torch.bfloat16, generator=gen)
+    b = (torch.randn(npr, K_TOTAL, device=dev, dtype=torch.float32, generator=gen) * K_TOTAL ** -0.5).to(torch.bfloat16)
+    c = torch.empty(M_TOTAL, npr, device=dev, dtype=torch.bfloat16)
+    ctx = G.create_ag_gemm_intra_node_context(a, b, rank, world, max_M=M_TOTAL, group=group)
+    flops = 2.0 * M_TOTAL * N_TOTAL * K_TOTAL
+
+    def sync():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier(group)
+            torch.cuda.synchronize()
+
+    def timed(fn, steps, warmup):
+        for _ in range(warmup):
+            fn()
+        sync()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(steps):
+            fn()
+        e1.record()
+        sync()
+        ms = torch.tensor([e0.elapsed_time(e1) / steps], device=dev)
+        if world > 1:
+            dist.all_reduce(ms, op=dist.ReduceOp.MAX, group=group)
+        return float(ms.item())
+
+    # ---- correctness guard (one step against torch) so a wrong kernel never reports a number
+    out = G.ag_gemm_intra_node(a, b, ctx, out=c)
+    check_status()
+    gathered = torch.empty(M_TOTAL, K_TOTAL, device=dev, dtype=torch.bfloat16)
+    if world > 1:
+        dist.all_gather_into_tensor(gathered, a, group=group)
+    else:
+        gathered.copy_(a)
+    ref_rows = gathered[::257].float() @ b.float().t()
+    err = (out[::257].float() - ref_rows).abs().max().item()
+    if not (err < 0.1):
+        raise SystemExit(f"ag_gemm result is wrong (max abs err {err})")
+    del ref_rows
+
+    # ---- headline: device-timed fused op
+    launches_before = G.launch_count
+    sampler = ClockSampler(torch.cuda.current_device())
+    if rank == 0:
+        sampler.start()
+    ms = timed(lambda: G.ag_gemm_intra_node(a, b, ctx, out=c), K_STEPS, W)
+    clocks = sampler.stop() if rank == 0 else None
+    check_status()
+    launches = (G.launch_count - launches_before) * K_STEPS // (K_STEPS + W)
+    value = flops / (ms * 1e-3) / 1e12
+
+    # ---- end to end through the public API: H2D of the step's input, op, D2H of a result slice
+    a_host = torch.empty(mpr, K_TOTAL, dtype=torch.bfloat16).pin_memory()
+    a_host.copy_(a)
+    probe_host = torch.empty(npr, dtype=torch.bfloat16).pin_memory()
+    a_dev = torch.empty_like(a)
+
+    def e2e_step():
+        a_dev.copy_(a_host, non_blocking=True)
+        o = G.ag_gemm_intra_node(a_dev, b, ctx, out=c)
+        probe_host.copy_(o[rank * mpr], non_blocking=True)
+
+    e2e_ms = timed(e2e_step, K_STEPS, W)
+    check_status()
+    e2e = {"value": flops / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOP/s", "ms_per_step": e2e_ms,
+           "h2d_bytes_per_step": a_host.numel() * 2, "d2h_bytes_per_step": probe_host.numel() * 2}
+
+    extra = {}
+    if not args.no_extra:
+        # non-overlapped torch baseline: NCCL all_gather + cuBLAS
+        def torch_step():
+            if world > 1:
+                dist.all_gather_into_tensor(gathered, a, group=group)
+                torch.matmul(gathered, b.t(), out=c)
+            else:
+                torch.matmul(a, b.t(), out=c)
+        tb_ms = timed(torch_step, K_STEPS, W)
+        extra["torch_nccl_cublas_ag_gemm"] = {"ms_per_step": tb_ms, "tflops": flops / (tb_ms * 1e-3) / 1e12}
+        extra["ag_gemm_speedup_vs_torch"] = tb_ms / ms
+        extra["reference_published_speedup_vs_torch_h800"] = REFERENCE_PUBLISHED_SPEEDUP
+        del gathered
+        # GEMM-RS on the BASELINE shape: A [8192, 49152/N], B [12288, 49152/N] -> [8192/N, 12288]
+        kl = N_TOTAL // world
+        x = torch.randn(M_TOTAL, kl, device=dev, dtype=torch.bfloat16, generator=gen)
+        v = (torch.randn(K_TOTAL, kl, device=dev, dtype=torch.float32, generator=gen) * N_TOTAL ** -0.5).to(torch.bfloat16)
+        rctx = G.create_gemm_rs_context(M_TOTAL, K_TOTAL, rank, world, output_dtype=torch.bfloat16, group=group, device=dev)
+        ro = torch.empty(mpr, K_TOTAL, device=dev, dtype=torch.bfloat16)
+        rs_ms = timed(lambda: G.gemm_rs(x, v, rctx, out=ro), K_STEPS, W)
+        check_status()
+        full = torch.empty(M_TOTAL, K_TOTAL, device=dev, dtype=torch.bfloat16)
+
+        def torch_rs():
+            torch.matmul(x, v.t(), out=full)
+            if world > 1:
+                dist.reduce_scatter_tensor(ro, full, group=group)
+        trs_ms = timed(torch_rs, K_STEPS, W)
+        extra["gemm_rs"] = {"ms_per_step": rs_ms, "tflops": flops / (rs_ms * 1e-3) / 1e12,
+                            "torch_nccl_cublas_ms": trs_ms, "speedup_vs_torch": trs_ms / rs_ms}
+
+    if rank == 0:
+        line = {
+            "metric": "AG-GEMM aggregate TFLOP/s (m8192 n49152 k12288, TP over N GPUs)",
+            "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": K_STEPS, "warmup": W,
+            "ms_per_step": ms, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+            "dtype": "bf16", "data": "synthetic (random-init weights and activations of the named shape)",
+            "config": {"model": "TP AllGather-GEMM A[8192,12288] x B[12288,49152]", "global_batch": M_TOTAL,
+                       "seq_len": K_TOTAL, "parallelism": f"tp{world}",
+                       "l2": "operands of one step exceed the 126 MB L2 (no explicit flush)",
+                       "timing": "CUDA events, max over ranks"},
+            "clocks": clocks, "e2e": e2e, "gpu_launches": launches, "impl": "ours", "extra": extra,
+            "check_max_abs_err": err,
+        }
+        print(json.dumps(line), flush=True)
+    finalize_distributed()
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

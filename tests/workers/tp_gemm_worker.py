@@ -1,0 +1,107 @@
+"""Multi-rank check of the symmetric heap and the fused AG-GEMM / GEMM-RS ops.
+
+Runs under torchrun on CUDA (NCCL oracle: all_gather_into_tensor + matmul, matmul +
+reduce_scatter_tensor) or on CPU (gloo; BASELINE plumbing config: fp32, seed 0, rtol 1e-5).
+Follows the reference's test_ag_gemm_intra_node.py:129-149 and test_gemm_rs.py:43-115:
+fresh random inputs every iteration, non-tile-aligned M, stale-workspace poisoning.
+"""
+import json
+import os
+import sys
+
+import torch
+import torch.distributed as dist
+
+from triton_distributed_b200.ops import gemm as G
+from triton_distributed_b200.runtime import check_status, finalize_distributed, initialize_distributed, symm_heap
+
+
+def main():
+    group = initialize_distributed(seed=0)
+    rank, world = dist.get_rank(), dist.get_world_size()
+    cuda = torch.cuda.is_available()
+    dev = torch.device("cuda", torch.cuda.current_device()) if cuda else torch.device("cpu")
+    dtype = torch.bfloat16 if cuda else torch.float32
+    res = {"world": world, "device": dev.type}
+
+    if cuda:
+        heap = symm_heap(group)
+        t = heap.zeros((world, 16), torch.int32)
+        t.local[rank].fill_(rank + 1)
+        heap.barrier()
+        seen = [int(t.peers[p].to(dev)[p, 0].item()) for p in range(world)]
+        res["heap_backend"] = heap._segments[0].cleanup is not None and ("vmm" if hasattr(heap._segments[0], "base_va") else "ipc")
+        assert seen == [p + 1 for p in range(world)], seen
+        heap.barrier()
+
+    # ---------------- AG-GEMM ----------------
+    shapes = [(128, 256, 256), (999, 264, 520)] if cuda else [(128, 256, 256)]
+    if cuda:
+        shapes.append((1024, 1024, 2048))
+    ag_err = 0.0
+    for (mpr, n_per, K) in shapes:
+        gen = torch.Generator(device="cpu").manual_seed(0)
+        ctx = None
+        for it in range(3 if cuda else 1):
+            A_full = torch.randn(world * mpr, K, generator=gen)
+            W_full = torch.randn(world * n_per, K, generator=gen) * (0.02 if not cuda else K ** -0.5)
+            a = A_full[rank * mpr:(rank + 1) * mpr].to(dev, dtype).contiguous()
+            w = W_full[rank * n_per:(rank + 1) * n_per].to(dev, dtype).contiguous()
+            if ctx is None:
+                ctx = G.create_ag_gemm_intra_node_context(a, w, rank, world, max_M=world * mpr, group=group,
+                                                          for_correctness=(it == 0))
+            if cuda and ctx.workspace is not None:
+                ctx.workspace.local.fill_(float("nan"))  # stale data must never be consumed
+                symm_heap().barrier()
+            c = G.ag_gemm_intra_node(a, w, ctx)
+            if cuda:
+                check_status()
+            gathered = torch.empty(world * mpr, K, device=dev, dtype=dtype)
+            dist.all_gather_into_tensor(gathered, a, group=group)
+            ref = gathered.float() @ w.float().t()
+            if cuda:
+                torch.testing.assert_close(c.float(), ref, atol=2e-2, rtol=2e-2)
+            else:
+                torch.testing.assert_close(c, ref, rtol=1e-5, atol=1e-5)
+                torch.testing.assert_close(c, A_full @ w.t(), rtol=1e-5, atol=1e-5)
+            ag_err = max(ag_err, (c.float() - ref).abs().max().item())
+            if cuda:
+                symm_heap().barrier()
+    res["ag_max_err"] = ag_err
+
+    # ---------------- GEMM-RS ----------------
+    shapes = [(128, 256, 128), (250, 520, 264), (1024, 2048, 1024)] if cuda else [(128, 256, 128)]
+    rs_err = 0.0
+    for (mpr, N, k_loc) in shapes:
+        gen = torch.Generator(device="cpu").manual_seed(0)
+        M = world * mpr
+        ctx = G.create_gemm_rs_context(M, N, rank, world, output_dtype=dtype, group=group, device=dev)
+        for it in range(3 if cuda else 1):
+            X_full = torch.randn(M, world * k_loc, generator=gen)
+            V_full = torch.randn(N, world * k_loc, generator=gen) * (0.02 if not cuda else (world * k_loc) ** -0.5)
+            x = X_full[:, rank * k_loc:(rank + 1) * k_loc].to(dev, dtype).contiguous()
+            v = V_full[:, rank * k_loc:(rank + 1) * k_loc].to(dev, dtype).contiguous()
+            out = G.gemm_rs(x, v, ctx)
+            if cuda:
+                check_status()
+            partial = x.float() @ v.float().t()
+            if cuda:
+                ref = torch.empty(mpr, N, device=dev, dtype=torch.float32)
+                dist.reduce_scatter_tensor(ref, partial, group=group)
+                torch.testing.assert_close(out.float(), ref, atol=3e-2, rtol=3e-2)
+            else:
+                ref = (X_full @ V_full.t())[rank * mpr:(rank + 1) * mpr]
+                torch.testing.assert_close(out, ref, rtol=1e-5, atol=1e-5)
+            rs_err = max(rs_err, (out.float() - ref).abs().max().item())
+    res["rs_max_err"] = rs_err
+
+    ok = torch.ones(1, device=dev)
+    dist.all_reduce(ok, group=group)
+    res["ranks_ok"] = int(ok.item())
+    if rank == 0:
+        print("RESULT " + json.dumps(res), flush=True)
+    finalize_distributed()
+
+
+if __name__ == "__main__":
+    main()
