@@ -15,13 +15,20 @@ from triton_distributed_b200.runtime import LocalWorld, check_status, global_sta
 pytestmark = pytest.mark.gpu
 
 
+@pytest.fixture(params=[0, 1], ids=["cta1", "cta_pair"])
+def tiling(request, monkeypatch):
+    """Run a test under both tilings of the kernel (one CTA per tile, CTA pair per tile)."""
+    monkeypatch.setattr(G, "CTA_PAIR", request.param)
+    return request.param
+
+
 def _rand(shape, dtype, dev, scale=1.0):
     return (torch.randn(shape, device=dev, dtype=torch.float32) * scale).to(dtype)
 
 
 @pytest.mark.parametrize("M,N,K", [(128, 256, 64), (256, 512, 512), (300, 264, 136), (1000, 1000, 992), (4096, 768, 2048)])
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
-def test_plain_gemm_matches_fp32_reference(cuda_device, M, N, K, dtype):
+def test_plain_gemm_matches_fp32_reference(cuda_device, tiling, M, N, K, dtype):
     torch.manual_seed(M + N + K)
     a = _rand((M, K), dtype, cuda_device)
     b = _rand((N, K), dtype, cuda_device, K ** -0.5)
@@ -34,7 +41,7 @@ def test_plain_gemm_matches_fp32_reference(cuda_device, M, N, K, dtype):
 
 
 @pytest.mark.parametrize("world,mpr,N,K", [(2, 128, 256, 128), (4, 250, 520, 264), (8, 96, 256, 512), (4, 999, 768, 1024)])
-def test_ag_gemm_single_rank_kernels_against_prepared_peers(cuda_device, world, mpr, N, K):
+def test_ag_gemm_single_rank_kernels_against_prepared_peers(cuda_device, tiling, world, mpr, N, K):
     """Each emulated rank's fused kernel runs alone: blocks of lower ranks were really pushed by
     their kernels, blocks of higher ranks are written by the host together with their flags."""
     torch.manual_seed(world * 1000 + mpr)
@@ -72,7 +79,7 @@ def test_ag_gemm_single_rank_kernels_against_prepared_peers(cuda_device, world, 
 
 
 @pytest.mark.parametrize("world,mpr,N,K", [(2, 128, 256, 128), (4, 250, 520, 264), (8, 96, 512, 256), (4, 512, 1024, 512)])
-def test_gemm_rs_single_rank_kernels_against_prepared_peers(cuda_device, world, mpr, N, K):
+def test_gemm_rs_single_rank_kernels_against_prepared_peers(cuda_device, tiling, world, mpr, N, K):
     torch.manual_seed(world * 77 + mpr)
     dtype = torch.bfloat16
     lw = LocalWorld(world, cuda_device)

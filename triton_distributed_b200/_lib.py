@@ -48,7 +48,7 @@ class GemmArgs(C.Structure):
         ("world", C.c_int), ("rank", C.c_int),
         ("mode", C.c_int), ("dtype", C.c_int),
         ("epoch", C.c_uint32),
-        ("num_sms", C.c_int), ("num_comm_sms", C.c_int), ("debug_delay_ns", C.c_int),
+        ("num_sms", C.c_int), ("num_comm_sms", C.c_int), ("debug_delay_ns", C.c_int), ("group_m", C.c_int), ("cta_pair", C.c_int),
         ("status", C.c_void_p),
         ("timeout_ns", C.c_uint64),
         ("stream", C.c_void_p),

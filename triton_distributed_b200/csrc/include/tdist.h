@@ -60,6 +60,8 @@ typedef struct TdistGemmArgs {
     int num_sms;       /* CTAs to use in total (0 = all SMs of the device) */
     int num_comm_sms;  /* AG: CTAs that only push this rank's shard to the peers */
     int debug_delay_ns;/* AG: the pusher sleeps this long before every block (race hunting) */
+    int group_m;       /* row-tiles per raster group (0 = default 8) */
+    int cta_pair;      /* -1 auto, 0 = one CTA per 128x256 tile, 1 = CTA pair per 256x256 tile */
     void* status;      /* device pointer of a TdistStatus, may be NULL */
     uint64_t timeout_ns;
     void* stream;

@@ -15,8 +15,14 @@
 //          (python/triton_dist/kernels/nvidia/gemm_reduce_scatter.py:104-232,482-538 and
 //          reduce_scatter.py:527-685), where scatter and reduction are separate streams.
 //
-// Tile 128 x 256 x 64, 4 TMA stages, fp32 accumulators double-buffered in TMEM (2 x 256
-// columns) so the epilogue of tile i overlaps the main loop of tile i+1.
+// Two tilings of the same kernel body:
+//   CTAS = 1  one CTA computes a 128 x 256 tile (tcgen05.mma cta_group::1), 4 TMA stages of 48 KB.
+//   CTAS = 2  a cluster of two CTAs computes a 256 x 256 tile (cta_group::2): each CTA loads its own
+//             128 rows of A and its own half (128 rows) of the B tile, the leader CTA issues the MMAs
+//             for both, 6 stages of 32 KB per CTA. B is read from L2 once per pair, which is what
+//             lifts the kernel to library-GEMM speed. No TMA load here uses cluster multicast.
+// In both, K advances 64 elements per stage and the fp32 accumulators are double-buffered in TMEM
+// (2 x 256 columns) so the epilogue of tile i overlaps the main loop of tile i+1.
 // Warp roles (192 threads): warp 0 = TMA producer, warp 1 = MMA issuer and TMEM owner,
 // warps 2..5 = epilogue (TMEM -> registers -> swizzled smem -> TMA store).
 #include <cuda.h>
@@ -33,21 +39,29 @@
 
 namespace tdist {
 
-constexpr int BM = 128;
-constexpr int BN = 256;
+constexpr int BM = 128;   // rows per CTA
+constexpr int BN = 256;   // columns per tile
 constexpr int BK = 64;
-constexpr int STAGES = 4;
 constexpr int UMMA_K = 16;
 constexpr int A_BYTES = BM * BK * 2;
-constexpr int B_BYTES = BN * BK * 2;
-constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
 constexpr int EPI_COLS = 64;                    // columns per epilogue store
 constexpr int EPI_BYTES = BM * EPI_COLS * 2;    // 16 KB
-constexpr int SMEM_TILES = STAGES * STAGE_BYTES + 2 * EPI_BYTES;
+constexpr int PIPE_BYTES = 192 * 1024;          // operand stages (either tiling)
+constexpr int SMEM_TILES = PIPE_BYTES + 2 * EPI_BYTES;
 constexpr int SMEM_BYTES = SMEM_TILES + 1024 /*alignment slack*/ + 256 /*barriers*/;
 constexpr int THREADS = 192;
 constexpr int TMEM_COLS = 512;
-constexpr int GROUP_M = 8;
+constexpr int DEFAULT_GROUP_M = 8;
+constexpr int MAX_STAGES = 6;
+
+template <int CTAS>
+struct Tiling {
+    static constexpr int B_ROWS = BN / CTAS;              // rows of the B tile this CTA loads
+    static constexpr int B_BYTES = B_ROWS * BK * 2;
+    static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+    static constexpr int STAGES = PIPE_BYTES / STAGE_BYTES;  // 4 or 6
+    static_assert(STAGES <= MAX_STAGES, "barrier area too small");
+};
 
 // Pusher pipeline (AG): PUSH_STAGES buffers of PUSH_CHUNK bytes, loads run PUSH_AHEAD chunks
 // ahead of the stores.
@@ -72,8 +86,10 @@ struct GemmParams {
     int m_per_rank, n, k;
     int world, rank;
     int seg_m_tiles, n_tiles, k_blocks;
+    int seg_blocks;  // 128-row blocks per segment (flag granularity)
     int num_tiles;
     int num_comm;
+    int group_m;
     int is_f16;
     uint32_t epoch;
     int debug_delay_ns;
@@ -88,7 +104,7 @@ struct TileCoord {
 // `first_seg`; inside a segment, groups of GROUP_M row-tiles sweep all column-tiles so that
 // concurrently running CTAs share A rows and B columns in L2.
 __device__ __forceinline__ TileCoord decode_tile(int t, int first_seg, int world, int seg_m_tiles,
-                                                 int n_tiles) {
+                                                 int n_tiles, int GROUP_M) {
     const int per_seg = seg_m_tiles * n_tiles;
     const int si = t / per_seg;
     int r = t - si * per_seg;
@@ -112,15 +128,15 @@ __device__ __forceinline__ TileCoord decode_tile(int t, int first_seg, int world
 // ------------------------------------------------------------------------------------------
 __device__ void ag_pusher(const GemmParams& p, uint8_t* smem, uint64_t* bars) {
     if (threadIdx.x != 0) return;
-    const int nitems = (p.world - 1) * p.seg_m_tiles;
+    const int nitems = (p.world - 1) * p.seg_blocks;
     const size_t row_bytes = static_cast<size_t>(p.k) * 2;
     uint32_t full[PUSH_STAGES];
     for (int s = 0; s < PUSH_STAGES; ++s) full[s] = smem_u32(&bars[s]);
     uint32_t it_load = 0, it_store = 0;  // running chunk counters (stage = counter % PUSH_STAGES)
 
     for (int item = static_cast<int>(blockIdx.x); item < nitems; item += p.num_comm) {
-        const int hop = item / p.seg_m_tiles + 1;
-        const int mb = item - (hop - 1) * p.seg_m_tiles;
+        const int hop = item / p.seg_blocks + 1;
+        const int mb = item - (hop - 1) * p.seg_blocks;
         int dst = p.rank - hop;
         if (dst < 0) dst += p.world;
         const int rows = min(BM, p.m_per_rank - mb * BM);
@@ -159,15 +175,15 @@ __device__ void ag_pusher(const GemmParams& p, uint8_t* smem, uint64_t* bars) {
         bulk_wait<0>();
         fence_proxy_async();
         fence_acq_rel_sys();
-        st_release_sys_u32(p.flags_peer[dst] + p.rank * p.seg_m_tiles + mb, p.epoch);
+        st_release_sys_u32(p.flags_peer[dst] + p.rank * p.seg_blocks + mb, p.epoch);
     }
 }
 
 // ------------------------------------------------------------------------------------------
 // RS reduce: sum the `world` partial copies of one owned tile in fp32, write bf16/f16.
 // ------------------------------------------------------------------------------------------
-__device__ __forceinline__ void rs_reduce_tile(const GemmParams& p, int m_in_seg, int n_tile) {
-    const int row0 = m_in_seg * BM;
+__device__ __forceinline__ void rs_reduce_tile(const GemmParams& p, int block, int n_tile) {
+    const int row0 = block * BM;
     const int col0 = n_tile * BN;
     const int rows = min(BM, p.m_per_rank - row0);
     const int cols = min(BN, p.n - col0);
@@ -210,18 +226,21 @@ __device__ __forceinline__ void rs_reduce_tile(const GemmParams& p, int m_in_seg
     }
 }
 
-template <int MODE>
+template <int MODE, int CTAS>
 __global__ void __launch_bounds__(THREADS, 1) gemm_sm100_kernel(const __grid_constant__ GemmParams p) {
+    using T = Tiling<CTAS>;
+    constexpr int STAGES = T::STAGES;
+    constexpr int STAGE_BYTES = T::STAGE_BYTES;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem + SMEM_TILES);
     // barrier slots: [0,S) full, [S,2S) empty, [2S,2S+2) tmem_full, [2S+2,2S+4) tmem_empty
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 4);
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * MAX_STAGES + 4);
 
     const int warp = static_cast<int>(threadIdx.x) >> 5;
     const int lane = static_cast<int>(threadIdx.x) & 31;
 
-    // ---------------- pusher CTAs (AG only) ----------------
+    // ---------------- pusher CTAs (AG only; whole clusters when CTAS == 2) ----------------
     if (MODE == TDIST_GEMM_AG && static_cast<int>(blockIdx.x) < p.num_comm) {
         if (threadIdx.x == 0) {
             for (int s = 0; s < PUSH_STAGES; ++s) mbar_init(smem_u32(&bars[s]), 1);
@@ -232,79 +251,107 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_sm100_kernel(const __grid_con
         return;
     }
 
+    // `unit` = the CTA (CTAS == 1) or the CTA pair (CTAS == 2) that owns a tile.
     const int cta = static_cast<int>(blockIdx.x) - p.num_comm;
     const int num_cta = static_cast<int>(gridDim.x) - p.num_comm;
+    const int unit = cta / CTAS;
+    const int num_units = num_cta / CTAS;
+    const int cta_rank = (CTAS == 2) ? static_cast<int>(cluster_ctarank()) : 0;
     const int first_seg = (MODE == TDIST_GEMM_RS) ? (p.rank + 1) % p.world : p.rank;
+
+    // shared-memory addresses of the barriers (computed, not tabulated, to stay in registers)
+    const uint32_t bars_u32 = smem_u32(bars);
+    struct {
+        uint32_t base;
+        __device__ uint32_t operator()(int slot) const { return base + static_cast<uint32_t>(slot) * 8u; }
+    } bar{bars_u32};
+#define bar_full(s) bar(s)
+#define bar_empty(s) bar(MAX_STAGES + (s))
+#define bar_tfull(b) bar(2 * MAX_STAGES + (b))
+#define bar_tempty(b) bar(2 * MAX_STAGES + 2 + (b))
 
     if (threadIdx.x == 0) {
         prefetch_tensormap(&p.tm_a);
         prefetch_tensormap(&p.tm_b);
         if (MODE == TDIST_GEMM_AG) prefetch_tensormap(&p.tm_a_own);
         for (int s = 0; s < STAGES; ++s) {
-            mbar_init(smem_u32(&bars[s]), 1);
-            mbar_init(smem_u32(&bars[STAGES + s]), 1);
+            mbar_init(bar_full(s), 1);
+            mbar_init(bar_empty(s), 1);
         }
         for (int b = 0; b < 2; ++b) {
-            mbar_init(smem_u32(&bars[2 * STAGES + b]), 1);
-            mbar_init(smem_u32(&bars[2 * STAGES + 2 + b]), 128);
+            mbar_init(bar_tfull(b), 1);
+            mbar_init(bar_tempty(b), 4 * CTAS);  // one arrival per epilogue warp of every CTA
         }
         fence_mbar_init();
     }
     if (warp == 1) {
-        tmem_alloc<1>(smem_u32(tmem_slot), TMEM_COLS);
-        tmem_relinquish<1>();
+        tmem_alloc<CTAS>(smem_u32(tmem_slot), TMEM_COLS);
+        tmem_relinquish<CTAS>();
     }
     tc_fence_before();
-    __syncthreads();
+    if (CTAS == 2) {
+        // the peer CTA signals this CTA's barriers: they must exist cluster-wide before any use
+        cluster_arrive();
+        cluster_wait();
+    } else {
+        __syncthreads();
+    }
     tc_fence_after();
     const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(tmem_slot);
 
     if (warp == 0) {
-        // ===================== TMA producer =====================
+        // ===================== TMA producer (every CTA loads its own A rows and B rows) ==========
         if (lane == 0) {
             uint32_t it = 0;
-            for (int t = cta; t < p.num_tiles; t += num_cta) {
-                const TileCoord tc = decode_tile(t, first_seg, p.world, p.seg_m_tiles, p.n_tiles);
+            for (int t = unit; t < p.num_tiles; t += num_units) {
+                const TileCoord tc = decode_tile(t, first_seg, p.world, p.seg_m_tiles, p.n_tiles, p.group_m);
+                const int block = tc.m_in_seg * CTAS + cta_rank;  // 128-row block inside the segment
                 const CUtensorMap* am = &p.tm_a;
                 int az = tc.seg;
                 if (MODE == TDIST_GEMM_AG) {
                     if (tc.seg == p.rank) {
                         am = &p.tm_a_own;
                         az = 0;
-                    } else {
-                        wait_flag_ge_sys(p.flags + tc.seg * p.seg_m_tiles + tc.m_in_seg, p.epoch, p.wctx,
-                                         tc.seg, tc.m_in_seg, 1);
+                    } else if (block < p.seg_blocks) {
+                        wait_flag_ge_sys(p.flags + tc.seg * p.seg_blocks + block, p.epoch, p.wctx, tc.seg, block, 1);
                         fence_proxy_async();
                     }
                 }
-                const int row = tc.m_in_seg * BM;
-                const int col = tc.n_tile * BN;
+                const int row = block * BM;
+                const int col = tc.n_tile * BN + cta_rank * T::B_ROWS;
                 for (int kb = 0; kb < p.k_blocks; ++kb, ++it) {
                     const uint32_t s = it % STAGES;
-                    mbar_wait(smem_u32(&bars[STAGES + s]), ((it / STAGES) & 1u) ^ 1u, p.wctx, 2);
-                    const uint32_t full = smem_u32(&bars[s]);
-                    mbar_expect_tx(full, STAGE_BYTES);
+                    mbar_wait(bar_empty(s), ((it / STAGES) & 1u) ^ 1u, p.wctx, 2);
                     const uint32_t sa = smem_u32(smem + s * STAGE_BYTES);
-                    tma_load_3d(sa, am, full, kb * BK, row, az);
-                    tma_load_3d(sa + A_BYTES, &p.tm_b, full, kb * BK, col, 0);
+                    if (CTAS == 1) {
+                        mbar_expect_tx(bar_full(s), STAGE_BYTES);
+                        tma_load_3d(sa, am, bar_full(s), kb * BK, row, az);
+                        tma_load_3d(sa + A_BYTES, &p.tm_b, bar_full(s), kb * BK, col, 0);
+                    } else {
+                        // both CTAs' bytes are counted on the leader's barrier
+                        if (cta_rank == 0) mbar_expect_tx(bar_full(s), 2 * STAGE_BYTES);
+                        const uint32_t leader_full = mapa_u32(bar_full(s), 0);
+                        tma_load_3d_pair(sa, am, leader_full, kb * BK, row, az);
+                        tma_load_3d_pair(sa + A_BYTES, &p.tm_b, leader_full, kb * BK, col, 0);
+                    }
                 }
             }
         }
         __syncwarp();
     } else if (warp == 1) {
-        // ===================== MMA issuer =====================
-        if (lane == 0) {
-            const uint32_t idesc = umma_idesc(p.is_f16 ? 0u : 1u, p.is_f16 ? 0u : 1u, BM, BN);
+        // ===================== MMA issuer (leader CTA only when CTAS == 2) =====================
+        if (lane == 0 && cta_rank == 0) {
+            const uint32_t idesc = umma_idesc(p.is_f16 ? 0u : 1u, p.is_f16 ? 0u : 1u, BM * CTAS, BN);
             uint32_t it = 0;
             uint32_t local_tile = 0;
-            for (int t = cta; t < p.num_tiles; t += num_cta, ++local_tile) {
+            for (int t = unit; t < p.num_tiles; t += num_units, ++local_tile) {
                 const uint32_t buf = local_tile & 1u;
-                mbar_wait(smem_u32(&bars[2 * STAGES + 2 + buf]), ((local_tile >> 1) & 1u) ^ 1u, p.wctx, 3);
+                mbar_wait(bar_tempty(buf), ((local_tile >> 1) & 1u) ^ 1u, p.wctx, 3);
                 tc_fence_after();
                 const uint32_t d_tmem = tmem_base + buf * BN;
                 for (int kb = 0; kb < p.k_blocks; ++kb, ++it) {
                     const uint32_t s = it % STAGES;
-                    mbar_wait(smem_u32(&bars[s]), (it / STAGES) & 1u, p.wctx, 4);
+                    mbar_wait(bar_full(s), (it / STAGES) & 1u, p.wctx, 4);
                     tc_fence_after();
                     const uint32_t sa = smem_u32(smem + s * STAGE_BYTES);
                     const uint64_t adesc = umma_desc_k_sw128(sa);
@@ -312,11 +359,14 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_sm100_kernel(const __grid_con
 #pragma unroll
                     for (int k = 0; k < BK / UMMA_K; ++k) {
                         // 16 elements of K = 32 bytes = 2 descriptor address units
-                        umma_bf16<1>(d_tmem, adesc + 2 * k, bdesc + 2 * k, idesc, (kb | k) != 0 ? 1u : 0u);
+                        umma_bf16<CTAS>(d_tmem, adesc + 2 * k, bdesc + 2 * k, idesc, (kb | k) != 0 ? 1u : 0u);
                     }
-                    umma_commit(smem_u32(&bars[STAGES + s]));  // frees the smem stage when the MMAs retire
+                    // frees the smem stage (in both CTAs) when the MMAs retire
+                    if (CTAS == 1) umma_commit(bar_empty(s));
+                    else umma_commit_pair(bar_empty(s), 3);
                 }
-                umma_commit(smem_u32(&bars[2 * STAGES + buf]));  // accumulator ready
+                if (CTAS == 1) umma_commit(bar_tfull(buf));  // accumulator ready
+                else umma_commit_pair(bar_tfull(buf), 3);
             }
         }
         __syncwarp();
@@ -325,16 +375,17 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_sm100_kernel(const __grid_con
         const int q = warp & 3;                 // TMEM lane quadrant this warp may read
         const int row_in_tile = q * 32 + lane;
         const bool issuer = (warp == 2 && lane == 0);
-        uint8_t* cstage = smem + STAGES * STAGE_BYTES;
+        uint8_t* cstage = smem + PIPE_BYTES;
         uint32_t local_tile = 0;
-        for (int t = cta; t < p.num_tiles; t += num_cta, ++local_tile) {
-            const TileCoord tc = decode_tile(t, first_seg, p.world, p.seg_m_tiles, p.n_tiles);
+        for (int t = unit; t < p.num_tiles; t += num_units, ++local_tile) {
+            const TileCoord tc = decode_tile(t, first_seg, p.world, p.seg_m_tiles, p.n_tiles, p.group_m);
             const uint32_t buf = local_tile & 1u;
-            mbar_wait(smem_u32(&bars[2 * STAGES + buf]), (local_tile >> 1) & 1u, p.wctx, 5);
+            mbar_wait(bar_tfull(buf), (local_tile >> 1) & 1u, p.wctx, 5);
             tc_fence_after();
             const CUtensorMap* cm = (MODE == TDIST_GEMM_RS) ? &p.tm_c[tc.seg] : &p.tm_c[0];
             const int cz = (MODE == TDIST_GEMM_RS) ? p.rank : tc.seg;
-            const int row = tc.m_in_seg * BM;
+            const int block = tc.m_in_seg * CTAS + cta_rank;
+            const int row = block * BM;
             const int col = tc.n_tile * BN;
 #pragma unroll 1
             for (int c = 0; c < BN / EPI_COLS; ++c) {
@@ -344,9 +395,13 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_sm100_kernel(const __grid_con
                 tmem_ld_32x32(taddr + 32, r1);
                 tmem_ld_wait();
                 if (c == BN / EPI_COLS - 1) {
-                    // accumulator fully read: hand the TMEM buffer back to the MMA warp
+                    // accumulator fully read: hand the TMEM buffer back to the MMA issuer
                     tc_fence_before();
-                    mbar_arrive(smem_u32(&bars[2 * STAGES + 2 + buf]));
+                    __syncwarp();
+                    if (lane == 0) {
+                        if (CTAS == 1) mbar_arrive(bar_tempty(buf));
+                        else mbar_arrive_cluster(bar_tempty(buf), 0);
+                    }
                 }
                 uint8_t* cs = cstage + (c & 1) * EPI_BYTES;
                 named_barrier(1, 128);  // the store that last read this buffer has drained
@@ -356,15 +411,14 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_sm100_kernel(const __grid_con
                 for (int j = 0; j < 4; ++j) {
                     uint4 v0, v1;
                     if (p.is_f16) {
-                        __half2 h;
-                        h = __floats2half2_rn(__uint_as_float(r0[8 * j + 0]), __uint_as_float(r0[8 * j + 1])); v0.x = *reinterpret_cast<uint32_t*>(&h);
-                        h = __floats2half2_rn(__uint_as_float(r0[8 * j + 2]), __uint_as_float(r0[8 * j + 3])); v0.y = *reinterpret_cast<uint32_t*>(&h);
-                        h = __floats2half2_rn(__uint_as_float(r0[8 * j + 4]), __uint_as_float(r0[8 * j + 5])); v0.z = *reinterpret_cast<uint32_t*>(&h);
-                        h = __floats2half2_rn(__uint_as_float(r0[8 * j + 6]), __uint_as_float(r0[8 * j + 7])); v0.w = *reinterpret_cast<uint32_t*>(&h);
-                        h = __floats2half2_rn(__uint_as_float(r1[8 * j + 0]), __uint_as_float(r1[8 * j + 1])); v1.x = *reinterpret_cast<uint32_t*>(&h);
-                        h = __floats2half2_rn(__uint_as_float(r1[8 * j + 2]), __uint_as_float(r1[8 * j + 3])); v1.y = *reinterpret_cast<uint32_t*>(&h);
-                        h = __floats2half2_rn(__uint_as_float(r1[8 * j + 4]), __uint_as_float(r1[8 * j + 5])); v1.z = *reinterpret_cast<uint32_t*>(&h);
-                        h = __floats2half2_rn(__uint_as_float(r1[8 * j + 6]), __uint_as_float(r1[8 * j + 7])); v1.w = *reinterpret_cast<uint32_t*>(&h);
+                        v0.x = pack_f16x2(__uint_as_float(r0[8 * j + 0]), __uint_as_float(r0[8 * j + 1]));
+                        v0.y = pack_f16x2(__uint_as_float(r0[8 * j + 2]), __uint_as_float(r0[8 * j + 3]));
+                        v0.z = pack_f16x2(__uint_as_float(r0[8 * j + 4]), __uint_as_float(r0[8 * j + 5]));
+                        v0.w = pack_f16x2(__uint_as_float(r0[8 * j + 6]), __uint_as_float(r0[8 * j + 7]));
+                        v1.x = pack_f16x2(__uint_as_float(r1[8 * j + 0]), __uint_as_float(r1[8 * j + 1]));
+                        v1.y = pack_f16x2(__uint_as_float(r1[8 * j + 2]), __uint_as_float(r1[8 * j + 3]));
+                        v1.z = pack_f16x2(__uint_as_float(r1[8 * j + 4]), __uint_as_float(r1[8 * j + 5]));
+                        v1.w = pack_f16x2(__uint_as_float(r1[8 * j + 6]), __uint_as_float(r1[8 * j + 7]));
                     } else {
                         v0.x = pack_bf16x2(__uint_as_float(r0[8 * j + 0]), __uint_as_float(r0[8 * j + 1]));
                         v0.y = pack_bf16x2(__uint_as_float(r0[8 * j + 2]), __uint_as_float(r0[8 * j + 3]));
@@ -382,7 +436,7 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_sm100_kernel(const __grid_con
                 fence_proxy_async_smem();
                 named_barrier(1, 128);  // the staging buffer is complete
                 if (issuer) {
-                    if (col + c * EPI_COLS < p.n) {
+                    if (col + c * EPI_COLS < p.n && row < p.m_per_rank) {
                         tma_store_3d(cm, smem_u32(cs), col + c * EPI_COLS, row, cz);
                         bulk_commit();
                     }
@@ -394,30 +448,40 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_sm100_kernel(const __grid_con
                 bulk_wait<0>();
                 fence_proxy_async();
                 fence_acq_rel_sys();
-                const int tile_in_seg = tc.m_in_seg * p.n_tiles + tc.n_tile;
-                st_release_sys_u32(p.flags_peer[tc.seg] + tile_in_seg * p.world + p.rank, p.epoch);
+                st_release_sys_u32(p.flags_peer[tc.seg] + (block * p.n_tiles + tc.n_tile) * p.world + p.rank, p.epoch);
             }
         }
         if (issuer) bulk_wait<0>();
+        __syncwarp();
     }
 
     tc_fence_before();
-    __syncthreads();
-    if (warp == 1) tmem_dealloc<1>(tmem_base, TMEM_COLS);
+    if (CTAS == 2) {
+        // neither CTA may free TMEM or exit while its partner can still touch its TMEM, smem or barriers
+        cluster_arrive();
+        cluster_wait();
+    } else {
+        __syncthreads();
+    }
+    if (warp == 1) tmem_dealloc<CTAS>(tmem_base, TMEM_COLS);
 
     if (MODE == TDIST_GEMM_RS) {
-        // ===================== reduce the tiles this rank owns =====================
-        const int own_tiles = p.seg_m_tiles * p.n_tiles;
-        for (int ti = cta; ti < own_tiles; ti += num_cta) {
+        // ===================== reduce the 128-row blocks this rank owns =====================
+        const int own_units = p.seg_blocks * p.n_tiles;
+        for (int u = cta; u < own_units; u += num_cta) {
             if (warp == 0) {
                 if (lane < p.world)
-                    wait_flag_ge_sys(p.flags + ti * p.world + lane, p.epoch, p.wctx, lane, ti, 6);
+                    wait_flag_ge_sys(p.flags + u * p.world + lane, p.epoch, p.wctx, lane, u, 6);
             }
             __syncthreads();
-            rs_reduce_tile(p, ti / p.n_tiles, ti % p.n_tiles);
+            rs_reduce_tile(p, u / p.n_tiles, u % p.n_tiles);
         }
     }
 }
+#undef bar_full
+#undef bar_empty
+#undef bar_tfull
+#undef bar_tempty
 
 }  // namespace tdist
 
@@ -427,25 +491,89 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_sm100_kernel(const __grid_con
 using namespace tdist;
 using tdist_host::fail;
 
-static int plan_grid(const TdistGemmArgs* a, int* num_comm_out, int* num_tiles_out) {
-    const int seg_m_tiles = (a->m_per_rank + BM - 1) / BM;
-    const int n_tiles = (a->n + BN - 1) / BN;
-    const int num_tiles = seg_m_tiles * n_tiles * a->world;
-    int sms = a->num_sms > 0 ? a->num_sms : tdist_host::sm_count();
-    int num_comm = 0;
-    if (a->mode == TDIST_GEMM_AG && a->world > 1) {
-        num_comm = a->num_comm_sms > 0 ? a->num_comm_sms : 8;
-        if (num_comm > sms - 1) num_comm = sms - 1;
-    }
-    int gemm_ctas = sms - num_comm;
-    if (gemm_ctas > num_tiles) gemm_ctas = num_tiles;
-    if (gemm_ctas < 1) gemm_ctas = 1;
-    if (num_comm_out) *num_comm_out = num_comm;
-    if (num_tiles_out) *num_tiles_out = num_tiles;
-    return gemm_ctas + num_comm;
+static bool use_pair(const TdistGemmArgs* a) {
+    if (a->cta_pair == 0) return false;
+    if (a->cta_pair > 0) return true;
+    return a->m_per_rank > BM;  // a second CTA would only compute padding otherwise
 }
 
-extern "C" int tdist_gemm_grid(const TdistGemmArgs* a) { return plan_grid(a, nullptr, nullptr); }
+struct GridPlan {
+    int ctas_per_tile, num_comm, num_tiles, grid;
+};
+
+template <int CTAS>
+static const void* kernel_for(int mode) {
+    switch (mode) {
+        case TDIST_GEMM_PLAIN: return reinterpret_cast<const void*>(&gemm_sm100_kernel<TDIST_GEMM_PLAIN, CTAS>);
+        case TDIST_GEMM_AG: return reinterpret_cast<const void*>(&gemm_sm100_kernel<TDIST_GEMM_AG, CTAS>);
+        default: return reinterpret_cast<const void*>(&gemm_sm100_kernel<TDIST_GEMM_RS, CTAS>);
+    }
+}
+
+// CTAs of this kernel that can be resident at once on the current device (all of them wait on
+// one another through flags, so the grid must never exceed this). Cached per device/variant.
+static int resident_ctas(int ctas, int mode) {
+    static int cache[64][2][3] = {};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return tdist_host::sm_count();
+    int& slot = cache[dev][ctas - 1][mode];
+    if (slot > 0) return slot;
+    const void* fn = ctas == 2 ? kernel_for<2>(mode) : kernel_for<1>(mode);
+    int result = 0;
+    if (cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES) == cudaSuccess) {
+        if (ctas == 2) {
+            cudaLaunchConfig_t cfg;
+            memset(&cfg, 0, sizeof(cfg));
+            cfg.gridDim = dim3(tdist_host::sm_count() & ~1);
+            cfg.blockDim = dim3(THREADS);
+            cfg.dynamicSmemBytes = SMEM_BYTES;
+            cudaLaunchAttribute attr[1];
+            attr[0].id = cudaLaunchAttributeClusterDimension;
+            attr[0].val.clusterDim.x = 2;
+            attr[0].val.clusterDim.y = 1;
+            attr[0].val.clusterDim.z = 1;
+            cfg.attrs = attr;
+            cfg.numAttrs = 1;
+            int clusters = 0;
+            if (cudaOccupancyMaxActiveClusters(&clusters, fn, &cfg) == cudaSuccess && clusters > 0) result = clusters * 2;
+        } else {
+            int per_sm = 0;
+            if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, fn, THREADS, SMEM_BYTES) == cudaSuccess && per_sm > 0)
+                result = per_sm * tdist_host::sm_count();
+        }
+    }
+    cudaGetLastError();
+    if (result <= 0) result = tdist_host::sm_count() & ~(ctas - 1);
+    slot = result;
+    return result;
+}
+
+static GridPlan plan_grid(const TdistGemmArgs* a) {
+    GridPlan g;
+    g.ctas_per_tile = use_pair(a) ? 2 : 1;
+    const int seg_m_tiles = (a->m_per_rank + BM * g.ctas_per_tile - 1) / (BM * g.ctas_per_tile);
+    const int n_tiles = (a->n + BN - 1) / BN;
+    g.num_tiles = seg_m_tiles * n_tiles * a->world;
+    const int capacity = resident_ctas(g.ctas_per_tile, a->mode);
+    int sms = a->num_sms > 0 ? a->num_sms : capacity;
+    if (sms > capacity) sms = capacity;
+    if (g.ctas_per_tile == 2) sms &= ~1;
+    if (sms < g.ctas_per_tile) sms = g.ctas_per_tile;
+    g.num_comm = 0;
+    if (a->mode == TDIST_GEMM_AG && a->world > 1) {
+        g.num_comm = a->num_comm_sms > 0 ? a->num_comm_sms : 8;
+        if (g.ctas_per_tile == 2) g.num_comm = (g.num_comm + 1) & ~1;
+        if (g.num_comm > sms - g.ctas_per_tile) g.num_comm = sms - g.ctas_per_tile;
+        if (g.num_comm < g.ctas_per_tile) g.num_comm = g.ctas_per_tile;
+    }
+    int units = (sms - g.num_comm) / g.ctas_per_tile;
+    if (units > g.num_tiles) units = g.num_tiles;
+    if (units < 1) units = 1;
+    g.grid = units * g.ctas_per_tile + g.num_comm;
+    return g;
+}
+
+extern "C" int tdist_gemm_grid(const TdistGemmArgs* a) { return plan_grid(a).grid; }
 
 extern "C" int tdist_gemm_run(const TdistGemmArgs* a) {
     if (a == nullptr) return fail(TDIST_EINVAL, "null args");
@@ -456,6 +584,8 @@ extern "C" int tdist_gemm_run(const TdistGemmArgs* a) {
         return fail(TDIST_EINVAL, "K and N must be multiples of 8 (16-byte rows for TMA)");
     if (a->mode < TDIST_GEMM_PLAIN || a->mode > TDIST_GEMM_RS) return fail(TDIST_EINVAL, "bad mode");
 
+    const GridPlan plan = plan_grid(a);
+    const int ctas = plan.ctas_per_tile;
     GemmParams p;
     memset(&p, 0, sizeof(p));
     const CUtensorMapDataType dt = a->dtype == TDIST_F16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
@@ -480,7 +610,7 @@ extern "C" int tdist_gemm_run(const TdistGemmArgs* a) {
     {
         uint64_t dims[3] = {K, N, 1};
         uint64_t strides[2] = {K * 2, N * K * 2};
-        uint32_t box[3] = {BK, BN, 1};
+        uint32_t box[3] = {BK, static_cast<uint32_t>(BN / ctas), 1};
         if ((rc = tdist_host::encode_tmap(&p.tm_b, dt, 2, 3, a->b, dims, strides, box, tdist_host::Swizzle::B128))) return rc;
     }
     {
@@ -510,7 +640,8 @@ extern "C" int tdist_gemm_run(const TdistGemmArgs* a) {
     p.k = a->k;
     p.world = a->world;
     p.rank = a->rank;
-    p.seg_m_tiles = (a->m_per_rank + BM - 1) / BM;
+    p.seg_blocks = (a->m_per_rank + BM - 1) / BM;
+    p.seg_m_tiles = (a->m_per_rank + BM * ctas - 1) / (BM * ctas);
     p.n_tiles = (a->n + BN - 1) / BN;
     p.k_blocks = (a->k + BK - 1) / BK;
     p.is_f16 = a->dtype == TDIST_F16;
@@ -520,7 +651,9 @@ extern "C" int tdist_gemm_run(const TdistGemmArgs* a) {
     p.wctx.timeout_ns = a->timeout_ns;
     p.wctx.kernel_id = kKernelGemm;
     p.wctx.rank = a->rank;
-    const int grid = plan_grid(a, &p.num_comm, &p.num_tiles);
+    p.num_comm = plan.num_comm;
+    p.group_m = a->group_m > 0 ? a->group_m : DEFAULT_GROUP_M;
+    p.num_tiles = plan.num_tiles;
 
     if (a->mode == TDIST_GEMM_AG && a->world > 1) {
         if (a->flags == nullptr) return fail(TDIST_EINVAL, "AG needs flags");
@@ -535,21 +668,21 @@ extern "C" int tdist_gemm_run(const TdistGemmArgs* a) {
     }
 
     cudaStream_t stream = static_cast<cudaStream_t>(a->stream);
-    static bool attr_set[64][3] = {};
-    int dev = 0;
-    TDIST_CUDA_OK(cudaGetDevice(&dev));
-    if (dev < 0 || dev >= 64) return fail(TDIST_EINVAL, "device ordinal out of range");
-    const void* fn = nullptr;
-    switch (a->mode) {
-        case TDIST_GEMM_PLAIN: fn = reinterpret_cast<const void*>(&gemm_sm100_kernel<TDIST_GEMM_PLAIN>); break;
-        case TDIST_GEMM_AG: fn = reinterpret_cast<const void*>(&gemm_sm100_kernel<TDIST_GEMM_AG>); break;
-        default: fn = reinterpret_cast<const void*>(&gemm_sm100_kernel<TDIST_GEMM_RS>); break;
-    }
-    if (!attr_set[dev][a->mode]) {
-        TDIST_CUDA_OK(cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
-        attr_set[dev][a->mode] = true;
-    }
+    const void* fn = ctas == 2 ? kernel_for<2>(a->mode) : kernel_for<1>(a->mode);  // smem opt-in done by resident_ctas()
     void* kargs[] = {&p};
-    TDIST_CUDA_OK(cudaLaunchKernel(fn, dim3(grid), dim3(THREADS), kargs, SMEM_BYTES, stream));
+    cudaLaunchConfig_t cfg;
+    memset(&cfg, 0, sizeof(cfg));
+    cfg.gridDim = dim3(plan.grid);
+    cfg.blockDim = dim3(THREADS);
+    cfg.dynamicSmemBytes = SMEM_BYTES;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = ctas;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    TDIST_CUDA_OK(cudaLaunchKernelExC(&cfg, fn, kargs));
     return 0;
 }

@@ -16,6 +16,7 @@ serves as the oracle and as the gloo plumbing path.
 from __future__ import annotations
 
 import ctypes as C
+import os
 from dataclasses import dataclass, field
 from typing import Optional
 
@@ -34,6 +35,10 @@ _DTYPES = {torch.bfloat16: _lib.DT_BF16, torch.float16: _lib.DT_F16}
 
 # number of native launches since import (bench.py reports it)
 launch_count = 0
+# tiling choice handed to the kernel: -1 = automatic, 0 = one CTA per 128x256 tile,
+# 1 = CTA pair (cta_group::2) per 256x256 tile
+CTA_PAIR = int(os.environ.get("TDIST_GEMM_CTA_PAIR", "-1"))
+GROUP_M = int(os.environ.get("TDIST_GEMM_GROUP_M", "0"))  # row-tiles per raster group, 0 = kernel default
 
 
 def _cdiv(a: int, b: int) -> int:
@@ -64,6 +69,8 @@ def _base_args(a, b, world, rank, mode, stream=None) -> "_lib.GemmArgs":
     st = global_status()
     g.status = st.device_ptr if st is not None else None
     g.timeout_ns = default_timeout_ns()
+    g.cta_pair = CTA_PAIR
+    g.group_m = GROUP_M
     g.stream = (stream or torch.cuda.current_stream(a.device)).cuda_stream
     return g
 
@@ -223,7 +230,8 @@ def create_gemm_rs_context(max_M: int, N: int, rank: int, world_size: int, local
     if on_cuda:
         heap = heap or symm_heap(group)
         ctx.staging = heap.empty((2, world_size * max_mpr * N), output_dtype)
-        tiles = _cdiv(max_mpr, BLOCK_M_TILE) * _cdiv(N, BLOCK_N_TILE)
+        # one flag per (128-row block, 256-column tile, source); +1 block: a CTA pair may own a padding block
+        tiles = (_cdiv(max_mpr, BLOCK_M_TILE) + 1) * _cdiv(N, BLOCK_N_TILE)
         ctx.flags = heap.zeros((2, tiles * world_size), torch.int32)
     return ctx
 
