@@ -37,57 +37,82 @@ REFERENCE_PUBLISHED_SPEEDUP = 1.36  # AG-GEMM m8192 n49152 k12288 vs PyTorch+NCC
 
 
 class ClockSampler:
-    """Samples SM clock and throttle reasons of one GPU with nvidia-smi while a region runs."""
+    """SM clock, power and throttle reasons of one GPU, read through NVML (the library behind
+    nvidia-smi; read-only queries) from the benchmark's own thread.
 
-    QUERY = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
-             "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
-             "clocks_event_reasons.sw_power_cap")
+    Every NVML query costs milliseconds and briefly stalls work on the GPU it touches, and one
+    stalled rank stalls every rank of a fused collective kernel, so sampling is sparse: one
+    sample as soon as the timed launches are queued (the GPU is then inside the timed region),
+    then one every 250 ms until the region's closing event has fired.
+    BENCH_SAMPLER=off disables sampling; =smi shells out to nvidia-smi per sample instead."""
+
+    REASONS = {"hw_slowdown": 0x8, "hw_thermal_slowdown": 0x40, "sw_thermal_slowdown": 0x20, "sw_power_cap": 0x4}
 
     def __init__(self, index: int):
         self.index = index
-        self.proc = None
-        self.lines = []
-
-    def start(self):
-        try:
-            self.proc = subprocess.Popen(
-                ["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits", "-lms", "100"],
-                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
-            threading.Thread(target=self._pump, daemon=True).start()
-        except OSError:
-            self.proc = None
-
-    def _pump(self):
-        for line in self.proc.stdout:
-            self.lines.append(line.strip())
-
-    def stop(self) -> dict:
-        if self.proc is None:
-            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
-        time.sleep(0.15)
-        self.proc.terminate()
-        try:
-            self.proc.wait(timeout=5)
-        except subprocess.TimeoutExpired:
-            self.proc.kill()
-        sm, mx, pw, reasons = [], [], [], set()
-        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        for line in self.lines:
-            parts = [p.strip() for p in line.split(",")]
-            if len(parts) < 7:
-                continue
+        self.kind = os.environ.get("BENCH_SAMPLER", "nvml")
+        self.samples = []  # (sm_mhz, watts, reasons_bitmask)
+        self.max_mhz = None
+        if self.kind == "nvml":
             try:
-                sm.append(float(parts[0]))
-                mx.append(float(parts[1]))
-                pw.append(float(parts[2]))
-            except ValueError:
-                continue
-            for name, val in zip(names, parts[3:7]):
-                if val.lower().startswith("active"):
-                    reasons.add(name)
-        busy = [s for s, p in zip(sm, pw) if p > 300] or sm
-        return {"sm_mhz": statistics.median(busy) if busy else None, "sm_max_mhz": max(mx) if mx else None,
-                "power_w_max": max(pw) if pw else None, "samples": len(sm), "reasons": sorted(reasons)}
+                import pynvml
+                pynvml.nvmlInit()
+                self._nv = pynvml
+                self._handle = pynvml.nvmlDeviceGetHandleByIndex(index)
+                self.max_mhz = float(pynvml.nvmlDeviceGetMaxClockInfo(self._handle, pynvml.NVML_CLOCK_SM))
+            except Exception:  # noqa: BLE001 - fall back to the command-line tool
+                self.kind = "smi"
+
+    def sample(self) -> None:
+        try:
+            if self.kind == "nvml":
+                nv, h = self._nv, self._handle
+                sm = nv.nvmlDeviceGetClockInfo(h, nv.NVML_CLOCK_SM)
+                try:
+                    rs = nv.nvmlDeviceGetCurrentClocksEventReasons(h)
+                except AttributeError:
+                    rs = nv.nvmlDeviceGetCurrentClocksThrottleReasons(h)
+                pw = nv.nvmlDeviceGetPowerUsage(h) / 1000.0
+                self.samples.append((float(sm), pw, int(rs)))
+            elif self.kind == "smi":
+                q = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+                     "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+                     "clocks_event_reasons.sw_power_cap")
+                out = subprocess.run(["nvidia-smi", f"--id={self.index}", f"--query-gpu={q}", "--format=csv,noheader,nounits"],
+                                     capture_output=True, text=True, timeout=20).stdout
+                parts = [x.strip() for x in out.strip().split(",")]
+                mask = 0
+                for name, val in zip(["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"], parts[3:7]):
+                    if val.lower().startswith("active"):
+                        mask |= self.REASONS[name]
+                self.max_mhz = float(parts[1])
+                self.samples.append((float(parts[0]), float(parts[2]), mask))
+        except Exception:  # noqa: BLE001 - a failed sample is just missing
+            pass
+
+    def watch(self, done_event) -> None:
+        """Sample while `done_event` (a CUDA event recorded after the timed launches) is pending."""
+        if self.kind == "off":
+            return
+        while True:
+            self.sample()
+            if done_event.query():
+                return
+            for _ in range(25):
+                time.sleep(0.01)
+                if done_event.query():
+                    return
+
+    def summary(self) -> dict:
+        if not self.samples:
+            return {"sm_mhz": None, "sm_max_mhz": self.max_mhz, "reasons": ["no samples (" + self.kind + ")"]}
+        mask = 0
+        for x in self.samples:
+            mask |= x[2]
+        reasons = sorted(n for n, bit in self.REASONS.items() if mask & bit)
+        return {"sm_mhz": statistics.median(x[0] for x in self.samples), "sm_max_mhz": self.max_mhz,
+                "power_w_max": max(x[1] for x in self.samples), "samples": len(self.samples),
+                "reasons": reasons, "source": self.kind}
 
 
 def main():
@@ -139,7 +164,7 @@ def main():
             dist.barrier(group)
             torch.cuda.synchronize()
 
-    def timed(fn, steps, warmup):
+    def timed(fn, steps, warmup, sampler=None):
         for _ in range(warmup):
             fn()
         sync()
@@ -148,6 +173,8 @@ def main():
         for _ in range(steps):
             fn()
         e1.record()
+        if sampler is not None:
+            sampler.watch(e1)  # the launches above are asynchronous: the GPU is inside the region now
         sync()
         ms = torch.tensor([e0.elapsed_time(e1) / steps], device=dev)
         if world > 1:
@@ -169,14 +196,9 @@ def main():
     del ref_rows
 
     # ---- headline: device-timed fused op
-    sampler = ClockSampler(torch.cuda.current_device())
-    if rank == 0:
-        sampler.start()
-        time.sleep(0.5)  # let nvidia-smi come up so that it samples the timed region
-    if world > 1:
-        dist.barrier(group)
-    ms = timed(lambda: G.ag_gemm_intra_node(a, b, ctx, out=c), K_STEPS, W)
-    clocks = sampler.stop() if rank == 0 else None
+    sampler = ClockSampler(torch.cuda.current_device()) if rank == 0 else None
+    ms = timed(lambda: G.ag_gemm_intra_node(a, b, ctx, out=c), K_STEPS, W, sampler)
+    clocks = sampler.summary() if rank == 0 else None
     check_status()
     launches = K_STEPS  # one fused kernel per step
     value = flops / (ms * 1e-3) / 1e12

@@ -52,6 +52,7 @@ class GemmArgs(C.Structure):
         ("status", C.c_void_p),
         ("timeout_ns", C.c_uint64),
         ("stream", C.c_void_p),
+        ("trace", C.c_void_p),
     ]
 
 
@@ -70,8 +71,10 @@ def available() -> bool:
 def _declare(lib):
     lib.tdist_last_error.restype = C.c_char_p
     lib.tdist_last_error.argtypes = []
-    lib.tdist_status_create.argtypes = [C.POINTER(C.POINTER(Status)), C.POINTER(C.c_void_p)]
-    lib.tdist_status_destroy.argtypes = [C.POINTER(Status)]
+    lib.tdist_status_create.argtypes = [C.POINTER(C.c_void_p)]
+    lib.tdist_status_read.argtypes = [C.c_void_p, C.POINTER(Status)]
+    lib.tdist_status_reset.argtypes = [C.c_void_p]
+    lib.tdist_status_destroy.argtypes = [C.c_void_p]
     lib.tdist_gemm_run.argtypes = [C.POINTER(GemmArgs)]
     lib.tdist_gemm_grid.argtypes = [C.POINTER(GemmArgs)]
 

@@ -19,8 +19,8 @@ namespace tdist {
 
 constexpr int kMaxRanks = 8;
 
-// One per process, in host-pinned mapped memory; the device writes, the host reads after
-// the stream has been synchronised.
+// One per process, in device memory (spin loops poll `abort`, so it must not sit behind PCIe);
+// the host copies it back after the stream has been synchronised.
 struct Status {
     int abort;       // sticky: non-zero once any wait gave up
     int code;        // kStatus*
@@ -55,7 +55,7 @@ __device__ __forceinline__ bool aborted(const WaitCtx& w) {
     return w.status != nullptr && *reinterpret_cast<volatile int*>(&w.status->abort) != 0;
 }
 
-__device__ __noinline__ void report_timeout(const WaitCtx& w, int code, int peer, int index,
+static __device__ __noinline__ void report_timeout(const WaitCtx& w, int code, int peer, int index,
                                             long long expected, long long seen, int where) {
     if (w.status == nullptr) return;
     if (atomicCAS(&w.status->abort, 0, 1) == 0) {
@@ -68,7 +68,7 @@ __device__ __noinline__ void report_timeout(const WaitCtx& w, int code, int peer
         w.status->seen = seen;
         w.status->block = static_cast<int>(blockIdx.x);
         w.status->where = where;
-        __threadfence_system();
+        __threadfence();
     }
 }
 

@@ -17,15 +17,17 @@ extern "C" {
 const char* tdist_last_error(void);
 
 /* ------------------------------------------------------------------ status block */
-/* Host-pinned, device-mapped record that bounded device waits write when they give up. */
+/* Device-memory record that bounded device waits write when they give up. */
 typedef struct TdistStatus {
     int abort_flag, code, kernel_id, rank, peer, index;
     long long expected, seen;
     int block, where;
     int reserved[4];
 } TdistStatus;
-int tdist_status_create(TdistStatus** host_ptr, void** device_ptr);
-int tdist_status_destroy(TdistStatus* host_ptr);
+int tdist_status_create(void** device_ptr);
+int tdist_status_read(const void* device_ptr, TdistStatus* out); /* blocking device-to-host copy */
+int tdist_status_reset(void* device_ptr);
+int tdist_status_destroy(void* device_ptr);
 
 /* ------------------------------------------------------------------ tcgen05 GEMM family */
 enum { TDIST_GEMM_PLAIN = 0, TDIST_GEMM_AG = 1, TDIST_GEMM_RS = 2 };
@@ -65,6 +67,10 @@ typedef struct TdistGemmArgs {
     void* status;      /* device pointer of a TdistStatus, may be NULL */
     uint64_t timeout_ns;
     void* stream;
+    /* Optional timeline, 2048 uint64 %globaltimer stamps (NULL = off). Pusher CTA b < 16 writes at
+     * [40b]: begin, end, then (start, end) of its first 19 blocks. GEMM CTA c < 64 writes at
+     * [1024 + 4c]: producer begin, producer end, ns spent waiting on flags, waits longer than 2 us. */
+    void* trace;
 } TdistGemmArgs;
 
 int tdist_gemm_run(const TdistGemmArgs* args);

@@ -93,6 +93,7 @@ struct GemmParams {
     int is_f16;
     uint32_t epoch;
     int debug_delay_ns;
+    unsigned long long* trace;  // optional timeline (see tdist.h), nullptr = off
     WaitCtx wctx;
 };
 
@@ -133,6 +134,9 @@ __device__ void ag_pusher(const GemmParams& p, uint8_t* smem, uint64_t* bars) {
     uint32_t full[PUSH_STAGES];
     for (int s = 0; s < PUSH_STAGES; ++s) full[s] = smem_u32(&bars[s]);
     uint32_t it_load = 0, it_store = 0;  // running chunk counters (stage = counter % PUSH_STAGES)
+    unsigned long long* tr = (p.trace != nullptr && blockIdx.x < 16) ? p.trace + blockIdx.x * 40 : nullptr;
+    int tr_item = 0;
+    if (tr) tr[0] = globaltimer_ns();
 
     for (int item = static_cast<int>(blockIdx.x); item < nitems; item += p.num_comm) {
         const int hop = item / p.seg_blocks + 1;
@@ -146,6 +150,7 @@ __device__ void ag_pusher(const GemmParams& p, uint8_t* smem, uint64_t* bars) {
                     (static_cast<size_t>(p.rank) * p.m_per_rank + static_cast<size_t>(mb) * BM) * row_bytes;
         const int nchunks = static_cast<int>((bytes + PUSH_CHUNK - 1) / PUSH_CHUNK);
         if (p.debug_delay_ns > 0) __nanosleep(p.debug_delay_ns);
+        if (tr && tr_item < 19) tr[2 + 2 * tr_item] = globaltimer_ns();
 
         for (int c = 0; c < nchunks + PUSH_AHEAD; ++c) {
             if (c < nchunks) {
@@ -176,7 +181,10 @@ __device__ void ag_pusher(const GemmParams& p, uint8_t* smem, uint64_t* bars) {
         fence_proxy_async();
         fence_acq_rel_sys();
         st_release_sys_u32(p.flags_peer[dst] + p.rank * p.seg_blocks + mb, p.epoch);
+        if (tr && tr_item < 19) tr[3 + 2 * tr_item] = globaltimer_ns();
+        ++tr_item;
     }
+    if (tr) tr[1] = globaltimer_ns();
 }
 
 // ------------------------------------------------------------------------------------------
@@ -303,6 +311,9 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_sm100_kernel(const __grid_con
         // ===================== TMA producer (every CTA loads its own A rows and B rows) ==========
         if (lane == 0) {
             uint32_t it = 0;
+            unsigned long long* tr = (p.trace != nullptr && cta < 64) ? p.trace + 1024 + cta * 4 : nullptr;
+            unsigned long long waited = 0, blocked = 0;
+            if (tr) tr[0] = globaltimer_ns();
             for (int t = unit; t < p.num_tiles; t += num_units) {
                 const TileCoord tc = decode_tile(t, first_seg, p.world, p.seg_m_tiles, p.n_tiles, p.group_m);
                 const int block = tc.m_in_seg * CTAS + cta_rank;  // 128-row block inside the segment
@@ -313,8 +324,14 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_sm100_kernel(const __grid_con
                         am = &p.tm_a_own;
                         az = 0;
                     } else if (block < p.seg_blocks) {
+                        const unsigned long long w0 = tr ? globaltimer_ns() : 0;
                         wait_flag_ge_sys(p.flags + tc.seg * p.seg_blocks + block, p.epoch, p.wctx, tc.seg, block, 1);
                         fence_proxy_async();
+                        if (tr) {
+                            const unsigned long long dt = globaltimer_ns() - w0;
+                            waited += dt;
+                            blocked += dt > 2000 ? 1 : 0;
+                        }
                     }
                 }
                 const int row = block * BM;
@@ -335,6 +352,11 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_sm100_kernel(const __grid_con
                         tma_load_3d_pair(sa + A_BYTES, &p.tm_b, leader_full, kb * BK, col, 0);
                     }
                 }
+            }
+            if (tr) {
+                tr[1] = globaltimer_ns();
+                tr[2] = waited;
+                tr[3] = blocked;
             }
         }
         __syncwarp();
@@ -647,6 +669,7 @@ extern "C" int tdist_gemm_run(const TdistGemmArgs* a) {
     p.is_f16 = a->dtype == TDIST_F16;
     p.epoch = a->epoch;
     p.debug_delay_ns = a->debug_delay_ns;
+    p.trace = static_cast<unsigned long long*>(a->trace);
     p.wctx.status = static_cast<Status*>(a->status);
     p.wctx.timeout_ns = a->timeout_ns;
     p.wctx.kernel_id = kKernelGemm;

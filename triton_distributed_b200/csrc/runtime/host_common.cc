@@ -122,18 +122,28 @@ int sm_count() {
 
 extern "C" const char* tdist_last_error(void) { return tdist_host::g_last_error.c_str(); }
 
-extern "C" int tdist_status_create(TdistStatus** host_ptr, void** device_ptr) {
-    void* h = nullptr;
-    TDIST_CUDA_OK(cudaHostAlloc(&h, sizeof(TdistStatus), cudaHostAllocMapped | cudaHostAllocPortable));
-    std::memset(h, 0, sizeof(TdistStatus));
+// The status block lives in device memory: waiting kernels poll its abort word, and a poll that
+// crossed PCIe to host memory would slow every spin loop down whenever the bus is busy.
+extern "C" int tdist_status_create(void** device_ptr) {
     void* d = nullptr;
-    TDIST_CUDA_OK(cudaHostGetDevicePointer(&d, h, 0));
-    *host_ptr = static_cast<TdistStatus*>(h);
+    TDIST_CUDA_OK(cudaMalloc(&d, sizeof(TdistStatus)));
+    TDIST_CUDA_OK(cudaMemset(d, 0, sizeof(TdistStatus)));
     *device_ptr = d;
     return 0;
 }
 
-extern "C" int tdist_status_destroy(TdistStatus* host_ptr) {
-    if (host_ptr != nullptr) TDIST_CUDA_OK(cudaFreeHost(host_ptr));
+// Blocking copy of the block to the host (call after the producing stream was synchronised).
+extern "C" int tdist_status_read(const void* device_ptr, TdistStatus* out) {
+    TDIST_CUDA_OK(cudaMemcpy(out, device_ptr, sizeof(TdistStatus), cudaMemcpyDeviceToHost));
+    return 0;
+}
+
+extern "C" int tdist_status_reset(void* device_ptr) {
+    TDIST_CUDA_OK(cudaMemset(device_ptr, 0, sizeof(TdistStatus)));
+    return 0;
+}
+
+extern "C" int tdist_status_destroy(void* device_ptr) {
+    if (device_ptr != nullptr) TDIST_CUDA_OK(cudaFree(device_ptr));
     return 0;
 }

@@ -127,6 +127,7 @@ class AllGatherGEMMTensorParallelContext:
     num_sms: int = 0
     for_correctness: bool = False
     debug_delay_ns: int = 0
+    trace: Optional[torch.Tensor] = None  # int64[2048] timeline buffer, filled by the kernel when set
 
 
 def create_ag_gemm_intra_node_context(tensor_A: torch.Tensor, tensor_B: torch.Tensor, rank: int, num_ranks: int,
@@ -178,6 +179,8 @@ def ag_gemm_intra_node(a: torch.Tensor, b: torch.Tensor, ctx: Optional[AllGather
     g.num_sms = ctx.num_sms
     g.num_comm_sms = ctx.num_comm_sms
     g.debug_delay_ns = ctx.debug_delay_ns
+    if ctx.trace is not None:
+        g.trace = ctx.trace.data_ptr()
     if ctx.world > 1:
         half = ctx.epoch & 1
         g.a_ws = ctx.workspace.local[half].data_ptr()

@@ -22,36 +22,42 @@ def default_timeout_ns() -> int:
 
 
 class StatusBlock:
-    """One per process. ``device_ptr`` goes into kernel arguments; :meth:`check` is called after
-    the stream has been synchronised and raises :class:`TdistTimeoutError` if any wait gave up."""
+    """One per process, in device memory. ``device_ptr`` goes into kernel arguments; :meth:`check`
+    is called after the stream has been synchronised, copies the block back and raises
+    :class:`TdistTimeoutError` if any wait gave up."""
 
     def __init__(self):
-        self._host = C.POINTER(_lib.Status)()
         dptr = C.c_void_p()
-        _lib.check(_lib.lib().tdist_status_create(C.byref(self._host), C.byref(dptr)), "tdist_status_create")
+        _lib.check(_lib.lib().tdist_status_create(C.byref(dptr)), "tdist_status_create")
         self.device_ptr = dptr.value
 
     @property
     def record(self) -> "_lib.Status":
-        return self._host.contents
+        """Snapshot of the block (blocking device-to-host copy)."""
+        rec = _lib.Status()
+        _lib.check(_lib.lib().tdist_status_read(self.device_ptr, C.byref(rec)), "tdist_status_read")
+        return rec
 
     def aborted(self) -> bool:
         return self.record.abort_flag != 0
 
-    def describe(self) -> str:
-        s = self.record
+    @staticmethod
+    def _describe(s) -> str:
         return (f"{_CODES.get(s.code, s.code)} in kernel {_KERNELS.get(s.kernel_id, s.kernel_id)} on rank {s.rank} "
                 f"(block {s.block}, site {s.where}): peer {s.peer}, index {s.index}, expected {s.expected}, seen {s.seen}")
 
+    def describe(self) -> str:
+        return self._describe(self.record)
+
     def reset(self) -> None:
-        C.memset(self._host, 0, C.sizeof(_lib.Status))
+        _lib.check(_lib.lib().tdist_status_reset(self.device_ptr), "tdist_status_reset")
 
     def check(self, reset: bool = True) -> None:
-        if self.aborted():
-            msg = self.describe()
+        rec = self.record
+        if rec.abort_flag != 0:
             if reset:
                 self.reset()
-            raise _lib.TdistTimeoutError(msg)
+            raise _lib.TdistTimeoutError(self._describe(rec))
 
 
 _GLOBAL: Optional[StatusBlock] = None
