@@ -1,0 +1,125 @@
+"""MoE routing kernels and the low-latency all-to-all on one GPU (ranks emulated: all send halves,
+then all receive halves). Oracles: torch softmax/topk/sort, the torch restatement of the aligned
+sort, and a direct gather of the rows each rank should receive (the reference checks the same
+against NCCL all_to_all_single, test_all_to_all.py:184-241)."""
+import pytest
+import torch
+
+from triton_distributed_b200.ops import all_to_all as A
+from triton_distributed_b200.ops import moe_utils as MU
+from triton_distributed_b200.runtime import LocalWorld, check_status
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.mark.parametrize("T,E,K", [(128, 256, 8), (7, 64, 2), (1000, 32, 4), (33, 1024, 8)])
+def test_topk_softmax(cuda_device, T, E, K):
+    torch.manual_seed(T + E)
+    logits = torch.randn(T, E, device=cuda_device)
+    ids, w = MU.topk_softmax(logits, K)
+    ref_ids, ref_w = MU.topk_softmax(logits.cpu(), K)
+    assert torch.equal(ids.cpu(), ref_ids)
+    torch.testing.assert_close(w.cpu(), ref_w, atol=1e-6, rtol=1e-4)
+    _, wn = MU.topk_softmax(logits, K, renormalize=True)
+    torch.testing.assert_close(wn.sum(-1).cpu(), torch.ones(T), atol=1e-5, rtol=1e-5)
+
+
+@pytest.mark.parametrize("T,E,K", [(128, 256, 8), (5, 16, 2), (4096, 64, 6), (600, 300, 3)])
+def test_route_is_a_stable_expert_sort(cuda_device, T, E, K):
+    torch.manual_seed(T)
+    ids = torch.randint(0, E, (T, K), dtype=torch.int32, device=cuda_device)
+    r = MU.route(ids, E)
+    ref = MU.route(ids.cpu(), E)
+    for got, want in zip(r, ref):
+        assert torch.equal(got.cpu(), want)
+
+
+@pytest.mark.parametrize("ranks,tpr,E,K,bs", [(8, 128, 32, 2, 128), (4, 1000, 8, 4, 64), (2, 17, 256, 8, 16), (1, 300, 60, 5, 128)])
+def test_align_block_size_matches_oracle(cuda_device, ranks, tpr, E, K, bs):
+    torch.manual_seed(ranks * tpr)
+    ids = torch.randint(0, E, (ranks * tpr, K), dtype=torch.int32, device=cuda_device)
+    got = MU.sort_topk_ids_align_block_size(ids, E, ranks, tpr, bs)
+    want = MU.full_moe_align_block_size(ids, bs, E, ranks, tpr)
+    total = int(want[4].item())
+    assert int(got[4].item()) == total
+    assert torch.equal(got[0], want[0])  # sorted ids incl. padding up to capacity
+    nb = total // bs
+    assert torch.equal(got[1][:nb], want[1][:nb]) and torch.equal(got[2][:nb], want[2][:nb])
+    assert torch.equal(got[3], want[3])
+
+
+def _emulated(world, fn_send, fn_recv):
+    for r in range(world):
+        fn_send(r)
+    outs = [fn_recv(r) for r in range(world)]
+    check_status()
+    return outs
+
+
+@pytest.mark.parametrize("world,T,E,K,H,with_scale", [(2, 16, 8, 2, 256, True), (4, 128, 32, 4, 1024, False), (8, 128, 256, 8, 7168, True)])
+def test_fast_all_to_all_rows_land_in_source_slots(cuda_device, world, T, E, K, H, with_scale):
+    torch.manual_seed(world + T)
+    lw = LocalWorld(world, cuda_device)
+    epr = E // world
+    max_m = T * K
+    ctxs = [A.create_all_to_all_context(max_m, H, r, E, world, epr, heap=lw.heap(r), device=cuda_device) for r in range(world)]
+    for it in range(3):
+        sends, cums, scales = [], [], []
+        for r in range(world):
+            ids = torch.randint(0, E, (T, K), dtype=torch.int32, device=cuda_device)
+            rt = MU.route(ids, E)
+            x = torch.randn(T, H, device=cuda_device).to(torch.bfloat16)
+            sends.append(x[rt.sorted_token.long()].contiguous())
+            cums.append(rt.cumsum)
+            scales.append(torch.rand(T * K, device=cuda_device) if with_scale else None)
+        _emulated(world, lambda r: A.fast_all_to_all(ctxs[r], sends[r], cums[r], scales[r], phase=1), lambda r: None)
+        outs = [A.fast_all_to_all(ctxs[r], sends[r], cums[r], scales[r], phase=2) for r in range(world)]
+        check_status()
+        for d in range(world):
+            splits, recv, rscale = outs[d]
+            for s in range(world):
+                lo, hi = int(cums[s][d * epr]), int(cums[s][(d + 1) * epr])
+                assert torch.equal(recv[s * max_m: s * max_m + hi - lo], sends[s][lo:hi]), (it, d, s)
+                want = cums[s][d * epr + 1:(d + 1) * epr + 1] - cums[s][d * epr:(d + 1) * epr]
+                assert torch.equal(splits[s * epr:(s + 1) * epr], want)
+                if with_scale:
+                    assert torch.equal(rscale[s * max_m: s * max_m + hi - lo, 0], scales[s][lo:hi])
+            data, _ = A.all_to_all_post_process(ctxs[d], splits, recv, rscale)
+            assert data.shape[0] == int(splits.sum())
+
+
+@pytest.mark.parametrize("world,T,E,K,H", [(2, 8, 4, 2, 256), (8, 128, 256, 8, 7168), (4, 100, 64, 6, 2048)])
+def test_fused_dispatch_combine_roundtrip(cuda_device, world, T, E, K, H):
+    """Identity experts: out[t] = sum_k w[t,k] * dequant(quant(x[t]))."""
+    torch.manual_seed(world * 3 + T)
+    lw = LocalWorld(world, cuda_device)
+    ctxs = [A.create_moe_dispatch_context(T, H, K, E, r, world, heap=lw.heap(r), device=cuda_device) for r in range(world)]
+    for it in range(2):
+        xs = [torch.randn(T, H, device=cuda_device).to(torch.bfloat16) for _ in range(world)]
+        routed = [MU.topk_softmax(torch.randn(T, E, device=cuda_device), K) for _ in range(world)]
+        for r in range(world):
+            A.moe_dispatch(ctxs[r], xs[r], routed[r][0], routed[r][1], phase=1)
+        recvs = [A.moe_dispatch(ctxs[r], xs[r], routed[r][0], routed[r][1], phase=2) for r in range(world)]
+        check_status()
+        # quantisation matches the torch statement on what rank 0 received from rank 1 (or itself)
+        d, s = 0, world - 1
+        rx, rs, splits = recvs[d]
+        n = int(splits[s].sum())
+        rows = ctxs[s].routing.sorted_token.long()[int(ctxs[s].routing.cumsum[0]): int(ctxs[s].routing.cumsum[E // world])]
+        q_ref, s_ref = A.quant_fp8_reference(xs[s][rows])
+        mm = T * K
+        torch.testing.assert_close(rs[s * mm: s * mm + n], s_ref, rtol=1e-6, atol=0)
+        assert (rx[s * mm: s * mm + n].view(torch.uint8).int() - q_ref.view(torch.uint8).int()).abs().max() <= 1
+        # identity experts
+        ys = [A.dequant_fp8(recvs[r][0], recvs[r][1]) for r in range(world)]
+        outs = [None] * world
+        for r in range(world):
+            A.moe_combine(ctxs[r], ys[r], recvs[r][2], phase=1)
+        for r in range(world):
+            outs[r] = A.moe_combine(ctxs[r], ys[r], recvs[r][2], phase=2)
+        check_status()
+        for r in range(world):
+            q, sc = A.quant_fp8_reference(xs[r])
+            deq = (q.float().view(T, H // 128, 128) * sc.unsqueeze(-1)).view(T, H).to(torch.bfloat16).float()
+            ref = deq * routed[r][1].sum(-1, keepdim=True)
+            torch.testing.assert_close(outs[r].float(), ref, atol=2e-2, rtol=2e-2)

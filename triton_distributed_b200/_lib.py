@@ -56,8 +56,47 @@ class GemmArgs(C.Structure):
     ]
 
 
+class CollArgs(C.Structure):
+    _fields_ = [
+        ("buf_peer", C.c_void_p * MAX_RANKS),
+        ("sig_peer", C.c_void_p * MAX_RANKS),
+        ("ll_peer", C.c_void_p * MAX_RANKS),
+        ("counters", C.c_void_p),
+        ("input", C.c_void_p),
+        ("output", C.c_void_p),
+        ("seg_bytes", C.c_size_t),
+        ("world", C.c_int), ("rank", C.c_int),
+        ("mode", C.c_int), ("phase", C.c_int), ("ctas_per_peer", C.c_int), ("dtype", C.c_int),
+        ("epoch", C.c_uint64),
+        ("status", C.c_void_p),
+        ("timeout_ns", C.c_uint64),
+        ("stream", C.c_void_p),
+    ]
+
+
+class A2AArgs(C.Structure):
+    _fields_ = [
+        ("send", C.c_void_p), ("src_index", C.c_void_p), ("counts", C.c_void_p), ("send_scale", C.c_void_p),
+        ("recv_peer", C.c_void_p * MAX_RANKS), ("scale_peer", C.c_void_p * MAX_RANKS),
+        ("splits_peer", C.c_void_p * MAX_RANKS), ("sig_peer", C.c_void_p * MAX_RANKS),
+        ("counters", C.c_void_p),
+        ("slot_of", C.c_void_p), ("cumsum", C.c_void_p), ("topk_ids", C.c_void_p), ("topk_w", C.c_void_p),
+        ("out", C.c_void_p),
+        ("ntok", C.c_int), ("topk", C.c_int),
+        ("row_bytes_in", C.c_int), ("row_bytes_out", C.c_int), ("scale_cols", C.c_int), ("hidden", C.c_int),
+        ("max_m", C.c_int), ("epr", C.c_int), ("world", C.c_int), ("rank", C.c_int),
+        ("mode", C.c_int), ("quant", C.c_int), ("reduce", C.c_int), ("phase", C.c_int), ("ctas_per_peer", C.c_int),
+        ("epoch", C.c_uint64),
+        ("status", C.c_void_p),
+        ("timeout_ns", C.c_uint64),
+        ("stream", C.c_void_p),
+    ]
+
+
 GEMM_PLAIN, GEMM_AG, GEMM_RS = 0, 1, 2
-DT_BF16, DT_F16 = 0, 1
+A2A_DISPATCH, A2A_COMBINE = 0, 1
+DT_BF16, DT_F16, DT_F32, DT_I32 = 0, 1, 2, 3
+AG_PULL, AG_PUSH, AG_LL = 0, 1, 2
 
 
 def lib_path() -> Path:
@@ -77,6 +116,19 @@ def _declare(lib):
     lib.tdist_status_destroy.argtypes = [C.c_void_p]
     lib.tdist_gemm_run.argtypes = [C.POINTER(GemmArgs)]
     lib.tdist_gemm_grid.argtypes = [C.POINTER(GemmArgs)]
+    lib.tdist_allgather.argtypes = [C.POINTER(CollArgs)]
+    lib.tdist_reduce_scatter.argtypes = [C.POINTER(CollArgs)]
+    lib.tdist_barrier_all.argtypes = [C.POINTER(C.c_void_p), C.c_void_p, C.c_int, C.c_int, C.c_void_p, C.c_uint64, C.c_void_p]
+    lib.tdist_p2p_copy.argtypes = [C.c_void_p, C.c_void_p, C.c_size_t, C.c_int, C.c_int, C.c_int, C.c_int,
+                                   C.c_void_p, C.c_uint64, C.c_void_p]
+    lib.tdist_a2a.argtypes = [C.POINTER(A2AArgs)]
+    lib.tdist_dequant_fp8.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_void_p]
+    lib.tdist_moe_route.argtypes = [C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]
+    lib.tdist_moe_align_block_size.argtypes = [C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_int,
+                                               C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]
+    lib.tdist_moe_topk_softmax.argtypes = [C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_void_p, C.c_void_p]
+    lib.tdist_stream_write_value.argtypes = [C.c_void_p, C.c_uint64, C.c_uint64, C.c_int]
+    lib.tdist_stream_wait_value.argtypes = [C.c_void_p, C.c_uint64, C.c_uint64, C.c_int, C.c_int]
 
 
 def lib():

@@ -31,7 +31,7 @@ int tdist_status_destroy(void* device_ptr);
 
 /* ------------------------------------------------------------------ tcgen05 GEMM family */
 enum { TDIST_GEMM_PLAIN = 0, TDIST_GEMM_AG = 1, TDIST_GEMM_RS = 2 };
-enum { TDIST_BF16 = 0, TDIST_F16 = 1 };
+enum { TDIST_BF16 = 0, TDIST_F16 = 1, TDIST_F32 = 2, TDIST_I32 = 3 };
 
 typedef struct TdistGemmArgs {
     /* A operand. PLAIN/RS: the whole local A, [world*m_per_rank, K] row-major (K contiguous).
@@ -76,6 +76,87 @@ typedef struct TdistGemmArgs {
 int tdist_gemm_run(const TdistGemmArgs* args);
 /* Number of CTAs a call with these arguments launches (for occupancy planning and tests). */
 int tdist_gemm_grid(const TdistGemmArgs* args);
+
+/* ------------------------------------------------------------------ standalone collectives */
+enum { TDIST_AG_PULL = 0, TDIST_AG_PUSH = 1, TDIST_AG_LL = 2 };
+
+typedef struct TdistCollArgs {
+    /* all-gather: the in-place symmetric buffer [world * seg_bytes] of every rank as mapped here.
+     * reduce-scatter: the symmetric staging [world][seg_bytes] of every rank (the caller alternates
+     * between two such buffers from call to call). */
+    void* buf_peer[TDIST_MAX_RANKS];
+    void* sig_peer[TDIST_MAX_RANKS];  /* uint64 flags [world] of every rank */
+    void* ll_peer[TDIST_MAX_RANKS];   /* LL all-gather only: staging [world][2 * seg_bytes], alternated like above */
+    void* counters;                   /* local uint32 [world], zero on first use */
+    const void* input;                /* reduce-scatter: local [world * seg_bytes] */
+    void* output;                     /* reduce-scatter: local [seg_bytes] */
+    size_t seg_bytes;
+    int world, rank;
+    int mode;           /* TDIST_AG_* (all-gather only) */
+    int phase;          /* 0 or 3 = whole op; 1 = send half only, 2 = receive half only (emulated ranks) */
+    int ctas_per_peer;  /* 0 = default 4 */
+    int dtype;          /* reduce-scatter element type */
+    uint64_t epoch;     /* strictly increasing per context, starts at 1 */
+    void* status;
+    uint64_t timeout_ns;
+    void* stream;
+} TdistCollArgs;
+
+int tdist_allgather(const TdistCollArgs* args);
+int tdist_reduce_scatter(const TdistCollArgs* args);
+/* Device-side barrier of all ranks on `stream`: flags_peer[r] = rank r's uint64[8] flag array as
+ * mapped here, epoch_local = a local uint64 counter owned by the barrier. */
+int tdist_barrier_all(void* const* flags_peer, void* epoch_local, int world, int rank, void* status,
+                      uint64_t timeout_ns, void* stream);
+
+/* Peer-to-peer copy in one of five data paths (see csrc/kernels/p2p_copy.cu). */
+int tdist_p2p_copy(const void* src, void* dst, size_t bytes, int mode, int ctas, int threads, int chunk,
+                   void* status, uint64_t timeout_ns, void* stream);
+
+/* ------------------------------------------------------------------ MoE all-to-all */
+enum { TDIST_A2A_DISPATCH = 0, TDIST_A2A_COMBINE = 1 };
+
+typedef struct TdistA2AArgs {
+    const void* send;        /* DISPATCH: [rows, row_bytes_in]; COMBINE: receive-layout [world*max_m, row_bytes_in] */
+    const void* src_index;   /* DISPATCH, optional int32 [rows]: source row of each expert-sorted row */
+    const void* counts;      /* DISPATCH: int32 cumsum [G+1]; COMBINE: int32 received splits [world*epr] */
+    const void* send_scale;  /* optional fp32 [rows, scale_cols], travels with the rows (no quantisation) */
+    void* recv_peer[TDIST_MAX_RANKS];   /* this call's parity of every rank: [world(src)][max_m][row_bytes_out] */
+    void* scale_peer[TDIST_MAX_RANKS];  /* fp32 [world(src)][max_m][scale_cols], may be NULL */
+    void* splits_peer[TDIST_MAX_RANKS]; /* int32 [world(src)][epr] (DISPATCH) */
+    void* sig_peer[TDIST_MAX_RANKS];    /* uint64 [world] */
+    void* counters;                     /* local uint32 [world], zero on first use */
+    /* fused top-k weighted reduction after COMBINE (reduce = 1) */
+    const void* slot_of;     /* int32 [ntok*topk] from tdist_moe_route */
+    const void* cumsum;      /* int32 [G+1] of this rank's dispatch */
+    const void* topk_ids;    /* int32 [ntok*topk] */
+    const void* topk_w;      /* fp32 [ntok*topk] */
+    void* out;               /* bf16 [ntok, hidden] */
+    int ntok, topk;
+    int row_bytes_in, row_bytes_out, scale_cols, hidden;
+    int max_m, epr, world, rank;
+    int mode;                /* TDIST_A2A_* */
+    int quant;               /* DISPATCH: 1 = bf16 -> fp8 e4m3 with one fp32 scale per 128 values */
+    int reduce;
+    int phase;               /* 0/3 whole op, 1 send half, 2 receive half */
+    int ctas_per_peer;       /* 0 = default 8 */
+    uint64_t epoch;
+    void* status;
+    uint64_t timeout_ns;
+    void* stream;
+} TdistA2AArgs;
+
+int tdist_a2a(const TdistA2AArgs* args);
+int tdist_dequant_fp8(const void* x, const void* scale, void* out_bf16, int rows, int hidden, void* stream);
+
+/* ------------------------------------------------------------------ MoE routing */
+int tdist_moe_route(const void* ids, int n, int topk, int num_experts, void* splits, void* cumsum,
+                    void* sorted_token, void* slot_of, void* stream);
+int tdist_moe_align_block_size(const void* ids, int numel_per_rank, int num_experts, int num_ranks, int block_size,
+                               void* sorted_ids, int sorted_cap, void* expert_ids, void* block_barrier_ids,
+                               void* rank_block_num, void* num_tokens_post_pad, void* stream);
+int tdist_moe_topk_softmax(const void* logits_f32, int ntok, int num_experts, int topk, int renormalize,
+                           void* ids, void* weights, void* stream);
 
 #ifdef __cplusplus
 }

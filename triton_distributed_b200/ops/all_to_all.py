@@ -1,0 +1,320 @@
+"""Low-latency MoE all-to-all (expert-parallel dispatch / combine).
+
+Two levels:
+
+* the reference's generic op — ``create_all_to_all_context`` / ``fast_all_to_all(ctx, send[ntok,hidden],
+  send_split_cumsum[G+1], send_scale) -> (recv_splits[G], recv[ws*max_m, hidden], recv_scale)`` and
+  ``all_to_all_post_process`` (reference kernels/nvidia/low_latency_all_to_all.py:125-270): rows
+  already sorted by expert, source rank ``r`` lands in rows ``[r*max_m, r*max_m + count_r)``;
+* a fused MoE pair ``moe_dispatch`` / ``moe_combine`` for the serving layout of the reference's
+  tutorial 04 (tutorials/04-deepseek-infer-all2all.py:150-201): dispatch gathers rows by the routing
+  permutation, quantises bf16 to fp8 e4m3 with one fp32 scale per 128 values on the fly and ships
+  rows + scales + per-expert counts in one launch; combine ships the experts' bf16 outputs back and
+  applies the top-k weights in the same launch.
+
+CUDA tensors run ``csrc/kernels/a2a.cu``; CPU tensors run a torch.distributed restatement.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from dataclasses import dataclass
+from typing import Optional, Tuple
+
+import torch
+import torch.distributed as dist
+
+from .. import _lib
+from ..runtime import SymmTensor, default_timeout_ns, global_status, symm_heap
+from . import moe_utils
+
+launch_count = 0
+
+
+@dataclass
+class AllToAllContext:
+    max_m: int
+    hidden: int
+    rank: int
+    num_tot_experts: int
+    WORLD_SIZE: int
+    experts_per_rank: int
+    dtype: torch.dtype
+    scale_dtype: torch.dtype
+    scale_cols: int = 1
+    recv_buf: Optional[SymmTensor] = None        # [2, world*max_m, hidden]
+    scale_recv_buf: Optional[SymmTensor] = None  # [2, world*max_m, scale_cols] fp32
+    split_recv_buf: Optional[SymmTensor] = None  # [2, world*epr] int32
+    signal_buf: Optional[SymmTensor] = None      # int64 [8]
+    counters: Optional[torch.Tensor] = None
+    call_count: int = 0
+    ctas_per_peer: int = 0
+    group: object = None
+
+
+def create_all_to_all_context(max_m: int, hidden: int, rank: int, num_tot_experts: int, WORLD_SIZE: int,
+                              experts_per_rank: int, dtype: torch.dtype = torch.bfloat16,
+                              scale_dtype: torch.dtype = torch.float32, scale_cols: int = 1, heap=None, group=None,
+                              device=None) -> AllToAllContext:
+    """``max_m`` = most rows one rank sends in one call (tokens * topk). ``scale_cols`` = fp32 scales
+    carried per row (1 in the reference's test, hidden/128 for block-scaled fp8)."""
+    ctx = AllToAllContext(max_m, hidden, rank, num_tot_experts, WORLD_SIZE, experts_per_rank, dtype, scale_dtype,
+                          scale_cols, group=group)
+    on_cuda = (device is not None and torch.device(device).type == "cuda") or (device is None and torch.cuda.is_available())
+    if on_cuda:
+        heap = heap or symm_heap(group)
+        ctx.recv_buf = heap.empty((2, WORLD_SIZE * max_m, hidden), dtype)
+        ctx.scale_recv_buf = heap.empty((2, WORLD_SIZE * max_m, scale_cols), torch.float32)
+        ctx.split_recv_buf = heap.zeros((2, WORLD_SIZE * experts_per_rank), torch.int32)
+        ctx.signal_buf = heap.zeros((_lib.MAX_RANKS,), torch.int64)
+        ctx.counters = torch.zeros(_lib.MAX_RANKS, dtype=torch.int32, device=ctx.signal_buf.local.device)
+    return ctx
+
+
+def _fill_common(a: "_lib.A2AArgs", ctx: AllToAllContext, half: int, phase: int, device, stream) -> None:
+    a.recv_peer = _lib.ptr_array([t[half].data_ptr() for t in ctx.recv_buf.peers])
+    a.scale_peer = _lib.ptr_array([t[half].data_ptr() for t in ctx.scale_recv_buf.peers])
+    a.splits_peer = _lib.ptr_array([t[half].data_ptr() for t in ctx.split_recv_buf.peers])
+    a.sig_peer = _lib.ptr_array(ctx.signal_buf.ptrs)
+    a.counters = ctx.counters.data_ptr()
+    a.max_m, a.epr, a.world, a.rank = ctx.max_m, ctx.experts_per_rank, ctx.WORLD_SIZE, ctx.rank
+    a.phase = phase
+    a.ctas_per_peer = ctx.ctas_per_peer
+    a.epoch = ctx.call_count
+    st = global_status()
+    a.status = st.device_ptr if st is not None else None
+    a.timeout_ns = default_timeout_ns()
+    a.stream = (stream or torch.cuda.current_stream(device)).cuda_stream
+
+
+def _next_call(ctx: AllToAllContext, phase: int) -> int:
+    """Advance the call counter (not for a receive-only half) and return the buffer parity."""
+    if phase != 2:
+        ctx.call_count += 1
+    return ctx.call_count & 1
+
+
+def _launch(a: "_lib.A2AArgs") -> None:
+    global launch_count
+    _lib.check(_lib.lib().tdist_a2a(C.byref(a)), "tdist_a2a")
+    launch_count += 1
+
+
+def fast_all_to_all(ctx: AllToAllContext, send_tensor: torch.Tensor, send_split_cumsum: torch.Tensor,
+                    send_scale: Optional[torch.Tensor] = None, phase: int = 3, stream=None):
+    """Rows ``[cumsum[e], cumsum[e+1])`` of ``send_tensor`` go to the rank owning expert ``e``.
+    Returns views into this call's half of the receive buffers: ``(recv_splits[G] int32 laid out
+    [source rank, local expert], recv[ws*max_m, hidden], recv_scale[ws*max_m, scale_cols] | None)``.
+    The views stay valid until the call after next."""
+    ntok = send_tensor.shape[0]
+    if ntok > ctx.max_m:
+        raise ValueError(f"{ntok} rows exceed the context's max_m {ctx.max_m}")
+    if send_tensor.device.type != "cuda":
+        return _fast_all_to_all_cpu(ctx, send_tensor, send_split_cumsum, send_scale)
+    if not send_tensor.is_contiguous() or send_tensor.shape[1] != ctx.hidden or send_tensor.dtype != ctx.dtype:
+        raise ValueError("send_tensor must be contiguous [rows, hidden] of the context's dtype")
+    half = _next_call(ctx, phase)
+    a = _lib.A2AArgs()
+    a.send = send_tensor.data_ptr()
+    cums = send_split_cumsum if send_split_cumsum.dtype == torch.int32 else send_split_cumsum.to(torch.int32)
+    a.counts = cums.data_ptr()
+    scale = None
+    if send_scale is not None:
+        scale = send_scale.reshape(ntok, -1).to(torch.float32).contiguous()
+        if scale.shape[1] != ctx.scale_cols:
+            raise ValueError(f"send_scale has {scale.shape[1]} columns, context was built for {ctx.scale_cols}")
+        a.send_scale = scale.data_ptr()
+    a.row_bytes_in = a.row_bytes_out = ctx.hidden * send_tensor.element_size()
+    a.scale_cols, a.hidden = ctx.scale_cols, ctx.hidden
+    a.mode = _lib.A2A_DISPATCH
+    _fill_common(a, ctx, half, phase, send_tensor.device, stream)
+    _launch(a)
+    return (ctx.split_recv_buf.local[half], ctx.recv_buf.local[half],
+            ctx.scale_recv_buf.local[half] if send_scale is not None else None)
+
+
+def all_to_all_post_process(ctx: AllToAllContext, input_splits: torch.Tensor, recv_buffer: torch.Tensor,
+                            scale_buffer: Optional[torch.Tensor] = None):
+    """Compact the per-source slots of a receive buffer into one contiguous tensor (host sync on
+    the counts, like the reference)."""
+    per_rank = input_splits.reshape(ctx.WORLD_SIZE, -1).sum(dim=1).tolist()
+    data = torch.cat([recv_buffer[i * ctx.max_m: i * ctx.max_m + n] for i, n in enumerate(per_rank)])
+    scale = None
+    if scale_buffer is not None:
+        scale = torch.cat([scale_buffer[i * ctx.max_m: i * ctx.max_m + n] for i, n in enumerate(per_rank)])
+    return data, scale
+
+
+def _fast_all_to_all_cpu(ctx, send, cumsum, scale):
+    W, epr, mm = ctx.WORLD_SIZE, ctx.experts_per_rank, ctx.max_m
+    pad = torch.zeros((mm, send.shape[1]), dtype=send.dtype)
+    pad[: send.shape[0]] = send
+    cums = cumsum.to(torch.int32)
+    scol = ctx.scale_cols
+    spad = torch.zeros((mm, scol), dtype=torch.float32)
+    if scale is not None:
+        spad[: send.shape[0]] = scale.reshape(send.shape[0], -1).float()
+    if W > 1:
+        all_rows = [torch.empty_like(pad) for _ in range(W)]
+        all_cums = [torch.empty_like(cums) for _ in range(W)]
+        all_scales = [torch.empty_like(spad) for _ in range(W)]
+        dist.all_gather(all_rows, pad, group=ctx.group)
+        dist.all_gather(all_cums, cums, group=ctx.group)
+        dist.all_gather(all_scales, spad, group=ctx.group)
+    else:
+        all_rows, all_cums, all_scales = [pad], [cums], [spad]
+    recv = torch.zeros((W * mm, send.shape[1]), dtype=send.dtype)
+    rscale = torch.zeros((W * mm, scol), dtype=torch.float32)
+    splits = torch.zeros(W * epr, dtype=torch.int32)
+    for s in range(W):
+        c = all_cums[s]
+        lo, hi = int(c[ctx.rank * epr]), int(c[(ctx.rank + 1) * epr])
+        recv[s * mm: s * mm + hi - lo] = all_rows[s][lo:hi]
+        rscale[s * mm: s * mm + hi - lo] = all_scales[s][lo:hi]
+        splits[s * epr:(s + 1) * epr] = c[ctx.rank * epr + 1:(ctx.rank + 1) * epr + 1] - c[ctx.rank * epr:(ctx.rank + 1) * epr]
+    return splits, recv, (rscale if scale is not None else None)
+
+
+# ---------------------------------------------------------------------------- fused MoE pair
+@dataclass
+class MoEDispatchContext:
+    """State of the fused dispatch/combine pair: one all-to-all context per direction (fp8 rows
+    with hidden/128 scales out, bf16 rows back) and the routing of the call in flight."""
+
+    dispatch: AllToAllContext
+    combine: AllToAllContext
+    num_experts: int
+    topk: int
+    hidden: int
+    routing: Optional[moe_utils.Routing] = None
+    topk_ids: Optional[torch.Tensor] = None
+    topk_weights: Optional[torch.Tensor] = None
+    ntok: int = 0
+
+
+def create_moe_dispatch_context(max_tokens: int, hidden: int, topk: int, num_experts: int, rank: int, world_size: int,
+                                heap=None, group=None, device=None) -> MoEDispatchContext:
+    epr = num_experts // world_size
+    max_m = max_tokens * topk
+    d = create_all_to_all_context(max_m, hidden, rank, num_experts, world_size, epr, dtype=torch.float8_e4m3fn,
+                                  scale_cols=hidden // 128, heap=heap, group=group, device=device)
+    c = create_all_to_all_context(max_m, hidden, rank, num_experts, world_size, epr, dtype=torch.bfloat16,
+                                  heap=heap, group=group, device=device)
+    return MoEDispatchContext(d, c, num_experts, topk, hidden)
+
+
+def moe_dispatch(ctx: MoEDispatchContext, x: torch.Tensor, topk_ids: torch.Tensor, topk_weights: torch.Tensor,
+                 phase: int = 3, stream=None) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
+    """Send every token to the ranks of its ``topk`` experts as fp8 e4m3 with per-128 fp32 scales.
+
+    ``x`` bf16 ``[T, hidden]``, ``topk_ids`` int32 ``[T, topk]``. Returns views into the receive
+    buffers: ``(recv_x fp8 [ws*max_m, hidden], recv_scale fp32 [ws*max_m, hidden/128], recv_splits
+    int32 [ws, experts_per_rank])``; source ``s`` occupies rows ``[s*max_m, s*max_m + sum(splits[s]))``
+    sorted by local expert."""
+    T = x.shape[0]
+    d = ctx.dispatch
+    if T * ctx.topk > d.max_m:
+        raise ValueError("more tokens than the context was built for")
+    if x.device.type != "cuda":
+        return _moe_dispatch_cpu(ctx, x, topk_ids, topk_weights)
+    if x.dtype != torch.bfloat16 or not x.is_contiguous():
+        raise ValueError("x must be contiguous bf16")
+    if phase != 2:
+        ctx.routing = moe_utils.route(topk_ids, ctx.num_experts, ctx.routing if ctx.ntok == T else None)
+        ctx.topk_ids = topk_ids.to(torch.int32).contiguous()
+        ctx.topk_weights = topk_weights.to(torch.float32).contiguous()
+        ctx.ntok = T
+    half = _next_call(d, phase)
+    a = _lib.A2AArgs()
+    a.send = x.data_ptr()
+    a.src_index = ctx.routing.sorted_token.data_ptr()
+    a.counts = ctx.routing.cumsum.data_ptr()
+    a.row_bytes_in, a.row_bytes_out = ctx.hidden * 2, ctx.hidden
+    a.scale_cols, a.hidden = ctx.hidden // 128, ctx.hidden
+    a.mode, a.quant = _lib.A2A_DISPATCH, 1
+    _fill_common(a, d, half, phase, x.device, stream)
+    _launch(a)
+    return (d.recv_buf.local[half], d.scale_recv_buf.local[half],
+            d.split_recv_buf.local[half].view(d.WORLD_SIZE, d.experts_per_rank))
+
+
+def moe_combine(ctx: MoEDispatchContext, expert_out: torch.Tensor, recv_splits: torch.Tensor,
+                out: Optional[torch.Tensor] = None, phase: int = 3, stream=None) -> torch.Tensor:
+    """Return the experts' outputs to their source ranks and reduce over ``topk`` with the gate
+    weights of the matching ``moe_dispatch``.
+
+    ``expert_out`` bf16 ``[ws*max_m, hidden]`` in the receive layout of ``moe_dispatch`` (row i of
+    the output corresponds to row i of ``recv_x``). Returns bf16 ``[T, hidden]``."""
+    c = ctx.combine
+    if expert_out.device.type != "cuda":
+        return _moe_combine_cpu(ctx, expert_out, recv_splits)
+    if expert_out.dtype != torch.bfloat16 or not expert_out.is_contiguous():
+        raise ValueError("expert_out must be contiguous bf16")
+    T = ctx.ntok
+    o = out if out is not None else torch.empty((T, ctx.hidden), dtype=torch.bfloat16, device=expert_out.device)
+    half = _next_call(c, phase)
+    a = _lib.A2AArgs()
+    a.send = expert_out.data_ptr()
+    a.counts = recv_splits.contiguous().data_ptr()
+    a.row_bytes_in = a.row_bytes_out = ctx.hidden * 2
+    a.scale_cols, a.hidden = 1, ctx.hidden
+    a.mode, a.reduce = _lib.A2A_COMBINE, 1
+    a.slot_of = ctx.routing.slot_of.data_ptr()
+    a.cumsum = ctx.routing.cumsum.data_ptr()
+    a.topk_ids = ctx.topk_ids.data_ptr()
+    a.topk_w = ctx.topk_weights.data_ptr()
+    a.out = o.data_ptr()
+    a.ntok, a.topk = T, ctx.topk
+    _fill_common(a, c, half, phase, expert_out.device, stream)
+    _launch(a)
+    return o
+
+
+def dequant_fp8(x: torch.Tensor, scale: torch.Tensor, rows: Optional[int] = None) -> torch.Tensor:
+    """fp8 e4m3 ``[R, hidden]`` with fp32 scales ``[R, hidden/128]`` -> bf16 ``[R, hidden]``."""
+    global launch_count
+    R = x.shape[0] if rows is None else rows
+    hidden = x.shape[1]
+    if x.device.type != "cuda":
+        return (x[:R].float().view(R, hidden // 128, 128) * scale[:R].float().unsqueeze(-1)).view(R, hidden).to(torch.bfloat16)
+    out = torch.empty((x.shape[0], hidden), dtype=torch.bfloat16, device=x.device)
+    _lib.check(_lib.lib().tdist_dequant_fp8(x.data_ptr(), scale.data_ptr(), out.data_ptr(), R, hidden,
+                                            torch.cuda.current_stream(x.device).cuda_stream), "tdist_dequant_fp8")
+    launch_count += 1
+    return out
+
+
+def quant_fp8_reference(x: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
+    """Torch statement of the on-the-fly quantisation (oracle): per row, per 128 values,
+    scale = amax / 448, q = x / scale rounded to e4m3."""
+    R, H = x.shape
+    g = x.float().view(R, H // 128, 128)
+    scale = g.abs().amax(-1).clamp_min(1e-10) / 448.0
+    q = (g / scale.unsqueeze(-1)).view(R, H).to(torch.float8_e4m3fn)
+    return q, scale
+
+
+def _moe_dispatch_cpu(ctx, x, topk_ids, topk_weights):
+    ctx.routing = moe_utils.route(topk_ids, ctx.num_experts)
+    ctx.topk_ids, ctx.topk_weights, ctx.ntok = topk_ids.to(torch.int32), topk_weights.float(), x.shape[0]
+    q, scale = quant_fp8_reference(x)
+    rows = ctx.routing.sorted_token.long()
+    d = ctx.dispatch
+    # fp8 tensors do not travel through gloo: ship the bytes
+    splits, recv, rscale = _fast_all_to_all_cpu(d, q[rows].view(torch.uint8), ctx.routing.cumsum, scale[rows])
+    return recv.view(torch.float8_e4m3fn), rscale, splits.view(d.WORLD_SIZE, d.experts_per_rank)
+
+
+def _moe_combine_cpu(ctx, expert_out, recv_splits):
+    c = ctx.combine
+    W, epr, mm = c.WORLD_SIZE, c.experts_per_rank, c.max_m
+    per_src = recv_splits.reshape(W, epr).sum(1)
+    compact = torch.cat([expert_out[s * mm: s * mm + int(per_src[s])] for s in range(W)])
+    cums = torch.zeros(W * epr + 1, dtype=torch.int32)
+    cums[1:] = torch.cumsum(recv_splits.reshape(-1), 0)
+    _splits, back, _ = _fast_all_to_all_cpu(c, compact, cums, None)
+    r = ctx.routing
+    T, K = ctx.ntok, ctx.topk
+    er = (ctx.topk_ids.reshape(-1).long() // epr)
+    row = er * mm + (r.slot_of.long() - r.cumsum.long()[er * epr])
+    vals = back[row].float() * ctx.topk_weights.reshape(-1, 1)
+    return vals.view(T, K, -1).sum(1).to(torch.bfloat16)

@@ -1,0 +1,314 @@
+"""Standalone collectives on symmetric buffers and the host-side stream primitives.
+
+Public surface (names and argument conventions of the reference):
+
+* ``barrier_all_on_stream``, ``wait_eq``, ``set_signal``
+  (reference python/triton_dist/kernels/nvidia/common_ops.py:162-211)
+* ``create_fast_allgather_context`` / ``fast_allgather(symm_buffer, ctx, mode=...)`` — in place on a
+  symmetric byte buffer, rank r's segment at ``r * nbytes / world``
+  (reference kernels/nvidia/low_latency_allgather.py:781-990)
+* ``AllGatherMethod``, ``get_auto_all_gather_method``, ``cp_engine_producer_all_gather_intra_node``
+  — the copy-engine variant kept as a baseline (reference kernels/nvidia/allgather.py:44-135,261-288)
+* ``create_reduce_scater_2d_ctx`` / ``reduce_scatter_2d_op(input[M,N], ctx) -> [M/ws, N]``, ``ring_reduce``
+  (reference kernels/nvidia/reduce_scatter.py:143-183,752-799)
+
+On CUDA every collective is one kernel launch from ``csrc/kernels/collectives.cu``; on CPU tensors
+the same functions go through ``torch.distributed`` (gloo), which is also the test oracle.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import enum
+from dataclasses import dataclass
+from typing import List, Optional
+
+import torch
+import torch.distributed as dist
+
+from .. import _lib
+from ..runtime import SymmTensor, default_timeout_ns, global_status, symm_heap
+
+launch_count = 0
+
+_AG_MODES = {
+    "pull": _lib.AG_PULL,
+    "push": _lib.AG_PUSH, "push2d": _lib.AG_PUSH, "push3d": _lib.AG_PUSH, "push_numa_2d": _lib.AG_PUSH,
+    "ll": _lib.AG_LL, "push2d_ll": _lib.AG_LL, "push3d_ll": _lib.AG_LL, "push_numa_2d_ll": _lib.AG_LL,
+    "push_numa_2d_ll_multinode": _lib.AG_LL, "push2d_ll_multimem": _lib.AG_LL,
+}
+_RS_DTYPES = {torch.bfloat16: _lib.DT_BF16, torch.float16: _lib.DT_F16, torch.float32: _lib.DT_F32, torch.int32: _lib.DT_I32}
+
+
+def _status_ptr():
+    st = global_status()
+    return st.device_ptr if st is not None else None
+
+
+def _stream_ptr(device, stream=None):
+    return (stream or torch.cuda.current_stream(device)).cuda_stream
+
+
+# ---------------------------------------------------------------------------- barrier / flags
+@dataclass
+class BarrierContext:
+    """Symmetric flag array and local epoch counter of the device-side barrier."""
+
+    flags: SymmTensor          # int64 [8]
+    epoch: torch.Tensor        # int64 [1], local
+    rank: int
+    world: int
+    group: object = None
+
+
+_BARRIER: Optional[BarrierContext] = None
+
+
+def create_barrier_context(heap=None, group=None) -> BarrierContext:
+    heap = heap or symm_heap(group)
+    flags = heap.zeros((_lib.MAX_RANKS,), torch.int64)
+    epoch = torch.zeros(1, dtype=torch.int64, device=flags.local.device)
+    return BarrierContext(flags, epoch, heap.rank, heap.world, group)
+
+
+def barrier_all_on_stream(stream=None, is_intra_node: bool = True, symm_barrier_buf=None, local_world_size: int = 0,
+                          barrier_value: int = 1, ctx: Optional[BarrierContext] = None) -> None:
+    """Barrier of all ranks, ordered on ``stream`` (no host synchronisation): work enqueued after
+    it on any rank starts after the work enqueued before it on every rank. The reference's extra
+    arguments are accepted and ignored (one node, one barrier kernel)."""
+    global _BARRIER, launch_count
+    if not torch.cuda.is_available():
+        if dist.is_initialized():
+            dist.barrier()
+        return
+    if ctx is None:
+        if _BARRIER is None:
+            _BARRIER = create_barrier_context()
+        ctx = _BARRIER
+    if ctx.world == 1:
+        return
+    dev = ctx.flags.local.device
+    arr = (C.c_void_p * _lib.MAX_RANKS)(*[C.c_void_p(p) for p in ctx.flags.ptrs])
+    _lib.check(_lib.lib().tdist_barrier_all(arr, C.c_void_p(ctx.epoch.data_ptr()), ctx.world, ctx.rank,
+                                            C.c_void_p(_status_ptr()), C.c_uint64(default_timeout_ns()),
+                                            C.c_void_p(_stream_ptr(dev, stream))), "tdist_barrier_all")
+    launch_count += 1
+
+
+def set_signal(ptr: int, signal: int, stream=None, require_i64: bool = False) -> None:
+    """Stream-ordered write of ``signal`` to the 32/64-bit word at device address ``ptr``
+    (``cuStreamWriteValue``)."""
+    dev = torch.device("cuda", torch.cuda.current_device())
+    _lib.check(_lib.lib().tdist_stream_write_value(C.c_void_p(_stream_ptr(dev, stream)), C.c_uint64(ptr),
+                                                   C.c_uint64(signal), int(require_i64)), "set_signal")
+
+
+def wait_eq(ptr: int, signal: int, stream=None, require_i64: bool = False) -> None:
+    """Make ``stream`` wait until the word at ``ptr`` equals ``signal`` (``cuStreamWaitValue``).
+    The wait itself has no time limit: only use it for a value that is certain to be written."""
+    dev = torch.device("cuda", torch.cuda.current_device())
+    _lib.check(_lib.lib().tdist_stream_wait_value(C.c_void_p(_stream_ptr(dev, stream)), C.c_uint64(ptr),
+                                                  C.c_uint64(signal), int(require_i64), 0), "wait_eq")
+
+
+# ---------------------------------------------------------------------------- all-gather
+class AllGatherMethod(enum.Enum):
+    Auto = 0
+    All2All_IntraNode = 1
+    All2All_InterNode = 2
+    Ring1D_IntraNode = 3
+    Ring2D_IntraNode = 4
+    Ring2D_InterNode = 5
+
+
+def get_auto_all_gather_method(num_ranks: int, num_local_ranks: int) -> AllGatherMethod:
+    """NVSwitch node: every peer is one hop away, so full-mesh is always the choice."""
+    return AllGatherMethod.All2All_IntraNode if num_ranks <= num_local_ranks else AllGatherMethod.All2All_InterNode
+
+
+def cp_engine_producer_all_gather_intra_node(rank: int, num_ranks: int, local_tensor: torch.Tensor,
+                                             remote_tensor_buffers: List[torch.Tensor], barrier_buffers=None,
+                                             stream=None, for_correctness: bool = False,
+                                             all_gather_method: AllGatherMethod = AllGatherMethod.Auto) -> None:
+    """Copy-engine full-mesh pull: for every peer, ``cudaMemcpyAsync`` its segment out of its
+    buffer into ``remote_tensor_buffers[rank]`` on ``stream``. Baseline for the in-kernel paths;
+    the caller is responsible for the peers' segments being ready (e.g. ``barrier_all_on_stream``)."""
+    rows = local_tensor.shape[0]
+    mine = remote_tensor_buffers[rank]
+    with torch.cuda.stream(stream or torch.cuda.current_stream()):
+        mine[rank * rows:(rank + 1) * rows].copy_(local_tensor)
+        for step in range(1, num_ranks):
+            src = (rank + step) % num_ranks
+            mine[src * rows:(src + 1) * rows].copy_(remote_tensor_buffers[src][src * rows:(src + 1) * rows])
+
+
+@dataclass
+class FastAllGatherContext:
+    rank: int
+    world: int
+    max_buffer_size: int
+    signal: Optional[SymmTensor] = None       # int64 [8]
+    ll_buffer: Optional[SymmTensor] = None    # uint8 [2 * 2 * ll_max]: two parities of LL packets
+    ll_max: int = 0                           # largest buffer the LL path serves (larger ones are pushed)
+    counters: Optional[torch.Tensor] = None   # int32 [8], local
+    epoch: int = 0
+    ctas_per_peer: int = 0
+    group: object = None
+
+
+def create_fast_allgather_context(rank: int, node: int = 0, num_ranks: int = 1, num_nodes: int = 1,
+                                  max_buffer_size: int = 2 * 32 * 1024 * 1024, heap=None, group=None,
+                                  device=None) -> FastAllGatherContext:
+    ctx = FastAllGatherContext(rank=rank, world=num_ranks, max_buffer_size=max_buffer_size, group=group)
+    on_cuda = (device is not None and torch.device(device).type == "cuda") or (device is None and torch.cuda.is_available())
+    if on_cuda and num_ranks > 1:
+        heap = heap or symm_heap(group)
+        ctx.signal = heap.zeros((_lib.MAX_RANKS,), torch.int64)
+        ctx.ll_max = min(max_buffer_size, 8 << 20)
+        ctx.ll_buffer = heap.zeros((4 * ctx.ll_max,), torch.uint8)
+        ctx.counters = torch.zeros(_lib.MAX_RANKS, dtype=torch.int32, device=ctx.signal.local.device)
+    return ctx
+
+
+def fast_allgather(symm_buffer: SymmTensor, ctx: Optional[FastAllGatherContext] = None, rank: Optional[int] = None,
+                   node: int = 0, num_ranks: Optional[int] = None, num_nodes: int = 1, mode: str = "pull",
+                   phase: int = 3, stream=None) -> torch.Tensor:
+    """In-place all-gather of a symmetric buffer: on entry rank r has written its own segment
+    (bytes ``[r*seg, (r+1)*seg)`` with ``seg = nbytes / world``); on return (stream-ordered) the
+    local copy holds every rank's segment. The buffer must not be rewritten by any rank before all
+    ranks have finished reading the previous result (use distinct buffers or a barrier)."""
+    global launch_count
+    local = symm_buffer.local
+    if ctx is None:
+        ctx = create_fast_allgather_context(rank, node, num_ranks, num_nodes, max_buffer_size=local.numel() * local.element_size())
+    if mode not in _AG_MODES:
+        raise ValueError(f"unknown all-gather mode {mode!r}; known: {sorted(_AG_MODES)}")
+    nbytes = local.numel() * local.element_size()
+    if nbytes % ctx.world:
+        raise ValueError("buffer size must be divisible by the world size")
+    if local.device.type != "cuda":
+        if ctx.world > 1:
+            flat = local.reshape(-1).view(torch.uint8)
+            seg = nbytes // ctx.world
+            mine = flat[ctx.rank * seg:(ctx.rank + 1) * seg].clone()
+            dist.all_gather_into_tensor(flat, mine, group=ctx.group)
+        return local
+    if ctx.world == 1:
+        return local
+    if nbytes > ctx.max_buffer_size:
+        raise ValueError(f"buffer of {nbytes} bytes exceeds the context's max_buffer_size {ctx.max_buffer_size}")
+    a = _lib.CollArgs()
+    a.buf_peer = _lib.ptr_array(symm_buffer.ptrs)
+    a.sig_peer = _lib.ptr_array(ctx.signal.ptrs)
+    a.counters = ctx.counters.data_ptr()
+    a.seg_bytes = nbytes // ctx.world
+    a.world, a.rank = ctx.world, ctx.rank
+    a.mode = _AG_MODES[mode]
+    if a.mode == _lib.AG_LL and nbytes > ctx.ll_max:
+        a.mode = _lib.AG_PUSH  # LL doubles the bytes on the wire: only worth it for small messages
+    a.phase = phase
+    a.ctas_per_peer = ctx.ctas_per_peer or (1 if a.seg_bytes <= (64 << 10) else (4 if a.seg_bytes <= (4 << 20) else 16))
+    if phase != 2:
+        ctx.epoch += 1
+    a.epoch = ctx.epoch
+    half_bytes = 2 * ctx.ll_max
+    a.ll_peer = _lib.ptr_array([p + (ctx.epoch & 1) * half_bytes for p in ctx.ll_buffer.ptrs])
+    a.status = _status_ptr()
+    a.timeout_ns = default_timeout_ns()
+    a.stream = _stream_ptr(local.device, stream)
+    _lib.check(_lib.lib().tdist_allgather(C.byref(a)), "tdist_allgather")
+    launch_count += 1
+    return local
+
+
+# ---------------------------------------------------------------------------- reduce-scatter
+@dataclass
+class ReduceScatter2DContext:
+    max_M: int
+    N: int
+    rank: int
+    world: int
+    dtype: torch.dtype
+    staging: Optional[SymmTensor] = None      # [2, world * max_M/world * N]
+    signal: Optional[SymmTensor] = None
+    counters: Optional[torch.Tensor] = None
+    epoch: int = 0
+    ctas_per_peer: int = 0
+    group: object = None
+
+
+def create_reduce_scater_2d_ctx(max_M: int, N: int, rank: int, world_size: int, local_world_size: Optional[int] = None,
+                                dtype: torch.dtype = torch.bfloat16, overlap_with_gemm: bool = True,
+                                num_reduction_sms: int = 15, heap=None, group=None, device=None) -> ReduceScatter2DContext:
+    """(The reference spells it ``scater``.) Allocates double-buffered staging ``[2, max_M, N]`` that
+    peers scatter into, and the arrival flags."""
+    ctx = ReduceScatter2DContext(max_M=max_M, N=N, rank=rank, world=world_size, dtype=dtype, group=group)
+    on_cuda = (device is not None and torch.device(device).type == "cuda") or (device is None and torch.cuda.is_available())
+    if on_cuda:
+        heap = heap or symm_heap(group)
+        ctx.staging = heap.empty((2, max_M * N), dtype)
+        ctx.signal = heap.zeros((_lib.MAX_RANKS,), torch.int64)
+        ctx.counters = torch.zeros(_lib.MAX_RANKS, dtype=torch.int32, device=ctx.signal.local.device)
+    return ctx
+
+
+create_reduce_scatter_2d_ctx = create_reduce_scater_2d_ctx
+
+
+def reduce_scatter_2d_op(input: torch.Tensor, ctx: ReduceScatter2DContext, out: Optional[torch.Tensor] = None,
+                         phase: int = 3, stream=None) -> torch.Tensor:
+    """``out[M/ws, N] = sum over ranks of input_r[rank*M/ws:(rank+1)*M/ws]`` (fp32 accumulation for
+    floating types, exact for int32)."""
+    global launch_count
+    M, N = input.shape
+    if M % ctx.world:
+        raise ValueError("M must be divisible by the world size")
+    mpr = M // ctx.world
+    if input.device.type != "cuda":
+        acc = input.to(torch.float32) if input.dtype in (torch.bfloat16, torch.float16) else input.clone()
+        if ctx.world > 1:
+            dist.all_reduce(acc, group=ctx.group)
+        return acc[ctx.rank * mpr:(ctx.rank + 1) * mpr].to(input.dtype)
+    if input.dtype not in _RS_DTYPES:
+        raise TypeError(f"reduce-scatter supports {list(_RS_DTYPES)}, got {input.dtype}")
+    if not input.is_contiguous():
+        raise ValueError("input must be contiguous")
+    esize = input.element_size()
+    seg_bytes = mpr * N * esize
+    if seg_bytes % 16:
+        raise ValueError("rows per rank * N * element size must be a multiple of 16 bytes")
+    if M * N > ctx.max_M * ctx.N:
+        raise ValueError("input exceeds the context's staging")
+    o = out if out is not None else torch.empty((mpr, N), dtype=input.dtype, device=input.device)
+    a = _lib.CollArgs()
+    half = (ctx.epoch + (1 if phase != 2 else 0)) & 1
+    bases = [t[half].data_ptr() for t in ctx.staging.peers]
+    a.buf_peer = _lib.ptr_array(bases)
+    a.sig_peer = _lib.ptr_array(ctx.signal.ptrs)
+    a.counters = ctx.counters.data_ptr()
+    a.input = input.data_ptr()
+    a.output = o.data_ptr()
+    a.seg_bytes = seg_bytes
+    a.world, a.rank = ctx.world, ctx.rank
+    a.phase = phase
+    a.dtype = _RS_DTYPES[input.dtype]
+    a.ctas_per_peer = ctx.ctas_per_peer or (1 if seg_bytes <= (64 << 10) else (4 if seg_bytes <= (4 << 20) else 16))
+    if phase != 2:
+        ctx.epoch += 1
+    a.epoch = ctx.epoch
+    a.status = _status_ptr()
+    a.timeout_ns = default_timeout_ns()
+    a.stream = _stream_ptr(input.device, stream)
+    _lib.check(_lib.lib().tdist_reduce_scatter(C.byref(a)), "tdist_reduce_scatter")
+    launch_count += 1
+    return o
+
+
+def ring_reduce(input: torch.Tensor, output: torch.Tensor, begin_idx: int, num_splits: int, num_sms: int = -1) -> torch.Tensor:
+    """Sum the ``num_splits`` row blocks of ``input`` (starting the rotation at ``begin_idx``) into
+    ``output``; accumulation in fp32 (reference kernels/nvidia/reduce_scatter.py:752-763)."""
+    M = input.shape[0] // num_splits
+    blocks = input.view(num_splits, M, *input.shape[1:])
+    order = [(begin_idx + i) % num_splits for i in range(num_splits)]
+    acc_dtype = torch.float32 if input.dtype in (torch.bfloat16, torch.float16) else input.dtype
+    output.copy_(blocks[order].to(acc_dtype).sum(dim=0).to(output.dtype))
+    return output

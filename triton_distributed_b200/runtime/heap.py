@@ -133,6 +133,12 @@ class SymmetricHeap:
     # ------------------------------------------------------------------ allocation
     def empty(self, shape: Sequence[int], dtype: torch.dtype) -> SymmTensor:
         shape = tuple(int(s) for s in shape)
+        if self.backend == "host":
+            # Host memory of another process is not mapped: only the local copy exists and the CPU
+            # paths of the ops go through torch.distributed collectives instead of peer pointers.
+            local = torch.empty(shape, dtype=dtype)
+            peers = [local if r == self.rank else torch.empty(0, dtype=dtype) for r in range(self.world)]
+            return SymmTensor(local, peers, self.rank)
         esize = torch.empty((), dtype=dtype).element_size()
         nbytes = max(1, math.prod(shape)) * esize
         seg, off = None, None
