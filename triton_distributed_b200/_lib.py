@@ -93,6 +93,23 @@ class A2AArgs(C.Structure):
     ]
 
 
+class DecodeArgs(C.Structure):
+    _fields_ = [
+        ("q", C.c_void_p), ("k_cache", C.c_void_p), ("v_cache", C.c_void_p), ("block_table", C.c_void_p),
+        ("kv_lens", C.c_void_p), ("partial", C.c_void_p), ("counters", C.c_void_p), ("out", C.c_void_p),
+        ("ll_peer", C.c_void_p * MAX_RANKS),
+        ("B", C.c_int), ("Hq", C.c_int), ("Hkv", C.c_int), ("head_dim", C.c_int), ("page_size", C.c_int),
+        ("max_blocks", C.c_int), ("splits", C.c_int),
+        ("stride_block", C.c_longlong), ("stride_token", C.c_longlong), ("stride_head", C.c_longlong),
+        ("scale", C.c_float), ("soft_cap", C.c_float),
+        ("mode", C.c_int), ("dtype", C.c_int), ("world", C.c_int), ("rank", C.c_int),
+        ("epoch", C.c_uint32), ("push_only", C.c_int),
+        ("status", C.c_void_p),
+        ("timeout_ns", C.c_uint64),
+        ("stream", C.c_void_p),
+    ]
+
+
 GEMM_PLAIN, GEMM_AG, GEMM_RS = 0, 1, 2
 A2A_DISPATCH, A2A_COMBINE = 0, 1
 DT_BF16, DT_F16, DT_F32, DT_I32 = 0, 1, 2, 3
@@ -122,6 +139,8 @@ def _declare(lib):
     lib.tdist_p2p_copy.argtypes = [C.c_void_p, C.c_void_p, C.c_size_t, C.c_int, C.c_int, C.c_int, C.c_int,
                                    C.c_void_p, C.c_uint64, C.c_void_p]
     lib.tdist_a2a.argtypes = [C.POINTER(A2AArgs)]
+    lib.tdist_flash_decode.argtypes = [C.POINTER(DecodeArgs)]
+    lib.tdist_lse_combine.argtypes = [C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_int, C.c_void_p]
     lib.tdist_dequant_fp8.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_void_p]
     lib.tdist_moe_route.argtypes = [C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]
     lib.tdist_moe_align_block_size.argtypes = [C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_int,

@@ -158,6 +158,35 @@ int tdist_moe_align_block_size(const void* ids, int numel_per_rank, int num_expe
 int tdist_moe_topk_softmax(const void* logits_f32, int ntok, int num_experts, int topk, int renormalize,
                            void* ids, void* weights, void* stream);
 
+/* ------------------------------------------------------------------ GQA flash decode */
+typedef struct TdistDecodeArgs {
+    const void* q;            /* [B, Hq, D] bf16/fp16 */
+    const void* k_cache;      /* [blocks, page, Hkv, D] (any strides that are multiples of 8 elements) */
+    const void* v_cache;
+    const void* block_table;  /* int32 [B, max_blocks] */
+    const void* kv_lens;      /* int32 [B]: keys held by THIS rank per sequence */
+    void* partial;            /* fp32 workspace [B, Hq, splits, D + 2] */
+    void* counters;           /* uint32 [B * Hkv], zero on first use */
+    void* out;                /* mode 0/2: [B, Hq, D] in q's dtype; mode 1: fp32 [B, Hq, D + 1] (O || LSE) */
+    void* ll_peer[TDIST_MAX_RANKS]; /* mode 2: gather buffer of every rank, this call's parity:
+                                       [world][B * Hq * (D + 2) / 2] 16-byte packets */
+    int B, Hq, Hkv, head_dim, page_size, max_blocks, splits;
+    long long stride_block, stride_token, stride_head; /* cache strides in elements */
+    float scale, soft_cap;
+    int mode;                 /* 0 = final output, 1 = O || LSE for a later cross-rank merge, 2 = sequence-parallel */
+    int dtype;
+    int world, rank;
+    uint32_t epoch;           /* mode 2: non-zero, increasing per call */
+    int push_only;            /* mode 2: 1 = compute and send, do not gather (emulated ranks) */
+    void* status;
+    uint64_t timeout_ns;
+    void* stream;
+} TdistDecodeArgs;
+
+int tdist_flash_decode(const TdistDecodeArgs* args);
+/* parts fp32 [ranks, heads, D + 1] -> out [heads, D] */
+int tdist_lse_combine(const void* parts, int ranks, int heads, int head_dim, void* out, int dtype, void* stream);
+
 #ifdef __cplusplus
 }
 #endif
