@@ -1,0 +1,79 @@
+"""Tensor-parallel MoE ops on one GPU (ranks emulated send-half / receive-half). Oracle: masked
+per-expert fp32 matmuls, as in the reference's test_ag_moe.py:24-39 and test_moe_reduce_rs.py."""
+import pytest
+import torch
+
+from triton_distributed_b200.ops import moe_tp as MT
+from triton_distributed_b200.ops import moe_utils as MU
+from triton_distributed_b200.runtime import LocalWorld, check_status
+
+pytestmark = pytest.mark.gpu
+
+
+def _expert_matmul(rows, ids, b_ekn):
+    out = torch.zeros(rows.shape[0], b_ekn.shape[2], device=rows.device)
+    for e in range(b_ekn.shape[0]):
+        m = ids == e
+        if m.any():
+            out[m] = rows[m].float() @ b_ekn[e].float()
+    return out
+
+
+@pytest.mark.parametrize("T,E,K,N,topk", [(256, 8, 256, 512, 2), (1000, 32, 520, 264, 4), (64, 60, 128, 1024, 6)])
+def test_group_gemm_blocks_pick_their_expert(cuda_device, T, E, K, N, topk):
+    torch.manual_seed(T + E)
+    x = torch.randn(T, K, device=cuda_device).to(torch.bfloat16)
+    b = (torch.randn(E, K, N, device=cuda_device) * K ** -0.5).to(torch.bfloat16)
+    ids = torch.randint(0, E, (T, topk), dtype=torch.int32, device=cuda_device)
+    sorted_ids, expert_ids, _, _, post_pad = MU.sort_topk_ids_align_block_size(ids, E, 1, T, 128)
+    n = int(post_pad)
+    a_sorted, pos_of = MT.gather_rows(x, sorted_ids[:n].contiguous(), topk, T * topk, want_inverse=True)
+    c = MT.group_gemm(a_sorted, b.transpose(1, 2).contiguous(), expert_ids, (post_pad // 128).to(torch.int32))
+    check_status()
+    got = c[pos_of.long()].float()
+    ref = _expert_matmul(x[torch.arange(T * topk, device=cuda_device) // topk], ids.reshape(-1), b)
+    torch.testing.assert_close(got, ref, atol=3e-2, rtol=3e-2)
+    red = MT.topk_reduce(c, pos_of, torch.ones(T, topk, device=cuda_device), T, topk)
+    torch.testing.assert_close(red.float(), ref.view(T, topk, N).sum(1), atol=6e-2, rtol=3e-2)
+
+
+@pytest.mark.parametrize("world,tpr,E,K,N,topk", [(1, 256, 8, 256, 256, 2), (4, 128, 16, 512, 264, 2), (8, 64, 32, 256, 512, 4)])
+def test_ag_group_gemm(cuda_device, world, tpr, E, K, N, topk):
+    torch.manual_seed(world * 7 + tpr)
+    lw = LocalWorld(world, cuda_device)
+    M = world * tpr
+    shards = [torch.randn(tpr, K, device=cuda_device).to(torch.bfloat16) for _ in range(world)]
+    bs = [(torch.randn(E, K, N, device=cuda_device) * K ** -0.5).to(torch.bfloat16) for _ in range(world)]
+    ids = torch.randint(0, E, (M, topk), dtype=torch.int32, device=cuda_device)
+    ctxs = [MT.create_ag_group_gemm_intra_node_context(None, shards[r], bs[r], ids, E, max_M=M, rank=r, num_ranks=world,
+                                                       heap=lw.heap(r)) for r in range(world)]
+    if world > 1:
+        for r in range(world):
+            MT.ag_group_gemm_intra_node(shards[r], bs[r], ctxs[r], phase=1)
+    outs = [MT.ag_group_gemm_intra_node(shards[r], bs[r], ctxs[r], phase=2 if world > 1 else 3) for r in range(world)]
+    check_status()
+    full = torch.cat(shards)
+    rows = full[torch.arange(M * topk, device=cuda_device) // topk]
+    for r in range(world):
+        ref = _expert_matmul(rows, ids.reshape(-1), bs[r])
+        torch.testing.assert_close(outs[r].float(), ref, atol=3e-2, rtol=3e-2)
+
+
+@pytest.mark.parametrize("world,M,E,Kl,N,topk", [(1, 256, 8, 256, 256, 2), (2, 512, 16, 128, 512, 2), (4, 256, 32, 256, 1024, 4)])
+def test_moe_reduce_rs(cuda_device, world, M, E, Kl, N, topk):
+    torch.manual_seed(world * 11 + M)
+    lw = LocalWorld(world, cuda_device)
+    ids = torch.randint(0, E, (M, topk), dtype=torch.int32, device=cuda_device)
+    w = torch.rand(M, topk, device=cuda_device)
+    a = [torch.randn(M * topk, Kl, device=cuda_device).to(torch.bfloat16) for _ in range(world)]
+    b = [(torch.randn(E, Kl, N, device=cuda_device) * (Kl * world) ** -0.5).to(torch.bfloat16) for _ in range(world)]
+    ctxs = [MT.create_moe_rs_context(None, r, world, world, M, N, E, topk, torch.bfloat16, torch.bfloat16, cuda_device,
+                                     full_topk_ids=ids, full_topk_weight=w, heap=lw.heap(r)) for r in range(world)]
+    for r in range(world):
+        MT.moe_reduce_rs(r, world, world, a[r], b[r], ctxs[r], phase=1)
+    outs = [MT.moe_reduce_rs(r, world, world, a[r], b[r], ctxs[r], phase=2) for r in range(world)]
+    check_status()
+    total = sum((_expert_matmul(a[r], ids.reshape(-1), b[r]).view(M, topk, N) * w.view(M, topk, 1)).sum(1) for r in range(world))
+    mpr = M // world
+    for r in range(world):
+        torch.testing.assert_close(outs[r].float(), total[r * mpr:(r + 1) * mpr], atol=6e-2, rtol=3e-2)

@@ -53,6 +53,7 @@ class GemmArgs(C.Structure):
         ("timeout_ns", C.c_uint64),
         ("stream", C.c_void_p),
         ("trace", C.c_void_p),
+        ("expert_ids", C.c_void_p), ("num_m_blocks", C.c_void_p), ("num_experts", C.c_int),
     ]
 
 
@@ -145,6 +146,8 @@ def _declare(lib):
     lib.tdist_moe_route.argtypes = [C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]
     lib.tdist_moe_align_block_size.argtypes = [C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_int,
                                                C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]
+    lib.tdist_gather_rows.argtypes = [C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_void_p, C.c_void_p]
+    lib.tdist_topk_reduce.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_void_p]
     lib.tdist_moe_topk_softmax.argtypes = [C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_void_p, C.c_void_p]
     lib.tdist_stream_write_value.argtypes = [C.c_void_p, C.c_uint64, C.c_uint64, C.c_int]
     lib.tdist_stream_wait_value.argtypes = [C.c_void_p, C.c_uint64, C.c_uint64, C.c_int, C.c_int]

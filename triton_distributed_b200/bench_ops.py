@@ -38,7 +38,13 @@ def peaks() -> dict:
 NVLINK_GBS = 770.0  # measured peer-copy bandwidth per direction per GPU on this pool
 
 
+PRESLEEP_CYCLES = 0  # set by --presleep-ms: a spin kernel queued ahead of the timed launches
+
+
 def timed_us(fn, iters: int, warmup: int, world: int, group=None) -> float:
+    """Device time per call over `iters` back-to-back calls, max over ranks. With a pre-sleep the
+    host enqueues all timed launches while the GPU is still spinning, so the figure excludes host
+    launch overhead (the reference does the same: test_fast_allgather.py `torch.cuda._sleep(1e9)`)."""
     for _ in range(warmup):
         fn()
     torch.cuda.synchronize()
@@ -46,6 +52,8 @@ def timed_us(fn, iters: int, warmup: int, world: int, group=None) -> float:
         dist.barrier(group)
         torch.cuda.synchronize()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    if PRESLEEP_CYCLES > 0:
+        torch.cuda._sleep(PRESLEEP_CYCLES)
     e0.record()
     for _ in range(iters):
         fn()
@@ -57,32 +65,11 @@ def timed_us(fn, iters: int, warmup: int, world: int, group=None) -> float:
     return float(t.item())
 
 
-def main(argv=None) -> int:
-    ap = argparse.ArgumentParser()
-    ap.add_argument("--op", required=True, choices=["gemm", "ag_gemm", "gemm_rs"])
-    ap.add_argument("--m", type=int, default=8192)
-    ap.add_argument("--n", type=int, default=6144)
-    ap.add_argument("--k", type=int, default=12288)
-    ap.add_argument("--iters", type=int, default=20)
-    ap.add_argument("--warmup", type=int, default=3)
-    ap.add_argument("--dtype", default="bf16", choices=["bf16", "fp16"])
-    ap.add_argument("--cta-pair", type=int, default=-1)
-    ap.add_argument("--no-baseline", action="store_true")
-    args = ap.parse_args(argv)
-
+def _bench_gemm_family(args, world, rank, group, dev, dtype, pk, row):
     from .ops import gemm as G
-    from .runtime import check_status, finalize_distributed, initialize_distributed
-
-    world = int(os.environ.get("WORLD_SIZE", "1"))
-    group = initialize_distributed(seed=0) if world > 1 or "RANK" in os.environ else None
-    rank = dist.get_rank() if dist.is_initialized() else 0
-    dev = torch.device("cuda", torch.cuda.current_device())
-    dtype = torch.bfloat16 if args.dtype == "bf16" else torch.float16
-    G.CTA_PAIR = args.cta_pair
-    pk = peaks()
     M, N, K = args.m, args.n, args.k
-    row = {"op": args.op, "m": M, "n": N, "k": K, "world": world, "dtype": args.dtype, "peaks": pk["source"]}
-
+    row.update({"m": M, "n": N, "k": K})
+    G.CTA_PAIR = args.cta_pair
     if args.op == "gemm":
         a = torch.randn(M, K, device=dev, dtype=dtype)
         b = (torch.randn(N, K, device=dev) * K ** -0.5).to(dtype)
@@ -129,13 +116,172 @@ def main(argv=None) -> int:
                 if world > 1:
                     dist.reduce_scatter_tensor(o, full, group=group)
             base = timed_us(ref, args.iters, args.warmup, world, group)
-    check_status()
     compute_us = flops / (pk["bf16_tflops"] * 1e6)
     row.update({"us": round(us, 2), "tflops_per_gpu": round(flops / us / 1e6, 1),
                 "roofline_us": round(max(compute_us, link_us), 2),
                 "roofline_fraction": round(max(compute_us, link_us) / us, 3)})
     if base is not None:
         row.update({"torch_us": round(base, 2), "speedup_vs_torch": round(base / us, 3)})
+
+
+def _bench_decode(args, world, rank, group, dev, dtype, pk, row):
+    """--kv = TOTAL keys per sequence (split evenly over the ranks for sp_decode)."""
+    import math
+
+    from .ops import flash_decode as FD
+    B, Hq, Hkv, D, page = args.batch, args.hq, args.hkv, args.head_dim, args.page_size
+    kv_local = args.kv // world
+    nblk = (kv_local + page - 1) // page
+    k = torch.randn(B * nblk, page, Hkv, D, device=dev, dtype=dtype)
+    v = torch.randn(B * nblk, page, Hkv, D, device=dev, dtype=dtype)
+    table = torch.arange(B * nblk, device=dev, dtype=torch.int32).view(B, nblk)
+    q = torch.randn(B, Hq, D, device=dev, dtype=dtype)
+    scale = 1.0 / math.sqrt(D)
+    out = torch.empty_like(q)
+    row.update({"batch": B, "hq": Hq, "hkv": Hkv, "head_dim": D, "kv_total": args.kv, "kv_per_rank": kv_local})
+    if args.op == "decode":
+        lens = torch.full((B,), kv_local, dtype=torch.int32, device=dev)
+        us = timed_us(lambda: FD.gqa_fwd_batch_decode(q, k, v, None, None, lens, table, scale, output_combine=out),
+                      args.iters, args.warmup, 1)
+        base = None
+    else:
+        glens = torch.full((world, B), kv_local, dtype=torch.int32, device=dev)
+        ctx = FD.create_sp_decode_context(rank, world, B, Hq, D, group=group, device=dev)
+        us = timed_us(lambda: FD.sp_gqa_fwd_batch_decode(ctx, q, k, v, glens, table, scale, out=out),
+                      args.iters, args.warmup, world, group)
+        base = None
+        if not args.no_baseline:
+            # local partial (our kernel) + NCCL all_gather + torch merge = the non-fused pipeline
+            parts = torch.empty(world, B, Hq, D + 1, device=dev, dtype=torch.float32)
+
+            def ref():
+                mine = FD.gqa_fwd_batch_decode_intra_rank(q, k, v, None, None, glens[rank], table, scale)
+                if world > 1:
+                    dist.all_gather_into_tensor(parts, mine, group=group)
+                else:
+                    parts[0].copy_(mine)
+                FD.inter_rank_combine(parts, dtype, out=out)
+            base = timed_us(ref, args.iters, args.warmup, world, group)
+    kv_bytes = 2.0 * B * kv_local * Hkv * D * 2
+    hbm_us = kv_bytes / (pk["hbm_gbs"] * 1e3)
+    row.update({"us": round(us, 2), "kv_gbps": round(kv_bytes / us / 1e3, 1), "roofline_us": round(hbm_us, 2),
+                "roofline_fraction": round(hbm_us / us, 3)})
+    if base is not None:
+        row.update({"unfused_us": round(base, 2), "speedup_vs_unfused": round(base / us, 3)})
+
+
+def _bench_a2a(args, world, rank, group, dev, dtype, pk, row):
+    from .ops import all_to_all as A
+    from .ops import moe_utils as MU
+    T, H, E, K = args.tokens, args.hidden, args.experts, args.topk
+    row.update({"tokens_per_rank": T, "hidden": H, "experts": E, "topk": K})
+    x = torch.randn(T, H, device=dev).to(torch.bfloat16)
+    ids, w = MU.topk_softmax(torch.randn(T, E, device=dev), K)
+    ctx = A.create_moe_dispatch_context(T, H, K, E, rank, world, group=group, device=dev)
+    state = {}
+
+    def dispatch():
+        state["recv"] = A.moe_dispatch(ctx, x, ids, w)
+
+    def both():
+        rx, rs, splits = A.moe_dispatch(ctx, x, ids, w)
+        y = A.dequant_fp8(rx, rs)
+        A.moe_combine(ctx, y, splits)
+
+    dispatch()
+    y = A.dequant_fp8(*state["recv"][:2])
+    us_d = timed_us(dispatch, args.iters, args.warmup, world, group)
+    us_c = timed_us(lambda: A.moe_combine(ctx, y, state["recv"][2]), args.iters, args.warmup, world, group)
+    us_b = timed_us(both, args.iters, args.warmup, world, group)
+    out_bytes = T * K * (H + H // 128 * 4) * (world - 1) / world
+    back_bytes = T * K * H * 2 * (world - 1) / world
+    link_us = (out_bytes + back_bytes) / (NVLINK_GBS * 1e3)
+    row.update({"dispatch_us": round(us_d, 2), "combine_us": round(us_c, 2), "dispatch_dequant_combine_us": round(us_b, 2),
+                "us": round(us_d + us_c, 2), "roofline_us": round(link_us, 2),
+                "roofline_fraction": round(link_us / (us_d + us_c), 3)})
+    if not args.no_baseline and world > 1:
+        # NCCL all_to_all_single of the same payload with equal splits (bf16 both ways)
+        rows = T * K // world * world
+        send = torch.randn(rows, H, device=dev).to(torch.bfloat16)
+        recv = torch.empty_like(send)
+        base = timed_us(lambda: (dist.all_to_all_single(recv, send, group=group), dist.all_to_all_single(send, recv, group=group)),
+                        args.iters, args.warmup, world, group)
+        row.update({"nccl_a2a_x2_us": round(base, 2), "speedup_vs_nccl": round(base / (us_d + us_c), 3)})
+
+
+def _bench_allgather(args, world, rank, group, dev, dtype, pk, row):
+    from .ops import collectives as CO
+    from .runtime import symm_heap
+    nbytes = args.bytes // world * world
+    heap = symm_heap(group)
+    buf = heap.empty((nbytes,), torch.uint8)
+    ctx = CO.create_fast_allgather_context(rank, 0, world, 1, max_buffer_size=nbytes, group=group, device=dev)
+    row.update({"bytes": nbytes, "mode": args.mode})
+
+    def step():
+        CO.fast_allgather(buf, ctx, mode=args.mode)
+        CO.barrier_all_on_stream()  # in-place buffer: nobody may start the next round early
+    us = timed_us(step, args.iters, args.warmup, world, group)
+    us_bar = timed_us(CO.barrier_all_on_stream, args.iters, args.warmup, world, group)
+    link_us = nbytes * (world - 1) / world / (NVLINK_GBS * 1e3)
+    row.update({"us": round(us - us_bar, 2), "barrier_us": round(us_bar, 2), "bus_gbps": round(nbytes * (world - 1) / world / max(us - us_bar, 1e-3) / 1e3, 1),
+                "roofline_us": round(link_us, 2), "roofline_fraction": round(link_us / max(us - us_bar, 1e-3), 3)})
+    if not args.no_baseline and world > 1:
+        mine = torch.empty(nbytes // world, dtype=torch.uint8, device=dev)
+        full = torch.empty(nbytes, dtype=torch.uint8, device=dev)
+        base = timed_us(lambda: dist.all_gather_into_tensor(full, mine, group=group), args.iters, args.warmup, world, group)
+        row.update({"nccl_us": round(base, 2)})
+
+
+def main(argv=None) -> int:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--op", required=True, choices=["gemm", "ag_gemm", "gemm_rs", "decode", "sp_decode", "a2a", "allgather"])
+    ap.add_argument("--m", type=int, default=8192)
+    ap.add_argument("--n", type=int, default=6144)
+    ap.add_argument("--k", type=int, default=12288)
+    ap.add_argument("--batch", type=int, default=1)
+    ap.add_argument("--hq", type=int, default=32)
+    ap.add_argument("--hkv", type=int, default=8)
+    ap.add_argument("--head-dim", type=int, default=128)
+    ap.add_argument("--page-size", type=int, default=16)
+    ap.add_argument("--kv", type=int, default=131072, help="total keys per sequence")
+    ap.add_argument("--tokens", type=int, default=128)
+    ap.add_argument("--hidden", type=int, default=7168)
+    ap.add_argument("--experts", type=int, default=256)
+    ap.add_argument("--topk", type=int, default=8)
+    ap.add_argument("--bytes", type=int, default=1 << 20)
+    ap.add_argument("--mode", default="push2d")
+    ap.add_argument("--iters", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--dtype", default="bf16", choices=["bf16", "fp16"])
+    ap.add_argument("--cta-pair", type=int, default=-1)
+    ap.add_argument("--no-baseline", action="store_true")
+    ap.add_argument("--presleep-ms", type=float, default=-1.0,
+                    help="spin the GPU this long before each timed loop (default: 30 ms for the latency ops, 0 for GEMMs)")
+    args = ap.parse_args(argv)
+    global PRESLEEP_CYCLES
+    if args.presleep_ms < 0:
+        args.presleep_ms = 0.0 if args.op in ("gemm", "ag_gemm", "gemm_rs") else 30.0
+    PRESLEEP_CYCLES = int(args.presleep_ms * 1.9e6)
+
+    from .runtime import check_status, finalize_distributed, initialize_distributed
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    group = initialize_distributed(seed=0) if world > 1 or "RANK" in os.environ else None
+    rank = dist.get_rank() if dist.is_initialized() else 0
+    dev = torch.device("cuda", torch.cuda.current_device())
+    dtype = torch.bfloat16 if args.dtype == "bf16" else torch.float16
+    pk = peaks()
+    row = {"op": args.op, "world": world, "dtype": args.dtype, "peaks": pk["source"]}
+    if args.op in ("gemm", "ag_gemm", "gemm_rs"):
+        _bench_gemm_family(args, world, rank, group, dev, dtype, pk, row)
+    elif args.op in ("decode", "sp_decode"):
+        _bench_decode(args, world, rank, group, dev, dtype, pk, row)
+    elif args.op == "a2a":
+        _bench_a2a(args, world, rank, group, dev, dtype, pk, row)
+    else:
+        _bench_allgather(args, world, rank, group, dev, dtype, pk, row)
+    check_status()
     if rank == 0:
         print(json.dumps(row), flush=True)
     if dist.is_initialized():

@@ -71,6 +71,11 @@ typedef struct TdistGemmArgs {
      * [40b]: begin, end, then (start, end) of its first 19 blocks. GEMM CTA c < 64 writes at
      * [1024 + 4c]: producer begin, producer end, ns spent waiting on flags, waits longer than 2 us. */
     void* trace;
+    /* Grouped GEMM (PLAIN mode, world 1): B is [num_experts, N, K]; 128-row block i of A and C uses
+     * B[expert_ids[i]]; blocks at or past *num_m_blocks (device int32, may be NULL) are skipped. */
+    const void* expert_ids;
+    const void* num_m_blocks;
+    int num_experts;
 } TdistGemmArgs;
 
 int tdist_gemm_run(const TdistGemmArgs* args);
@@ -155,6 +160,12 @@ int tdist_moe_route(const void* ids, int n, int topk, int num_experts, void* spl
 int tdist_moe_align_block_size(const void* ids, int numel_per_rank, int num_experts, int num_ranks, int block_size,
                                void* sorted_ids, int sorted_cap, void* expert_ids, void* block_barrier_ids,
                                void* rank_block_num, void* num_tokens_post_pad, void* stream);
+/* dst[p] = src[index[p] / div] (zeros where index[p] is outside [0, limit)); pos_of (optional) gets the inverse map */
+int tdist_gather_rows(const void* src, const void* index, int rows_out, int div, int limit, int row_bytes,
+                      void* dst, void* pos_of, void* stream);
+/* out[t] = sum_k weights[t,k] * y[pos_of[t*topk+k]] (bf16 rows, fp32 accumulation; weights may be NULL = 1) */
+int tdist_topk_reduce(const void* y, const void* pos_of, const void* weights, int ntok, int topk, int row_bytes,
+                      void* out, void* stream);
 int tdist_moe_topk_softmax(const void* logits_f32, int ntok, int num_experts, int topk, int renormalize,
                            void* ids, void* weights, void* stream);
 

@@ -94,6 +94,8 @@ struct GemmParams {
     uint32_t epoch;
     int debug_delay_ns;
     unsigned long long* trace;  // optional timeline (see tdist.h), nullptr = off
+    const int* expert_ids;      // grouped GEMM: expert (slice of B) of every 128-row block, nullptr = plain
+    const int* num_m_blocks;    // grouped GEMM: device count of live 128-row blocks (rest is padding)
     WaitCtx wctx;
 };
 
@@ -314,9 +316,12 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_sm100_kernel(const __grid_con
             unsigned long long* tr = (p.trace != nullptr && cta < 64) ? p.trace + 1024 + cta * 4 : nullptr;
             unsigned long long waited = 0, blocked = 0;
             if (tr) tr[0] = globaltimer_ns();
+            const int live_blocks = p.num_m_blocks ? *p.num_m_blocks : 0x7fffffff;
             for (int t = unit; t < p.num_tiles; t += num_units) {
                 const TileCoord tc = decode_tile(t, first_seg, p.world, p.seg_m_tiles, p.n_tiles, p.group_m);
+                if (tc.m_in_seg * CTAS >= live_blocks) continue;  // padding tile of a grouped GEMM: every role skips it
                 const int block = tc.m_in_seg * CTAS + cta_rank;  // 128-row block inside the segment
+                const int bz = p.expert_ids ? p.expert_ids[block] : 0;
                 const CUtensorMap* am = &p.tm_a;
                 int az = tc.seg;
                 if (MODE == TDIST_GEMM_AG) {
@@ -343,13 +348,13 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_sm100_kernel(const __grid_con
                     if (CTAS == 1) {
                         mbar_expect_tx(bar_full(s), STAGE_BYTES);
                         tma_load_3d(sa, am, bar_full(s), kb * BK, row, az);
-                        tma_load_3d(sa + A_BYTES, &p.tm_b, bar_full(s), kb * BK, col, 0);
+                        tma_load_3d(sa + A_BYTES, &p.tm_b, bar_full(s), kb * BK, col, bz);
                     } else {
                         // both CTAs' bytes are counted on the leader's barrier
                         if (cta_rank == 0) mbar_expect_tx(bar_full(s), 2 * STAGE_BYTES);
                         const uint32_t leader_full = mapa_u32(bar_full(s), 0);
                         tma_load_3d_pair(sa, am, leader_full, kb * BK, row, az);
-                        tma_load_3d_pair(sa + A_BYTES, &p.tm_b, leader_full, kb * BK, col, 0);
+                        tma_load_3d_pair(sa + A_BYTES, &p.tm_b, leader_full, kb * BK, col, bz);
                     }
                 }
             }
@@ -366,7 +371,11 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_sm100_kernel(const __grid_con
             const uint32_t idesc = umma_idesc(p.is_f16 ? 0u : 1u, p.is_f16 ? 0u : 1u, BM * CTAS, BN);
             uint32_t it = 0;
             uint32_t local_tile = 0;
-            for (int t = unit; t < p.num_tiles; t += num_units, ++local_tile) {
+            const int live_blocks = p.num_m_blocks ? *p.num_m_blocks : 0x7fffffff;
+            for (int t = unit; t < p.num_tiles; t += num_units) {
+                if (p.num_m_blocks != nullptr &&
+                    decode_tile(t, first_seg, p.world, p.seg_m_tiles, p.n_tiles, p.group_m).m_in_seg * CTAS >= live_blocks)
+                    continue;
                 const uint32_t buf = local_tile & 1u;
                 mbar_wait(bar_tempty(buf), ((local_tile >> 1) & 1u) ^ 1u, p.wctx, 3);
                 tc_fence_after();
@@ -389,6 +398,7 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_sm100_kernel(const __grid_con
                 }
                 if (CTAS == 1) umma_commit(bar_tfull(buf));  // accumulator ready
                 else umma_commit_pair(bar_tfull(buf), 3);
+                ++local_tile;
             }
         }
         __syncwarp();
@@ -399,8 +409,10 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_sm100_kernel(const __grid_con
         const bool issuer = (warp == 2 && lane == 0);
         uint8_t* cstage = smem + PIPE_BYTES;
         uint32_t local_tile = 0;
-        for (int t = unit; t < p.num_tiles; t += num_units, ++local_tile) {
+        const int live_blocks = p.num_m_blocks ? *p.num_m_blocks : 0x7fffffff;
+        for (int t = unit; t < p.num_tiles; t += num_units) {
             const TileCoord tc = decode_tile(t, first_seg, p.world, p.seg_m_tiles, p.n_tiles, p.group_m);
+            if (tc.m_in_seg * CTAS >= live_blocks) continue;
             const uint32_t buf = local_tile & 1u;
             mbar_wait(bar_tfull(buf), (local_tile >> 1) & 1u, p.wctx, 5);
             tc_fence_after();
@@ -472,6 +484,7 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_sm100_kernel(const __grid_con
                 fence_acq_rel_sys();
                 st_release_sys_u32(p.flags_peer[tc.seg] + (block * p.n_tiles + tc.n_tile) * p.world + p.rank, p.epoch);
             }
+            ++local_tile;
         }
         if (issuer) bulk_wait<0>();
         __syncwarp();
@@ -514,6 +527,7 @@ using namespace tdist;
 using tdist_host::fail;
 
 static bool use_pair(const TdistGemmArgs* a) {
+    if (a->expert_ids != nullptr) return false;  // one expert per 128-row block
     if (a->cta_pair == 0) return false;
     if (a->cta_pair > 0) return true;
     return a->m_per_rank > BM;  // a second CTA would only compute padding otherwise
@@ -605,6 +619,8 @@ extern "C" int tdist_gemm_run(const TdistGemmArgs* a) {
     if (a->k % 8 != 0 || a->n % 8 != 0)
         return fail(TDIST_EINVAL, "K and N must be multiples of 8 (16-byte rows for TMA)");
     if (a->mode < TDIST_GEMM_PLAIN || a->mode > TDIST_GEMM_RS) return fail(TDIST_EINVAL, "bad mode");
+    if (a->expert_ids != nullptr && (a->mode != TDIST_GEMM_PLAIN || a->world != 1))
+        return fail(TDIST_EINVAL, "grouped GEMM (expert_ids) is a single-rank plain-mode feature");
 
     const GridPlan plan = plan_grid(a);
     const int ctas = plan.ctas_per_tile;
@@ -630,7 +646,8 @@ extern "C" int tdist_gemm_run(const TdistGemmArgs* a) {
         if ((rc = tdist_host::encode_tmap(&p.tm_a_own, dt, 2, 3, a->a, dims, strides, box, tdist_host::Swizzle::B128))) return rc;
     }
     {
-        uint64_t dims[3] = {K, N, 1};
+        const uint64_t E = a->num_experts > 0 ? a->num_experts : 1;
+        uint64_t dims[3] = {K, N, E};
         uint64_t strides[2] = {K * 2, N * K * 2};
         uint32_t box[3] = {BK, static_cast<uint32_t>(BN / ctas), 1};
         if ((rc = tdist_host::encode_tmap(&p.tm_b, dt, 2, 3, a->b, dims, strides, box, tdist_host::Swizzle::B128))) return rc;
@@ -670,6 +687,8 @@ extern "C" int tdist_gemm_run(const TdistGemmArgs* a) {
     p.epoch = a->epoch;
     p.debug_delay_ns = a->debug_delay_ns;
     p.trace = static_cast<unsigned long long*>(a->trace);
+    p.expert_ids = static_cast<const int*>(a->expert_ids);
+    p.num_m_blocks = static_cast<const int*>(a->num_m_blocks);
     p.wctx.status = static_cast<Status*>(a->status);
     p.wctx.timeout_ns = a->timeout_ns;
     p.wctx.kernel_id = kKernelGemm;

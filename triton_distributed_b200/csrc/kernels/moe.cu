@@ -205,6 +205,56 @@ __global__ void moe_topk_softmax_kernel(const float* logits, int ntok, int E, in
     }
 }
 
+// ---------------------------------------------------------------------------- row gather / top-k reduce
+// dst[p] = src[index[p] / div] for index[p] < limit, zeros otherwise (padding rows of the aligned
+// sort); optionally records the inverse map pos_of[index[p]] = p. One warp per row, 16-byte vectors.
+__global__ void gather_rows_kernel(const uint4* src, const int* index, int rows_out, int div, int limit, int vec_per_row,
+                                   uint4* dst, int* pos_of) {
+    const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+    const int lane = threadIdx.x & 31;
+    const int nwarps = (gridDim.x * blockDim.x) >> 5;
+    for (int p = warp; p < rows_out; p += nwarps) {
+        const int id = index[p];
+        const bool live = id >= 0 && id < limit;
+        if (live && pos_of != nullptr && lane == 0) pos_of[id] = p;
+        const uint4* s = src + static_cast<size_t>(live ? id / div : 0) * vec_per_row;
+        uint4* d = dst + static_cast<size_t>(p) * vec_per_row;
+        for (int c = lane; c < vec_per_row; c += 32) d[c] = live ? s[c] : make_uint4(0, 0, 0, 0);
+    }
+}
+
+// out[t] = sum_k w[t*topk+k] * y[pos_of[t*topk+k]] in fp32 (bf16 in/out). One warp per token.
+__global__ void topk_reduce_kernel(const uint4* y, const int* pos_of, const float* w, int ntok, int topk, int vec_per_row,
+                                   uint4* out) {
+    const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+    const int lane = threadIdx.x & 31;
+    const int nwarps = (gridDim.x * blockDim.x) >> 5;
+    for (int t = warp; t < ntok; t += nwarps) {
+        for (int c = lane; c < vec_per_row; c += 32) {
+            float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+            for (int k = 0; k < topk; ++k) {
+                const float wk = w ? w[t * topk + k] : 1.f;
+                const uint4 q = y[static_cast<size_t>(pos_of[t * topk + k]) * vec_per_row + c];
+                const uint32_t u[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    acc[2 * i] += wk * __uint_as_float(u[i] << 16);
+                    acc[2 * i + 1] += wk * __uint_as_float(u[i] & 0xffff0000u);
+                }
+            }
+            uint4 o;
+            uint32_t* ow = reinterpret_cast<uint32_t*>(&o);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                uint32_t r;
+                asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(acc[2 * i + 1]), "f"(acc[2 * i]));
+                ow[i] = r;
+            }
+            out[static_cast<size_t>(t) * vec_per_row + c] = o;
+        }
+    }
+}
+
 }  // namespace tdist
 
 using namespace tdist;
@@ -259,6 +309,30 @@ extern "C" int tdist_moe_topk_softmax(const void* logits, int ntok, int num_expe
     moe_topk_softmax_kernel<<<blocks, warps_per_block * 32, 0, static_cast<cudaStream_t>(stream)>>>(
         static_cast<const float*>(logits), ntok, num_experts, topk, renormalize, static_cast<int*>(ids),
         static_cast<float*>(weights));
+    TDIST_CUDA_OK(cudaGetLastError());
+    return 0;
+}
+
+extern "C" int tdist_gather_rows(const void* src, const void* index, int rows_out, int div, int limit, int row_bytes,
+                                 void* dst, void* pos_of, void* stream) {
+    if (row_bytes % 16 || div < 1) return fail(TDIST_EINVAL, "gather_rows: rows must be multiples of 16 bytes");
+    if (rows_out <= 0) return 0;
+    const int blocks = (rows_out + 7) / 8 < 1184 ? (rows_out + 7) / 8 : 1184;
+    gather_rows_kernel<<<blocks, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+        static_cast<const uint4*>(src), static_cast<const int*>(index), rows_out, div, limit, row_bytes / 16,
+        static_cast<uint4*>(dst), static_cast<int*>(pos_of));
+    TDIST_CUDA_OK(cudaGetLastError());
+    return 0;
+}
+
+extern "C" int tdist_topk_reduce(const void* y, const void* pos_of, const void* weights, int ntok, int topk, int row_bytes,
+                                 void* out, void* stream) {
+    if (row_bytes % 16 || topk < 1) return fail(TDIST_EINVAL, "topk_reduce: rows must be multiples of 16 bytes");
+    if (ntok <= 0) return 0;
+    const int blocks = (ntok + 7) / 8 < 1184 ? (ntok + 7) / 8 : 1184;
+    topk_reduce_kernel<<<blocks, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+        static_cast<const uint4*>(y), static_cast<const int*>(pos_of), static_cast<const float*>(weights), ntok, topk,
+        row_bytes / 16, static_cast<uint4*>(out));
     TDIST_CUDA_OK(cudaGetLastError());
     return 0;
 }

@@ -71,10 +71,10 @@ def create_all_to_all_context(max_m: int, hidden: int, rank: int, num_tot_expert
 
 
 def _fill_common(a: "_lib.A2AArgs", ctx: AllToAllContext, half: int, phase: int, device, stream) -> None:
-    a.recv_peer = _lib.ptr_array([t[half].data_ptr() for t in ctx.recv_buf.peers])
-    a.scale_peer = _lib.ptr_array([t[half].data_ptr() for t in ctx.scale_recv_buf.peers])
-    a.splits_peer = _lib.ptr_array([t[half].data_ptr() for t in ctx.split_recv_buf.peers])
-    a.sig_peer = _lib.ptr_array(ctx.signal_buf.ptrs)
+    a.recv_peer = ctx.recv_buf.half_ptr_arrays()[half]
+    a.scale_peer = ctx.scale_recv_buf.half_ptr_arrays()[half]
+    a.splits_peer = ctx.split_recv_buf.half_ptr_arrays()[half]
+    a.sig_peer = ctx.signal_buf.cached_ptr_array()
     a.counters = ctx.counters.data_ptr()
     a.max_m, a.epr, a.world, a.rank = ctx.max_m, ctx.experts_per_rank, ctx.WORLD_SIZE, ctx.rank
     a.phase = phase
@@ -106,8 +106,10 @@ def fast_all_to_all(ctx: AllToAllContext, send_tensor: torch.Tensor, send_split_
     [source rank, local expert], recv[ws*max_m, hidden], recv_scale[ws*max_m, scale_cols] | None)``.
     The views stay valid until the call after next."""
     ntok = send_tensor.shape[0]
-    if ntok > ctx.max_m:
-        raise ValueError(f"{ntok} rows exceed the context's max_m {ctx.max_m}")
+    # one destination never gets more than max_m rows from one source; the sender as a whole may hold
+    # up to world * max_m rows (the combine direction sends back everything it received)
+    if ntok > ctx.WORLD_SIZE * ctx.max_m:
+        raise ValueError(f"{ntok} rows exceed world * max_m = {ctx.WORLD_SIZE * ctx.max_m}")
     if send_tensor.device.type != "cuda":
         return _fast_all_to_all_cpu(ctx, send_tensor, send_split_cumsum, send_scale)
     if not send_tensor.is_contiguous() or send_tensor.shape[1] != ctx.hidden or send_tensor.dtype != ctx.dtype:
@@ -146,11 +148,11 @@ def all_to_all_post_process(ctx: AllToAllContext, input_splits: torch.Tensor, re
 
 def _fast_all_to_all_cpu(ctx, send, cumsum, scale):
     W, epr, mm = ctx.WORLD_SIZE, ctx.experts_per_rank, ctx.max_m
-    pad = torch.zeros((mm, send.shape[1]), dtype=send.dtype)
+    pad = torch.zeros((W * mm, send.shape[1]), dtype=send.dtype)
     pad[: send.shape[0]] = send
     cums = cumsum.to(torch.int32)
     scol = ctx.scale_cols
-    spad = torch.zeros((mm, scol), dtype=torch.float32)
+    spad = torch.zeros((W * mm, scol), dtype=torch.float32)
     if scale is not None:
         spad[: send.shape[0]] = scale.reshape(send.shape[0], -1).float()
     if W > 1:

@@ -153,6 +153,7 @@ class FastAllGatherContext:
     epoch: int = 0
     ctas_per_peer: int = 0
     group: object = None
+    _ll_arrays: object = None
 
 
 def create_fast_allgather_context(rank: int, node: int = 0, num_ranks: int = 1, num_nodes: int = 1,
@@ -197,8 +198,8 @@ def fast_allgather(symm_buffer: SymmTensor, ctx: Optional[FastAllGatherContext] 
     if nbytes > ctx.max_buffer_size:
         raise ValueError(f"buffer of {nbytes} bytes exceeds the context's max_buffer_size {ctx.max_buffer_size}")
     a = _lib.CollArgs()
-    a.buf_peer = _lib.ptr_array(symm_buffer.ptrs)
-    a.sig_peer = _lib.ptr_array(ctx.signal.ptrs)
+    a.buf_peer = symm_buffer.cached_ptr_array()
+    a.sig_peer = ctx.signal.cached_ptr_array()
     a.counters = ctx.counters.data_ptr()
     a.seg_bytes = nbytes // ctx.world
     a.world, a.rank = ctx.world, ctx.rank
@@ -211,7 +212,9 @@ def fast_allgather(symm_buffer: SymmTensor, ctx: Optional[FastAllGatherContext] 
         ctx.epoch += 1
     a.epoch = ctx.epoch
     half_bytes = 2 * ctx.ll_max
-    a.ll_peer = _lib.ptr_array([p + (ctx.epoch & 1) * half_bytes for p in ctx.ll_buffer.ptrs])
+    if ctx._ll_arrays is None:
+        ctx._ll_arrays = tuple(_lib.ptr_array([p + h * half_bytes for p in ctx.ll_buffer.ptrs]) for h in range(2))
+    a.ll_peer = ctx._ll_arrays[ctx.epoch & 1]
     a.status = _status_ptr()
     a.timeout_ns = default_timeout_ns()
     a.stream = _stream_ptr(local.device, stream)
@@ -281,9 +284,8 @@ def reduce_scatter_2d_op(input: torch.Tensor, ctx: ReduceScatter2DContext, out: 
     o = out if out is not None else torch.empty((mpr, N), dtype=input.dtype, device=input.device)
     a = _lib.CollArgs()
     half = (ctx.epoch + (1 if phase != 2 else 0)) & 1
-    bases = [t[half].data_ptr() for t in ctx.staging.peers]
-    a.buf_peer = _lib.ptr_array(bases)
-    a.sig_peer = _lib.ptr_array(ctx.signal.ptrs)
+    a.buf_peer = ctx.staging.half_ptr_arrays()[half]
+    a.sig_peer = ctx.signal.cached_ptr_array()
     a.counters = ctx.counters.data_ptr()
     a.input = input.data_ptr()
     a.output = o.data_ptr()

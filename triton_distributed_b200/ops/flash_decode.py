@@ -126,7 +126,7 @@ def _launch(q, k_cache, v_cache, kv_lens, block_table, scale, soft_cap, out, mod
     a.mode, a.dtype, a.world, a.rank, a.epoch = mode, _DTYPES[q.dtype], world, rank, epoch
     a.push_only = int(push_only)
     if ll_ptrs is not None:
-        a.ll_peer = _lib.ptr_array(ll_ptrs)
+        a.ll_peer = ll_ptrs
     st = global_status()
     a.status = st.device_ptr if st is not None else None
     a.timeout_ns = default_timeout_ns()
@@ -235,5 +235,5 @@ def sp_gqa_fwd_batch_decode(ctx: SpDecodeContext, q, k_cache, v_cache, global_kv
     o = out if out is not None else torch.empty_like(q)
     return _launch(q, k_cache, v_cache, global_kv_lens[ctx.rank], block_table, scale, soft_cap, o, 2, kv_split,
                    max_kv=int(block_table.shape[1]) * k_cache.shape[1],
-                   ll_ptrs=[t[half].data_ptr() for t in ctx.gather.peers], world=ctx.world, rank=ctx.rank, epoch=ctx.epoch,
+                   ll_ptrs=ctx.gather.half_ptr_arrays()[half], world=ctx.world, rank=ctx.rank, epoch=ctx.epoch,
                    push_only=(phase == 1))

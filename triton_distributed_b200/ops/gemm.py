@@ -184,9 +184,9 @@ def ag_gemm_intra_node(a: torch.Tensor, b: torch.Tensor, ctx: Optional[AllGather
     if ctx.world > 1:
         half = ctx.epoch & 1
         g.a_ws = ctx.workspace.local[half].data_ptr()
-        g.a_ws_peer = _lib.ptr_array([t[half].data_ptr() for t in ctx.workspace.peers])
+        g.a_ws_peer = ctx.workspace.half_ptr_arrays()[half]
         g.flags = ctx.flags.local[half].data_ptr()
-        g.flags_peer = _lib.ptr_array([t[half].data_ptr() for t in ctx.flags.peers])
+        g.flags_peer = ctx.flags.half_ptr_arrays()[half]
     _launch(g)
     return c
 
@@ -261,9 +261,9 @@ def gemm_rs(a: torch.Tensor, b: torch.Tensor, ctx: GEMMReduceScatterTensorParall
     g.epoch = ctx.epoch
     g.num_sms = ctx.num_sms
     half = ctx.epoch & 1
-    g.c_stage_peer = _lib.ptr_array([t[half].data_ptr() for t in ctx.staging.peers])
+    g.c_stage_peer = ctx.staging.half_ptr_arrays()[half]
     g.flags = ctx.flags.local[half].data_ptr()
-    g.flags_peer = _lib.ptr_array([t[half].data_ptr() for t in ctx.flags.peers])
+    g.flags_peer = ctx.flags.half_ptr_arrays()[half]
     g.rs_out = o.data_ptr()
     _launch(g)
     return o

@@ -1,0 +1,284 @@
+"""Tensor-parallel MoE ops: grouped GEMM on tcgen05, AllGather + GroupGEMM, GroupGEMM + top-k
+reduce + ReduceScatter.
+
+Public surface (names of the reference):
+
+* ``select_experts(pg, num_ranks, topk, input_dtype, device, router_logits)``
+  (reference kernels/nvidia/moe_reduce_rs.py:180-197)
+* ``create_ag_group_gemm_intra_node_context`` / ``ag_group_gemm_intra_node(a[M/ws,K], b[E,K,N/ws], ctx)
+  -> [M*topk, N/ws]`` (reference kernels/nvidia/allgather_group_gemm.py:555-691)
+* ``create_moe_rs_context`` / ``moe_reduce_rs(rank, world, local_world, a[M*topk,K/ws], b[E,K/ws,N], ctx)
+  -> [M/ws, N]`` (reference kernels/nvidia/moe_reduce_rs.py:280-361,889-1029)
+* ``group_gemm(a_sorted, b[E,N,K], expert_ids, num_blocks)`` — the grouped tcgen05 GEMM itself.
+
+Pipeline on CUDA (each stage one hand-written kernel): all-gather of the token shards (push kernel
+over NVLink) -> block-aligned expert sort (``moe_align_block_size``) -> row gather into the sorted,
+128-row-padded layout -> grouped GEMM (the persistent tcgen05 kernel picking B[expert] per 128-row
+block) -> un-permute / top-k weighted reduce -> reduce-scatter kernel. The stages are not yet fused
+across the collective the way AG-GEMM and GEMM-RS are.
+
+CPU tensors run a torch restatement (masked per-expert matmul, the reference's own oracle:
+test/nvidia/test_ag_moe.py:24-39).
+"""
+from __future__ import annotations
+
+import ctypes as C
+from dataclasses import dataclass
+from typing import Optional, Tuple
+
+import torch
+import torch.distributed as dist
+
+from .. import _lib
+from ..runtime import symm_heap
+from . import collectives as CO
+from . import gemm as G
+from . import moe_utils as MU
+
+GROUP_BLOCK_M = 128
+launch_count = 0
+
+
+def _stream(t):
+    return torch.cuda.current_stream(t.device).cuda_stream
+
+
+def select_experts(pg, num_ranks: int, topk: int, input_dtype, device, router_logits: torch.Tensor
+                   ) -> Tuple[torch.Tensor, torch.Tensor]:
+    """softmax -> top-k on this rank's tokens, then all-gather ids and weights of every rank's
+    tokens (NCCL / gloo: this is set-up, not a hot path). Returns ``(full_topk_ids int32 [M, topk],
+    full_topk_weight [M, topk])``."""
+    ids, w = MU.topk_softmax(router_logits, topk)
+    if num_ranks > 1:
+        full_ids = torch.empty((ids.shape[0] * num_ranks, topk), dtype=ids.dtype, device=ids.device)
+        full_w = torch.empty((w.shape[0] * num_ranks, topk), dtype=w.dtype, device=w.device)
+        dist.all_gather_into_tensor(full_ids, ids, group=pg)
+        dist.all_gather_into_tensor(full_w, w, group=pg)
+        return full_ids, full_w.to(input_dtype)
+    return ids, w.to(input_dtype)
+
+
+# ---------------------------------------------------------------------------- grouped GEMM
+def gather_rows(src: torch.Tensor, index: torch.Tensor, div: int, limit: int, want_inverse: bool = False):
+    """``dst[p] = src[index[p] // div]`` (zeros where ``index[p]`` is padding); optionally also the
+    inverse map ``pos_of[index[p]] = p``."""
+    global launch_count
+    rows_out = index.shape[0]
+    dst = torch.empty((rows_out, src.shape[1]), dtype=src.dtype, device=src.device)
+    pos_of = torch.zeros(limit, dtype=torch.int32, device=src.device) if want_inverse else None
+    if src.device.type != "cuda":
+        live = (index >= 0) & (index < limit)
+        rows = torch.where(live, index.long() // div, torch.zeros_like(index).long())
+        dst.copy_(src[rows] * live.unsqueeze(-1).to(src.dtype))
+        if want_inverse:
+            pos_of[index[live].long()] = torch.arange(rows_out, dtype=torch.int32)[live]
+        return dst, pos_of
+    _lib.check(_lib.lib().tdist_gather_rows(src.data_ptr(), index.data_ptr(), rows_out, div, limit,
+                                            src.shape[1] * src.element_size(), dst.data_ptr(),
+                                            pos_of.data_ptr() if want_inverse else None, _stream(src)), "tdist_gather_rows")
+    launch_count += 1
+    return dst, pos_of
+
+
+def topk_reduce(y: torch.Tensor, pos_of: torch.Tensor, weights: Optional[torch.Tensor], ntok: int, topk: int) -> torch.Tensor:
+    """``out[t] = sum_k weights[t,k] * y[pos_of[t*topk+k]]`` (fp32 accumulation)."""
+    global launch_count
+    out = torch.empty((ntok, y.shape[1]), dtype=y.dtype, device=y.device)
+    if y.device.type != "cuda" or y.dtype != torch.bfloat16:
+        rows = y[pos_of.long()].float().view(ntok, topk, -1)
+        w = weights.float().view(ntok, topk, 1) if weights is not None else 1.0
+        return (rows * w).sum(1).to(y.dtype)
+    w = weights.float().contiguous() if weights is not None else None
+    _lib.check(_lib.lib().tdist_topk_reduce(y.data_ptr(), pos_of.data_ptr(), w.data_ptr() if w is not None else None,
+                                            ntok, topk, y.shape[1] * 2, out.data_ptr(), _stream(y)), "tdist_topk_reduce")
+    launch_count += 1
+    return out
+
+
+def group_gemm(a_sorted: torch.Tensor, b: torch.Tensor, expert_ids: torch.Tensor, num_blocks: Optional[torch.Tensor] = None,
+               out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``out[i*128:(i+1)*128] = a_sorted[i*128:(i+1)*128] @ b[expert_ids[i]].T`` for every live
+    128-row block. ``a_sorted`` ``[blocks*128, K]``, ``b`` ``[E, N, K]`` (K contiguous), ``num_blocks``
+    an int32 device scalar (blocks past it are padding and are skipped)."""
+    rows, K = a_sorted.shape
+    E, N, _ = b.shape
+    if rows % GROUP_BLOCK_M:
+        raise ValueError("grouped GEMM rows must be a multiple of 128")
+    if a_sorted.device.type != "cuda":
+        o = torch.zeros((rows, N), dtype=a_sorted.dtype)
+        nb = rows // GROUP_BLOCK_M if num_blocks is None else int(num_blocks)
+        for i in range(nb):
+            blk = slice(i * GROUP_BLOCK_M, (i + 1) * GROUP_BLOCK_M)
+            o[blk] = (a_sorted[blk].float() @ b[int(expert_ids[i])].float().t()).to(o.dtype)
+        return o
+    G._check_operands(a_sorted, b.view(E * N, K))
+    c = out if out is not None else torch.empty((rows, N), dtype=a_sorted.dtype, device=a_sorted.device)
+    g = G._base_args(a_sorted, b.view(E * N, K), 1, 0, _lib.GEMM_PLAIN)
+    g.n = N
+    g.c = c.data_ptr()
+    g.m_per_rank = rows
+    g.epoch = 1
+    g.expert_ids = expert_ids.data_ptr()
+    g.num_m_blocks = num_blocks.data_ptr() if num_blocks is not None else None
+    g.num_experts = E
+    G._launch(g)
+    return c
+
+
+# ---------------------------------------------------------------------------- AG + GroupGEMM
+@dataclass
+class MoEAllGatherGroupGEMMTensorParallelContext:
+    rank: int
+    world: int
+    num_experts: int
+    topk: int
+    max_M: int
+    K: int
+    full_topk_ids: torch.Tensor
+    group: object = None
+    gather_buf: Optional[object] = None          # symmetric [max_M, K]
+    ag_ctx: Optional[CO.FastAllGatherContext] = None
+    sorted_ids: Optional[torch.Tensor] = None
+    expert_ids: Optional[torch.Tensor] = None
+    block_barrier_ids: Optional[torch.Tensor] = None
+    rank_block_num: Optional[torch.Tensor] = None
+    num_blocks: Optional[torch.Tensor] = None    # int32 [1]: live 128-row blocks
+    b_nk: Optional[torch.Tensor] = None          # [E, N, K] copy of the weights (K contiguous)
+
+
+def sort_topk_ids_align_block_size(topk_ids, num_experts, num_ranks, num_tokens_per_rank, block_size, moe_stream=None):
+    return MU.sort_topk_ids_align_block_size(topk_ids, num_experts, num_ranks, num_tokens_per_rank, block_size, moe_stream)
+
+
+def create_ag_group_gemm_intra_node_context(tp_pg, A: torch.Tensor, B: torch.Tensor, full_topk_ids: torch.Tensor,
+                                            num_experts: int, max_M: int = 2 ** 14, BLOCK_M: int = 128, BLOCK_N: int = 256,
+                                            BLOCK_K: int = 64, GROUP_SIZE_M: int = 8, stages: int = 4, warps: int = 8,
+                                            ag_stream=None, group_gemm_stream=None, rank: Optional[int] = None,
+                                            num_ranks: Optional[int] = None, heap=None
+                                            ) -> MoEAllGatherGroupGEMMTensorParallelContext:
+    """``A`` is this rank's ``[M/ws, K]`` token shard, ``B`` ``[E, K, N/ws]`` the expert weights,
+    ``full_topk_ids`` ``[M, topk]`` the routing of ALL ranks' tokens."""
+    rank = dist.get_rank(tp_pg) if rank is None else rank
+    world = dist.get_world_size(tp_pg) if num_ranks is None else num_ranks
+    M, topk = full_topk_ids.shape
+    K = A.shape[1]
+    ctx = MoEAllGatherGroupGEMMTensorParallelContext(rank, world, num_experts, topk, max(max_M, M), K,
+                                                     full_topk_ids.to(torch.int32).contiguous(), group=tp_pg)
+    tpr = M // world
+    (sorted_ids, ctx.expert_ids, ctx.block_barrier_ids, ctx.rank_block_num, post_pad) = \
+        MU.sort_topk_ids_align_block_size(ctx.full_topk_ids, num_experts, world, tpr, GROUP_BLOCK_M)
+    # set-up time: read the padded length once so that the per-call gather and GEMM cover only live blocks
+    ctx.sorted_ids = sorted_ids[: int(post_pad)].contiguous()
+    ctx.num_blocks = (post_pad // GROUP_BLOCK_M).to(torch.int32)
+    ctx.b_nk = B.transpose(1, 2).contiguous()
+    if A.device.type == "cuda" and world > 1:
+        heap = heap or symm_heap(tp_pg)
+        ctx.gather_buf = heap.empty((ctx.max_M, K), A.dtype)
+        ctx.ag_ctx = CO.create_fast_allgather_context(rank, 0, world, 1, max_buffer_size=ctx.max_M * K * A.element_size(),
+                                                      heap=heap, group=tp_pg, device=A.device)
+    return ctx
+
+
+def ag_group_gemm_intra_node(a: torch.Tensor, b: torch.Tensor, ctx: MoEAllGatherGroupGEMMTensorParallelContext,
+                             phase: int = 3) -> torch.Tensor:
+    """``C[M*topk, N/ws]``: row ``t*topk+k`` = ``allgather(a)[t] @ b[full_topk_ids[t,k]]``."""
+    mpr, K = a.shape
+    M = mpr * ctx.world
+    numel = M * ctx.topk
+    if a.device.type != "cuda":
+        full = a
+        if ctx.world > 1:
+            full = torch.empty((M, K), dtype=a.dtype)
+            dist.all_gather_into_tensor(full, a.contiguous(), group=ctx.group)
+        out = torch.empty((numel, b.shape[2]), dtype=a.dtype)
+        ids = ctx.full_topk_ids.reshape(-1).long()
+        rows = full[torch.arange(numel) // ctx.topk].float()
+        for e in range(ctx.num_experts):
+            m = ids == e
+            out[m] = (rows[m] @ b[e].float()).to(a.dtype)
+        return out
+    if ctx.world > 1:
+        buf = ctx.gather_buf.view_as((M, K), a.dtype)
+        if phase != 2:
+            buf.local[ctx.rank * mpr:(ctx.rank + 1) * mpr].copy_(a)
+        CO.fast_allgather(buf, ctx.ag_ctx, mode="push", phase=phase)
+        if phase == 1:
+            return None
+        full = buf.local
+    else:
+        full = a
+    a_sorted, pos_of = gather_rows(full, ctx.sorted_ids, ctx.topk, numel, want_inverse=True)
+    b_nk = ctx.b_nk if ctx.b_nk is not None else b.transpose(1, 2).contiguous()
+    c_sorted = group_gemm(a_sorted, b_nk, ctx.expert_ids, ctx.num_blocks)
+    out, _ = gather_rows(c_sorted, pos_of, 1, c_sorted.shape[0])
+    return out
+
+
+# ---------------------------------------------------------------------------- GroupGEMM + reduce + RS
+@dataclass
+class MoEReduceRSContext:
+    rank: int
+    world: int
+    max_token_num: int
+    hidden_dim: int
+    num_experts: int
+    topk: int
+    full_topk_ids: torch.Tensor
+    full_topk_weight: torch.Tensor
+    group: object = None
+    sorted_ids: Optional[torch.Tensor] = None
+    expert_ids: Optional[torch.Tensor] = None
+    num_blocks: Optional[torch.Tensor] = None
+    rs_ctx: Optional[CO.ReduceScatter2DContext] = None
+    b_nk: Optional[torch.Tensor] = None   # [E, N, K/ws] copy of the weights, made on first use
+    _partial: Optional[torch.Tensor] = None
+
+
+def create_moe_rs_context(pg, local_rank: int, world_size: int, local_world_size: int, max_token_num: int, hidden_dim: int,
+                          num_experts: int, topk: int, input_dtype, output_dtype, device, moe_block_size: int = 128,
+                          router_logits: Optional[torch.Tensor] = None, full_topk_ids: Optional[torch.Tensor] = None,
+                          full_topk_weight: Optional[torch.Tensor] = None, heap=None) -> MoEReduceRSContext:
+    """Routing comes either from ``router_logits`` of this rank's tokens (then ``select_experts``
+    gathers everybody's) or directly as ``full_topk_ids`` / ``full_topk_weight`` ``[M, topk]``."""
+    if full_topk_ids is None:
+        full_topk_ids, full_topk_weight = select_experts(pg, world_size, topk, input_dtype, device, router_logits)
+    M = full_topk_ids.shape[0]
+    ctx = MoEReduceRSContext(local_rank, world_size, max(max_token_num, M), hidden_dim, num_experts, topk,
+                             full_topk_ids.to(torch.int32).contiguous(), full_topk_weight.float().contiguous(), group=pg)
+    # one "rank" in the aligned sort: the reduction is over all tokens, ordering by source is irrelevant
+    sorted_ids, ctx.expert_ids, _bb, _rbn, post_pad = MU.sort_topk_ids_align_block_size(
+        ctx.full_topk_ids, num_experts, 1, M, GROUP_BLOCK_M)
+    ctx.sorted_ids = sorted_ids[: int(post_pad)].contiguous()
+    ctx.num_blocks = (post_pad // GROUP_BLOCK_M).to(torch.int32)
+    ctx.rs_ctx = CO.create_reduce_scater_2d_ctx(ctx.max_token_num, hidden_dim, local_rank, world_size, dtype=output_dtype,
+                                                heap=heap, group=pg, device=device)
+    return ctx
+
+
+def moe_reduce_rs(rank: int, world_size: int, local_world_size: int, a: torch.Tensor, b: torch.Tensor,
+                  ctx: MoEReduceRSContext, dump_ir: bool = False, debug_sync: bool = False, do_initial_sync: bool = True,
+                  do_final_sync: bool = True, phase: int = 3) -> torch.Tensor:
+    """``a`` ``[M*topk, K/ws]`` (row ``t*topk+k`` = token t's input to its k-th expert), ``b``
+    ``[E, K/ws, N]``. Returns this rank's ``[M/ws, N]`` rows of
+    ``sum_ranks sum_k w[t,k] * a[t*topk+k] @ b[ids[t,k]]``."""
+    numel, _ = a.shape
+    M = numel // ctx.topk
+    N = b.shape[2]
+    if a.device.type != "cuda":
+        ids = ctx.full_topk_ids.reshape(-1).long()
+        y = torch.empty((numel, N), dtype=torch.float32)
+        for e in range(ctx.num_experts):
+            m = ids == e
+            y[m] = a[m].float() @ b[e].float()
+        part = (y.view(M, ctx.topk, N) * ctx.full_topk_weight.view(M, ctx.topk, 1)).sum(1).to(a.dtype)
+        return CO.reduce_scatter_2d_op(part, ctx.rs_ctx)
+    if phase != 2:
+        a_sorted, pos_of = gather_rows(a, ctx.sorted_ids, 1, numel, want_inverse=True)
+        if ctx.b_nk is None:
+            ctx.b_nk = b.transpose(1, 2).contiguous()
+        y_sorted = group_gemm(a_sorted, ctx.b_nk, ctx.expert_ids, ctx.num_blocks)
+        ctx._partial = topk_reduce(y_sorted, pos_of, ctx.full_topk_weight, M, ctx.topk)
+    out = CO.reduce_scatter_2d_op(ctx._partial, ctx.rs_ctx, phase=phase)
+    if debug_sync:
+        torch.cuda.synchronize()
+    return out

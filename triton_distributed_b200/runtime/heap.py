@@ -73,6 +73,23 @@ class SymmTensor:
     def ptr_array(self):
         return _lib.ptr_array(self.ptrs)
 
+    def half_ptr_arrays(self):
+        """For a symmetric object whose leading dimension is the call parity (size 2): the two ctypes
+        pointer arrays (one per parity) of every rank's half, built once and cached — slicing tensors
+        and boxing pointers on every launch costs tens of microseconds."""
+        cached = getattr(self, "_half_arrays", None)
+        if cached is None:
+            cached = tuple(_lib.ptr_array([t[h].data_ptr() for t in self.peers]) for h in range(2))
+            object.__setattr__(self, "_half_arrays", cached)
+        return cached
+
+    def cached_ptr_array(self):
+        cached = getattr(self, "_ptr_array", None)
+        if cached is None:
+            cached = _lib.ptr_array(self.ptrs)
+            object.__setattr__(self, "_ptr_array", cached)
+        return cached
+
     def symm_at(self, peer: int) -> torch.Tensor:
         return self.peers[peer]
 

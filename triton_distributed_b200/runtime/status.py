@@ -17,8 +17,17 @@ _CODES = {0: "ok", 1: "flag wait timed out", 2: "mbarrier wait timed out", 3: "b
 _KERNELS = {1: "gemm_sm100", 2: "collectives", 3: "a2a", 4: "flash_decode", 5: "primitives", 6: "moe"}
 
 
+_TIMEOUT_CACHE = [None, 0]
+
+
 def default_timeout_ns() -> int:
-    return int(float(os.environ.get("TDIST_WAIT_TIMEOUT_MS", "4000")) * 1e6)
+    """Limit of every bounded device wait, from TDIST_WAIT_TIMEOUT_MS (default 4 s); the parsed value is
+    cached per distinct setting because this sits on every launch path."""
+    raw = os.environ.get("TDIST_WAIT_TIMEOUT_MS", "4000")
+    if _TIMEOUT_CACHE[0] != raw:
+        _TIMEOUT_CACHE[0] = raw
+        _TIMEOUT_CACHE[1] = int(float(raw) * 1e6)
+    return _TIMEOUT_CACHE[1]
 
 
 class StatusBlock:
