@@ -1,0 +1,75 @@
+"""Host utilities that need no GPU: autotuner protocol, verbose comparison, data generation, trace
+merging, and the torch restatements the CPU paths of the ops rely on."""
+import pytest
+import torch
+
+import triton_distributed_b200.utils as U
+from triton_distributed_b200.ops import flash_decode as FD
+from triton_distributed_b200.ops import moe_utils as MU
+from triton_distributed_b200.utils.autotuner import ContextualAutoTuner
+from triton_distributed_b200.utils.profile import merge_traces
+
+
+def test_contextual_autotune_picks_the_fastest_config(monkeypatch, tmp_path):
+    monkeypatch.chdir(tmp_path)
+    cost = {1: 3.0, 2: 1.0, 3: 2.0}
+    seen = []
+
+    @U.tunable(configs=[{"x": 1}, {"x": 2}, {"x": 3}], key=lambda n: n)
+    def op(n, *, config):
+        seen.append(config["x"])
+        return n * config["x"]
+
+    monkeypatch.setattr(ContextualAutoTuner, "timer", staticmethod(lambda fn: (lambda r: (r, cost[seen[-1]]))(fn())))
+
+    @U.contextual_autotune(n_repeat=2, n_warmup=1)
+    def step():
+        return op(5) + op(7)
+
+    assert step() == 5 * 2 + 7 * 2
+    assert op.cache == {5: {"x": 2}, 7: {"x": 2}}
+    # each config of each key was measured warmup + repeat times, one measurement per thunk run
+    assert seen.count(1) == seen.count(3) == 2 * 3
+    assert (tmp_path / ".autotune_logs" / "rank-0.log").read_text().count("best-config-id: 1") == 2
+    n = len(seen)
+    step()
+    assert len(seen) == n + 2  # tuned: no more measuring
+
+
+def test_assert_allclose_reports_where(capsys):
+    a = torch.zeros(4, 4)
+    b = a.clone()
+    b[2, 3] = 1.0
+    U.assert_allclose(a, a)
+    with pytest.raises(AssertionError) as e:
+        U.assert_allclose(a, b, atol=1e-3)
+    assert "1 of 16" in str(e.value) and "(2, 3)" in str(e.value)
+
+
+def test_generate_data_shapes_and_ranges():
+    gen = U.generate_data([((3, 4), torch.float32, (2.0, 1.0)), ((5,), torch.int32, (3, 0))], device="cpu")
+    x, y = next(gen)
+    assert x.shape == (3, 4) and y.dtype == torch.int32
+    assert x.min() >= -1.0 and x.max() <= 3.0 and y.abs().max() <= 3
+    x2, _ = next(gen)
+    assert not torch.equal(x, x2)
+
+
+def test_merge_traces_separates_ranks():
+    t0 = {"traceEvents": [{"pid": 7, "tid": 1, "name": "k", "ph": "X"}], "schemaVersion": 1}
+    t1 = {"traceEvents": [{"pid": 7, "tid": 1, "name": "k", "ph": "X"}]}
+    merged = merge_traces([t0, t1])
+    pids = sorted(e["pid"] for e in merged["traceEvents"])
+    assert pids == [7, 100_000_007] and merged["schemaVersion"] == 1
+
+
+def test_cpu_restatements_agree_with_each_other():
+    torch.manual_seed(0)
+    ids = torch.randint(0, 6, (40, 3), dtype=torch.int32)
+    r = MU.route(ids, 6)
+    flat = ids.reshape(-1)
+    assert torch.equal(flat[(r.sorted_token.long() * 0 + torch.argsort(r.slot_of.long()))], torch.sort(flat, stable=True).values)
+    assert int(r.cumsum[-1]) == flat.numel()
+    # lse merge of one part is the identity
+    part = torch.cat([torch.randn(2, 3, 8), torch.randn(2, 3, 1)], -1)
+    torch.testing.assert_close(FD.ref_lse_merge(part.unsqueeze(0)), part[..., :-1])

@@ -1,0 +1,17 @@
+"""Host utilities: timing, rank-filtered printing, verbose comparison, data generation, topology
+probes, merged multi-rank profiling, contextual autotuning.
+
+Counterparts of the reference's ``python/triton_dist/utils.py`` (``perf_func`` :186-198, ``dist_print``
+:201-230, ``group_profile`` :282-501, ``assert_allclose`` :610-639, ``generate_data``, NVLink / NUMA
+probes) and ``python/triton_dist/autotuner.py`` (``contextual_autotune``).
+"""
+from .autotuner import contextual_autotune, tunable
+from .misc import (assert_allclose, check_p2p_native_atomic_supported, dist_print, generate_data, get_has_nvlink,
+                   get_numa_world_size, p2p_bandwidth, perf_func, perf_func_max_over_ranks)
+from .profile import get_torch_prof_ctx, group_profile
+
+__all__ = [
+    "contextual_autotune", "tunable", "assert_allclose", "check_p2p_native_atomic_supported", "dist_print",
+    "generate_data", "get_has_nvlink", "get_numa_world_size", "p2p_bandwidth", "perf_func", "perf_func_max_over_ranks",
+    "get_torch_prof_ctx", "group_profile",
+]
