@@ -204,8 +204,9 @@ def fast_allgather(symm_buffer: SymmTensor, ctx: Optional[FastAllGatherContext] 
     a.seg_bytes = nbytes // ctx.world
     a.world, a.rank = ctx.world, ctx.rank
     a.mode = _AG_MODES[mode]
-    if a.mode == _lib.AG_LL and nbytes > ctx.ll_max:
-        a.mode = _lib.AG_PUSH  # LL doubles the bytes on the wire: only worth it for small messages
+    if a.mode == _lib.AG_LL and (nbytes > ctx.ll_max or (nbytes // ctx.world) % 8):
+        # LL doubles the bytes on the wire (only worth it for small messages) and moves 8-byte words
+        a.mode = _lib.AG_PUSH
     a.phase = phase
     a.ctas_per_peer = ctx.ctas_per_peer or (1 if a.seg_bytes <= (64 << 10) else (4 if a.seg_bytes <= (4 << 20) else 16))
     if phase != 2:
