@@ -27,6 +27,11 @@ def run_workers(script: str, world: int, args=(), timeout: int = 600, env=None, 
         full_env.update(env)
     proc = subprocess.run(cmd, capture_output=True, text=True, timeout=timeout, env=full_env, cwd=ROOT)
     out = proc.stdout + "\n" + proc.stderr
+    log_dir = os.environ.get("TDIST_TEST_LOG_DIR")
+    if log_dir:
+        os.makedirs(log_dir, exist_ok=True)
+        with open(os.path.join(log_dir, f"{os.path.splitext(script)[0]}_w{world}.log"), "w") as f:
+            f.write(out)
     if proc.returncode != expect_rc:
         raise AssertionError(f"{script} exited {proc.returncode} (expected {expect_rc}):\n{out[-6000:]}")
     result = None

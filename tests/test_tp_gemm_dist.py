@@ -16,6 +16,6 @@ def test_cpu_gloo_world2_plumbing():
 def test_fused_ops_on_gpus(world):
     if torch.cuda.device_count() < world:
         pytest.skip(f"needs {world} GPUs")
-    res, out = run_workers("tp_gemm_worker.py", world, env={"NCCL_NVLS_ENABLE": "0"})
+    res, out = run_workers("tp_gemm_worker.py", world, env={"NCCL_NVLS_ENABLE": "0", "TDIST_WAIT_TIMEOUT_MS": "20000"})
     assert res["ranks_ok"] == world, out[-3000:]
     assert res["ag_max_err"] < 0.1 and res["rs_max_err"] < 0.1

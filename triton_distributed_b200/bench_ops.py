@@ -233,9 +233,50 @@ def _bench_allgather(args, world, rank, group, dev, dtype, pk, row):
         row.update({"nccl_us": round(base, 2)})
 
 
+def _run_suite(args, world, rank, group, dev, dtype, pk):
+    """Every headline configuration in one process (one NCCL / heap bring-up): the two tensor-parallel
+    GEMMs on the m8192 n49152 k12288 problem, MoE dispatch+combine (128 tokens, hidden 7168, 256 experts,
+    top-8), sequence-parallel decode (32/8 heads, D 128, batch 1 and 8, 32K / 128K / 1M keys in total),
+    and the all-gather modes at 64 KB and 16 MB."""
+    import copy
+    global PRESLEEP_CYCLES
+
+    def emit(row):
+        if rank == 0:
+            print(json.dumps(row), flush=True)
+
+    def run(op, fn, **over):
+        a = copy.copy(args)
+        a.op = op
+        for k, v in over.items():
+            setattr(a, k, v)
+        row = {"op": op, "world": world, "dtype": a.dtype, "peaks": pk["source"]}
+        try:
+            fn(a, world, rank, group, dev, dtype, pk, row)
+        except Exception as e:  # noqa: BLE001 - keep the rest of the suite alive
+            row["error"] = repr(e)[:300]
+        emit(row)
+        torch.cuda.synchronize()
+        torch.cuda.empty_cache()
+
+    PRESLEEP_CYCLES = 0
+    run("ag_gemm", _bench_gemm_family, m=8192, n=49152, k=12288)
+    run("gemm_rs", _bench_gemm_family, m=8192, n=12288, k=49152)
+    PRESLEEP_CYCLES = int(30 * 1.9e6)
+    if world > 1 or True:
+        run("a2a", _bench_a2a, tokens=128, hidden=7168, experts=256, topk=8, iters=50)
+    for batch in (1, 8):
+        for kv in (32768, 131072, 1048576):
+            run("sp_decode", _bench_decode, batch=batch, kv=kv, hq=32, hkv=8, head_dim=128, iters=30)
+    if world > 1:
+        for mode in ("pull", "push2d", "push2d_ll"):
+            for nbytes in (65536, 16 << 20):
+                run("allgather", _bench_allgather, mode=mode, bytes=nbytes, iters=30)
+
+
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser()
-    ap.add_argument("--op", required=True, choices=["gemm", "ag_gemm", "gemm_rs", "decode", "sp_decode", "a2a", "allgather"])
+    ap.add_argument("--op", required=True, choices=["gemm", "ag_gemm", "gemm_rs", "decode", "sp_decode", "a2a", "allgather", "suite"])
     ap.add_argument("--m", type=int, default=8192)
     ap.add_argument("--n", type=int, default=6144)
     ap.add_argument("--k", type=int, default=12288)
@@ -273,6 +314,12 @@ def main(argv=None) -> int:
     dtype = torch.bfloat16 if args.dtype == "bf16" else torch.float16
     pk = peaks()
     row = {"op": args.op, "world": world, "dtype": args.dtype, "peaks": pk["source"]}
+    if args.op == "suite":
+        _run_suite(args, world, rank, group, dev, dtype, pk)
+        check_status()
+        if dist.is_initialized():
+            finalize_distributed()
+        return 0
     if args.op in ("gemm", "ag_gemm", "gemm_rs"):
         _bench_gemm_family(args, world, rank, group, dev, dtype, pk, row)
     elif args.op in ("decode", "sp_decode"):
