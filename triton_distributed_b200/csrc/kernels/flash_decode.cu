@@ -24,6 +24,7 @@
 #include "../device/ll.cuh"
 #include "../device/signal.cuh"
 #include "../include/tdist.h"
+#include "../include/tdist_noalloc.h"
 #include "../runtime/host_common.h"
 
 namespace tdist {
@@ -430,7 +431,7 @@ static int launch_decode(const DecodeParams& p, cudaStream_t stream) {
     return 0;
 }
 
-extern "C" int tdist_flash_decode(const TdistDecodeArgs* a) {
+static int flash_decode_impl(const TdistDecodeArgs* a) {
     if (a->B < 1 || a->Hq < 1 || a->Hkv < 1 || a->Hq % a->Hkv) return fail(TDIST_EINVAL, "decode: bad head counts");
     if (a->Hq / a->Hkv > 16) return fail(TDIST_ELIMIT, "decode: at most 16 query heads per kv head");
     if (a->splits < 1 || a->splits > 256) return fail(TDIST_EINVAL, "decode: splits must be in [1, 256]");
@@ -490,6 +491,47 @@ extern "C" int tdist_flash_decode(const TdistDecodeArgs* a) {
     }
 #undef TDIST_DECODE_CASE
     return fail(TDIST_EINVAL, "decode: dtype must be bf16 or fp16");
+}
+
+extern "C" int tdist_flash_decode(const TdistDecodeArgs* a) { return flash_decode_impl(a); }
+
+// ---------------------------------------------------------------------------------------------
+// Allocation-free variant (contract in ../include/tdist_noalloc.h): the split-merge workspace and
+// the arrival counters live in this array instead of caller-provided buffers.
+// Layout: [0, counters_bytes) uint32 counters, then fp32 partials. In host code the name below is
+// only a handle for cudaGetSymbolAddress, never a device address.
+static __device__ __align__(256) unsigned char g_decode_static_scratch[TDIST_DECODE_STATIC_SCRATCH_BYTES];
+
+extern "C" int tdist_flash_decode_static(const TdistDecodeArgs* a) {
+    if (a == nullptr) return fail(TDIST_EINVAL, "decode(static): null args");
+    if (a->mode != 0 && a->mode != 1)
+        return fail(TDIST_EINVAL, "decode(static): only modes 0 and 1 (the sequence-parallel mode needs caller-owned symmetric memory)");
+    if (a->B < 1 || a->Hq < 1 || a->Hkv < 1 || a->splits < 1 || a->head_dim < 1)
+        return fail(TDIST_EINVAL, "decode(static): bad sizes");
+    const size_t counters_bytes = (static_cast<size_t>(a->B) * a->Hkv * sizeof(unsigned) + 255) / 256 * 256;
+    const size_t partial_bytes = static_cast<size_t>(a->B) * a->Hq * a->splits * (a->head_dim + 2) * sizeof(float);
+    if (counters_bytes + partial_bytes > TDIST_DECODE_STATIC_SCRATCH_BYTES)
+        return fail(TDIST_ELIMIT, "decode(static): B*Hq*splits*(head_dim+2)*4 + counters = " +
+                                      std::to_string(counters_bytes + partial_bytes) + " bytes exceeds the built-in scratch of " +
+                                      std::to_string(TDIST_DECODE_STATIC_SCRATCH_BYTES) + " bytes; use fewer splits or tdist_flash_decode");
+    // once per device, with that device current: resolve the array's device address
+    static unsigned char* scratch_of_device[64] = {};
+    int dev = 0;
+    TDIST_CUDA_OK(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= 64) return fail(TDIST_EINVAL, "decode(static): device ordinal out of range");
+    if (scratch_of_device[dev] == nullptr) {
+        unsigned char* ptr = nullptr;
+        TDIST_CUDA_OK(cudaGetSymbolAddress(reinterpret_cast<void**>(&ptr), g_decode_static_scratch));
+        if (ptr == nullptr) return fail(TDIST_EDRIVER, "decode(static): cudaGetSymbolAddress returned a null address");
+        scratch_of_device[dev] = ptr;
+    }
+    unsigned char* base = scratch_of_device[dev];
+    // the counters must start at zero whatever the previous call left behind
+    TDIST_CUDA_OK(cudaMemsetAsync(base, 0, counters_bytes, static_cast<cudaStream_t>(a->stream)));
+    TdistDecodeArgs b = *a;
+    b.counters = base;
+    b.partial = base + counters_bytes;
+    return flash_decode_impl(&b);
 }
 
 extern "C" int tdist_lse_combine(const void* parts, int ranks, int heads, int head_dim, void* out, int dtype, void* stream) {
