@@ -52,44 +52,62 @@ struct A2AParams {
     WaitCtx wctx;
 };
 
+// Row copy by one warp, four 16-byte loads in flight per lane (a row is a few KB: latency, not
+// bandwidth, decides how long one warp takes).
 __device__ __forceinline__ void copy_row_warp(char* dst, const char* src, int bytes, int lane) {
-    for (int i = lane * 16; i < bytes; i += 32 * 16) st_v4(dst + i, ld_nc_v4(src + i));
+    int i = lane * 16;
+    for (; i + 3 * 512 < bytes; i += 4 * 512) {
+        const uint4 a = ld_nc_v4(src + i), b = ld_nc_v4(src + i + 512), c = ld_nc_v4(src + i + 1024), d = ld_nc_v4(src + i + 1536);
+        st_v4(dst + i, a);
+        st_v4(dst + i + 512, b);
+        st_v4(dst + i + 1024, c);
+        st_v4(dst + i + 1536, d);
+    }
+    for (; i < bytes; i += 512) st_v4(dst + i, ld_nc_v4(src + i));
 }
 
 // bf16 row -> fp8 e4m3 row with one fp32 scale per 128 values (scale = amax / 448).
-// A half-warp (16 lanes x 8 values) owns a group of 128.
+// A half-warp (16 lanes x 8 values) owns a group of 128; four groups per half-warp are loaded
+// before any is processed, so that one row costs a handful of memory round trips, not dozens.
 __device__ __forceinline__ void quant_row_warp(char* dst, float* dst_scale, const char* src, int hidden, int lane) {
     const int groups = hidden / 128;
-    for (int g0 = 0; g0 < groups; g0 += 2) {
-        const int g = g0 + (lane >> 4);
-        const bool active = g < groups;
-        float v[8];
-        float amax = 0.f;
-        if (active) {
-            const uint4 q = ld_nc_v4(src + (static_cast<size_t>(g) * 128 + (lane & 15) * 8) * 2);
-            const uint32_t w[4] = {q.x, q.y, q.z, q.w};
+    const int half = lane >> 4, sub = lane & 15;
+    for (int g0 = 0; g0 < groups; g0 += 8) {
+        uint4 q[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            const int g = g0 + 2 * u + half;
+            q[u] = g < groups ? ld_nc_v4(src + (static_cast<size_t>(g) * 128 + sub * 8) * 2) : make_uint4(0, 0, 0, 0);
+        }
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            const int g = g0 + 2 * u + half;
+            const bool active = g < groups;
+            const uint32_t w[4] = {q[u].x, q[u].y, q[u].z, q[u].w};
+            float v[8];
+            float amax = 0.f;
 #pragma unroll
             for (int i = 0; i < 4; ++i) {
                 v[2 * i] = __uint_as_float(w[i] << 16);
                 v[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
                 amax = fmaxf(amax, fmaxf(fabsf(v[2 * i]), fabsf(v[2 * i + 1])));
             }
-        }
 #pragma unroll
-        for (int o = 8; o >= 1; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
-        if (active) {
-            const float scale = fmaxf(amax, 1e-10f) / 448.f;
-            const float inv = 1.f / scale;
-            uint32_t lo = 0, hi = 0;
+            for (int o = 8; o >= 1; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+            if (active) {
+                const float scale = fmaxf(amax, 1e-10f) / 448.f;
+                const float inv = 1.f / scale;
+                uint32_t lo = 0, hi = 0;
 #pragma unroll
-            for (int i = 0; i < 4; ++i) {
-                const uint32_t b0 = __nv_cvt_float_to_fp8(v[i] * inv, __NV_SATFINITE, __NV_E4M3);
-                const uint32_t b1 = __nv_cvt_float_to_fp8(v[4 + i] * inv, __NV_SATFINITE, __NV_E4M3);
-                lo |= b0 << (8 * i);
-                hi |= b1 << (8 * i);
+                for (int i = 0; i < 4; ++i) {
+                    const uint32_t b0 = __nv_cvt_float_to_fp8(v[i] * inv, __NV_SATFINITE, __NV_E4M3);
+                    const uint32_t b1 = __nv_cvt_float_to_fp8(v[4 + i] * inv, __NV_SATFINITE, __NV_E4M3);
+                    lo |= b0 << (8 * i);
+                    hi |= b1 << (8 * i);
+                }
+                *reinterpret_cast<uint2*>(dst + static_cast<size_t>(g) * 128 + sub * 8) = make_uint2(lo, hi);
+                if (sub == 0) dst_scale[g] = scale;
             }
-            *reinterpret_cast<uint2*>(dst + static_cast<size_t>(g) * 128 + (lane & 15) * 8) = make_uint2(lo, hi);
-            if ((lane & 15) == 0) dst_scale[g] = scale;
         }
     }
 }
@@ -160,30 +178,44 @@ __global__ void __launch_bounds__(kA2AThreads) a2a_kernel(const A2AParams p) {
     const char* rlocal = p.recv_peer[p.rank];
     const int gw = static_cast<int>(blockIdx.x) * warps + warp;
     const int nw = static_cast<int>(gridDim.x) * warps;
-    for (int t = gw; t < p.ntok; t += nw) {
-        for (int c0 = lane * 8; c0 < p.hidden; c0 += 256) {
-            float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-            for (int k = 0; k < p.topk; ++k) {
-                const int pair = t * p.topk + k;
-                const int e = p.topk_ids[pair];
-                const int er = e / p.epr;
-                const int row = er * p.max_m + (p.slot_of[pair] - p.cumsum[er * p.epr]);
-                const float w = p.topk_w[pair];
-                const uint4 q = ld_nc_v4(rlocal + static_cast<size_t>(row) * p.row_bytes_out + static_cast<size_t>(c0) * 2);
-                const uint32_t u[4] = {q.x, q.y, q.z, q.w};
+    const int chunks = (p.hidden + 255) / 256;  // a warp covers 256 columns (8 per lane) per item
+    for (int item = gw; item < p.ntok * chunks; item += nw) {
+        const int t = item / chunks;
+        const int c0 = (item - t * chunks) * 256 + lane * 8;
+        if (c0 >= p.hidden) continue;
+        float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+        for (int k0 = 0; k0 < p.topk; k0 += 8) {
+            uint4 q[8];
+            float w[8];
 #pragma unroll
-                for (int i = 0; i < 4; ++i) {
-                    acc[2 * i] += w * __uint_as_float(u[i] << 16);
-                    acc[2 * i + 1] += w * __uint_as_float(u[i] & 0xffff0000u);
+            for (int j = 0; j < 8; ++j) {
+                const int k = k0 + j;
+                w[j] = 0.f;
+                q[j] = make_uint4(0, 0, 0, 0);
+                if (k < p.topk) {
+                    const int pair = t * p.topk + k;
+                    const int er = p.topk_ids[pair] / p.epr;
+                    const int row = er * p.max_m + (p.slot_of[pair] - p.cumsum[er * p.epr]);
+                    w[j] = p.topk_w[pair];
+                    q[j] = ld_nc_v4(rlocal + static_cast<size_t>(row) * p.row_bytes_out + static_cast<size_t>(c0) * 2);
                 }
             }
-            uint4 o;
-            o.x = pack_bf16x2(acc[0], acc[1]);
-            o.y = pack_bf16x2(acc[2], acc[3]);
-            o.z = pack_bf16x2(acc[4], acc[5]);
-            o.w = pack_bf16x2(acc[6], acc[7]);
-            st_v4(reinterpret_cast<char*>(p.out) + (static_cast<size_t>(t) * p.hidden + c0) * 2, o);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                const uint32_t u[4] = {q[j].x, q[j].y, q[j].z, q[j].w};
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    acc[2 * i] += w[j] * __uint_as_float(u[i] << 16);
+                    acc[2 * i + 1] += w[j] * __uint_as_float(u[i] & 0xffff0000u);
+                }
+            }
         }
+        uint4 o;
+        o.x = pack_bf16x2(acc[0], acc[1]);
+        o.y = pack_bf16x2(acc[2], acc[3]);
+        o.z = pack_bf16x2(acc[4], acc[5]);
+        o.w = pack_bf16x2(acc[6], acc[7]);
+        st_v4(reinterpret_cast<char*>(p.out) + (static_cast<size_t>(t) * p.hidden + c0) * 2, o);
     }
 }
 
@@ -262,7 +294,7 @@ extern "C" int tdist_a2a(const TdistA2AArgs* a) {
     p.quant = a->quant;
     p.reduce = a->reduce;
     p.phase = a->phase ? a->phase : 3;
-    p.ctas_per_peer = a->ctas_per_peer > 0 ? a->ctas_per_peer : 8;
+    p.ctas_per_peer = a->ctas_per_peer > 0 ? a->ctas_per_peer : 16;
     if (p.ctas_per_peer > 16) p.ctas_per_peer = 16;
     p.epoch = a->epoch;
     p.wctx.status = static_cast<Status*>(a->status);

@@ -106,11 +106,15 @@ __device__ __forceinline__ uint32_t tile_off(int row, int chunk) {
     return static_cast<uint32_t>(row * (D * 2) + ((chunk ^ (row & 7)) << 4));
 }
 
+// Ring depth: D <= 64 -> 4 stages (68 KB, 3 CTAs/SM); D = 128 -> 3 stages (100 KB, 2 CTAs/SM);
+// D = 256 -> 2 stages (136 KB, 1 CTA/SM).
+__host__ __device__ constexpr int decode_stages(int d) { return d <= 64 ? 4 : (d <= 128 ? 3 : 2); }
+
 template <typename T, int D>
-__global__ void __launch_bounds__(kDecodeThreads) flash_decode_kernel(const DecodeParams p) {
+__global__ void __launch_bounds__(kDecodeThreads, (D <= 128 ? 2 : 1)) flash_decode_kernel(const DecodeParams p) {
     constexpr int CH = D / 8;                      // 16-byte chunks per row
     constexpr int TILE = kTok * D * 2;             // bytes of one K or V block
-    constexpr int NS = (D <= 128) ? 4 : 2;         // cp.async ring depth per warp
+    constexpr int NS = decode_stages(D);           // cp.async ring depth per warp
     constexpr int KS = D / 16;                     // k-steps of QK^T
     constexpr int NT = D / 8;                      // n-tiles of PV
     extern __shared__ __align__(128) uint8_t smem[];
@@ -148,19 +152,23 @@ __global__ void __launch_bounds__(kDecodeThreads) flash_decode_kernel(const Deco
     const int my_blocks = (blk1 - blk0 - warp + kDecodeWarps - 1) / kDecodeWarps;  // may be <= 0
 
     uint8_t* my_ring = ring + static_cast<size_t>(warp) * NS * 2 * TILE;
-    auto issue = [&](int i) {  // i-th block of this warp -> ring slot i % NS
-        const int blk = blk0 + warp + i * kDecodeWarps;
-        uint8_t* ks = my_ring + static_cast<size_t>(i % NS) * 2 * TILE;
-        uint8_t* vs = ks + TILE;
-        // lane r < 16 resolves token r of the block through the page table
+    // Page-table lookup for block i of this warp: lane r < 16 resolves token r. It is issued one
+    // block ahead of the copies that need it, so its latency hides behind a block's worth of math
+    // instead of stalling the (in-order) warp right before every batch of cp.async.
+    auto lookup = [&](int i) -> long long {
         long long base = -1;
-        if (lane < kTok) {
-            const int t = blk * kTok + lane;
+        if (i < my_blocks && lane < kTok) {
+            const int t = (blk0 + warp + i * kDecodeWarps) * kTok + lane;
             if (t < kv_len) {
                 const int page = table[t / p.page_size];
                 base = static_cast<long long>(page) * p.stride_block + static_cast<long long>(t % p.page_size) * p.stride_token;
             }
         }
+        return base;
+    };
+    auto issue = [&](int i, long long base) {  // i-th block of this warp -> ring slot i % NS
+        uint8_t* ks = my_ring + static_cast<size_t>(i % NS) * 2 * TILE;
+        uint8_t* vs = ks + TILE;
 #pragma unroll
         for (int j = 0; j < (kTok * CH) / 32; ++j) {
             const int c = j * 32 + lane;
@@ -179,12 +187,19 @@ __global__ void __launch_bounds__(kDecodeThreads) flash_decode_kernel(const Deco
     float m_run[2] = {-CUDART_INF_F, -CUDART_INF_F}, l_run[2] = {0.f, 0.f};
     const float sl2 = p.scale * 1.4426950408889634f;
 
+    long long base_next = lookup(0);
     for (int i = 0; i < NS - 1; ++i) {
-        if (i < my_blocks) issue(i);
+        const long long base = base_next;
+        base_next = lookup(i + 1);
+        if (i < my_blocks) issue(i, base);
         cp_async_commit();
     }
     for (int i = 0; i < my_blocks; ++i) {
-        if (i + NS - 1 < my_blocks) issue(i + NS - 1);
+        if (i + NS - 1 < my_blocks) {
+            const long long base = base_next;
+            base_next = lookup(i + NS);
+            issue(i + NS - 1, base);
+        }
         cp_async_commit();
         cp_async_wait<NS - 1>();
         __syncwarp();
@@ -416,7 +431,7 @@ using tdist_host::fail;
 
 template <typename T, int D>
 static int launch_decode(const DecodeParams& p, cudaStream_t stream) {
-    constexpr int NS = (D <= 128) ? 4 : 2;
+    constexpr int NS = decode_stages(D);
     constexpr int smem = kTok * D * 2 + kDecodeWarps * NS * 2 * kTok * D * 2;
     static_assert(smem >= kDecodeWarps * 16 * D * 4, "the warp-merge buffer reuses the ring");
     static bool done[64] = {};

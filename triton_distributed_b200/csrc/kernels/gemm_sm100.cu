@@ -597,7 +597,28 @@ static GridPlan plan_grid(const TdistGemmArgs* a) {
     if (sms < g.ctas_per_tile) sms = g.ctas_per_tile;
     g.num_comm = 0;
     if (a->mode == TDIST_GEMM_AG && a->world > 1) {
-        g.num_comm = a->num_comm_sms > 0 ? a->num_comm_sms : 8;
+        g.num_comm = a->num_comm_sms;
+        if (g.num_comm <= 0) {
+            // Enough pushers to deliver the shard within about half of the GEMM's run time (one pusher CTA
+            // sustains ~40 GB/s over NVLink), then nudged so that the remaining CTAs need the fewest waves.
+            const double push_bytes = static_cast<double>(a->world - 1) * a->m_per_rank * a->k * 2.0;
+            const double gemm_s = 2.0 * a->world * a->m_per_rank * static_cast<double>(a->n) * a->k / 1.4e15;
+            int need = static_cast<int>(push_bytes / (gemm_s * 0.5 > 1e-6 ? gemm_s * 0.5 : 1e-6) / 40e9) + 1;
+            need = (need + 1) & ~1;
+            if (need < 2) need = 2;
+            if (need > 18) need = 18;
+            int best = need, best_waves = 1 << 30;
+            for (int c = (need - 2 >= 2 ? need - 2 : 2); c <= need + 8; c += 2) {
+                const int units = (sms - c) / g.ctas_per_tile;
+                if (units < 1) break;
+                const int waves = (g.num_tiles + units - 1) / units;
+                if (waves < best_waves) {
+                    best_waves = waves;
+                    best = c;
+                }
+            }
+            g.num_comm = best;
+        }
         if (g.ctas_per_tile == 2) g.num_comm = (g.num_comm + 1) & ~1;
         if (g.num_comm > sms - g.ctas_per_tile) g.num_comm = sms - g.ctas_per_tile;
         if (g.num_comm < g.ctas_per_tile) g.num_comm = g.ctas_per_tile;

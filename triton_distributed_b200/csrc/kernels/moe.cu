@@ -74,15 +74,27 @@ __global__ void __launch_bounds__(kMoeThreads) moe_route_kernel(const int* ids, 
     int* running = sm + E;
     int* cnt = sm + 2 * E;
     histogram(ids, n, E, hist);
-    if (threadIdx.x == 0) {
-        int acc = 0;
-        for (int e = 0; e < E; ++e) {
+    if (threadIdx.x < 32) {
+        // exclusive scan of the histogram by one warp: a contiguous chunk of experts per lane
+        const int lane = threadIdx.x;
+        const int per = (E + 31) / 32;
+        const int e0 = min(E, lane * per), e1 = min(E, e0 + per);
+        int local = 0;
+        for (int e = e0; e < e1; ++e) local += hist[e];
+        int incl = local;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            const int up = __shfl_up_sync(0xffffffffu, incl, o);
+            if (lane >= o) incl += up;
+        }
+        int acc = incl - local;
+        for (int e = e0; e < e1; ++e) {
             running[e] = acc;
             cumsum[e] = acc;
             splits[e] = hist[e];
             acc += hist[e];
         }
-        cumsum[E] = acc;
+        if (lane == 31) cumsum[E] = incl;
     }
     __syncthreads();
     stable_positions(ids, n, E, running, cnt, [&](int i, int pos) {

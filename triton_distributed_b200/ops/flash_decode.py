@@ -74,9 +74,11 @@ def ref_lse_merge(parts: torch.Tensor) -> torch.Tensor:
     return (o * w.unsqueeze(-1)).sum(0) / den.unsqueeze(-1)
 
 
-def default_splits(B: int, Hkv: int, max_kv: int, device) -> int:
-    """Enough (batch, kv head, split) CTAs for one wave of the machine, but at least 64 tokens each."""
-    want = max(1, _sm_count(device) // max(1, B * Hkv))
+def default_splits(B: int, Hkv: int, max_kv: int, device, head_dim: int = 128) -> int:
+    """Enough (batch, kv head, split) CTAs for one wave of the machine (two CTAs fit an SM up to
+    head_dim 128), but at least 64 tokens each."""
+    per_sm = 2 if head_dim <= 128 else 1
+    want = max(1, per_sm * _sm_count(device) // max(1, B * Hkv))
     cap = max(1, (max_kv + 63) // 64)
     return max(1, min(want, cap, 256))
 
@@ -111,7 +113,7 @@ def _launch(q, k_cache, v_cache, kv_lens, block_table, scale, soft_cap, out, mod
     if splits <= 0:
         if max_kv is None:
             max_kv = page * block_table.shape[1]
-        splits = default_splits(B, Hkv, max_kv, q.device)
+        splits = default_splits(B, Hkv, max_kv, q.device, D)
     partial, counters = workspace if workspace is not None else _Workspace.get(q.device, B, Hq, Hkv, D, splits)
     a = _lib.DecodeArgs()
     a.q, a.k_cache, a.v_cache = q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr()

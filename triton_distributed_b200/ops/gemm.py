@@ -123,7 +123,7 @@ class AllGatherGEMMTensorParallelContext:
     workspace: Optional[SymmTensor] = None
     flags: Optional[SymmTensor] = None
     epoch: int = 0
-    num_comm_sms: int = 8
+    num_comm_sms: int = 0   # 0 = sized per call from the bytes to push and the expected GEMM time
     num_sms: int = 0
     for_correctness: bool = False
     debug_delay_ns: int = 0
@@ -135,7 +135,7 @@ def create_ag_gemm_intra_node_context(tensor_A: torch.Tensor, tensor_B: torch.Te
                                       BLOCK_N: int = 256, BLOCK_K: int = 64, stages: int = 4,
                                       for_correctness: bool = False, ag_stream=None, gemm_stream=None,
                                       serial: bool = False, autotune: bool = False, heap=None, group=None,
-                                      num_comm_sms: int = 8) -> AllGatherGEMMTensorParallelContext:
+                                      num_comm_sms: int = 0) -> AllGatherGEMMTensorParallelContext:
     """Allocate the symmetric state for ``ag_gemm_intra_node``. ``max_M`` is the largest gathered
     row count. Tile shape, stage and stream arguments are accepted for source compatibility; the
     sm_100a kernel has one tuned configuration and needs no side streams."""
@@ -177,7 +177,7 @@ def ag_gemm_intra_node(a: torch.Tensor, b: torch.Tensor, ctx: Optional[AllGather
     ctx.epoch += 1
     g.epoch = ctx.epoch
     g.num_sms = ctx.num_sms
-    g.num_comm_sms = ctx.num_comm_sms
+    g.num_comm_sms = ctx.num_comm_sms  # 0 = the launcher sizes it from the bytes to push and the GEMM's length
     g.debug_delay_ns = ctx.debug_delay_ns
     if ctx.trace is not None:
         g.trace = ctx.trace.data_ptr()
