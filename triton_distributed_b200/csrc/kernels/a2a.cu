@@ -52,62 +52,68 @@ struct A2AParams {
     WaitCtx wctx;
 };
 
-// Row copy by one warp, four 16-byte loads in flight per lane (a row is a few KB: latency, not
-// bandwidth, decides how long one warp takes).
-__device__ __forceinline__ void copy_row_warp(char* dst, const char* src, int bytes, int lane) {
-    int i = lane * 16;
-    for (; i + 3 * 512 < bytes; i += 4 * 512) {
-        const uint4 a = ld_nc_v4(src + i), b = ld_nc_v4(src + i + 512), c = ld_nc_v4(src + i + 1024), d = ld_nc_v4(src + i + 1536);
-        st_v4(dst + i, a);
-        st_v4(dst + i + 512, b);
-        st_v4(dst + i + 1024, c);
-        st_v4(dst + i + 1536, d);
+// Work is dealt to warps in (row, segment) items so that a 128-row message still occupies every
+// warp of the grid and each item costs about one memory round trip.
+constexpr int kSegBytes = 2048;    // plain copy: 4 x 16 bytes per lane in flight
+constexpr int kSegGroups = 8;      // quantising copy: 8 groups of 128 values (1024 elements)
+
+__device__ __forceinline__ void copy_seg_warp(char* dst, const char* src, int bytes, int seg, int lane) {
+    const int b0 = seg * kSegBytes;
+    const int b1 = min(bytes, b0 + kSegBytes);
+    uint4 q[4];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+        const int i = b0 + u * 512 + lane * 16;
+        if (i < b1) q[u] = ld_nc_v4(src + i);
     }
-    for (; i < bytes; i += 512) st_v4(dst + i, ld_nc_v4(src + i));
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+        const int i = b0 + u * 512 + lane * 16;
+        if (i < b1) st_v4(dst + i, q[u]);
+    }
 }
 
-// bf16 row -> fp8 e4m3 row with one fp32 scale per 128 values (scale = amax / 448).
-// A half-warp (16 lanes x 8 values) owns a group of 128; four groups per half-warp are loaded
-// before any is processed, so that one row costs a handful of memory round trips, not dozens.
-__device__ __forceinline__ void quant_row_warp(char* dst, float* dst_scale, const char* src, int hidden, int lane) {
+// bf16 -> fp8 e4m3 with one fp32 scale per 128 values (scale = amax / 448) for groups
+// [8*seg, 8*seg + 8) of one row. A half-warp (16 lanes x 8 values) owns a group; the four groups of
+// each half-warp are loaded before any is processed.
+__device__ __forceinline__ void quant_seg_warp(char* dst, float* dst_scale, const char* src, int hidden, int seg, int lane) {
     const int groups = hidden / 128;
     const int half = lane >> 4, sub = lane & 15;
-    for (int g0 = 0; g0 < groups; g0 += 8) {
-        uint4 q[4];
+    const int g0 = seg * kSegGroups;
+    uint4 q[4];
 #pragma unroll
-        for (int u = 0; u < 4; ++u) {
-            const int g = g0 + 2 * u + half;
-            q[u] = g < groups ? ld_nc_v4(src + (static_cast<size_t>(g) * 128 + sub * 8) * 2) : make_uint4(0, 0, 0, 0);
+    for (int u = 0; u < 4; ++u) {
+        const int g = g0 + 2 * u + half;
+        q[u] = g < groups ? ld_nc_v4(src + (static_cast<size_t>(g) * 128 + sub * 8) * 2) : make_uint4(0, 0, 0, 0);
+    }
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+        const int g = g0 + 2 * u + half;
+        const bool active = g < groups;
+        const uint32_t w[4] = {q[u].x, q[u].y, q[u].z, q[u].w};
+        float v[8];
+        float amax = 0.f;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            v[2 * i] = __uint_as_float(w[i] << 16);
+            v[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
+            amax = fmaxf(amax, fmaxf(fabsf(v[2 * i]), fabsf(v[2 * i + 1])));
         }
 #pragma unroll
-        for (int u = 0; u < 4; ++u) {
-            const int g = g0 + 2 * u + half;
-            const bool active = g < groups;
-            const uint32_t w[4] = {q[u].x, q[u].y, q[u].z, q[u].w};
-            float v[8];
-            float amax = 0.f;
+        for (int o = 8; o >= 1; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+        if (active) {
+            const float scale = fmaxf(amax, 1e-10f) / 448.f;
+            const float inv = 1.f / scale;
+            uint32_t lo = 0, hi = 0;
 #pragma unroll
             for (int i = 0; i < 4; ++i) {
-                v[2 * i] = __uint_as_float(w[i] << 16);
-                v[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
-                amax = fmaxf(amax, fmaxf(fabsf(v[2 * i]), fabsf(v[2 * i + 1])));
+                const uint32_t b0 = __nv_cvt_float_to_fp8(v[i] * inv, __NV_SATFINITE, __NV_E4M3);
+                const uint32_t b1 = __nv_cvt_float_to_fp8(v[4 + i] * inv, __NV_SATFINITE, __NV_E4M3);
+                lo |= b0 << (8 * i);
+                hi |= b1 << (8 * i);
             }
-#pragma unroll
-            for (int o = 8; o >= 1; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
-            if (active) {
-                const float scale = fmaxf(amax, 1e-10f) / 448.f;
-                const float inv = 1.f / scale;
-                uint32_t lo = 0, hi = 0;
-#pragma unroll
-                for (int i = 0; i < 4; ++i) {
-                    const uint32_t b0 = __nv_cvt_float_to_fp8(v[i] * inv, __NV_SATFINITE, __NV_E4M3);
-                    const uint32_t b1 = __nv_cvt_float_to_fp8(v[4 + i] * inv, __NV_SATFINITE, __NV_E4M3);
-                    lo |= b0 << (8 * i);
-                    hi |= b1 << (8 * i);
-                }
-                *reinterpret_cast<uint2*>(dst + static_cast<size_t>(g) * 128 + sub * 8) = make_uint2(lo, hi);
-                if (sub == 0) dst_scale[g] = scale;
-            }
+            *reinterpret_cast<uint2*>(dst + static_cast<size_t>(g) * 128 + sub * 8) = make_uint2(lo, hi);
+            if (sub == 0) dst_scale[g] = scale;
         }
     }
 }
@@ -133,16 +139,18 @@ __global__ void __launch_bounds__(kA2AThreads) a2a_kernel(const A2AParams p) {
         count = min(count, p.max_m);
         char* rbase = p.recv_peer[dest] + static_cast<size_t>(p.rank) * p.max_m * p.row_bytes_out;
         float* sbase = p.scale_peer[dest] ? p.scale_peer[dest] + static_cast<size_t>(p.rank) * p.max_m * p.scale_cols : nullptr;
-        for (int i = slice * warps + warp; i < count; i += p.ctas_per_peer * warps) {
+        const int segs = p.quant ? (p.hidden / 128 + kSegGroups - 1) / kSegGroups : (p.row_bytes_in + kSegBytes - 1) / kSegBytes;
+        for (int item = slice * warps + warp; item < count * segs; item += p.ctas_per_peer * warps) {
+            const int i = item / segs, seg = item - i * segs;
             int srow = first + i;
             if (p.src_index != nullptr) srow = p.src_index[srow];
             const char* src = p.send + static_cast<size_t>(srow) * p.row_bytes_in;
             char* dst = rbase + static_cast<size_t>(i) * p.row_bytes_out;
             if (p.quant) {
-                quant_row_warp(dst, sbase + static_cast<size_t>(i) * p.scale_cols, src, p.hidden, lane);
+                quant_seg_warp(dst, sbase + static_cast<size_t>(i) * p.scale_cols, src, p.hidden, seg, lane);
             } else {
-                copy_row_warp(dst, src, p.row_bytes_in, lane);
-                if (sbase != nullptr && p.send_scale != nullptr)
+                copy_seg_warp(dst, src, p.row_bytes_in, seg, lane);
+                if (seg == 0 && sbase != nullptr && p.send_scale != nullptr)
                     for (int c = lane; c < p.scale_cols; c += 32)
                         sbase[static_cast<size_t>(i) * p.scale_cols + c] = p.send_scale[static_cast<size_t>(srow) * p.scale_cols + c];
             }
@@ -294,8 +302,10 @@ extern "C" int tdist_a2a(const TdistA2AArgs* a) {
     p.quant = a->quant;
     p.reduce = a->reduce;
     p.phase = a->phase ? a->phase : 3;
-    p.ctas_per_peer = a->ctas_per_peer > 0 ? a->ctas_per_peer : 16;
-    if (p.ctas_per_peer > 16) p.ctas_per_peer = 16;
+    // about one CTA per SM in total: the rows of a small message are spread over the whole machine
+    p.ctas_per_peer = a->ctas_per_peer > 0 ? a->ctas_per_peer : 144 / a->world;
+    if (p.ctas_per_peer > 72) p.ctas_per_peer = 72;
+    if (p.ctas_per_peer < 1) p.ctas_per_peer = 1;
     p.epoch = a->epoch;
     p.wctx.status = static_cast<Status*>(a->status);
     p.wctx.timeout_ns = a->timeout_ns;

@@ -328,35 +328,68 @@ __global__ void __launch_bounds__(kDecodeThreads, (D <= 128 ? 2 : 1)) flash_deco
     if (!last_s) return;
     __threadfence();
 
-    float* merged = o_s;                       // [G][W2] merged O || LSE of this rank
-    for (int idx = tid; idx < G * D; idx += kDecodeThreads) {
-        const int g = idx / D, c = idx % D;
-        const float* src = p.partial + (static_cast<size_t>(b) * p.Hq + kvh * G + g) * p.splits * W2;
-        float mm = -CUDART_INF_F;
-        for (int sidx = 0; sidx < p.splits; ++sidx) mm = fmaxf(mm, src[sidx * W2 + D]);
-        const float mu = mm == -CUDART_INF_F ? 0.f : mm;
-        float wsum = 0.f, acc = 0.f;
-        for (int sidx = 0; sidx < p.splits; ++sidx) {
-            const float f = __expf(src[sidx * W2 + D] - mu);
-            wsum += f;
-            acc += f * src[sidx * W2 + c];
-        }
-        const float val = wsum > 0.f ? acc / wsum : 0.f;
-        const float lse = wsum > 0.f ? mm + logf(wsum) : -CUDART_INF_F;
+    // A warp per query head: lanes first turn the per-split LSEs into normalised weights (kept in
+    // shared memory), then every lane merges 4 output columns with independent 16-byte loads.
+    float* merged = o_s;                       // [G][W2] merged O || LSE of this rank (SP mode)
+    float* w_s = o_s + 16 * W2;                // [warps][256] split weights
+    for (int g = warp; g < G; g += kDecodeWarps) {
         const size_t head = static_cast<size_t>(b) * p.Hq + kvh * G + g;
-        if (p.mode == 0) {
-            static_cast<T*>(p.out)[head * D + c] = from_float<T>(val);
-        } else if (p.mode == 1) {
-            float* dst = static_cast<float*>(p.out) + head * (D + 1);
-            dst[c] = val;
-            if (c == 0) dst[D] = lse;
-        } else {
-            merged[g * W2 + c] = val;
-            if (c == 0) {
+        const float* src = p.partial + head * p.splits * W2;
+        float mm = -CUDART_INF_F;
+        for (int sidx = lane; sidx < p.splits; sidx += 32) mm = fmaxf(mm, src[sidx * W2 + D]);
+#pragma unroll
+        for (int o2 = 16; o2; o2 >>= 1) mm = fmaxf(mm, __shfl_xor_sync(0xffffffffu, mm, o2));
+        const float mu = mm == -CUDART_INF_F ? 0.f : mm;
+        float wsum = 0.f;
+        for (int sidx = lane; sidx < p.splits; sidx += 32) {
+            const float f = __expf(src[sidx * W2 + D] - mu);
+            w_s[warp * 256 + sidx] = f;
+            wsum += f;
+        }
+#pragma unroll
+        for (int o2 = 16; o2; o2 >>= 1) wsum += __shfl_xor_sync(0xffffffffu, wsum, o2);
+        __syncwarp();
+        const float inv = wsum > 0.f ? 1.f / wsum : 0.f;
+        const float lse = wsum > 0.f ? mm + logf(wsum) : -CUDART_INF_F;
+        for (int c = lane * 4; c < D; c += 128) {
+            float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll 8
+            for (int sidx = 0; sidx < p.splits; ++sidx) {
+                // rows of the workspace are D + 2 floats: 8-byte aligned, so two float2 loads
+                const float2 lo = *reinterpret_cast<const float2*>(src + sidx * W2 + c);
+                const float2 hi = *reinterpret_cast<const float2*>(src + sidx * W2 + c + 2);
+                const float f = w_s[warp * 256 + sidx];
+                acc.x += f * lo.x;
+                acc.y += f * lo.y;
+                acc.z += f * hi.x;
+                acc.w += f * hi.y;
+            }
+            acc.x *= inv;
+            acc.y *= inv;
+            acc.z *= inv;
+            acc.w *= inv;
+            if (p.mode == 0) {
+                T* dst = static_cast<T*>(p.out) + head * D + c;
+                *reinterpret_cast<uint2*>(dst) = make_uint2(pack2<T>(acc.x, acc.y), pack2<T>(acc.z, acc.w));
+            } else if (p.mode == 1) {
+                float* dst = static_cast<float*>(p.out) + head * (D + 1) + c;  // rows of D + 1 floats: scalar stores
+                dst[0] = acc.x;
+                dst[1] = acc.y;
+                dst[2] = acc.z;
+                dst[3] = acc.w;
+            } else {
+                *reinterpret_cast<float2*>(merged + g * W2 + c) = make_float2(acc.x, acc.y);
+                *reinterpret_cast<float2*>(merged + g * W2 + c + 2) = make_float2(acc.z, acc.w);
+            }
+        }
+        if (lane == 0) {
+            if (p.mode == 1) static_cast<float*>(p.out)[head * (D + 1) + D] = lse;
+            if (p.mode == 2) {
                 merged[g * W2 + D] = lse;
                 merged[g * W2 + D + 1] = 0.f;
             }
         }
+        __syncwarp();
     }
     if (p.mode != 2) return;
     __syncthreads();
