@@ -248,8 +248,15 @@ def main():
             if world > 1:
                 dist.reduce_scatter_tensor(ro, full, group=group)
         trs_ms = timed(torch_rs, K_STEPS, W)
+        ref_out = ro.clone()                       # torch result of the last baseline step
+        G.gemm_rs(x, v, rctx, out=ro)
+        check_status()
+        rs_err = (ro.float() - ref_out.float()).abs().max().item()
+        if not (rs_err < 0.25):
+            raise SystemExit(f"gemm_rs result is wrong (max abs err {rs_err})")
         extra["gemm_rs"] = {"ms_per_step": rs_ms, "tflops": flops / (rs_ms * 1e-3) / 1e12,
-                            "torch_nccl_cublas_ms": trs_ms, "speedup_vs_torch": trs_ms / rs_ms}
+                            "torch_nccl_cublas_ms": trs_ms, "speedup_vs_torch": trs_ms / rs_ms,
+                            "check_max_abs_err_vs_torch": rs_err}
 
     if rank == 0:
         line = {
