@@ -470,10 +470,12 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_sm100_kernel(const __grid_con
                 fence_proxy_async_smem();
                 named_barrier(1, 128);  // the staging buffer is complete
                 if (issuer) {
-                    if (col + c * EPI_COLS < p.n && row < p.m_per_rank) {
+                    if (col + c * EPI_COLS < p.n && row < p.m_per_rank)
                         tma_store_3d(cm, smem_u32(cs), col + c * EPI_COLS, row, cz);
-                        bulk_commit();
-                    }
+                    // One group per chunk even when the chunk lies outside the matrix and stores
+                    // nothing: "at most one group pending" below then always means that the store
+                    // which last read the OTHER staging buffer (two chunks back) has drained.
+                    bulk_commit();
                     bulk_wait_read<1>();
                 }
             }
