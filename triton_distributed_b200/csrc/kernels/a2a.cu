@@ -159,8 +159,11 @@ __global__ void __launch_bounds__(kA2AThreads) a2a_kernel(const A2AParams p) {
             const int e = dest * p.epr + threadIdx.x;
             p.splits_peer[dest][p.rank * p.epr + threadIdx.x] = p.counts[e + 1] - p.counts[e];
         }
-        // publish: last CTA of the group raises this source's flag on the destination
-        fence_acq_rel_sys();
+        // Publish: the last CTA of the group raises this source's flag on the destination. Only one
+        // thread per CTA fences: the CTA barrier orders every thread's stores before thread 0's
+        // release (gpu scope, chained through the counter), and the last CTA's system-scope fence +
+        // release store makes all of them visible to the destination before the flag. A system
+        // fence in every one of the grid's ~70K threads costs tens of microseconds.
         __syncthreads();
         if (threadIdx.x == 0) {
             const uint32_t old = atom_add_acq_rel_gpu_u32(p.counters + dest, 1);

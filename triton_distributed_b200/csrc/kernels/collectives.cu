@@ -55,7 +55,7 @@ __device__ __forceinline__ void slice_range(size_t bytes, int i, int n, size_t* 
 
 // Last CTA of the group (all its stores fenced) publishes this rank's flag on `peer`.
 __device__ __forceinline__ void group_signal(const CollParams& p, int peer) {
-    fence_acq_rel_sys();
+    // one fencing thread per CTA: the barrier orders the CTA's stores before thread 0's release
     __syncthreads();
     if (threadIdx.x == 0) {
         const uint32_t old = atom_add_acq_rel_gpu_u32(p.counters + peer, 1);
