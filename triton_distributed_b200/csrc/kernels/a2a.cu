@@ -54,40 +54,41 @@ struct A2AParams {
 
 // Work is dealt to warps in (row, segment) items so that a 128-row message still occupies every
 // warp of the grid and each item costs about one memory round trip.
-constexpr int kSegBytes = 2048;    // plain copy: 4 x 16 bytes per lane in flight
-constexpr int kSegGroups = 8;      // quantising copy: 8 groups of 128 values (1024 elements)
+constexpr int kSegLoads = 8;                      // 16-byte loads in flight per lane
+constexpr int kSegBytes = kSegLoads * 512;        // plain copy: bytes per item
+constexpr int kSegGroups = kSegLoads * 2;         // quantising copy: groups of 128 values per item
 
 __device__ __forceinline__ void copy_seg_warp(char* dst, const char* src, int bytes, int seg, int lane) {
     const int b0 = seg * kSegBytes;
     const int b1 = min(bytes, b0 + kSegBytes);
-    uint4 q[4];
+    uint4 q[kSegLoads];
 #pragma unroll
-    for (int u = 0; u < 4; ++u) {
+    for (int u = 0; u < kSegLoads; ++u) {
         const int i = b0 + u * 512 + lane * 16;
         if (i < b1) q[u] = ld_nc_v4(src + i);
     }
 #pragma unroll
-    for (int u = 0; u < 4; ++u) {
+    for (int u = 0; u < kSegLoads; ++u) {
         const int i = b0 + u * 512 + lane * 16;
         if (i < b1) st_v4(dst + i, q[u]);
     }
 }
 
 // bf16 -> fp8 e4m3 with one fp32 scale per 128 values (scale = amax / 448) for groups
-// [8*seg, 8*seg + 8) of one row. A half-warp (16 lanes x 8 values) owns a group; the four groups of
-// each half-warp are loaded before any is processed.
+// [16*seg, 16*seg + 16) of one row. A half-warp (16 lanes x 8 values) owns a group; the eight groups
+// of each half-warp are loaded before any is processed.
 __device__ __forceinline__ void quant_seg_warp(char* dst, float* dst_scale, const char* src, int hidden, int seg, int lane) {
     const int groups = hidden / 128;
     const int half = lane >> 4, sub = lane & 15;
     const int g0 = seg * kSegGroups;
-    uint4 q[4];
+    uint4 q[kSegLoads];
 #pragma unroll
-    for (int u = 0; u < 4; ++u) {
+    for (int u = 0; u < kSegLoads; ++u) {
         const int g = g0 + 2 * u + half;
         q[u] = g < groups ? ld_nc_v4(src + (static_cast<size_t>(g) * 128 + sub * 8) * 2) : make_uint4(0, 0, 0, 0);
     }
 #pragma unroll
-    for (int u = 0; u < 4; ++u) {
+    for (int u = 0; u < kSegLoads; ++u) {
         const int g = g0 + 2 * u + half;
         const bool active = g < groups;
         const uint32_t w[4] = {q[u].x, q[u].y, q[u].z, q[u].w};
