@@ -1,0 +1,59 @@
+"""`torch.ops.tdist.*` registrations: every op is reachable through the dispatcher, runs on CPU
+tensors (the torch restatement path) and has a fake implementation that yields the right shapes."""
+import math
+
+import torch
+from torch._subclasses.fake_tensor import FakeTensorMode
+
+import triton_distributed_b200.torch_ops as T
+from triton_distributed_b200.ops import flash_decode as FD
+from triton_distributed_b200.ops import gemm as G
+
+
+def test_every_op_is_registered():
+    for name in T.OP_NAMES:
+        assert hasattr(torch.ops.tdist, name), name
+
+
+def test_gemm_family_through_the_dispatcher_on_cpu():
+    torch.manual_seed(0)
+    a, b = torch.randn(16, 32), torch.randn(24, 32)
+    torch.testing.assert_close(torch.ops.tdist.gemm(a, b), a @ b.t())
+    h = T.register_context(G.create_ag_gemm_intra_node_context(a, b, 0, 1, max_M=16))
+    torch.testing.assert_close(torch.ops.tdist.ag_gemm(a, b, h), a @ b.t())
+    h2 = T.register_context(G.create_gemm_rs_context(16, 24, 0, 1, device="cpu"))
+    torch.testing.assert_close(torch.ops.tdist.gemm_rs(a, b, h2), a @ b.t())
+    T.release_context(h)
+    T.release_context(h2)
+
+
+def test_decode_and_moe_ops_on_cpu():
+    torch.manual_seed(1)
+    q = torch.randn(2, 8, 64)
+    k, v = torch.randn(6, 4, 2, 64), torch.randn(6, 4, 2, 64)
+    table = torch.arange(6, dtype=torch.int32).view(2, 3)
+    lens = torch.tensor([5, 12], dtype=torch.int32)
+    out = torch.ops.tdist.gqa_fwd_batch_decode(q, k, v, lens, table, 0.125, 0.0)
+    part = torch.ops.tdist.gqa_fwd_batch_decode_intra_rank(q, k, v, lens, table, 0.125, 0.0)
+    torch.testing.assert_close(out, part[..., :64], atol=1e-5, rtol=1e-5)
+    torch.testing.assert_close(torch.ops.tdist.lse_combine(torch.stack([part, part])).float(), out, atol=2e-2, rtol=2e-2)
+    ids, w = torch.ops.tdist.moe_topk_softmax(torch.randn(5, 16), 2, True)
+    assert ids.shape == (5, 2) and torch.allclose(w.sum(-1), torch.ones(5))
+    outs = torch.ops.tdist.moe_ag_scatter_align_block_size(torch.randint(0, 4, (8, 2), dtype=torch.int32), 4, 2, 4, 4)
+    assert len(outs) == 5 and int(outs[4]) % 4 == 0
+
+
+def test_fake_implementations_propagate_shapes():
+    a, b = torch.randn(16, 32), torch.randn(24, 32)
+    h = T.register_context(G.create_ag_gemm_intra_node_context(a, b, 0, 4, max_M=64))
+    with FakeTensorMode():
+        fa, fb = torch.empty(16, 32), torch.empty(24, 32)
+        assert torch.ops.tdist.gemm(fa, fb).shape == (16, 24)
+        assert torch.ops.tdist.ag_gemm(fa, fb, h).shape == (64, 24)
+        q = torch.empty(2, 8, 64)
+        cache = torch.empty(6, 4, 2, 64)
+        assert torch.ops.tdist.gqa_fwd_batch_decode_intra_rank(q, cache, cache, torch.empty(2, dtype=torch.int32),
+                                                                 torch.empty(2, 3, dtype=torch.int32), 0.1, 0.0).shape == (2, 8, 65)
+        ids, w = torch.ops.tdist.moe_topk_softmax(torch.empty(5, 16), 2, False)
+        assert ids.shape == (5, 2) and w.dtype == torch.float32
+    T.release_context(h)
