@@ -1,0 +1,89 @@
+"""Each device primitive through its own kernel, ranks emulated on one GPU (send halves first, then
+the waiting halves). Follows the reference's test_notify.py, test_ring_put.py, test_nvshmem_api.py and
+test_common_ops.py (grid barrier over random grid sizes)."""
+import random
+
+import pytest
+import torch
+
+from triton_distributed_b200.ops import primitives as P
+from triton_distributed_b200.runtime import LocalWorld, check_status
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture
+def ring(cuda_device):
+    world = 4
+    lw = LocalWorld(world, cuda_device)
+    ctxs = [P.create_primitive_context(r, world, 4096, heap=lw.heap(r)) for r in range(world)]
+    for c in ctxs:
+        c.source.copy_(torch.randint(0, 256, (c.nbytes,), dtype=torch.uint8, device=cuda_device))
+    return ctxs
+
+
+def _both_phases(ctxs, op, **kw):
+    for c in ctxs:
+        P.run_primitive(c, op, phase=1, **kw)
+    for c in ctxs:
+        P.run_primitive(c, op, phase=2, **kw)
+    check_status()
+
+
+def test_ring_put_int_p(ring):
+    _both_phases(ring, "ring_put")
+    for r, c in enumerate(ring):
+        assert int(c.slot(0).view(torch.int32)[0]) == (r - 1) % len(ring) + 100
+
+
+def test_notify_wait_ring_and_consume_token(ring):
+    for value in (5, 6):  # two rounds: signals are plain values, no reset in between
+        _both_phases(ring, "notify_wait", value=value)
+        for r, c in enumerate(ring):
+            assert c.result[:2].tolist() == [1, (r - 1) % len(ring) + 7]
+
+
+def test_notify_add_to_rank0(ring):
+    _both_phases(ring, "notify_add", value=len(ring))
+    assert int(ring[0].result[0]) == 1 and int(ring[0].sig.local[1]) == len(ring)
+
+
+@pytest.mark.parametrize("scope", ["thread", "warp", "block"])
+def test_putmem_signal_scopes(ring, scope):
+    _both_phases(ring, "put_signal", value=42, scope=scope)
+    for r, c in enumerate(ring):
+        prev = (r - 1) % len(ring)
+        assert int(c.result[0]) == 1
+        assert torch.equal(c.slot(prev), ring[prev].source)
+
+
+def test_put_quiet_signal_add_and_get(ring):
+    _both_phases(ring, "put_quiet_signal", value=3)
+    for r, c in enumerate(ring):
+        prev = (r - 1) % len(ring)
+        assert int(c.result[0]) == 1 and torch.equal(c.slot(prev), ring[prev].source)
+        c.slot(prev).zero_()
+    _both_phases(ring, "get")
+    for r, c in enumerate(ring):
+        prev = (r - 1) % len(ring)
+        assert torch.equal(c.slot(prev), ring[prev].source)
+
+
+def test_broadcast_and_fcollect(ring):
+    _both_phases(ring, "broadcast")
+    for c in ring:
+        assert torch.equal(c.slot(0), ring[0].source)
+    _both_phases(ring, "fcollect")
+    for c in ring:
+        for s in range(len(ring)):
+            assert torch.equal(c.slot(s), ring[s].source)
+
+
+def test_grid_barrier_random_grids(cuda_device):
+    lw = LocalWorld(1, cuda_device)
+    ctx = P.create_primitive_context(0, 1, 4096, heap=lw.heap(0))
+    rng = random.Random(0)
+    for it in range(50):
+        P.run_primitive(ctx, "grid_barrier", value=it * 1000, grid=rng.randint(1, 148))
+    check_status()
+    assert int(ctx.result[0]) == 0  # no CTA saw a stale neighbour

@@ -111,6 +111,21 @@ class DecodeArgs(C.Structure):
     ]
 
 
+class PrimArgs(C.Structure):
+    _fields_ = [
+        ("data_peer", C.c_void_p * MAX_RANKS), ("sig_peer", C.c_void_p * MAX_RANKS),
+        ("result", C.c_void_p), ("grid_counter", C.c_void_p), ("barrier_epoch", C.c_void_p),
+        ("world", C.c_int), ("rank", C.c_int), ("op", C.c_int), ("phase", C.c_int), ("nbytes", C.c_int),
+        ("scope", C.c_int), ("grid", C.c_int),
+        ("value", C.c_uint64),
+        ("status", C.c_void_p),
+        ("timeout_ns", C.c_uint64),
+        ("stream", C.c_void_p),
+    ]
+
+
+(PRIM_RING_PUT, PRIM_NOTIFY_WAIT, PRIM_NOTIFY_ADD, PRIM_PUT_SIGNAL, PRIM_PUT_QUIET_SIGNAL, PRIM_GET, PRIM_BROADCAST,
+ PRIM_FCOLLECT, PRIM_GRID_BARRIER) = range(9)
 GEMM_PLAIN, GEMM_AG, GEMM_RS = 0, 1, 2
 A2A_DISPATCH, A2A_COMBINE = 0, 1
 DT_BF16, DT_F16, DT_F32, DT_I32 = 0, 1, 2, 3
@@ -140,6 +155,7 @@ def _declare(lib):
     lib.tdist_p2p_copy.argtypes = [C.c_void_p, C.c_void_p, C.c_size_t, C.c_int, C.c_int, C.c_int, C.c_int,
                                    C.c_void_p, C.c_uint64, C.c_void_p]
     lib.tdist_a2a.argtypes = [C.POINTER(A2AArgs)]
+    lib.tdist_primitive.argtypes = [C.POINTER(PrimArgs)]
     lib.tdist_flash_decode.argtypes = [C.POINTER(DecodeArgs)]
     lib.tdist_lse_combine.argtypes = [C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_int, C.c_void_p]
     lib.tdist_dequant_fp8.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_void_p]

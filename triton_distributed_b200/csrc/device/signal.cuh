@@ -253,6 +253,23 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, const W
     }
 }
 
+// Barrier of all CTAs of a grid that is fully resident (grid <= co-resident capacity): thread 0 of
+// each CTA adds 1 to a monotonic counter and spins until the counter reaches the next multiple of
+// the grid size; the CTA barriers on both sides extend it to all threads. No reset between uses.
+// (reference kernels/nvidia/common_ops.py:62-85 `barrier_on_this_grid`)
+__device__ __forceinline__ bool grid_barrier(uint32_t* counter, const WaitCtx& w) {
+    __shared__ int ok_s;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        const uint32_t n = gridDim.x * gridDim.y * gridDim.z;
+        const uint32_t old = atom_add_acq_rel_gpu_u32(counter, 1);
+        const uint32_t target = (old / n + 1) * n;
+        ok_s = wait_flag_ge_gpu(counter, target, w, -1, static_cast<int>(blockIdx.x), 300) ? 1 : 0;
+    }
+    __syncthreads();
+    return ok_s != 0;
+}
+
 // ---------------------------------------------------------------- dialect-level ops
 // Table of the same symmetric allocation as seen from this process: base[r] is the address at
 // which rank r's copy is mapped here (base[rank] is the local copy).

@@ -198,6 +198,30 @@ int tdist_flash_decode(const TdistDecodeArgs* args);
 /* parts fp32 [ranks, heads, D + 1] -> out [heads, D] */
 int tdist_lse_combine(const void* parts, int ranks, int heads, int head_dim, void* out, int dtype, void* stream);
 
+/* ------------------------------------------------------------------ device primitives, one test op each */
+enum {
+    TDIST_PRIM_RING_PUT = 0, TDIST_PRIM_NOTIFY_WAIT = 1, TDIST_PRIM_NOTIFY_ADD = 2, TDIST_PRIM_PUT_SIGNAL = 3,
+    TDIST_PRIM_PUT_QUIET_SIGNAL = 4, TDIST_PRIM_GET = 5, TDIST_PRIM_BROADCAST = 6, TDIST_PRIM_FCOLLECT = 7,
+    TDIST_PRIM_GRID_BARRIER = 8
+};
+
+typedef struct TdistPrimArgs {
+    void* data_peer[TDIST_MAX_RANKS]; /* symmetric byte buffer of (world + 2) * nbytes: slots 0..world-1 receive, slot `world` is the source */
+    void* sig_peer[TDIST_MAX_RANKS];  /* symmetric uint64[16]: words 0..7 signals, 8..15 barrier flags */
+    void* result;                     /* local int32[8] */
+    void* grid_counter;               /* local uint32, monotonic */
+    void* barrier_epoch;              /* local uint64 */
+    int world, rank, op, phase, nbytes;
+    int scope;                        /* PUT_SIGNAL: 0 thread, 1 warp, 2 block */
+    int grid;                         /* GRID_BARRIER: number of CTAs (must all be resident) */
+    uint64_t value;
+    void* status;
+    uint64_t timeout_ns;
+    void* stream;
+} TdistPrimArgs;
+
+int tdist_primitive(const TdistPrimArgs* args);
+
 #ifdef __cplusplus
 }
 #endif

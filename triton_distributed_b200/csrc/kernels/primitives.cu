@@ -1,0 +1,152 @@
+// One small kernel per device primitive, so that every function of signal.cuh / shmem.cuh can be
+// driven and checked from the host (and serves as a usage example). Mirrors what the reference
+// tests exercise through Triton kernels: test_notify.py (ring set, add-to-rank-0), test_ring_put.py
+// (int_p), test_nvshmem_api.py (put / get / putmem_signal at thread, warp and block scope,
+// signal_op + signal_wait_until, fence / quiet, barrier, broadcast, fcollect), test_common_ops.py
+// (grid barrier).
+//
+// Ops that wait take a `phase`: 1 = the sending half, 2 = the waiting / checking half, 3 = both.
+// With one process per GPU a test passes 3; with all ranks emulated on one GPU it runs phase 1 on
+// every rank first, so that no launch ever waits for a launch that has not run.
+#include <cuda_runtime.h>
+
+#include "../device/shmem.cuh"
+#include "../include/tdist.h"
+#include "../runtime/host_common.h"
+
+namespace tdist {
+
+constexpr int kKernelPrim = 5;
+
+struct PrimParams {
+    SymmWindow win;     // window of `data`
+    SymmWindow sigwin;  // window of `sig`
+    char* data;         // local symmetric buffer, >= (world + 2) * nbytes
+    uint64_t* sig;      // local symmetric uint64[16]
+    int* result;        // local (non-symmetric) int[8]: op-specific check results
+    uint32_t* grid_counter;
+    BarrierState barrier;
+    int op, phase, nbytes, scope;
+    uint64_t value;
+    WaitCtx wctx;
+};
+
+// data layout: slot s occupies [s * nbytes, (s + 1) * nbytes). Slot `world` is the local source.
+__device__ __forceinline__ char* slot(const PrimParams& p, int s) { return p.data + static_cast<size_t>(s) * p.nbytes; }
+
+__global__ void prim_kernel(const PrimParams p) {
+    const int rank = p.win.rank, world = p.win.world;
+    const int next = (rank + 1) % world, prev = (rank + world - 1) % world;
+    const bool t0 = threadIdx.x == 0 && blockIdx.x == 0;
+    switch (p.op) {
+        case TDIST_PRIM_RING_PUT:  // int_p: write my rank into the next rank's slot 0
+            if ((p.phase & 1) && t0) int_p(p.win, reinterpret_cast<int*>(slot(p, 0)), rank + 100, next);
+            break;
+        case TDIST_PRIM_NOTIFY_WAIT:  // ring: notify(next, value) ; wait for prev's notify
+            if ((p.phase & 1) && t0) {
+                *reinterpret_cast<volatile int*>(symm_at(p.win, reinterpret_cast<int*>(slot(p, 0)), next)) = rank + 7;
+                notify(p.sigwin, p.sig, next, p.value, kSignalSet);
+            }
+            if ((p.phase & 2) && blockIdx.x == 0 && threadIdx.x < 32) {
+                const bool token = wait(p.sig, 1, p.value, p.wctx, 1);
+                int* guarded = consume_token(reinterpret_cast<int*>(slot(p, 0)), token);
+                if (threadIdx.x == 0) {
+                    p.result[0] = token ? 1 : 0;
+                    p.result[1] = *reinterpret_cast<volatile int*>(guarded);  // must be prev + 7
+                }
+            }
+            break;
+        case TDIST_PRIM_NOTIFY_ADD:  // every rank adds 1 on rank 0's signal; rank 0 waits for world
+            if ((p.phase & 1) && t0) notify(p.sigwin, p.sig + 1, 0, 1, kSignalAdd);
+            if ((p.phase & 2) && t0 && rank == 0)
+                p.result[0] = signal_wait_until(p.sig + 1, kCmpGe, p.value, p.wctx, -1, 2) ? 1 : 0;
+            break;
+        case TDIST_PRIM_PUT_SIGNAL: {  // putmem_signal at the requested scope into next's slot `rank`
+            if (p.phase & 1) {
+                if (p.scope == 0) {
+                    if (t0) putmem_signal(p.win, slot(p, rank), slot(p, world), p.nbytes, p.sig + 2, p.value, kSignalSet, next);
+                } else if (p.scope == 1) {
+                    if (blockIdx.x == 0 && threadIdx.x < 32)
+                        putmem_signal_warp(p.win, slot(p, rank), slot(p, world), p.nbytes, p.sig + 2, p.value, kSignalSet, next);
+                } else if (blockIdx.x == 0) {
+                    putmem_signal_block(p.win, slot(p, rank), slot(p, world), p.nbytes, p.sig + 2, p.value, kSignalSet, next);
+                }
+            }
+            if ((p.phase & 2) && t0) p.result[0] = signal_wait_until(p.sig + 2, kCmpEq, p.value, p.wctx, prev, 3) ? 1 : 0;
+            break;
+        }
+        case TDIST_PRIM_PUT_QUIET_SIGNAL:  // putmem_nbi_block ; quiet ; signal_op(ADD) — the explicit form
+            if ((p.phase & 1) && blockIdx.x == 0) {
+                putmem_nbi_block(p.win, slot(p, rank), slot(p, world), p.nbytes, next);
+                quiet();
+                __syncthreads();
+                if (threadIdx.x == 0) {
+                    fence();
+                    signal_op(p.sigwin, p.sig + 3, p.value, kSignalAdd, next);
+                }
+            }
+            if ((p.phase & 2) && t0) p.result[0] = signal_wait_until(p.sig + 3, kCmpGe, p.value, p.wctx, prev, 4) ? 1 : 0;
+            break;
+        case TDIST_PRIM_GET:  // getmem_block: pull prev's source slot into my slot `prev`
+            if ((p.phase & 2) && blockIdx.x == 0) getmem_block(p.win, slot(p, prev), slot(p, world), p.nbytes, prev);
+            break;
+        case TDIST_PRIM_BROADCAST:  // root 0's source slot lands in everybody's slot 0, then a barrier
+            if ((p.phase & 1) && blockIdx.x == 0) broadcast_block(p.win, slot(p, 0), slot(p, world), p.nbytes, 0);
+            if ((p.phase & 2) && blockIdx.x == 0 && p.phase == 3) p.result[0] = barrier_all_block(p.sigwin, p.barrier, p.wctx) ? 1 : 0;
+            break;
+        case TDIST_PRIM_FCOLLECT:  // everybody's source slot lands in slot `rank` of everybody
+            if ((p.phase & 1) && blockIdx.x == 0) fcollect_block(p.win, slot(p, 0), slot(p, world), p.nbytes);
+            if ((p.phase & 2) && blockIdx.x == 0 && p.phase == 3) p.result[0] = barrier_all_block(p.sigwin, p.barrier, p.wctx) ? 1 : 0;
+            break;
+        case TDIST_PRIM_GRID_BARRIER: {  // every CTA publishes, all meet, every CTA reads its neighbour
+            int* buf = reinterpret_cast<int*>(slot(p, 0));
+            if (threadIdx.x == 0) buf[blockIdx.x] = static_cast<int>(blockIdx.x) + static_cast<int>(p.value);
+            const bool ok = grid_barrier(p.grid_counter, p.wctx);
+            if (threadIdx.x == 0) {
+                const int nb = (blockIdx.x + 1) % gridDim.x;
+                const int seen = *reinterpret_cast<volatile int*>(buf + nb);
+                if (!ok || seen != nb + static_cast<int>(p.value)) atomicAdd(p.result, 1);  // counts failures
+            }
+            break;
+        }
+        default: break;
+    }
+}
+
+}  // namespace tdist
+
+using namespace tdist;
+
+extern "C" int tdist_primitive(const TdistPrimArgs* a) {
+    if (a->world < 1 || a->world > TDIST_MAX_RANKS || a->rank < 0 || a->rank >= a->world)
+        return tdist_host::fail(TDIST_EINVAL, "primitive: world/rank out of range");
+    if (a->op < 0 || a->op > TDIST_PRIM_GRID_BARRIER) return tdist_host::fail(TDIST_EINVAL, "primitive: unknown op");
+    PrimParams p;
+    memset(&p, 0, sizeof(p));
+    for (int r = 0; r < a->world; ++r) {
+        p.win.base[r] = static_cast<char*>(a->data_peer[r]);
+        p.sigwin.base[r] = static_cast<char*>(a->sig_peer[r]);
+        if (!p.win.base[r] || !p.sigwin.base[r]) return tdist_host::fail(TDIST_EINVAL, "primitive: null peer pointer");
+    }
+    p.win.rank = p.sigwin.rank = a->rank;
+    p.win.world = p.sigwin.world = a->world;
+    p.data = p.win.base[a->rank];
+    p.sig = reinterpret_cast<uint64_t*>(p.sigwin.base[a->rank]);
+    p.result = static_cast<int*>(a->result);
+    p.grid_counter = static_cast<uint32_t*>(a->grid_counter);
+    p.barrier.flags = p.sig + 8;  // words 8..15 of the signal array are the barrier's flags
+    p.barrier.epoch = static_cast<uint64_t*>(a->barrier_epoch);
+    p.op = a->op;
+    p.phase = a->phase ? a->phase : 3;
+    p.nbytes = a->nbytes;
+    p.scope = a->scope;
+    p.value = a->value;
+    p.wctx.status = static_cast<Status*>(a->status);
+    p.wctx.timeout_ns = a->timeout_ns;
+    p.wctx.kernel_id = kKernelPrim;
+    p.wctx.rank = a->rank;
+    const int grid = a->op == TDIST_PRIM_GRID_BARRIER ? (a->grid > 0 ? a->grid : 64) : 1;
+    prim_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(a->stream)>>>(p);
+    TDIST_CUDA_OK(cudaGetLastError());
+    return 0;
+}
