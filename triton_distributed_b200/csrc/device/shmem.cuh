@@ -107,34 +107,43 @@ __device__ __forceinline__ void signal_op(const SymmWindow& w, uint64_t* sig, ui
     if (sig_op == kSignalAdd) red_release_sys_add_u64(remote, value);
     else st_release_sys_u64(remote, value);
 }
-// put, then signal `pe` once the whole block's data is ordered before the signal.
+// put, then signal `pe` once the data is ordered before the signal. `w` is the window of `dst`,
+// `sw` the window of `sig` (the same window when both live in one symmetric object).
 __device__ __forceinline__ void putmem_signal_block(const SymmWindow& w, void* dst, const void* src, size_t bytes,
-                                                    uint64_t* sig, uint64_t value, int sig_op, int pe) {
+                                                    const SymmWindow& sw, uint64_t* sig, uint64_t value, int sig_op, int pe) {
     putmem_block(w, dst, src, bytes, pe);
-    fence();
-    __syncthreads();
-    if (threadIdx.x == 0) signal_op(w, sig, value, sig_op, pe);
+    __syncthreads();  // one fencing thread: the barrier orders the block's stores before its release
+    if (threadIdx.x == 0) {
+        fence();
+        signal_op(sw, sig, value, sig_op, pe);
+    }
 }
 __device__ __forceinline__ void putmem_signal_warp(const SymmWindow& w, void* dst, const void* src, size_t bytes,
-                                                   uint64_t* sig, uint64_t value, int sig_op, int pe) {
+                                                   const SymmWindow& sw, uint64_t* sig, uint64_t value, int sig_op, int pe) {
     putmem_warp(w, dst, src, bytes, pe);
-    fence();
     __syncwarp();
-    if (lane_id() == 0) signal_op(w, sig, value, sig_op, pe);
+    if (lane_id() == 0) {
+        fence();
+        signal_op(sw, sig, value, sig_op, pe);
+    }
 }
 __device__ __forceinline__ void putmem_signal(const SymmWindow& w, void* dst, const void* src, size_t bytes,
-                                              uint64_t* sig, uint64_t value, int sig_op, int pe) {
+                                              const SymmWindow& sw, uint64_t* sig, uint64_t value, int sig_op, int pe) {
     putmem(w, dst, src, bytes, pe);
     fence();
-    signal_op(w, sig, value, sig_op, pe);
+    signal_op(sw, sig, value, sig_op, pe);
 }
 __device__ __forceinline__ void putmem_signal_nbi_block(const SymmWindow& w, void* dst, const void* src, size_t bytes,
-                                                        uint64_t* sig, uint64_t value, int sig_op, int pe) {
-    putmem_signal_block(w, dst, src, bytes, sig, value, sig_op, pe);
+                                                        const SymmWindow& sw, uint64_t* sig, uint64_t value, int sig_op, int pe) {
+    putmem_signal_block(w, dst, src, bytes, sw, sig, value, sig_op, pe);
 }
 __device__ __forceinline__ void putmem_signal_nbi_warp(const SymmWindow& w, void* dst, const void* src, size_t bytes,
-                                                       uint64_t* sig, uint64_t value, int sig_op, int pe) {
-    putmem_signal_warp(w, dst, src, bytes, sig, value, sig_op, pe);
+                                                       const SymmWindow& sw, uint64_t* sig, uint64_t value, int sig_op, int pe) {
+    putmem_signal_warp(w, dst, src, bytes, sw, sig, value, sig_op, pe);
+}
+__device__ __forceinline__ void putmem_signal_nbi(const SymmWindow& w, void* dst, const void* src, size_t bytes,
+                                                  const SymmWindow& sw, uint64_t* sig, uint64_t value, int sig_op, int pe) {
+    putmem_signal(w, dst, src, bytes, sw, sig, value, sig_op, pe);
 }
 
 // ---- barriers. `flags` is a symmetric array of kMaxRanks 64-bit words per rank, `epoch` a

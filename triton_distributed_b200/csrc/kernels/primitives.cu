@@ -64,12 +64,12 @@ __global__ void prim_kernel(const PrimParams p) {
         case TDIST_PRIM_PUT_SIGNAL: {  // putmem_signal at the requested scope into next's slot `rank`
             if (p.phase & 1) {
                 if (p.scope == 0) {
-                    if (t0) putmem_signal(p.win, slot(p, rank), slot(p, world), p.nbytes, p.sig + 2, p.value, kSignalSet, next);
+                    if (t0) putmem_signal(p.win, slot(p, rank), slot(p, world), p.nbytes, p.sigwin, p.sig + 2, p.value, kSignalSet, next);
                 } else if (p.scope == 1) {
                     if (blockIdx.x == 0 && threadIdx.x < 32)
-                        putmem_signal_warp(p.win, slot(p, rank), slot(p, world), p.nbytes, p.sig + 2, p.value, kSignalSet, next);
+                        putmem_signal_warp(p.win, slot(p, rank), slot(p, world), p.nbytes, p.sigwin, p.sig + 2, p.value, kSignalSet, next);
                 } else if (blockIdx.x == 0) {
-                    putmem_signal_block(p.win, slot(p, rank), slot(p, world), p.nbytes, p.sig + 2, p.value, kSignalSet, next);
+                    putmem_signal_block(p.win, slot(p, rank), slot(p, world), p.nbytes, p.sigwin, p.sig + 2, p.value, kSignalSet, next);
                 }
             }
             if ((p.phase & 2) && t0) p.result[0] = signal_wait_until(p.sig + 2, kCmpEq, p.value, p.wctx, prev, 3) ? 1 : 0;
