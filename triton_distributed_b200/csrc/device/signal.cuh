@@ -253,18 +253,35 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, const W
     }
 }
 
-// Barrier of all CTAs of a grid that is fully resident (grid <= co-resident capacity): thread 0 of
-// each CTA adds 1 to a monotonic counter and spins until the counter reaches the next multiple of
-// the grid size; the CTA barriers on both sides extend it to all threads. No reset between uses.
+// Barrier of all CTAs of a grid that is fully resident (grid <= co-resident capacity). Thread 0 of
+// each CTA adds to one 32-bit word: CTA 0 adds 0x80000000 - (n - 1), the others add 1, so a complete
+// round adds exactly 0x80000000 — the top bit flips and the low bits return to where they were.
+// Each CTA spins until the top bit differs from what its own add saw. Needs no reset and works
+// when consecutive launches use different grid sizes.
 // (reference kernels/nvidia/common_ops.py:62-85 `barrier_on_this_grid`)
 __device__ __forceinline__ bool grid_barrier(uint32_t* counter, const WaitCtx& w) {
     __shared__ int ok_s;
     __syncthreads();
     if (threadIdx.x == 0) {
         const uint32_t n = gridDim.x * gridDim.y * gridDim.z;
-        const uint32_t old = atom_add_acq_rel_gpu_u32(counter, 1);
-        const uint32_t target = (old / n + 1) * n;
-        ok_s = wait_flag_ge_gpu(counter, target, w, -1, static_cast<int>(blockIdx.x), 300) ? 1 : 0;
+        const uint32_t me = blockIdx.x + gridDim.x * (blockIdx.y + gridDim.y * blockIdx.z);
+        const uint32_t old = atom_add_acq_rel_gpu_u32(counter, me == 0 ? 0x80000000u - (n - 1) : 1u);
+        const uint64_t limit = w.timeout_ns ? w.timeout_ns : kDefaultTimeoutNs;
+        const uint64_t t0 = globaltimer_ns();
+        uint32_t spins = 0;
+        int ok = 1;
+        while (((old ^ ld_acquire_gpu_u32(counter)) & 0x80000000u) == 0) {
+            __nanosleep(40);
+            if ((++spins & 63u) == 0) {
+                if (aborted(w)) { ok = 0; break; }
+                if (globaltimer_ns() - t0 > limit) {
+                    report_timeout(w, kStatusFlagTimeout, -1, static_cast<int>(me), old ^ 0x80000000u, old, 300);
+                    ok = 0;
+                    break;
+                }
+            }
+        }
+        ok_s = ok;
     }
     __syncthreads();
     return ok_s != 0;
