@@ -13,6 +13,7 @@ import torch
 import torch.distributed as dist
 
 from triton_distributed_b200.ops import gemm as G
+from triton_distributed_b200.ops import gemm_fp8 as F8
 from triton_distributed_b200.runtime import check_status, finalize_distributed, initialize_distributed, symm_heap
 
 
@@ -94,6 +95,36 @@ def main():
                 torch.testing.assert_close(out, ref, rtol=1e-5, atol=1e-5)
             rs_err = max(rs_err, (out.float() - ref).abs().max().item())
     res["rs_max_err"] = rs_err
+
+    # ---------------- block-scaled fp8 AG-GEMM ----------------
+    # oracle: all_gather of rows and scales (NCCL / gloo), then the fp32 matmul of the dequantised operands
+    f8_err = 0.0
+    for (mpr, n_per, K) in ([(128, 256, 256), (250, 264, 384), (1024, 1024, 2048)] if cuda else [(64, 128, 256)]):
+        gen = torch.Generator(device="cpu").manual_seed(1)
+        ctx = F8.create_ag_gemm_fp8_context(world * mpr, K, rank, world, device=dev, group=group)
+        for it in range(3 if cuda else 1):
+            X = torch.randn(world * mpr, K, generator=gen)
+            Wt = torch.randn(world * n_per, K, generator=gen) * K ** -0.5
+            a, sa = F8.quantize_fp8_rowwise(X[rank * mpr:(rank + 1) * mpr].to(dev))
+            b, sb = F8.quantize_fp8_blockwise(Wt[rank * n_per:(rank + 1) * n_per].to(dev))
+            if cuda and ctx.workspace is not None:
+                ctx.workspace.local.fill_(0x7F)          # stale rows (e4m3 NaN) must never be consumed
+                ctx.scale_ws.local.fill_(float("nan"))
+                symm_heap().barrier()
+            c = F8.ag_gemm_fp8(a, sa, b, sb, ctx)
+            if cuda:
+                check_status()
+            rows = torch.empty(world * mpr, K, device=dev, dtype=torch.uint8)
+            scales = torch.empty(world * mpr, K // 128, device=dev, dtype=torch.float32)
+            dist.all_gather_into_tensor(rows, a.view(torch.uint8).contiguous(), group=group)
+            dist.all_gather_into_tensor(scales, sa.contiguous(), group=group)
+            ref = F8.dequantize_fp8(rows.view(F8.FP8), scales, 1) @ F8.dequantize_fp8(b, sb, 128).t()
+            assert torch.isfinite(c.float()).all()
+            torch.testing.assert_close(c.float(), ref, atol=5e-3 * ref.abs().max().item(), rtol=1e-2)
+            f8_err = max(f8_err, (c.float() - ref).abs().max().item())
+            if cuda:
+                symm_heap().barrier()
+    res["fp8_ag_max_err"] = f8_err
 
     ok = torch.ones(1, device=dev)
     dist.all_reduce(ok, group=group)

@@ -57,6 +57,22 @@ class GemmArgs(C.Structure):
     ]
 
 
+class GemmFp8Args(C.Structure):
+    _fields_ = [
+        ("a", C.c_void_p), ("sa", C.c_void_p), ("b", C.c_void_p), ("sb", C.c_void_p), ("c", C.c_void_p),
+        ("a_ws", C.c_void_p), ("sa_ws", C.c_void_p),
+        ("a_ws_peer", C.c_void_p * MAX_RANKS), ("sa_ws_peer", C.c_void_p * MAX_RANKS),
+        ("flags", C.c_void_p), ("flags_peer", C.c_void_p * MAX_RANKS),
+        ("m_per_rank", C.c_int), ("n", C.c_int), ("k", C.c_int),
+        ("world", C.c_int), ("rank", C.c_int), ("mode", C.c_int),
+        ("epoch", C.c_uint32),
+        ("num_sms", C.c_int), ("num_comm_sms", C.c_int),
+        ("status", C.c_void_p),
+        ("timeout_ns", C.c_uint64),
+        ("stream", C.c_void_p),
+    ]
+
+
 class CollArgs(C.Structure):
     _fields_ = [
         ("buf_peer", C.c_void_p * MAX_RANKS),
@@ -149,6 +165,7 @@ def _declare(lib):
     lib.tdist_status_destroy.argtypes = [C.c_void_p]
     lib.tdist_gemm_run.argtypes = [C.POINTER(GemmArgs)]
     lib.tdist_gemm_grid.argtypes = [C.POINTER(GemmArgs)]
+    lib.tdist_gemm_fp8_run.argtypes = [C.POINTER(GemmFp8Args)]
     lib.tdist_allgather.argtypes = [C.POINTER(CollArgs)]
     lib.tdist_reduce_scatter.argtypes = [C.POINTER(CollArgs)]
     lib.tdist_barrier_all.argtypes = [C.POINTER(C.c_void_p), C.c_void_p, C.c_int, C.c_int, C.c_void_p, C.c_uint64, C.c_void_p]

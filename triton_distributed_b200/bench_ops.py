@@ -124,6 +124,60 @@ def _bench_gemm_family(args, world, rank, group, dev, dtype, pk, row):
         row.update({"torch_us": round(base, 2), "speedup_vs_torch": round(base / us, 3)})
 
 
+def _bench_gemm_fp8(args, world, rank, group, dev, dtype, pk, row):
+    """Block-scaled fp8 GEMM / AG-GEMM. Baseline: NCCL all-gather of rows and scales +
+    ``torch._scaled_mm`` with the same 1x128 / 128x128 scales when this torch build takes them, else
+    the cuBLAS bf16 matmul of the same shape (named in ``baseline``)."""
+    from .ops import gemm_fp8 as F
+    M, N, K = args.m, args.n, args.k
+    ag = args.op == "ag_gemm_fp8"
+    mpr, npr = (M // world, N // world) if ag else (M, N)
+    row.update({"m": M, "n": N, "k": K, "dtype": "fp8_e4m3 (1x128 / 128x128 fp32 scales) -> bf16"})
+    a, sa = F.quantize_fp8_rowwise(torch.randn(mpr, K, device=dev))
+    b, sb = F.quantize_fp8_blockwise(torch.randn(npr, K, device=dev) * K ** -0.5)
+    c = torch.empty(M if ag else mpr, npr, device=dev, dtype=torch.bfloat16)
+    if ag:
+        ctx = F.create_ag_gemm_fp8_context(M, K, rank, world, device=dev, group=group)
+        us = timed_us(lambda: F.ag_gemm_fp8(a, sa, b, sb, ctx, out=c), args.iters, args.warmup, world, group)
+        link_us = (world - 1) * mpr * (K + K // 32) / (NVLINK_GBS * 1e3)
+    else:
+        us = timed_us(lambda: F.gemm_fp8_blockscaled(a, sa, b, sb, out=c), args.iters, args.warmup, 1)
+        link_us = 0.0
+    flops = 2.0 * c.shape[0] * npr * K
+    compute_us = flops / (2.0 * pk["bf16_tflops"] * 1e6)   # dense fp8 peak = 2 x the bf16 figure
+    row.update({"us": round(us, 2), "tflops_per_gpu": round(flops / us / 1e6, 1),
+                "roofline_us": round(max(compute_us, link_us), 2), "roofline_fraction": round(max(compute_us, link_us) / us, 3),
+                "roofline_note": "compute bound taken as 2 x the measured cuBLAS bf16 throughput"})
+    if args.no_baseline:
+        return
+    full = torch.empty(c.shape[0], K, device=dev, dtype=torch.uint8)
+    fs = torch.empty(c.shape[0], K // 128, device=dev, dtype=torch.float32)
+    a16, b16 = torch.empty(c.shape[0], K, device=dev, dtype=torch.bfloat16), b.to(torch.bfloat16)
+
+    def gather():
+        if ag and world > 1:
+            dist.all_gather_into_tensor(full, a.view(torch.uint8), group=group)
+            dist.all_gather_into_tensor(fs, sa, group=group)
+    fa = full.view(F.FP8) if ag and world > 1 else a
+    fsa = fs if ag and world > 1 else sa
+    name = "nccl all_gather + torch._scaled_mm (blockwise scales)"
+    try:
+        torch._scaled_mm(fa, b.t(), scale_a=fsa, scale_b=sb.t(), out_dtype=torch.bfloat16)
+
+        def ref():
+            gather()
+            torch._scaled_mm(fa, b.t(), scale_a=fsa, scale_b=sb.t(), out_dtype=torch.bfloat16)
+    except Exception:  # noqa: BLE001 - this torch build has no blockwise-scaled path on this device
+        name = "nccl all_gather + cuBLAS bf16 matmul of the same shape"
+
+        def ref():
+            gather()
+            torch.matmul(a16, b16.t(), out=c)
+    torch.cuda.synchronize()
+    base = timed_us(ref, args.iters, args.warmup, world, group)
+    row.update({"baseline": name, "torch_us": round(base, 2), "speedup_vs_torch": round(base / us, 3)})
+
+
 def _bench_decode(args, world, rank, group, dev, dtype, pk, row):
     """--kv = TOTAL keys per sequence (split evenly over the ranks for sp_decode)."""
     import math
@@ -262,6 +316,7 @@ def _run_suite(args, world, rank, group, dev, dtype, pk):
     PRESLEEP_CYCLES = 0
     run("ag_gemm", _bench_gemm_family, m=8192, n=49152, k=12288)
     run("gemm_rs", _bench_gemm_family, m=8192, n=12288, k=49152)
+    run("ag_gemm_fp8", _bench_gemm_fp8, m=8192, n=49152, k=12288)
     PRESLEEP_CYCLES = int(30 * 1.9e6)
     if world > 1 or True:
         run("a2a", _bench_a2a, tokens=128, hidden=7168, experts=256, topk=8, iters=50)
@@ -276,7 +331,8 @@ def _run_suite(args, world, rank, group, dev, dtype, pk):
 
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser()
-    ap.add_argument("--op", required=True, choices=["gemm", "ag_gemm", "gemm_rs", "decode", "sp_decode", "a2a", "allgather", "suite"])
+    ap.add_argument("--op", required=True, choices=["gemm", "ag_gemm", "gemm_rs", "gemm_fp8", "ag_gemm_fp8", "decode", "sp_decode", "a2a", "allgather", "suite"])
+    ap.add_argument("--shape", default="", help="MxNxK in one argument (torchrun swallows a bare --m)")
     ap.add_argument("--m", type=int, default=8192)
     ap.add_argument("--n", type=int, default=6144)
     ap.add_argument("--k", type=int, default=12288)
@@ -301,8 +357,10 @@ def main(argv=None) -> int:
                     help="spin the GPU this long before each timed loop (default: 30 ms for the latency ops, 0 for GEMMs)")
     args = ap.parse_args(argv)
     global PRESLEEP_CYCLES
+    if args.shape:
+        args.m, args.n, args.k = (int(v) for v in args.shape.lower().split("x"))
     if args.presleep_ms < 0:
-        args.presleep_ms = 0.0 if args.op in ("gemm", "ag_gemm", "gemm_rs") else 30.0
+        args.presleep_ms = 0.0 if args.op in ("gemm", "ag_gemm", "gemm_rs", "gemm_fp8", "ag_gemm_fp8") else 30.0
     PRESLEEP_CYCLES = int(args.presleep_ms * 1.9e6)
 
     from .runtime import check_status, finalize_distributed, initialize_distributed
@@ -322,6 +380,8 @@ def main(argv=None) -> int:
         return 0
     if args.op in ("gemm", "ag_gemm", "gemm_rs"):
         _bench_gemm_family(args, world, rank, group, dev, dtype, pk, row)
+    elif args.op in ("gemm_fp8", "ag_gemm_fp8"):
+        _bench_gemm_fp8(args, world, rank, group, dev, dtype, pk, row)
     elif args.op in ("decode", "sp_decode"):
         _bench_decode(args, world, rank, group, dev, dtype, pk, row)
     elif args.op == "a2a":

@@ -82,6 +82,35 @@ int tdist_gemm_run(const TdistGemmArgs* args);
 /* Number of CTAs a call with these arguments launches (for occupancy planning and tests). */
 int tdist_gemm_grid(const TdistGemmArgs* args);
 
+/* Block-scaled fp8 (e4m3) GEMM, plain or fused AllGather-GEMM (csrc/kernels/gemm_fp8_sm100.cu).
+ * C[m, n] = sum_kb sa[m, kb] * sb[n / 128, kb] * dot(A[m, 128kb : 128kb+128], B[n, same]); C is bf16. */
+typedef struct TdistGemmFp8Args {
+    const void* a;       /* PLAIN: [world*m_per_rank, K] e4m3; AG: this rank's shard [m_per_rank, K] */
+    const void* sa;      /* fp32 scales of `a`, [rows, K/128] */
+    const void* b;       /* [N, K] e4m3 */
+    const void* sb;      /* fp32 [ceil(N/128), K/128] */
+    void* c;             /* bf16 [world*m_per_rank, N] */
+    /* AG: gather workspaces for rows [world, m_per_rank, K] and scales [world, m_per_rank, K/128];
+     * *_peer[r] is rank r's as mapped here. flags[world][ceil(m_per_rank/128)], 32-bit epochs. */
+    void* a_ws;
+    void* sa_ws;
+    void* a_ws_peer[TDIST_MAX_RANKS];
+    void* sa_ws_peer[TDIST_MAX_RANKS];
+    uint32_t* flags;
+    uint32_t* flags_peer[TDIST_MAX_RANKS];
+    int m_per_rank, n, k;
+    int world, rank;
+    int mode;            /* TDIST_GEMM_PLAIN or TDIST_GEMM_AG */
+    uint32_t epoch;
+    int num_sms;         /* 0 = all */
+    int num_comm_sms;    /* AG pusher CTAs, 0 = default 8 */
+    void* status;
+    uint64_t timeout_ns;
+    void* stream;
+} TdistGemmFp8Args;
+
+int tdist_gemm_fp8_run(const TdistGemmFp8Args* args);
+
 /* ------------------------------------------------------------------ standalone collectives */
 enum { TDIST_AG_PULL = 0, TDIST_AG_PUSH = 1, TDIST_AG_LL = 2 };
 

@@ -25,6 +25,7 @@ from .ops import all_to_all as A
 from .ops import collectives as CO
 from .ops import flash_decode as FD
 from .ops import gemm as G
+from .ops import gemm_fp8 as F8
 from .ops import moe_tp as MT
 from .ops import moe_utils as MU
 
@@ -94,6 +95,28 @@ def group_gemm(a_sorted: torch.Tensor, b: torch.Tensor, expert_ids: torch.Tensor
 @group_gemm.register_fake
 def _(a_sorted, b, expert_ids, num_blocks):
     return a_sorted.new_empty((a_sorted.shape[0], b.shape[1]))
+
+
+@_op("tdist::gemm_fp8", mutates_args=())
+def gemm_fp8(a: torch.Tensor, sa: torch.Tensor, b: torch.Tensor, sb: torch.Tensor) -> torch.Tensor:
+    """block-scaled e4m3 a[M,K] (sa[M,K/128]) @ b[N,K]^T (sb[N/128,K/128]) -> bf16 [M,N]"""
+    return F8.gemm_fp8_blockscaled(a, sa, b, sb)
+
+
+@gemm_fp8.register_fake
+def _(a, sa, b, sb):
+    return a.new_empty((a.shape[0], b.shape[0]), dtype=torch.bfloat16)
+
+
+@_op("tdist::ag_gemm_fp8", mutates_args=())
+def ag_gemm_fp8(a: torch.Tensor, sa: torch.Tensor, b: torch.Tensor, sb: torch.Tensor, ctx: int) -> torch.Tensor:
+    """allgather of block-scaled e4m3 rows and scales fused with the GEMM -> bf16 [M, N/ws]"""
+    return F8.ag_gemm_fp8(a, sa, b, sb, _CONTEXTS[ctx])
+
+
+@ag_gemm_fp8.register_fake
+def _(a, sa, b, sb, ctx):
+    return a.new_empty((a.shape[0] * _CONTEXTS[ctx].world, b.shape[0]), dtype=torch.bfloat16)
 
 
 # ---------------------------------------------------------------------------- collectives
@@ -223,6 +246,6 @@ def _(partials):
     return partials.new_empty(tuple(partials.shape[1:-1]) + (partials.shape[-1] - 1,), dtype=torch.bfloat16)
 
 
-OP_NAMES = ["gemm", "ag_gemm", "gemm_rs", "group_gemm", "reduce_scatter", "barrier_all", "moe_topk_softmax",
+OP_NAMES = ["gemm", "ag_gemm", "gemm_rs", "gemm_fp8", "ag_gemm_fp8", "group_gemm", "reduce_scatter", "barrier_all", "moe_topk_softmax",
             "moe_ag_scatter_align_block_size", "moe_dispatch", "moe_combine", "gqa_fwd_batch_decode",
             "gqa_fwd_batch_decode_intra_rank", "sp_gqa_fwd_batch_decode", "lse_combine"]
