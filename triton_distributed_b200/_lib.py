@@ -73,6 +73,20 @@ class GemmFp8Args(C.Structure):
     ]
 
 
+class NvlsArgs(C.Structure):
+    _fields_ = [
+        ("mc", C.c_void_p), ("local", C.c_void_p),
+        ("sig_peer", C.c_void_p * MAX_RANKS),
+        ("counters", C.c_void_p), ("output", C.c_void_p),
+        ("seg_bytes", C.c_size_t),
+        ("world", C.c_int), ("rank", C.c_int), ("op", C.c_int), ("dtype", C.c_int), ("ctas", C.c_int),
+        ("epoch", C.c_uint64),
+        ("status", C.c_void_p),
+        ("timeout_ns", C.c_uint64),
+        ("stream", C.c_void_p),
+    ]
+
+
 class CollArgs(C.Structure):
     _fields_ = [
         ("buf_peer", C.c_void_p * MAX_RANKS),
@@ -167,6 +181,7 @@ def _declare(lib):
     lib.tdist_gemm_grid.argtypes = [C.POINTER(GemmArgs)]
     lib.tdist_gemm_fp8_run.argtypes = [C.POINTER(GemmFp8Args)]
     lib.tdist_allgather.argtypes = [C.POINTER(CollArgs)]
+    lib.tdist_nvls.argtypes = [C.POINTER(NvlsArgs)]
     lib.tdist_reduce_scatter.argtypes = [C.POINTER(CollArgs)]
     lib.tdist_barrier_all.argtypes = [C.POINTER(C.c_void_p), C.c_void_p, C.c_int, C.c_int, C.c_void_p, C.c_uint64, C.c_void_p]
     lib.tdist_p2p_copy.argtypes = [C.c_void_p, C.c_void_p, C.c_size_t, C.c_int, C.c_int, C.c_int, C.c_int,

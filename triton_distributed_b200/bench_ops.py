@@ -287,6 +287,39 @@ def _bench_allgather(args, world, rank, group, dev, dtype, pk, row):
         row.update({"nccl_us": round(base, 2)})
 
 
+def _bench_nvls(args, world, rank, group, dev, dtype, pk, row):
+    """NVLS (multimem) collectives; needs TDIST_NVLS=1 in the environment so that the heap has a multicast
+    alias. `--mode` is allgather, reduce_scatter or allreduce; baseline = the same NCCL collective."""
+    from .ops import nvls as NV
+    from .runtime import symm_heap
+    n = args.bytes // (2 * 16 * world) * (16 * world)   # bf16 elements, segments of whole 16-byte vectors
+    heap = symm_heap(group)
+    buf = heap.empty((n,), torch.bfloat16)
+    row.update({"bytes": n * 2, "mode": args.mode, "multicast": NV.nvls_available(buf)})
+    if not NV.nvls_available(buf):
+        row["error"] = "no multicast alias (run with TDIST_NVLS=1 on an NVSwitch system)"
+        return
+    ctx = NV.create_nvls_context(rank, world, heap=heap, group=group, device=dev)
+    buf.local.normal_()
+    out = torch.empty(n // world, dtype=torch.bfloat16, device=dev)
+    full = torch.empty(n, dtype=torch.bfloat16, device=dev)
+    if args.mode == "allgather":
+        fn, ref = (lambda: NV.nvls_allgather(buf, ctx)), (lambda: dist.all_gather_into_tensor(full, out, group=group))
+        wire = n * 2 * (world - 1) / world
+    elif args.mode == "reduce_scatter":
+        fn, ref = (lambda: NV.nvls_reduce_scatter(buf, ctx, out)), (lambda: dist.reduce_scatter_tensor(out, full, group=group))
+        wire = n * 2 * (world - 1) / world
+    else:
+        fn, ref = (lambda: NV.nvls_allreduce(buf, ctx)), (lambda: dist.all_reduce(full, group=group))
+        wire = 2 * n * 2 * (world - 1) / world
+    us = timed_us(fn, args.iters, args.warmup, world, group)
+    row.update({"us": round(us, 2), "bus_gbps": round(wire / us / 1e3, 1)})
+    if not args.no_baseline:
+        full.zero_()
+        base = timed_us(ref, args.iters, args.warmup, world, group)
+        row.update({"nccl_us": round(base, 2), "speedup_vs_nccl": round(base / us, 3)})
+
+
 def _run_suite(args, world, rank, group, dev, dtype, pk):
     """Every headline configuration in one process (one NCCL / heap bring-up): the two tensor-parallel
     GEMMs on the m8192 n49152 k12288 problem, MoE dispatch+combine (128 tokens, hidden 7168, 256 experts,
@@ -327,11 +360,15 @@ def _run_suite(args, world, rank, group, dev, dtype, pk):
         for mode in ("pull", "push2d", "push2d_ll"):
             for nbytes in (65536, 16 << 20):
                 run("allgather", _bench_allgather, mode=mode, bytes=nbytes, iters=30)
+        if os.environ.get("TDIST_NVLS", "0") == "1":
+            for mode in ("allgather", "reduce_scatter", "allreduce"):
+                for nbytes in (65536, 16 << 20, 256 << 20):
+                    run("nvls", _bench_nvls, mode=mode, bytes=nbytes, iters=30)
 
 
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser()
-    ap.add_argument("--op", required=True, choices=["gemm", "ag_gemm", "gemm_rs", "gemm_fp8", "ag_gemm_fp8", "decode", "sp_decode", "a2a", "allgather", "suite"])
+    ap.add_argument("--op", required=True, choices=["gemm", "ag_gemm", "gemm_rs", "gemm_fp8", "ag_gemm_fp8", "decode", "sp_decode", "a2a", "allgather", "nvls", "suite"])
     ap.add_argument("--shape", default="", help="MxNxK in one argument (torchrun swallows a bare --m)")
     ap.add_argument("--m", type=int, default=8192)
     ap.add_argument("--n", type=int, default=6144)
@@ -386,6 +423,8 @@ def main(argv=None) -> int:
         _bench_decode(args, world, rank, group, dev, dtype, pk, row)
     elif args.op == "a2a":
         _bench_a2a(args, world, rank, group, dev, dtype, pk, row)
+    elif args.op == "nvls":
+        _bench_nvls(args, world, rank, group, dev, dtype, pk, row)
     else:
         _bench_allgather(args, world, rank, group, dev, dtype, pk, row)
     check_status()

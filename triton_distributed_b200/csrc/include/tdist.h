@@ -143,6 +143,30 @@ int tdist_reduce_scatter(const TdistCollArgs* args);
 int tdist_barrier_all(void* const* flags_peer, void* epoch_local, int world, int rank, void* status,
                       uint64_t timeout_ns, void* stream);
 
+/* Collectives through the NVSwitch multicast engine (csrc/kernels/nvls.cu). `mc` is the multicast alias
+ * of a symmetric buffer [world * seg_bytes] that every rank bound to one multicast object, `local` this
+ * rank's own alias. sig_peer[r] = rank r's uint64[2 * TDIST_MAX_RANKS] flags as mapped here. */
+enum { TDIST_NVLS_ALLGATHER = 0, TDIST_NVLS_REDUCE_SCATTER = 1, TDIST_NVLS_ALLREDUCE = 2 };
+
+typedef struct TdistNvlsArgs {
+    void* mc;
+    void* local;
+    void* sig_peer[TDIST_MAX_RANKS];
+    void* counters;      /* local uint32[2], zero on first use */
+    void* output;        /* reduce-scatter: local [seg_bytes]; otherwise unused (in place) */
+    size_t seg_bytes;    /* multiple of 16 */
+    int world, rank;
+    int op;              /* TDIST_NVLS_* */
+    int dtype;           /* reductions: TDIST_BF16 / TDIST_F16 / TDIST_F32 */
+    int ctas;            /* 0 = sized from seg_bytes, at most 64 */
+    uint64_t epoch;      /* strictly increasing per buffer, starts at 1 */
+    void* status;
+    uint64_t timeout_ns;
+    void* stream;
+} TdistNvlsArgs;
+
+int tdist_nvls(const TdistNvlsArgs* args);
+
 /* Peer-to-peer copy in one of five data paths (see csrc/kernels/p2p_copy.cu). */
 int tdist_p2p_copy(const void* src, void* dst, size_t bytes, int mode, int ctas, int threads, int chunk,
                    void* status, uint64_t timeout_ns, void* stream);

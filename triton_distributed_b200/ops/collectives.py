@@ -34,8 +34,9 @@ _AG_MODES = {
     "pull": _lib.AG_PULL,
     "push": _lib.AG_PUSH, "push2d": _lib.AG_PUSH, "push3d": _lib.AG_PUSH, "push_numa_2d": _lib.AG_PUSH,
     "ll": _lib.AG_LL, "push2d_ll": _lib.AG_LL, "push3d_ll": _lib.AG_LL, "push_numa_2d_ll": _lib.AG_LL,
-    "push_numa_2d_ll_multinode": _lib.AG_LL, "push2d_ll_multimem": _lib.AG_LL,
+    "push_numa_2d_ll_multinode": _lib.AG_LL, "push2d_ll_multimem": _lib.AG_LL, "nvls": _lib.AG_LL,
 }
+_NVLS_MODES = ("push2d_ll_multimem", "nvls")  # served by multimem.st when the buffer has a multicast alias, else by LL
 _RS_DTYPES = {torch.bfloat16: _lib.DT_BF16, torch.float16: _lib.DT_F16, torch.float32: _lib.DT_F32, torch.int32: _lib.DT_I32}
 
 
@@ -153,6 +154,7 @@ class FastAllGatherContext:
     epoch: int = 0
     ctas_per_peer: int = 0
     group: object = None
+    nvls: object = None                       # NvlsContext, created on the first multimem call
     _ll_arrays: object = None
 
 
@@ -197,6 +199,11 @@ def fast_allgather(symm_buffer: SymmTensor, ctx: Optional[FastAllGatherContext] 
         return local
     if nbytes > ctx.max_buffer_size:
         raise ValueError(f"buffer of {nbytes} bytes exceeds the context's max_buffer_size {ctx.max_buffer_size}")
+    if mode in _NVLS_MODES and symm_buffer.mc is not None and phase == 3 and (nbytes // ctx.world) % 16 == 0:
+        from . import nvls as NV
+        if ctx.nvls is None:
+            ctx.nvls = NV.create_nvls_context(ctx.rank, ctx.world, group=ctx.group, device=local.device)
+        return NV.nvls_allgather(symm_buffer, ctx.nvls, stream=stream)
     a = _lib.CollArgs()
     a.buf_peer = symm_buffer.cached_ptr_array()
     a.sig_peer = ctx.signal.cached_ptr_array()

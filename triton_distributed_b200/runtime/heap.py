@@ -274,7 +274,53 @@ class SymmetricHeap:
         except Exception as e:  # noqa: BLE001 - every rank must reach the agreement step
             return None, f"{stage}: {e}"
 
-        def cleanup(va=va.value, seg_bytes=seg_bytes, handles=list(handles), mapped=list(mapped)):
+        # Optional NVLS alias: rank 0 creates a multicast object, every rank adds its device and binds its
+        # own segment, then maps the object. Every step is followed by an agreement so that a rank that
+        # failed never leaves the others inside a collective.
+        mc_va, mc_handle = 0, 0
+        if self.use_nvls and self.world > 1:
+            def agree(flag: bool) -> bool:
+                t = torch.tensor([1 if flag else 0], device=self.device, dtype=torch.int32)
+                dist.all_reduce(t, op=dist.ReduceOp.MIN, group=self.group)
+                return int(t.item()) == 1
+
+            mc_err = ""
+            mch, mfd = C.c_uint64(0), C.c_int(-1)
+            good = bool(caps.value & 2)
+            if good and self.rank == 0:
+                good = lib.tdist_mc_create(self.world, C.c_size_t(seg_bytes), C.byref(mch), C.byref(mfd)) == 0
+            if agree(good):
+                mine = [mfd.value] if self.rank == 0 else [os.open(os.devnull, os.O_RDONLY)]
+                got = exchange_fds(self.group, mine)
+                if self.rank != 0:
+                    good = lib.tdist_symm_import(got[0][0], C.byref(mch)) == 0
+                close_fds([f for fl in got for f in fl])
+                good = good and lib.tdist_mc_add_device(C.c_uint64(mch.value), dev) == 0
+                if agree(good):          # every device is added before any rank binds
+                    good = lib.tdist_mc_bind(C.c_uint64(mch.value), C.c_uint64(handles[self.rank]), C.c_size_t(seg_bytes)) == 0
+                    if good:
+                        mva = C.c_uint64(0)
+                        good = (lib.tdist_symm_reserve(C.c_size_t(seg_bytes), C.byref(mva)) == 0 and
+                                lib.tdist_symm_map(C.c_uint64(mva.value), C.c_size_t(seg_bytes), C.c_uint64(mch.value), dev) == 0)
+                        if good:
+                            mc_va, mc_handle = mva.value, mch.value
+                    if not agree(good):
+                        mc_err = "bind / map failed on some rank"
+                else:
+                    mc_err = "import / add-device failed on some rank"
+            else:
+                mc_err = "device without multicast support, or cuMulticastCreate failed"
+            if mc_err:
+                mc_va = 0
+                if self.rank == 0:
+                    print(f"[tdist] NVLS multicast unavailable ({mc_err}); multimem ops will refuse to run", flush=True)
+
+        def cleanup(va=va.value, seg_bytes=seg_bytes, handles=list(handles), mapped=list(mapped), mc_va=mc_va, mc_handle=mc_handle):
+            if mc_va:
+                lib.tdist_symm_unmap(C.c_uint64(mc_va), C.c_size_t(seg_bytes))
+                lib.tdist_symm_address_free(C.c_uint64(mc_va), C.c_size_t(seg_bytes))
+                lib.tdist_mc_unbind(C.c_uint64(mc_handle), dev, C.c_size_t(seg_bytes))
+                lib.tdist_symm_release(C.c_uint64(mc_handle))
             for r in mapped:
                 lib.tdist_symm_unmap(C.c_uint64(va + r * seg_bytes), C.c_size_t(seg_bytes))
             if va:
@@ -284,7 +330,8 @@ class SymmetricHeap:
                     lib.tdist_symm_release(C.c_uint64(hdl))
 
         peer_u8 = [tensor_from_ptr(va.value + r * seg_bytes, seg_bytes, self.device) for r in range(self.world)]
-        seg = _Segment(seg_bytes, peer_u8[self.rank], peer_u8, None, cleanup)
+        mc_u8 = tensor_from_ptr(mc_va, seg_bytes, self.device) if mc_va else None
+        seg = _Segment(seg_bytes, peer_u8[self.rank], peer_u8, mc_u8, cleanup)
         seg.base_va = va.value
         seg.handles = handles
         return seg, ""
