@@ -73,3 +73,32 @@ def test_cpu_restatements_agree_with_each_other():
     # lse merge of one part is the identity
     part = torch.cat([torch.randn(2, 3, 8), torch.randn(2, 3, 1)], -1)
     torch.testing.assert_close(FD.ref_lse_merge(part.unsqueeze(0)), part[..., :-1])
+
+
+def test_parallel_strategies_on_cpu():
+    """The strategy layer on one CPU process: column/row parallel linears (bf16-free fp32 path and the fp8
+    path), sequence sharding arithmetic, expert placement."""
+    import torch
+    from triton_distributed_b200 import parallel as P
+
+    st = P.init_parallel_state()
+    assert st.world == 1 and st.is_single_node and st.nnodes == 1
+    g = torch.Generator().manual_seed(0)
+    w, x = torch.randn(64, 256, generator=g), torch.randn(8, 256, generator=g)
+    torch.testing.assert_close(P.ColumnParallelLinear(w, 64, st)(x), x @ w.t(), rtol=1e-4, atol=1e-4)
+    w2 = torch.randn(128, 256, generator=g)
+    torch.testing.assert_close(P.RowParallelLinear(w2, 64, st)(x), x @ w2.t(), rtol=1e-4, atol=1e-4)
+    y8 = P.ColumnParallelLinear(w, 64, st, fp8=True)(x).float()
+    assert (y8 - x @ w.t()).abs().max() < 0.1 * (x @ w.t()).abs().max()
+    lens = torch.tensor([10, 100, 3, 0])
+    per_rank = P.kv_lens_per_rank(lens, 4)
+    assert per_rank.shape == (4, 4) and torch.equal(per_rank.sum(0), lens.to(torch.int32))
+    assert per_rank[:, 1].tolist() == [25, 25, 25, 25] and per_rank[:, 0].tolist() == [3, 3, 3, 1]
+    kv = P.SequenceParallelKVCache.allocate(2, 100, 2, 8, 1, 4, device="cpu", dtype=torch.float32)
+    assert kv.write(0, torch.ones(2, 8), torch.ones(2, 8), 30, 100) and not kv.write(0, torch.ones(2, 8), torch.ones(2, 8), 3, 100)
+    ep = P.ExpertPlacement(8, 4)
+    assert ep.owner(torch.tensor([0, 3, 7])).tolist() == [0, 1, 3]
+    assert ep.send_counts(torch.tensor([[0, 3], [7, 7]])).tolist() == [[1, 0], [0, 1], [0, 0], [0, 2]]
+    assert list(P.experts_of_rank(8, 2, 4)) == [4, 5]
+    assert P.shard_rows(torch.arange(8).view(4, 2), 1, 2).tolist() == [[4, 5], [6, 7]]
+    assert P.shard_columns(torch.arange(8).view(2, 4), 1, 2).tolist() == [[2, 3], [6, 7]]
