@@ -98,10 +98,13 @@ class SymmTensor:
         nbytes = math.prod(shape) * torch.empty((), dtype=dtype).element_size()
 
         def cut(t: torch.Tensor) -> torch.Tensor:
+            if t.numel() == 0:  # host heap: copies of other processes are not mapped
+                return torch.empty(0, dtype=dtype)
             flat = t.reshape(-1).view(torch.uint8)
             return flat[offset_bytes: offset_bytes + nbytes].view(dtype).view(*shape)
 
-        return SymmTensor(cut(self.local), [cut(t) for t in self.peers], self.rank,
+        local = cut(self.local)
+        return SymmTensor(local, [local if t is self.local else cut(t) for t in self.peers], self.rank,
                           None if self.mc is None else cut(self.mc))
 
 
