@@ -350,6 +350,11 @@ def _run_suite(args, world, rank, group, dev, dtype, pk):
     run("ag_gemm", _bench_gemm_family, m=8192, n=49152, k=12288)
     run("gemm_rs", _bench_gemm_family, m=8192, n=12288, k=49152)
     run("ag_gemm_fp8", _bench_gemm_fp8, m=8192, n=49152, k=12288)
+    # the shapes of the reference's published intra-node charts (speed-up over PyTorch + NCCL on 8 x H800)
+    for (n, k) in ((11008, 4096), (14336, 4096), (28672, 8192), (53248, 16384), (29568, 8192)):
+        run("ag_gemm", _bench_gemm_family, m=8192, n=n, k=k)
+    for (n, k) in ((4096, 11008), (4096, 14336), (3584, 14336), (4608, 36864), (8192, 28672), (8192, 29568)):
+        run("gemm_rs", _bench_gemm_family, m=8192, n=n, k=k)
     PRESLEEP_CYCLES = int(30 * 1.9e6)
     if world > 1 or True:
         run("a2a", _bench_a2a, tokens=128, hidden=7168, experts=256, topk=8, iters=50)
