@@ -4,10 +4,10 @@ A producer writes data into a peer's symmetric buffer and then *notifies* a flag
 *waits* on its own flag before it touches the data. In CUDA (``csrc/device/signal.cuh``):
 
     // producer (one thread, after the CTA's stores and a __syncthreads):
-    tdist::notify(win, flag, peer, value, tdist::kSignalSet, tdist::kScopeSys);   // fence + st.release.sys
-    // consumer:
-    tdist::wait(flag, 1, value, tdist::kScopeSys, wctx);                          // bounded ld.acquire.sys spin
-    token = ...; data = tdist::consume_token(data_ptr, token);                   // keeps loads after the wait
+    tdist::notify(win, flag, peer, value, tdist::kSignalSet);    // fence.acq_rel.sys + st.release.sys on the peer
+    // consumer (one warp):
+    bool token = tdist::wait(flag, 1, value, wctx);              // bounded ld.acquire.sys spin
+    data = tdist::consume_token(data, token);                    // + async-proxy fence if TMA reads the data next
 
 Every wait has a time limit: a flag that never comes makes the kernel record (kernel, rank, peer, site) in
 the status block and return, instead of hanging the GPU. ``check_status()`` turns that record into an
