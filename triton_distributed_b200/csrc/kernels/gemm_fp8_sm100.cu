@@ -101,14 +101,20 @@ __device__ __forceinline__ TileCoord decode_tile(int t, int first_seg, int world
     return c;
 }
 
-// acc2[0..8) (pairs of fp32) += r[0..16) * scale, two lanes per fma.rn.f32x2.
-__device__ __forceinline__ void fold(unsigned long long* acc2, const uint32_t (&r)[16], unsigned long long s2) {
+// acc2[0..N/2) (pairs of fp32) += r[0..N) * scale, two lanes per fma.rn.f32x2.
+template <int N>
+__device__ __forceinline__ void fold(unsigned long long* acc2, const uint32_t (&r)[N], unsigned long long s2) {
 #pragma unroll
-    for (int i = 0; i < 8; ++i) {
+    for (int i = 0; i < N / 2; ++i) {
         unsigned long long v;
         asm("mov.b64 %0, {%1, %2};" : "=l"(v) : "r"(r[2 * i]), "r"(r[2 * i + 1]));
         asm("fma.rn.f32x2 %0, %1, %2, %0;" : "+l"(acc2[i]) : "l"(v), "l"(s2));
     }
+}
+template <int N>
+__device__ __forceinline__ void tmem_ld_cols(uint32_t taddr, uint32_t (&r)[N]) {
+    if constexpr (N == 8) tmem_ld_32x8(taddr, r);
+    else tmem_ld_32x16(taddr, r);
 }
 
 // Pusher CTA: for each (destination, 128-row block) item all threads store the rows' scales into the
@@ -175,6 +181,7 @@ __device__ void pusher(const Params& p, uint8_t* smem, uint64_t* bars) {
     }
 }
 
+template <int STG>
 __global__ void __launch_bounds__(THREADS, 1) gemm_fp8_kernel(const __grid_constant__ Params p) {
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -314,26 +321,27 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_fp8_kernel(const __grid_const
                 mbar_wait(bar_tfull(buf), (it >> 1) & 1u, p.wctx, 5);
                 tc_fence_after();
                 const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + buf * BN + half * 128;
-                // Two 16-register staging buffers (the load of chunk c+1 is in flight while chunk c is folded in):
+                // Two STG-register staging buffers (the load of chunk c+1 is in flight while chunk c is folded in):
                 // with 128 accumulators per thread wider ones do not fit the 168 registers a 10-warp CTA gets,
                 // and spills inside this loop cost more than the wider loads gain.
-                uint32_t r0[16], r1[16];
-                tmem_ld_32x16(taddr, r0);
+                constexpr int NCH = 128 / STG;
+                uint32_t r0[STG], r1[STG];
+                tmem_ld_cols<STG>(taddr, r0);
 #pragma unroll
-                for (int c = 0; c < 8; c += 2) {
+                for (int c = 0; c < NCH; c += 2) {
                     tmem_ld_wait();
-                    tmem_ld_32x16(taddr + 16 * (c + 1), r1);
-                    fold(acc + 8 * c, r0, scale);
+                    tmem_ld_cols<STG>(taddr + STG * (c + 1), r1);
+                    fold<STG>(acc + (STG / 2) * c, r0, scale);
                     tmem_ld_wait();
-                    if (c + 2 < 8) {
-                        tmem_ld_32x16(taddr + 16 * (c + 2), r0);
+                    if (c + 2 < NCH) {
+                        tmem_ld_cols<STG>(taddr + STG * (c + 2), r0);
                     } else {
                         // the block's partial sums are in registers: hand the TMEM buffer back to the MMA issuer
                         tc_fence_before();
                         __syncwarp();
                         if (lane == 0) mbar_arrive(bar_tempty(buf));
                     }
-                    fold(acc + 8 * (c + 1), r1, scale);
+                    fold<STG>(acc + (STG / 2) * (c + 1), r1, scale);
                 }
             }
             // ---- epilogue: this warp's 128 columns in two passes of 64, one staging buffer per column half
@@ -393,8 +401,8 @@ int fp8_resident_ctas() {
     if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return tdist_host::sm_count();
     if (cache[dev] > 0) return cache[dev];
     int result = 0, per_sm = 0;
-    if (cudaFuncSetAttribute(gemm_fp8_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES) == cudaSuccess &&
-        cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, gemm_fp8_kernel, THREADS, SMEM_BYTES) == cudaSuccess && per_sm > 0)
+    if (cudaFuncSetAttribute(gemm_fp8_kernel<16>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES) == cudaSuccess &&
+        cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, gemm_fp8_kernel<16>, THREADS, SMEM_BYTES) == cudaSuccess && per_sm > 0)
         result = per_sm * tdist_host::sm_count();
     cudaGetLastError();
     if (result <= 0) result = tdist_host::sm_count();
@@ -480,7 +488,8 @@ extern "C" int tdist_gemm_fp8_run(const TdistGemmFp8Args* a) {
     int gemm_ctas = sms - p.num_comm;
     if (gemm_ctas > p.num_tiles) gemm_ctas = p.num_tiles;
     void* kargs[] = {&p};
-    TDIST_CUDA_OK(cudaLaunchKernel(reinterpret_cast<const void*>(&gemm_fp8_kernel), dim3(gemm_ctas + p.num_comm), dim3(THREADS), kargs,
+    const void* fn = reinterpret_cast<const void*>(&gemm_fp8_kernel<16>);  // 8-column staging measured the same
+    TDIST_CUDA_OK(cudaLaunchKernel(fn, dim3(gemm_ctas + p.num_comm), dim3(THREADS), kargs,
                                    SMEM_BYTES, static_cast<cudaStream_t>(a->stream)));
     return 0;
 }

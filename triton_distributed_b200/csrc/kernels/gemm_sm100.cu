@@ -205,8 +205,16 @@ __device__ __forceinline__ void rs_reduce_tile(const GemmParams& p, int block, i
         const int cv = v - r * vec_per_row;
         const size_t off = static_cast<size_t>(row0 + r) * p.n + col0 + cv * 8;
         float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-        for (int s = 0; s < p.world; ++s) {
-            const uint4 q = *reinterpret_cast<const uint4*>(p.stage_local + (s * slot + off) * 2);
+        // all sources' loads are issued before the first add: one dependent load per source would leave
+        // the tail latency-bound (it reads world x the output's size)
+        uint4 qs[kMaxRanks];
+#pragma unroll
+        for (int s = 0; s < kMaxRanks; ++s)
+            if (s < p.world) qs[s] = *reinterpret_cast<const uint4*>(p.stage_local + (s * slot + off) * 2);
+#pragma unroll
+        for (int s = 0; s < kMaxRanks; ++s) {
+            if (s >= p.world) break;
+            const uint4 q = qs[s];
             const uint32_t w[4] = {q.x, q.y, q.z, q.w};
 #pragma unroll
             for (int i = 0; i < 4; ++i) {

@@ -255,6 +255,8 @@ def gemm_rs(a: torch.Tensor, b: torch.Tensor, ctx: GEMMReduceScatterTensorParall
     if mpr > ctx.max_m_per_rank or N != ctx.n:
         raise ValueError(f"problem [{M},{N}] exceeds the context (max rows/rank {ctx.max_m_per_rank}, N {ctx.n})")
     o = out if out is not None else torch.empty((mpr, N), dtype=a.dtype, device=a.device)
+    if ctx.world == 1:
+        return gemm_persistent(a, b, out=o, num_sms=ctx.num_sms)  # nothing to scatter or reduce: skip the staging pass
     g = _base_args(a, b, ctx.world, ctx.rank, _lib.GEMM_RS)
     g.m_per_rank = mpr
     ctx.epoch += 1
