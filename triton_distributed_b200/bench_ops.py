@@ -373,7 +373,7 @@ def _run_suite(args, world, rank, group, dev, dtype, pk):
 
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser()
-    ap.add_argument("--op", required=True, choices=["gemm", "ag_gemm", "gemm_rs", "gemm_fp8", "ag_gemm_fp8", "decode", "sp_decode", "a2a", "allgather", "nvls", "suite"])
+    ap.add_argument("--op", required=True, choices=["gemm", "ag_gemm", "gemm_rs", "gemm_fp8", "ag_gemm_fp8", "decode", "sp_decode", "a2a", "allgather", "nvls", "nvls_suite", "suite"])
     ap.add_argument("--shape", default="", help="MxNxK in one argument (torchrun swallows a bare --m)")
     ap.add_argument("--m", type=int, default=8192)
     ap.add_argument("--n", type=int, default=6144)
@@ -414,6 +414,23 @@ def main(argv=None) -> int:
     dtype = torch.bfloat16 if args.dtype == "bf16" else torch.float16
     pk = peaks()
     row = {"op": args.op, "world": world, "dtype": args.dtype, "peaks": pk["source"]}
+    if args.op == "nvls_suite":
+        import copy
+        for mode in ("allgather", "reduce_scatter", "allreduce"):
+            for nbytes in (65536, 16 << 20, 256 << 20):
+                a2 = copy.copy(args)
+                a2.op, a2.mode, a2.bytes = "nvls", mode, nbytes
+                r2 = {"op": "nvls", "world": world, "dtype": "bf16", "peaks": pk["source"]}
+                try:
+                    _bench_nvls(a2, world, rank, group, dev, dtype, pk, r2)
+                except Exception as e:  # noqa: BLE001 - keep the other rows
+                    r2["error"] = repr(e)[:300]
+                if rank == 0:
+                    print(json.dumps(r2), flush=True)
+        check_status()
+        if dist.is_initialized():
+            finalize_distributed()
+        return 0
     if args.op == "suite":
         _run_suite(args, world, rank, group, dev, dtype, pk)
         check_status()
