@@ -87,3 +87,36 @@ def test_grid_barrier_random_grids(cuda_device):
         P.run_primitive(ctx, "grid_barrier", value=it * 1000, grid=rng.randint(1, 148))
     check_status()
     assert int(ctx.result[0]) == 0  # no CTA saw a stale neighbour
+
+
+def test_host_stream_ops_put_signal_wait(cuda_device):
+    """pynvshmem-style host API on emulated ranks of one GPU: rank 0 puts a block into rank 1 and raises a
+    signal in stream order; rank 1's stream-ordered wait passes; a wait on a word nothing sets runs out and
+    reports instead of blocking the stream for good."""
+    import torch
+    from triton_distributed_b200 import _lib
+    from triton_distributed_b200.runtime import LocalWorld, check_status, shmem_host as SH
+
+    lw = LocalWorld(2, cuda_device)
+    data = [lw.heap(r).zeros((4096,), torch.float32) for r in range(2)]
+    sig = [lw.heap(r).zeros((8,), torch.int64) for r in range(2)]
+    src = torch.arange(4096, device=cuda_device, dtype=torch.float32)
+    SH.putmem_signal_on_stream(data[0], src, sig[0], 3, 5, SH.NVSHMEM_SIGNAL_SET, pe=1)
+    SH.signal_op_on_stream(sig[0], 3, 2, SH.NVSHMEM_SIGNAL_ADD, pe=1)
+    SH.signal_wait_until_on_stream(sig[1], 3, SH.NVSHMEM_CMP_EQ, 7)
+    torch.cuda.synchronize()
+    check_status()
+    assert torch.equal(data[1].local, src) and int(sig[1].local[3]) == 7
+    got = torch.empty_like(src)
+    SH.getmem_on_stream(got, data[0], pe=1)
+    torch.cuda.synchronize()
+    assert torch.equal(got, src)
+    # a flag that nothing sets: the wait gives up after its limit (0.2 s here) and says so
+    from triton_distributed_b200.runtime import global_status
+    _lib.check(_lib.lib().tdist_signal_wait_on_stream(sig[1].local.data_ptr() + 8 * 5, SH.NVSHMEM_CMP_GE, 1, global_status().device_ptr,
+                                                      200_000_000, torch.cuda.current_stream().cuda_stream), "wait")
+    torch.cuda.synchronize()
+    with pytest.raises(_lib.TdistTimeoutError):
+        check_status()
+    torch.cuda.synchronize()
+    check_status()  # the record was cleared and the context still works

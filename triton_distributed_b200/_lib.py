@@ -187,6 +187,8 @@ def _declare(lib):
     lib.tdist_p2p_copy.argtypes = [C.c_void_p, C.c_void_p, C.c_size_t, C.c_int, C.c_int, C.c_int, C.c_int,
                                    C.c_void_p, C.c_uint64, C.c_void_p]
     lib.tdist_a2a.argtypes = [C.POINTER(A2AArgs)]
+    lib.tdist_signal_op_on_stream.argtypes = [C.c_void_p, C.c_uint64, C.c_int, C.c_void_p]
+    lib.tdist_signal_wait_on_stream.argtypes = [C.c_void_p, C.c_int, C.c_uint64, C.c_void_p, C.c_uint64, C.c_void_p]
     lib.tdist_primitive.argtypes = [C.POINTER(PrimArgs)]
     lib.tdist_flash_decode.argtypes = [C.POINTER(DecodeArgs)]
     lib.tdist_lse_combine.argtypes = [C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_int, C.c_void_p]

@@ -171,6 +171,12 @@ int tdist_nvls(const TdistNvlsArgs* args);
 int tdist_p2p_copy(const void* src, void* dst, size_t bytes, int mode, int ctas, int threads, int chunk,
                    void* status, uint64_t timeout_ns, void* stream);
 
+/* Stream-ordered signal operations on an address of this process (a peer's flag as mapped here, or a
+ * local one). sig_op: 9 = set, 10 = add. cmp: 0 EQ, 1 NE, 2 GT, 3 LE, 4 LT, 5 GE. The wait is bounded and
+ * reports through `status` like every device wait. */
+int tdist_signal_op_on_stream(void* sig, uint64_t value, int sig_op, void* stream);
+int tdist_signal_wait_on_stream(const void* sig, int cmp, uint64_t value, void* status, uint64_t timeout_ns, void* stream);
+
 /* ------------------------------------------------------------------ MoE all-to-all */
 enum { TDIST_A2A_DISPATCH = 0, TDIST_A2A_COMBINE = 1 };
 

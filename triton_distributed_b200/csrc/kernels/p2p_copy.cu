@@ -173,3 +173,38 @@ extern "C" int tdist_p2p_copy(const void* src, void* dst, size_t bytes, int mode
     TDIST_CUDA_OK(cudaGetLastError());
     return 0;
 }
+
+// ---- stream-ordered signal operations on raw (already peer-mapped) addresses: the host face of
+// signal_op / signal_wait_until (reference pynvshmem putmem_signal_on_stream, common_ops.py set_signal / wait_eq).
+namespace tdist {
+__global__ void signal_op_kernel(uint64_t* sig, uint64_t value, int sig_op) {
+    // everything the stream did before this kernel (e.g. the copy of putmem_signal_on_stream) is complete
+    fence_acq_rel_sys();
+    if (sig_op == kSignalAdd) red_release_sys_add_u64(sig, value);
+    else st_release_sys_u64(sig, value);
+}
+__global__ void signal_wait_kernel(const uint64_t* sig, int cmp, uint64_t value, WaitCtx wctx) {
+    signal_wait_until(sig, cmp, value, wctx, -1, 1);
+}
+}  // namespace tdist
+
+extern "C" int tdist_signal_op_on_stream(void* sig, uint64_t value, int sig_op, void* stream) {
+    if (sig == nullptr || (reinterpret_cast<uintptr_t>(sig) & 7)) return tdist_host::fail(TDIST_EINVAL, "signal_op: the signal must be an 8-byte aligned address");
+    if (sig_op != tdist::kSignalSet && sig_op != tdist::kSignalAdd) return tdist_host::fail(TDIST_EINVAL, "signal_op: sig_op must be 9 (set) or 10 (add)");
+    tdist::signal_op_kernel<<<1, 1, 0, static_cast<cudaStream_t>(stream)>>>(static_cast<uint64_t*>(sig), value, sig_op);
+    TDIST_CUDA_OK(cudaGetLastError());
+    return 0;
+}
+
+extern "C" int tdist_signal_wait_on_stream(const void* sig, int cmp, uint64_t value, void* status, uint64_t timeout_ns, void* stream) {
+    if (sig == nullptr || (reinterpret_cast<uintptr_t>(sig) & 7)) return tdist_host::fail(TDIST_EINVAL, "signal_wait: the signal must be an 8-byte aligned address");
+    if (cmp < 0 || cmp > 5) return tdist_host::fail(TDIST_EINVAL, "signal_wait: cmp must be 0..5 (EQ NE GT LE LT GE)");
+    tdist::WaitCtx w;
+    w.status = static_cast<tdist::Status*>(status);
+    w.timeout_ns = timeout_ns;
+    w.kernel_id = tdist::kKernelCopy;
+    w.rank = 0;
+    tdist::signal_wait_kernel<<<1, 1, 0, static_cast<cudaStream_t>(stream)>>>(static_cast<const uint64_t*>(sig), cmp, value, w);
+    TDIST_CUDA_OK(cudaGetLastError());
+    return 0;
+}

@@ -1,0 +1,121 @@
+"""Host-side symmetric-memory API with the reference's pynvshmem names.
+
+(reference shmem/nvshmem_bind/pynvshmem/src/pynvshmem.cc:107-215 and python/pynvshmem/__init__.py:93-171.)
+There is no NVSHMEM underneath: tensors come from :class:`SymmetricHeap`, "put" is a copy kernel of this
+library writing through the peer mapping, signals are 8-byte words in symmetric memory written with
+``st.release.sys`` / ``red.release.sys.add`` by a one-thread kernel in stream order, waits are bounded.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from typing import List, Optional, Sequence
+
+import torch
+import torch.distributed as dist
+
+from .. import _lib
+from .dist import symm_heap
+from .heap import SymmTensor
+from .status import default_timeout_ns, global_status
+
+NVSHMEM_CMP_EQ, NVSHMEM_CMP_NE, NVSHMEM_CMP_GT, NVSHMEM_CMP_LE, NVSHMEM_CMP_LT, NVSHMEM_CMP_GE = range(6)
+NVSHMEM_SIGNAL_SET, NVSHMEM_SIGNAL_ADD = 9, 10
+
+
+def _stream(device, stream=None) -> int:
+    return (stream or torch.cuda.current_stream(device)).cuda_stream
+
+
+def nvshmem_my_pe() -> int:
+    return dist.get_rank() if dist.is_initialized() else 0
+
+
+def nvshmem_n_pes() -> int:
+    return dist.get_world_size() if dist.is_initialized() else 1
+
+
+def nvshmem_create_tensor(shape: Sequence[int], dtype: torch.dtype) -> SymmTensor:
+    """A symmetric tensor: ``.local`` is this rank's copy, ``.peers[r]`` rank r's copy as mapped here."""
+    return symm_heap().empty(shape, dtype)
+
+
+def nvshmem_create_tensor_list_intra_node(shape: Sequence[int], dtype: torch.dtype) -> List[torch.Tensor]:
+    """The reference's list form: one tensor per local rank, entry ``rank`` being the local copy."""
+    return list(symm_heap().empty(shape, dtype).peers)
+
+
+symm_tensor = nvshmem_create_tensor
+
+
+def nvshmem_barrier_all() -> None:
+    symm_heap().barrier()
+
+
+def nvshmem_ptr(t: SymmTensor, pe: int) -> int:
+    """Address of rank ``pe``'s copy in this process."""
+    return t.ptrs[pe]
+
+
+def putmem_on_stream(dst: SymmTensor, src: torch.Tensor, pe: int, stream=None) -> None:
+    """Copy ``src`` (local) into rank ``pe``'s copy of ``dst``, stream-ordered."""
+    target = dst.peers[pe].reshape(-1).view(torch.uint8)
+    flat = src.contiguous().reshape(-1).view(torch.uint8)
+    n = flat.numel()
+    if n > target.numel():
+        raise ValueError("source larger than the symmetric destination")
+    if src.device.type != "cuda":
+        raise ValueError("putmem_on_stream moves device memory; on CPU use torch.distributed")
+    if n % 16 == 0 and flat.data_ptr() % 16 == 0 and target.data_ptr() % 16 == 0:
+        st = global_status()
+        _lib.check(_lib.lib().tdist_p2p_copy(flat.data_ptr(), target.data_ptr(), n, 0, min(64, max(1, n // 65536)), 512, 0,
+                                             st.device_ptr if st is not None else None, default_timeout_ns(),
+                                             _stream(src.device, stream)), "tdist_p2p_copy")
+    else:
+        with torch.cuda.stream(stream) if stream is not None else _null():
+            target[:n].copy_(flat)  # odd sizes: the driver's memcpy
+
+
+def getmem_on_stream(dst: torch.Tensor, src: SymmTensor, pe: int, stream=None) -> None:
+    """Copy rank ``pe``'s copy of ``src`` into the local tensor ``dst``, stream-ordered."""
+    source = src.peers[pe].reshape(-1).view(torch.uint8)
+    flat = dst.reshape(-1).view(torch.uint8)
+    n = flat.numel()
+    if n % 16 == 0 and flat.data_ptr() % 16 == 0 and source.data_ptr() % 16 == 0:
+        st = global_status()
+        _lib.check(_lib.lib().tdist_p2p_copy(source.data_ptr(), flat.data_ptr(), n, 0, min(64, max(1, n // 65536)), 512, 0,
+                                             st.device_ptr if st is not None else None, default_timeout_ns(),
+                                             _stream(dst.device, stream)), "tdist_p2p_copy")
+    else:
+        with torch.cuda.stream(stream) if stream is not None else _null():
+            flat.copy_(source[:n])
+
+
+def signal_op_on_stream(sig: SymmTensor, index: int, value: int, sig_op: int, pe: int, stream=None) -> None:
+    """Set (9) or add (10) ``value`` on word ``index`` of rank ``pe``'s copy of the int64 signal array, after
+    everything the stream did before."""
+    addr = sig.ptrs[pe] + 8 * index
+    _lib.check(_lib.lib().tdist_signal_op_on_stream(addr, value, sig_op, _stream(sig.local.device, stream)), "tdist_signal_op_on_stream")
+
+
+def putmem_signal_on_stream(dst: SymmTensor, src: torch.Tensor, sig: SymmTensor, index: int, value: int, sig_op: int, pe: int,
+                            stream=None) -> None:
+    """``putmem_on_stream`` followed by the signal: the data is complete at ``pe`` before the signal is."""
+    putmem_on_stream(dst, src, pe, stream)
+    signal_op_on_stream(sig, index, value, sig_op, pe, stream)
+
+
+def signal_wait_until_on_stream(sig: SymmTensor, index: int, cmp: int, value: int, stream=None) -> None:
+    """Block the stream until the local signal word compares true, with the library's wait limit: on expiry
+    the status block records it (``check_status()`` raises) and the stream moves on."""
+    st = global_status()
+    _lib.check(_lib.lib().tdist_signal_wait_on_stream(sig.local.data_ptr() + 8 * index, cmp, value,
+                                                      st.device_ptr if st is not None else None, default_timeout_ns(),
+                                                      _stream(sig.local.device, stream)), "tdist_signal_wait_on_stream")
+
+
+class _null:
+    def __enter__(self):
+        return self
+
+    def __exit__(self, *a):
+        return False
