@@ -69,6 +69,7 @@ def main():
             if cuda:
                 symm_heap().barrier()
     res["ag_max_err"] = ag_err
+    res["ag_multicast_pusher"] = bool(cuda and ctx is not None and ctx.workspace is not None and ctx.workspace.mc is not None and G.AG_NVLS)
 
     # ---------------- GEMM-RS ----------------
     shapes = [(128, 256, 128), (250, 520, 264), (1024, 2048, 1024)] if cuda else [(128, 256, 128)]
@@ -135,4 +136,14 @@ def main():
 
 
 if __name__ == "__main__":
-    main()
+    try:
+        main()
+    except BaseException:
+        # leave in an orderly way: the heap is closed (memory unbound from any multicast object) before exit
+        import traceback
+        traceback.print_exc()
+        try:
+            finalize_distributed()
+        except Exception:  # noqa: BLE001
+            pass
+        sys.exit(1)

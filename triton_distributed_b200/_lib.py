@@ -54,6 +54,7 @@ class GemmArgs(C.Structure):
         ("stream", C.c_void_p),
         ("trace", C.c_void_p),
         ("expert_ids", C.c_void_p), ("num_m_blocks", C.c_void_p), ("num_experts", C.c_int),
+        ("a_ws_mc", C.c_void_p),
     ]
 
 

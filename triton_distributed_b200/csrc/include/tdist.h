@@ -76,6 +76,9 @@ typedef struct TdistGemmArgs {
     const void* expert_ids;
     const void* num_m_blocks;
     int num_experts;
+    /* AG, optional: multicast alias of `a_ws` (a heap bound to an NVSwitch multicast object). When set, the
+     * pushers store every block once with multimem.st instead of once per peer. */
+    void* a_ws_mc;
 } TdistGemmArgs;
 
 int tdist_gemm_run(const TdistGemmArgs* args);

@@ -80,6 +80,7 @@ struct GemmParams {
     const char* a_own;            // AG pusher source
     char* a_ws_peer[kMaxRanks];
     const char* stage_local;      // RS reduce source [world][m_per_rank][N]
+    char* a_ws_mc;                // AG: multicast alias of the gather workspace (NVLS pusher), or nullptr
     void* rs_out;
     uint32_t* flags;
     uint32_t* flags_peer[kMaxRanks];
@@ -190,6 +191,64 @@ __device__ void ag_pusher(const GemmParams& p, uint8_t* smem, uint64_t* bars) {
 }
 
 // ------------------------------------------------------------------------------------------
+// AG pusher through the NVSwitch multicast engine: the workspace is bound to a multicast object, so ONE
+// multimem.st per 16 bytes lands in every rank's workspace. A pusher CTA owns whole 128-row blocks: thread
+// 0 streams the block into shared memory with bulk loads, all threads replay it from shared memory as
+// multimem.st, then one flag per peer is raised. A seventh of the stores of the unicast pusher, hence
+// far fewer CTAs taken from the GEMM.
+// ------------------------------------------------------------------------------------------
+__device__ __forceinline__ void multimem_st_v4(char* mc_addr, const uint4& v) {
+    asm volatile("multimem.st.weak.global.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(mc_addr), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w)
+                 : "memory");
+}
+__device__ void ag_pusher_nvls(const GemmParams& p, uint8_t* smem, uint64_t* bars) {
+    const int tid = static_cast<int>(threadIdx.x);
+    const size_t row_bytes = static_cast<size_t>(p.k) * 2;
+    uint32_t it_load = 0, it_use = 0;  // running chunk counters, the same in every thread
+    for (int mb = static_cast<int>(blockIdx.x); mb < p.seg_blocks; mb += p.num_comm) {
+        const int rows = min(BM, p.m_per_rank - mb * BM);
+        const size_t bytes = static_cast<size_t>(rows) * row_bytes;
+        const char* src = p.a_own + static_cast<size_t>(mb) * BM * row_bytes;
+        char* out = p.a_ws_mc + (static_cast<size_t>(p.rank) * p.m_per_rank + static_cast<size_t>(mb) * BM) * row_bytes;
+        const int nchunks = static_cast<int>((bytes + PUSH_CHUNK - 1) / PUSH_CHUNK);
+        if (p.debug_delay_ns > 0) __nanosleep(p.debug_delay_ns);
+        for (int c = 0; c < nchunks + PUSH_AHEAD; ++c) {
+            if (c < nchunks) {
+                // slot it_load % PUSH_STAGES was last read as chunk it_load - PUSH_STAGES, i.e. before the
+                // __syncthreads of an earlier iteration (PUSH_STAGES - 1 >= PUSH_AHEAD)
+                if (tid == 0) {
+                    const uint32_t s = it_load % PUSH_STAGES;
+                    const size_t off = static_cast<size_t>(c) * PUSH_CHUNK;
+                    const uint32_t sz = static_cast<uint32_t>(min(static_cast<size_t>(PUSH_CHUNK), bytes - off));
+                    mbar_expect_tx(smem_u32(&bars[s]), sz);
+                    bulk_load(smem_u32(smem + s * PUSH_CHUNK), src + off, sz, smem_u32(&bars[s]));
+                }
+                ++it_load;
+            }
+            if (c >= PUSH_AHEAD) {
+                const int cs = c - PUSH_AHEAD;
+                const uint32_t s = it_use % PUSH_STAGES;
+                mbar_wait(smem_u32(&bars[s]), (it_use / PUSH_STAGES) & 1u, p.wctx, 11);
+                const size_t off = static_cast<size_t>(cs) * PUSH_CHUNK;
+                const uint32_t sz = static_cast<uint32_t>(min(static_cast<size_t>(PUSH_CHUNK), bytes - off));
+                const uint8_t* buf = smem + s * PUSH_CHUNK;
+                for (uint32_t i = static_cast<uint32_t>(tid) * 16u; i < sz; i += THREADS * 16u)
+                    multimem_st_v4(out + off + i, *reinterpret_cast<const uint4*>(buf + i));
+                ++it_use;
+                __syncthreads();  // the slot is fully replayed before thread 0 may refill it
+            }
+        }
+        // every thread's stores were issued before the barrier above; thread 0's fence orders them
+        // (cumulatively) before the flags
+        if (tid == 0) {
+            fence_acq_rel_sys();
+            for (int r = 0; r < p.world; ++r)
+                if (r != p.rank) st_release_sys_u32(p.flags_peer[r] + p.rank * p.seg_blocks + mb, p.epoch);
+        }
+    }
+}
+
+// ------------------------------------------------------------------------------------------
 // RS reduce: sum the `world` partial copies of one owned tile in fp32, write bf16/f16.
 // ------------------------------------------------------------------------------------------
 __device__ __forceinline__ void rs_reduce_tile(const GemmParams& p, int block, int n_tile) {
@@ -265,7 +324,8 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_sm100_kernel(const __grid_con
             fence_mbar_init();
         }
         __syncthreads();
-        ag_pusher(p, smem, bars);
+        if (p.a_ws_mc != nullptr) ag_pusher_nvls(p, smem, bars);
+        else ag_pusher(p, smem, bars);
         return;
     }
 
@@ -611,9 +671,12 @@ static GridPlan plan_grid(const TdistGemmArgs* a) {
         if (g.num_comm <= 0) {
             // Enough pushers to deliver the shard within about half of the GEMM's run time (one pusher CTA
             // sustains ~40 GB/s over NVLink), then nudged so that the remaining CTAs need the fewest waves.
-            const double push_bytes = static_cast<double>(a->world - 1) * a->m_per_rank * a->k * 2.0;
+            // Through the multicast engine the shard is stored once instead of world-1 times, and a CTA replaying
+            // shared memory as multimem.st moves ~100 GB/s.
+            const bool nvls = a->a_ws_mc != nullptr;
+            const double push_bytes = static_cast<double>(nvls ? 1 : a->world - 1) * a->m_per_rank * a->k * 2.0;
             const double gemm_s = 2.0 * a->world * a->m_per_rank * static_cast<double>(a->n) * a->k / 1.4e15;
-            int need = static_cast<int>(push_bytes / (gemm_s * 0.5 > 1e-6 ? gemm_s * 0.5 : 1e-6) / 40e9) + 1;
+            int need = static_cast<int>(push_bytes / (gemm_s * 0.5 > 1e-6 ? gemm_s * 0.5 : 1e-6) / (nvls ? 100e9 : 40e9)) + 1;
             need = (need + 1) & ~1;
             if (need < 2) need = 2;
             if (need > 18) need = 18;
@@ -703,6 +766,7 @@ extern "C" int tdist_gemm_run(const TdistGemmArgs* a) {
         p.flags_peer[r] = a->flags_peer[r];
     }
     p.stage_local = static_cast<const char*>(a->c_stage_peer[a->rank]);
+    p.a_ws_mc = (a->mode == TDIST_GEMM_AG && a->world > 1) ? static_cast<char*>(a->a_ws_mc) : nullptr;
     p.rs_out = a->rs_out;
     p.flags = a->flags;
     p.m_per_rank = a->m_per_rank;
