@@ -127,7 +127,7 @@ def main():
     if args.impl == "reference":
         print(json.dumps({"impl": "reference",
                           "unavailable": "reference cannot be installed offline: its setup downloads Triton/LLVM and needs "
-                                         "NVSHMEM sources (pip install of /root/reference fails at metadata generation, no network)"}))
+                                         "NVSHMEM sources (pip install of the reference checkout fails at metadata generation, no network)"}))
         return 0
 
     import torch

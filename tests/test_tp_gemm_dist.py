@@ -29,7 +29,7 @@ def test_ag_gemm_with_multicast_pushers(world):
     block once with multimem.st instead of once per peer."""
     if torch.cuda.device_count() < world:
         pytest.skip(f"needs {world} GPUs")
-    res, out = run_workers("tp_gemm_worker.py", world, env={"NCCL_NVLS_ENABLE": "0", "TDIST_NVLS": "1", "TDIST_WAIT_TIMEOUT_MS": "20000"})
+    res, out = run_workers("tp_gemm_worker.py", world, env={"NCCL_NVLS_ENABLE": "0", "TDIST_NVLS": "1", "TDIST_AG_GEMM_NVLS": "2", "TDIST_WAIT_TIMEOUT_MS": "20000"})
     assert res["ranks_ok"] == world, out[-3000:]
     if not res["ag_multicast_pusher"]:
         pytest.skip("this system offers no NVLS multicast objects")

@@ -69,7 +69,7 @@ def main():
             if cuda:
                 symm_heap().barrier()
     res["ag_max_err"] = ag_err
-    res["ag_multicast_pusher"] = bool(cuda and ctx is not None and ctx.workspace is not None and ctx.workspace.mc is not None and G.AG_NVLS)
+    res["ag_multicast_pusher"] = bool(cuda and ctx is not None and ctx.workspace is not None and ctx.workspace.mc is not None and (G.AG_NVLS == 2 or world >= 4))
 
     # ---------------- GEMM-RS ----------------
     shapes = [(128, 256, 128), (250, 520, 264), (1024, 2048, 1024)] if cuda else [(128, 256, 128)]

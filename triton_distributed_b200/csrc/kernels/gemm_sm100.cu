@@ -671,12 +671,14 @@ static GridPlan plan_grid(const TdistGemmArgs* a) {
         if (g.num_comm <= 0) {
             // Enough pushers to deliver the shard within about half of the GEMM's run time (one pusher CTA
             // sustains ~40 GB/s over NVLink), then nudged so that the remaining CTAs need the fewest waves.
-            // Through the multicast engine the shard is stored once instead of world-1 times, and a CTA replaying
-            // shared memory as multimem.st moves ~100 GB/s.
+            // Through the multicast engine the shard is stored once instead of world-1 times; a CTA replaying
+            // shared memory as multimem.st was measured at ~33 GB/s, and the whole shard should land within a
+            // quarter of the run (every peer needs all of it when it reaches this rank's segment).
             const bool nvls = a->a_ws_mc != nullptr;
             const double push_bytes = static_cast<double>(nvls ? 1 : a->world - 1) * a->m_per_rank * a->k * 2.0;
             const double gemm_s = 2.0 * a->world * a->m_per_rank * static_cast<double>(a->n) * a->k / 1.4e15;
-            int need = static_cast<int>(push_bytes / (gemm_s * 0.5 > 1e-6 ? gemm_s * 0.5 : 1e-6) / (nvls ? 100e9 : 40e9)) + 1;
+            const double window = gemm_s * (nvls ? 0.25 : 0.5);
+            int need = static_cast<int>(push_bytes / (window > 1e-6 ? window : 1e-6) / (nvls ? 33e9 : 40e9)) + 1;
             need = (need + 1) & ~1;
             if (need < 2) need = 2;
             if (need > 18) need = 18;

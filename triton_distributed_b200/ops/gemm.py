@@ -38,8 +38,9 @@ launch_count = 0
 # tiling choice handed to the kernel: -1 = automatic, 0 = one CTA per 128x256 tile,
 # 1 = CTA pair (cta_group::2) per 256x256 tile
 CTA_PAIR = int(os.environ.get("TDIST_GEMM_CTA_PAIR", "-1"))
-# AG-GEMM pushers use multimem.st when the heap has a multicast alias (TDIST_NVLS=1); 0 keeps the unicast pusher
-AG_NVLS = os.environ.get("TDIST_AG_GEMM_NVLS", "1") != "0"
+# AG-GEMM pushers and multimem.st, when the heap has a multicast alias (TDIST_NVLS=1): 0 = never, 1 = from 4 ranks
+# up (with one peer a multicast store moves the same bytes as a unicast one), 2 = always
+AG_NVLS = int(os.environ.get("TDIST_AG_GEMM_NVLS", "1"))
 GROUP_M = int(os.environ.get("TDIST_GEMM_GROUP_M", "0"))  # row-tiles per raster group, 0 = kernel default
 
 
@@ -189,7 +190,7 @@ def ag_gemm_intra_node(a: torch.Tensor, b: torch.Tensor, ctx: Optional[AllGather
         g.a_ws_peer = ctx.workspace.half_ptr_arrays()[half]
         g.flags = ctx.flags.local[half].data_ptr()
         g.flags_peer = ctx.flags.half_ptr_arrays()[half]
-        if ctx.workspace.mc is not None and AG_NVLS:
+        if ctx.workspace.mc is not None and (AG_NVLS == 2 or (AG_NVLS == 1 and ctx.world >= 4)):
             g.a_ws_mc = ctx.workspace.mc[half].data_ptr()   # the pushers multicast through the switch
     _launch(g)
     return c
