@@ -105,13 +105,14 @@ __device__ __forceinline__ void quant_seg_warp(char* dst, float* dst_scale, cons
         if (active) {
             const float scale = fmaxf(amax, 1e-10f) / 448.f;
             const float inv = 1.f / scale;
+            // packed conversion: one cvt.rn.satfinite.e4m3x2.f32 per pair of values (.x lands in the low byte)
             uint32_t lo = 0, hi = 0;
 #pragma unroll
-            for (int i = 0; i < 4; ++i) {
-                const uint32_t b0 = __nv_cvt_float_to_fp8(v[i] * inv, __NV_SATFINITE, __NV_E4M3);
-                const uint32_t b1 = __nv_cvt_float_to_fp8(v[4 + i] * inv, __NV_SATFINITE, __NV_E4M3);
-                lo |= b0 << (8 * i);
-                hi |= b1 << (8 * i);
+            for (int i = 0; i < 2; ++i) {
+                const uint32_t b0 = __nv_cvt_float2_to_fp8x2(make_float2(v[2 * i] * inv, v[2 * i + 1] * inv), __NV_SATFINITE, __NV_E4M3);
+                const uint32_t b1 = __nv_cvt_float2_to_fp8x2(make_float2(v[4 + 2 * i] * inv, v[5 + 2 * i] * inv), __NV_SATFINITE, __NV_E4M3);
+                lo |= b0 << (16 * i);
+                hi |= b1 << (16 * i);
             }
             *reinterpret_cast<uint2*>(dst + static_cast<size_t>(g) * 128 + sub * 8) = make_uint2(lo, hi);
             if (sub == 0) dst_scale[g] = scale;
@@ -119,7 +120,7 @@ __device__ __forceinline__ void quant_seg_warp(char* dst, float* dst_scale, cons
     }
 }
 
-__global__ void __launch_bounds__(kA2AThreads) a2a_kernel(const A2AParams p) {
+__global__ void __launch_bounds__(kA2AThreads, 2) a2a_kernel(const A2AParams p) {
     const int g = static_cast<int>(blockIdx.x) / p.ctas_per_peer;
     const int slice = static_cast<int>(blockIdx.x) % p.ctas_per_peer;
     const int dest = (p.rank + g) % p.world;
@@ -244,9 +245,13 @@ __global__ void dequant_fp8_kernel(const uint8_t* x, const float* scale, __nv_bf
         const uint2 q = *reinterpret_cast<const uint2*>(x + e0);
         float v[8];
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {
-            v[j] = __half2float(__half(__nv_cvt_fp8_to_halfraw(static_cast<__nv_fp8_storage_t>((q.x >> (8 * j)) & 0xff), __NV_E4M3))) * s;
-            v[4 + j] = __half2float(__half(__nv_cvt_fp8_to_halfraw(static_cast<__nv_fp8_storage_t>((q.y >> (8 * j)) & 0xff), __NV_E4M3))) * s;
+        for (int j = 0; j < 2; ++j) {
+            const float2 a = __half22float2(__half2(__nv_cvt_fp8x2_to_halfraw2(static_cast<__nv_fp8x2_storage_t>((q.x >> (16 * j)) & 0xffff), __NV_E4M3)));
+            const float2 b = __half22float2(__half2(__nv_cvt_fp8x2_to_halfraw2(static_cast<__nv_fp8x2_storage_t>((q.y >> (16 * j)) & 0xffff), __NV_E4M3)));
+            v[2 * j] = a.x * s;
+            v[2 * j + 1] = a.y * s;
+            v[4 + 2 * j] = b.x * s;
+            v[5 + 2 * j] = b.y * s;
         }
         uint4 o;
         o.x = pack_bf16x2(v[0], v[1]);
@@ -307,8 +312,8 @@ extern "C" int tdist_a2a(const TdistA2AArgs* a) {
     p.reduce = a->reduce;
     p.phase = a->phase ? a->phase : 3;
     // about one CTA per SM in total: the rows of a small message are spread over the whole machine
-    p.ctas_per_peer = a->ctas_per_peer > 0 ? a->ctas_per_peer : 144 / a->world;
-    if (p.ctas_per_peer > 72) p.ctas_per_peer = 72;
+    p.ctas_per_peer = a->ctas_per_peer > 0 ? a->ctas_per_peer : 288 / a->world;  // two 512-thread CTAs per SM
+    if (p.ctas_per_peer > 144) p.ctas_per_peer = 144;
     if (p.ctas_per_peer < 1) p.ctas_per_peer = 1;
     p.epoch = a->epoch;
     p.wctx.status = static_cast<Status*>(a->status);
