@@ -669,21 +669,22 @@ static GridPlan plan_grid(const TdistGemmArgs* a) {
     if (a->mode == TDIST_GEMM_AG && a->world > 1) {
         g.num_comm = a->num_comm_sms;
         if (g.num_comm <= 0) {
-            // Enough pushers to deliver the shard within about half of the GEMM's run time (one pusher CTA
-            // sustains ~40 GB/s over NVLink), then nudged so that the remaining CTAs need the fewest waves.
-            // Through the multicast engine the shard is stored once instead of world-1 times; a CTA replaying
-            // shared memory as multimem.st was measured at ~33 GB/s, and the whole shard should land within a
-            // quarter of the run (every peer needs all of it when it reaches this rank's segment).
+            // Peers consume this rank's rows one segment-time after another (the rank that needs them first
+            // gets them first), so the pushers must sustain shard_bytes per segment time, i.e. all pushes within
+            // (world-1)/world of the run. One unicast pusher CTA sustains ~40 GB/s over NVLink. A multicast pusher
+            // stores the shard once instead of world-1 times but was measured at ~33 GB/s per CTA, and every peer
+            // needs the whole shard when it reaches this rank's segment: a quarter of the run.
             const bool nvls = a->a_ws_mc != nullptr;
             const double push_bytes = static_cast<double>(nvls ? 1 : a->world - 1) * a->m_per_rank * a->k * 2.0;
             const double gemm_s = 2.0 * a->world * a->m_per_rank * static_cast<double>(a->n) * a->k / 1.4e15;
-            const double window = gemm_s * (nvls ? 0.25 : 0.5);
+            const double window = nvls ? gemm_s * 0.25 : gemm_s * (a->world - 1) / a->world;
             int need = static_cast<int>(push_bytes / (window > 1e-6 ? window : 1e-6) / (nvls ? 33e9 : 40e9)) + 1;
             need = (need + 1) & ~1;
             if (need < 2) need = 2;
             if (need > 18) need = 18;
+            // then the count in [need, need + 8] that leaves the GEMM side the fewest waves (the smallest such)
             int best = need, best_waves = 1 << 30;
-            for (int c = (need - 2 >= 2 ? need - 2 : 2); c <= need + 8; c += 2) {
+            for (int c = need; c <= need + 8; c += 2) {
                 const int units = (sms - c) / g.ctas_per_tile;
                 if (units < 1) break;
                 const int waves = (g.num_tiles + units - 1) / units;
