@@ -86,3 +86,60 @@ def test_sequence_parallel_decode_emulated(cuda_device, world, B):
         ref = FD.ref_lse_merge(torch.stack(parts))
         for r in range(world):
             torch.testing.assert_close(outs[r].float(), ref, atol=5e-2, rtol=5e-2)
+
+
+@pytest.mark.parametrize("world,B", [(2, 2), (4, 3)])
+@pytest.mark.parametrize("graph", [False, True], ids=["eager", "cuda_graph"])
+def test_sequence_parallel_decode_with_device_call_number(cuda_device, world, B, graph):
+    """The call number lives in device memory and the kernel advances it, so the launches of a step (all
+    emulated ranks send, then all redo and gather) can be captured once and replayed: every replay uses the
+    next number and the other buffer parity."""
+    torch.manual_seed(world * 7 + B)
+    Hq, Hkv, D, page = 32, 8, 128, 16
+    lw = LocalWorld(world, cuda_device)
+    ctxs = [FD.create_sp_decode_context(r, world, B, Hq, D, heap=lw.heap(r), device=cuda_device, device_epoch=True)
+            for r in range(world)]
+    q = torch.randn(B, Hq, D, device=cuda_device).to(torch.bfloat16)
+    glens = torch.randint(1, 600, (world, B), dtype=torch.int32, device=cuda_device)
+    shards = [_make_cache(B, [600] * B, Hkv, D, page, torch.bfloat16, cuda_device) for r in range(world)]
+    outs = [torch.empty_like(q) for _ in range(world)]
+
+    def step():
+        for r in range(world):
+            FD.sp_gqa_fwd_batch_decode(ctxs[r], q, shards[r][0], shards[r][1], glens, shards[r][2], phase=1)
+        for r in range(world):
+            FD.sp_gqa_fwd_batch_decode(ctxs[r], q, shards[r][0], shards[r][1], glens, shards[r][2], phase=2, out=outs[r])
+
+    g = None
+    if graph:
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            step()                       # warm-up (advances every rank's call number by one)
+        torch.cuda.current_stream().wait_stream(side)
+        torch.cuda.synchronize()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            step()
+    for it in range(4):
+        q.copy_(torch.randn(B, Hq, D, device=cuda_device).to(torch.bfloat16))
+        glens.copy_(torch.randint(1, 600, (world, B), dtype=torch.int32, device=cuda_device))
+        if it == 2:
+            glens[1 % world] = 0         # a rank without keys
+            glens[0, :] = 9
+        if g is not None:
+            g.replay()
+        else:
+            step()
+        torch.cuda.synchronize()
+        check_status()
+        parts = []
+        for r in range(world):
+            o, l = FD.ref_paged_attn(q, shards[r][0], shards[r][1], glens[r], shards[r][2], 1.0 / math.sqrt(D), return_lse=True)
+            parts.append(torch.cat([o, l.unsqueeze(-1)], -1))
+        ref = FD.ref_lse_merge(torch.stack(parts))
+        for r in range(world):
+            torch.testing.assert_close(outs[r].float(), ref, atol=5e-2, rtol=5e-2)
+    done = 4 + (1 if graph else 0)
+    for r in range(world):
+        assert int(ctxs[r].epoch_dev[0]) == done and int(ctxs[r].epoch_dev[1]) == 0

@@ -139,6 +139,7 @@ class DecodeArgs(C.Structure):
         ("status", C.c_void_p),
         ("timeout_ns", C.c_uint64),
         ("stream", C.c_void_p),
+        ("epoch_ptr", C.c_void_p), ("epoch_done", C.c_void_p), ("ll_peer_alt", C.c_void_p * MAX_RANKS),
     ]
 
 

@@ -254,6 +254,14 @@ typedef struct TdistDecodeArgs {
     void* status;
     uint64_t timeout_ns;
     void* stream;
+    /* mode 2, optional: the call number lives on the device, so that a captured launch stays valid when it is
+     * replayed. epoch_ptr: uint32, the number of the last completed call (starts at 0); the kernel uses
+     * *epoch_ptr + 1 and stores it back when its last CTA finishes (not with push_only). epoch_done: uint32
+     * scratch, zero on first use. ll_peer then holds the gather buffers of EVEN call numbers and ll_peer_alt
+     * those of ODD ones; `epoch` is ignored. */
+    void* epoch_ptr;
+    void* epoch_done;
+    void* ll_peer_alt[TDIST_MAX_RANKS];
 } TdistDecodeArgs;
 
 int tdist_flash_decode(const TdistDecodeArgs* args);

@@ -51,6 +51,9 @@ struct DecodeParams {
     int world, rank;
     int push_only;          // SP: stop after the exchange's send half (ranks emulated one at a time)
     unsigned epoch;
+    unsigned* epoch_ptr;    // SP, optional: device-resident call number (see TdistDecodeArgs)
+    unsigned* epoch_done;
+    char* ll_peer_alt[kMaxRanks];
     WaitCtx wctx;
 };
 
@@ -395,6 +398,13 @@ __global__ void __launch_bounds__(kDecodeThreads, (D <= 128 ? 2 : 1)) flash_deco
     __syncthreads();
 
     // ---- sequence-parallel: exchange O||LSE of these G heads with every rank as LL packets
+    // Call number and buffer parity: from the arguments, or (replayable launches) from device memory.
+    unsigned epoch = p.epoch;
+    char* const* ll = p.ll_peer;
+    if (p.epoch_ptr != nullptr) {
+        epoch = *reinterpret_cast<volatile unsigned*>(p.epoch_ptr) + 1u;
+        ll = (epoch & 1u) ? p.ll_peer_alt : p.ll_peer;
+    }
     const int npk = G * W2 / 2;                                        // packets of this head group
     const size_t pk0 = (static_cast<size_t>(b) * p.Hq + kvh * G) * W2 / 2;  // first packet in a rank slot
     const size_t slot = static_cast<size_t>(p.B) * p.Hq * W2 / 2;      // packets per source rank
@@ -403,17 +413,17 @@ __global__ void __launch_bounds__(kDecodeThreads, (D <= 128 ? 2 : 1)) flash_deco
         for (int r = 0; r < p.world; ++r) {
             int peer = p.rank + r;
             if (peer >= p.world) peer -= p.world;
-            ll_store(p.ll_peer[peer] + (static_cast<size_t>(p.rank) * slot + pk0 + i) * 16, payload, p.epoch);
+            ll_store(ll[peer] + (static_cast<size_t>(p.rank) * slot + pk0 + i) * 16, payload, epoch);
         }
     }
     if (p.push_only) return;
     // gather: lse of every (source, head) first, then the weighted sum
     float* lse_s = reinterpret_cast<float*>(q_s);  // [world][G]  (Q tile is dead)
-    const char* mine = p.ll_peer[p.rank];
+    const char* mine = ll[p.rank];
     for (int idx = tid; idx < p.world * G; idx += kDecodeThreads) {
         const int r = idx / G, g = idx % G;
         uint64_t v;
-        ll_load(mine + (static_cast<size_t>(r) * slot + pk0 + (g * W2 + D) / 2) * 16, p.epoch, &v, p.wctx, r, g);
+        ll_load(mine + (static_cast<size_t>(r) * slot + pk0 + (g * W2 + D) / 2) * 16, epoch, &v, p.wctx, r, g);
         lse_s[idx] = __uint_as_float(static_cast<uint32_t>(v));
     }
     __syncthreads();
@@ -426,7 +436,7 @@ __global__ void __launch_bounds__(kDecodeThreads, (D <= 128 ? 2 : 1)) flash_deco
         for (int r = 0; r < p.world; ++r) {
             const float f = __expf(lse_s[r * G + g] - mu);
             uint64_t v;
-            ll_load(mine + (static_cast<size_t>(r) * slot + pk0 + (g * W2 + c) / 2) * 16, p.epoch, &v, p.wctx, r, i);
+            ll_load(mine + (static_cast<size_t>(r) * slot + pk0 + (g * W2 + c) / 2) * 16, epoch, &v, p.wctx, r, i);
             wsum += f;
             a0 += f * __uint_as_float(static_cast<uint32_t>(v));
             a1 += f * __uint_as_float(static_cast<uint32_t>(v >> 32));
@@ -434,6 +444,19 @@ __global__ void __launch_bounds__(kDecodeThreads, (D <= 128 ? 2 : 1)) flash_deco
         const float inv = wsum > 0.f ? 1.f / wsum : 0.f;
         T* dst = static_cast<T*>(p.out) + (static_cast<size_t>(b) * p.Hq + kvh * G + g) * D + c;
         *reinterpret_cast<uint32_t*>(dst) = pack2<T>(a0 * inv, a1 * inv);
+    }
+    if (p.epoch_ptr != nullptr) {
+        // The last of the B * Hkv exchanging CTAs records the call as done. Every one of them read the number
+        // before it got here, and CTAs that merge no head group never read it.
+        __syncthreads();
+        if (tid == 0) {
+            const unsigned old = atomicAdd(p.epoch_done, 1u);
+            if (old == static_cast<unsigned>(p.B * p.Hkv - 1)) {
+                *p.epoch_done = 0;
+                __threadfence();
+                *reinterpret_cast<volatile unsigned*>(p.epoch_ptr) = epoch;
+            }
+        }
     }
 }
 
@@ -520,7 +543,14 @@ static int flash_decode_impl(const TdistDecodeArgs* a) {
         return fail(TDIST_EINVAL, "decode: null pointer");
     if (a->mode == 2) {
         if (a->world < 1 || a->world > TDIST_MAX_RANKS || a->rank < 0 || a->rank >= a->world) return fail(TDIST_EINVAL, "decode: world/rank out of range");
-        if (a->epoch == 0) return fail(TDIST_EINVAL, "decode: the epoch of a sequence-parallel call must be non-zero");
+        if (a->epoch == 0 && a->epoch_ptr == nullptr) return fail(TDIST_EINVAL, "decode: the epoch of a sequence-parallel call must be non-zero");
+        if (a->epoch_ptr != nullptr && a->epoch_done == nullptr) return fail(TDIST_EINVAL, "decode: epoch_ptr needs epoch_done");
+        p.epoch_ptr = static_cast<unsigned*>(a->epoch_ptr);
+        p.epoch_done = static_cast<unsigned*>(a->epoch_done);
+        for (int r = 0; r < a->world && a->epoch_ptr != nullptr; ++r) {
+            p.ll_peer_alt[r] = static_cast<char*>(a->ll_peer_alt[r]);
+            if (!p.ll_peer_alt[r]) return fail(TDIST_EINVAL, "decode: null gather buffer (odd call numbers)");
+        }
         for (int r = 0; r < a->world; ++r) {
             p.ll_peer[r] = static_cast<char*>(a->ll_peer[r]);
             if (!p.ll_peer[r]) return fail(TDIST_EINVAL, "decode: null gather buffer");

@@ -100,7 +100,8 @@ class _Workspace:
 
 
 def _launch(q, k_cache, v_cache, kv_lens, block_table, scale, soft_cap, out, mode, splits, max_kv=None,
-            ll_ptrs=None, world=1, rank=0, epoch=0, workspace=None, stream=None, push_only=False):
+            ll_ptrs=None, world=1, rank=0, epoch=0, workspace=None, stream=None, push_only=False,
+            ll_ptrs_odd=None, epoch_dev=None):
     global launch_count
     B, Hq, D = q.shape
     blocks, page, Hkv, Dk = k_cache.shape
@@ -129,6 +130,10 @@ def _launch(q, k_cache, v_cache, kv_lens, block_table, scale, soft_cap, out, mod
     a.push_only = int(push_only)
     if ll_ptrs is not None:
         a.ll_peer = ll_ptrs
+    if epoch_dev is not None:       # call number kept on the device: the launch can be captured and replayed
+        a.ll_peer_alt = ll_ptrs_odd
+        a.epoch_ptr = epoch_dev.data_ptr()
+        a.epoch_done = epoch_dev.data_ptr() + 4
     st = global_status()
     a.status = st.device_ptr if st is not None else None
     a.timeout_ns = default_timeout_ns()
@@ -195,16 +200,21 @@ class SpDecodeContext:
     gather: Optional[SymmTensor] = None   # uint8 [2, world * max_batch * Hq * (D+2)/2 * 16]
     epoch: int = 0
     group: object = None
+    # With `device_epoch` the call number lives in device memory (int32 [2]: last completed call, scratch) and the
+    # kernel advances it itself, so a captured launch stays valid on replay. Every rank must choose the same way.
+    epoch_dev: Optional[torch.Tensor] = None
 
 
 def create_sp_decode_context(rank: int, world: int, max_batch: int, Hq: int, head_dim: int, heap=None, group=None,
-                             device=None) -> SpDecodeContext:
+                             device=None, device_epoch: bool = False) -> SpDecodeContext:
     ctx = SpDecodeContext(rank, world, max_batch, Hq, head_dim, group=group)
     on_cuda = (device is not None and torch.device(device).type == "cuda") or (device is None and torch.cuda.is_available())
     if on_cuda:
         heap = heap or symm_heap(group)
         half = world * max_batch * Hq * (head_dim + 2) // 2 * 16
         ctx.gather = heap.zeros((2, half), torch.uint8)
+        if device_epoch:
+            ctx.epoch_dev = torch.zeros(2, dtype=torch.int32, device=ctx.gather.local.device)
     return ctx
 
 
@@ -229,12 +239,17 @@ def sp_gqa_fwd_batch_decode(ctx: SpDecodeContext, q, k_cache, v_cache, global_kv
         return ref_lse_merge(mine).to(q.dtype)
     if B > ctx.max_batch or Hq != ctx.Hq or D != ctx.head_dim:
         raise ValueError("shape exceeds the sequence-parallel context")
+    o = out if out is not None else torch.empty_like(q)
+    if ctx.epoch_dev is not None:
+        halves = ctx.gather.half_ptr_arrays()
+        return _launch(q, k_cache, v_cache, global_kv_lens[ctx.rank], block_table, scale, soft_cap, o, 2, kv_split,
+                       max_kv=int(block_table.shape[1]) * k_cache.shape[1], ll_ptrs=halves[0], ll_ptrs_odd=halves[1],
+                       world=ctx.world, rank=ctx.rank, epoch=0, push_only=(phase == 1), epoch_dev=ctx.epoch_dev)
     if phase != 2:
         ctx.epoch += 1  # phase 1 = compute and send only, phase 2 = redo with the same epoch and gather
     half = ctx.epoch & 1
     # the kernel strides the per-source slots by B*Hq*(D+2)/2 packets: every rank passes the same B
     # (q is replicated)
-    o = out if out is not None else torch.empty_like(q)
     return _launch(q, k_cache, v_cache, global_kv_lens[ctx.rank], block_table, scale, soft_cap, o, 2, kv_split,
                    max_kv=int(block_table.shape[1]) * k_cache.shape[1],
                    ll_ptrs=ctx.gather.half_ptr_arrays()[half], world=ctx.world, rank=ctx.rank, epoch=ctx.epoch,
