@@ -128,13 +128,15 @@ class SpGQAFlashDecodeAttention:
 
     def __init__(self, rank: int, node: int, num_ranks: int, num_nodes: int, num_q_heads: int, num_kv_heads: int, q_head_dim: int,
                  v_head_dim: int, page_size: int = 1, scale: float = 1.0, soft_cap: float = 0.0, max_allowed_batch: int = 1,
-                 thrink_buffer_threshold: int = 500, stages: int = 20, heap=None, group=None, device=None):
+                 thrink_buffer_threshold: int = 500, stages: int = 20, heap=None, group=None, device=None,
+                 cuda_graph_safe: bool = False):
+        """``cuda_graph_safe`` keeps the call number on the device so that ``forward`` can be captured and replayed."""
         if q_head_dim != v_head_dim:
             raise ValueError("q and v head dims must match")
         self.rank, self.num_ranks = rank, num_ranks
         self.scale, self.soft_cap = scale, soft_cap
         self.ctx = FD.create_sp_decode_context(rank, num_ranks, max_allowed_batch, num_q_heads, q_head_dim, heap=heap,
-                                               group=group, device=device)
+                                               group=group, device=device, device_epoch=cuda_graph_safe)
 
     def forward(self, q, k_cache, v_cache, global_kv_lens, block_table, phase: int = 3):
         return FD.sp_gqa_fwd_batch_decode(self.ctx, q, k_cache, v_cache, global_kv_lens, block_table, self.scale,
