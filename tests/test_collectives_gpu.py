@@ -67,3 +67,31 @@ def test_ring_reduce(cuda_device):
     out = torch.empty(16, 32, device=cuda_device, dtype=torch.bfloat16)
     CO.ring_reduce(x, out, begin_idx=3, num_splits=8)
     torch.testing.assert_close(out.float(), x.float().view(8, 16, 32).sum(0), atol=5e-2, rtol=2e-2)
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16, torch.float32, torch.int32])
+@pytest.mark.parametrize("splits,begin", [(1, 0), (3, 2), (8, 5)])
+def test_ring_reduce_copy_and_add_kernels(cuda_device, dtype, splits, begin):
+    """Standalone reduce / copy / add helpers against torch in fp32 (exact for int32)."""
+    from triton_distributed_b200.ops import collectives as CO
+    torch.manual_seed(splits * 10 + begin)
+    M, N = 96, 520
+    if dtype == torch.int32:
+        x = torch.randint(-1000, 1000, (splits * M, N), device=cuda_device, dtype=dtype)
+    else:
+        x = torch.randn(splits * M, N, device=cuda_device).to(dtype)
+    out = torch.empty(M, N, device=cuda_device, dtype=dtype)
+    before = CO.launch_count
+    CO.ring_reduce(x, out, begin, splits)
+    assert CO.launch_count == before + 1            # the CUDA kernel ran, not the torch fallback
+    ref = x.view(splits, M, N).to(torch.float32 if dtype != torch.int32 else torch.int64).sum(0)
+    if dtype == torch.int32:
+        assert torch.equal(out.to(torch.int64), ref)
+    else:
+        torch.testing.assert_close(out.float(), ref, atol=2e-2 if dtype != torch.float32 else 1e-5, rtol=2e-2 if dtype != torch.float32 else 1e-5)
+    y = torch.empty_like(x)
+    CO.copy_continuous(x, y)
+    assert torch.equal(x, y)
+    if dtype != torch.int32:
+        z = CO.add_continuous(x[:M], x[:M])
+        torch.testing.assert_close(z.float(), 2 * x[:M].float(), atol=2e-2, rtol=2e-2)

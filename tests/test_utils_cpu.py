@@ -102,3 +102,28 @@ def test_parallel_strategies_on_cpu():
     assert list(P.experts_of_rank(8, 2, 4)) == [4, 5]
     assert P.shard_rows(torch.arange(8).view(4, 2), 1, 2).tolist() == [[4, 5], [6, 7]]
     assert P.shard_columns(torch.arange(8).view(2, 4), 1, 2).tolist() == [[2, 3], [6, 7]]
+
+
+def test_reference_names_resolve_on_cpu():
+    """Names the reference exports that map onto the single-level paths here."""
+    import torch
+    from triton_distributed_b200.ops import collectives as CO, flash_decode as FD, gemm as G, moe_tp as MT, moe_utils as MU
+
+    x = torch.randn(8, 4)
+    assert CO.add_continuous(x, x).allclose(2 * x) and CO.copy_continuous(x, torch.empty_like(x)).equal(x)
+    out = torch.empty(2, 4)
+    assert CO.ring_reduce(x, out, 1, 4).allclose(x.view(4, 2, 4).sum(0))
+    assert CO.inter_node_allgather is CO.cp_engine_producer_all_gather_intra_node
+    assert G.ag_gemm_inter_node is G.ag_gemm_intra_node and MT.ag_group_gemm_inter_node is MT.ag_group_gemm_intra_node
+    assert FD.gqa_fwd_batch_decode_aot is FD.gqa_fwd_batch_decode
+    padded = G.padded_to_BLOCK_M(torch.arange(12.0).view(6, 2), 2, 4)
+    assert padded.shape == (8, 2) and padded[3].abs().sum() == 0 and padded[4].tolist() == [6.0, 7.0]
+    ids = torch.tensor([[0, 3], [3, 1]], dtype=torch.int32)
+    assert MU.bincount(ids, 4).tolist() == [1, 1, 0, 2]
+    gather, scatter = MU.calc_gather_index(ids, 4)
+    assert gather.tolist() == [0, 1, 0, 1] and scatter.tolist() == [0, 2, 3, 1]
+    a, w = torch.randn(4, 8), torch.randn(6, 8)
+    ctx = G.create_ag_gemm_inter_node_context(a, w, 0, 1)
+    assert G.ag_gemm_inter_node(a, w, ctx).shape == (4, 6)
+    rs = G.create_gemm_rs_context(4, 6, 0, 1, output_dtype=torch.float32, device="cpu")
+    assert G.gemm_rs_op(a, w, rs).shape == (4, 6)

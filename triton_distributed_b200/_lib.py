@@ -185,6 +185,7 @@ def _declare(lib):
     lib.tdist_allgather.argtypes = [C.POINTER(CollArgs)]
     lib.tdist_nvls.argtypes = [C.POINTER(NvlsArgs)]
     lib.tdist_reduce_scatter.argtypes = [C.POINTER(CollArgs)]
+    lib.tdist_ring_reduce.argtypes = [C.c_void_p, C.c_void_p, C.c_size_t, C.c_int, C.c_int, C.c_int, C.c_void_p]
     lib.tdist_barrier_all.argtypes = [C.POINTER(C.c_void_p), C.c_void_p, C.c_int, C.c_int, C.c_void_p, C.c_uint64, C.c_void_p]
     lib.tdist_p2p_copy.argtypes = [C.c_void_p, C.c_void_p, C.c_size_t, C.c_int, C.c_int, C.c_int, C.c_int,
                                    C.c_void_p, C.c_uint64, C.c_void_p]

@@ -141,6 +141,9 @@ typedef struct TdistCollArgs {
 
 int tdist_allgather(const TdistCollArgs* args);
 int tdist_reduce_scatter(const TdistCollArgs* args);
+/* out [block_bytes] = sum of the `splits` consecutive blocks of `in`, fp32 accumulation for bf16 / fp16, blocks
+ * visited in ring order from `begin`. */
+int tdist_ring_reduce(const void* in, void* out, size_t block_bytes, int splits, int begin, int dtype, void* stream);
 /* Device-side barrier of all ranks on `stream`: flags_peer[r] = rank r's uint64[8] flag array as
  * mapped here, epoch_local = a local uint64 counter owned by the barrier. */
 int tdist_barrier_all(void* const* flags_peer, void* epoch_local, int world, int rank, void* status,

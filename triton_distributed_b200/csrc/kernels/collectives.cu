@@ -177,6 +177,40 @@ __global__ void __launch_bounds__(kCollThreads) reduce_scatter_kernel(const Coll
     }
 }
 
+// out[i] = sum over the `splits` row blocks of `in` (block stride `block_bytes`), fp32 accumulation, visiting the
+// blocks in ring order from `begin`. (reference kernels/nvidia/reduce_scatter.py:616-685 `kernel_ring_reduce_*`)
+template <typename T, typename Acc>
+__global__ void __launch_bounds__(kCollThreads) ring_reduce_kernel(const char* in, char* out, size_t block_bytes, int splits, int begin) {
+    constexpr int V = 16 / sizeof(T);
+    const size_t nvec = block_bytes / 16;
+    for (size_t i = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < nvec; i += static_cast<size_t>(gridDim.x) * blockDim.x) {
+        Acc acc[V];
+#pragma unroll
+        for (int j = 0; j < V; ++j) acc[j] = Acc(0);
+        for (int s0 = 0; s0 < splits; s0 += 4) {
+            uint4 q[4];
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                int s = begin + s0 + u;
+                if (s >= splits) s -= splits;
+                if (s0 + u < splits) q[u] = ld_nc_v4(in + static_cast<size_t>(s) * block_bytes + i * 16);
+            }
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                if (s0 + u >= splits) break;
+                const T* e = reinterpret_cast<const T*>(&q[u]);
+#pragma unroll
+                for (int j = 0; j < V; ++j) acc[j] += static_cast<Acc>(e[j]);
+            }
+        }
+        uint4 o;
+        T* oe = reinterpret_cast<T*>(&o);
+#pragma unroll
+        for (int j = 0; j < V; ++j) oe[j] = static_cast<T>(acc[j]);
+        st_v4(out + i * 16, o);
+    }
+}
+
 __global__ void barrier_all_kernel(SymmWindow win, BarrierState st, WaitCtx wctx) {
     barrier_all_block(win, st, wctx);
 }
@@ -263,6 +297,26 @@ extern "C" int tdist_barrier_all(void* const* flags_peer, void* epoch_local, int
     w.kernel_id = kKernelColl;
     w.rank = rank;
     barrier_all_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(win, st, w);
+    TDIST_CUDA_OK(cudaGetLastError());
+    return 0;
+}
+
+extern "C" int tdist_ring_reduce(const void* in, void* out, size_t block_bytes, int splits, int begin, int dtype, void* stream) {
+    if (in == nullptr || out == nullptr || splits < 1 || begin < 0 || begin >= splits) return fail(TDIST_EINVAL, "ring_reduce: bad arguments");
+    if (block_bytes == 0 || block_bytes % 16 != 0) return fail(TDIST_EINVAL, "ring_reduce: the block size must be a positive multiple of 16 bytes");
+    if ((reinterpret_cast<uintptr_t>(in) & 15) || (reinterpret_cast<uintptr_t>(out) & 15)) return fail(TDIST_EINVAL, "ring_reduce: pointers must be 16-byte aligned");
+    int grid = static_cast<int>((block_bytes / 16 + kCollThreads - 1) / kCollThreads);
+    if (grid > 1184) grid = 1184;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const char* i8 = static_cast<const char*>(in);
+    char* o8 = static_cast<char*>(out);
+    switch (dtype) {
+        case TDIST_BF16: ring_reduce_kernel<__nv_bfloat16, float><<<grid, kCollThreads, 0, st>>>(i8, o8, block_bytes, splits, begin); break;
+        case TDIST_F16: ring_reduce_kernel<__half, float><<<grid, kCollThreads, 0, st>>>(i8, o8, block_bytes, splits, begin); break;
+        case TDIST_F32: ring_reduce_kernel<float, float><<<grid, kCollThreads, 0, st>>>(i8, o8, block_bytes, splits, begin); break;
+        case TDIST_I32: ring_reduce_kernel<int, int><<<grid, kCollThreads, 0, st>>>(i8, o8, block_bytes, splits, begin); break;
+        default: return fail(TDIST_EINVAL, "ring_reduce: bad dtype");
+    }
     TDIST_CUDA_OK(cudaGetLastError());
     return 0;
 }

@@ -316,9 +316,59 @@ def reduce_scatter_2d_op(input: torch.Tensor, ctx: ReduceScatter2DContext, out: 
 def ring_reduce(input: torch.Tensor, output: torch.Tensor, begin_idx: int, num_splits: int, num_sms: int = -1) -> torch.Tensor:
     """Sum the ``num_splits`` row blocks of ``input`` (starting the rotation at ``begin_idx``) into
     ``output``; accumulation in fp32 (reference kernels/nvidia/reduce_scatter.py:752-763)."""
+    global launch_count
     M = input.shape[0] // num_splits
+    block_bytes = M * (input.numel() // max(1, input.shape[0])) * input.element_size()
+    if (input.device.type == "cuda" and input.dtype in _RS_DTYPES and output.dtype == input.dtype and input.is_contiguous()
+            and output.is_contiguous() and block_bytes % 16 == 0 and input.data_ptr() % 16 == 0 and output.data_ptr() % 16 == 0
+            and output.numel() * output.element_size() >= block_bytes):
+        _lib.check(_lib.lib().tdist_ring_reduce(input.data_ptr(), output.data_ptr(), block_bytes, num_splits, begin_idx % num_splits,
+                                                _RS_DTYPES[input.dtype], _stream_ptr(input.device)), "tdist_ring_reduce")
+        launch_count += 1
+        return output
     blocks = input.view(num_splits, M, *input.shape[1:])
     order = [(begin_idx + i) % num_splits for i in range(num_splits)]
     acc_dtype = torch.float32 if input.dtype in (torch.bfloat16, torch.float16) else input.dtype
     output.copy_(blocks[order].to(acc_dtype).sum(dim=0).to(output.dtype))
     return output
+
+
+# ---------------------------------------------------------------------------- reference names kept for source compatibility
+inter_node_allgather = cp_engine_producer_all_gather_intra_node   # reference allgather.py:470-624: one level on NVSwitch
+
+
+def reduce_scatter_multi_node(input: torch.Tensor, ctx: ReduceScatter2DContext, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """reference reduce_scatter.py:766-783 (per-node scatter, then a cross-node ring): a single node here."""
+    return reduce_scatter_2d_op(input, ctx, out=out)
+
+
+def reduce_scatter_ring_push_1d_intra_node_kernel(input: torch.Tensor, ctx: ReduceScatter2DContext,
+                                                  out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """reference reduce_scatter.py:344-426 (PCIe ring with SM copies). NVSwitch needs no ring: full-mesh push."""
+    return reduce_scatter_2d_op(input, ctx, out=out)
+
+
+reduce_scatter_ring_push_1d_intra_node_ce = reduce_scatter_ring_push_1d_intra_node_kernel  # reference :289-341
+
+
+def copy_continuous(src: torch.Tensor, dst: torch.Tensor, stream=None) -> torch.Tensor:
+    """Contiguous device copy with this library's vector copy kernel (reference reduce_scatter.py:228-269
+    ``copy_continuous_kernel``); ``dst`` may be a peer mapping."""
+    if src.device.type != "cuda":
+        dst.copy_(src)
+        return dst
+    n = src.numel() * src.element_size()
+    if n % 16 or src.data_ptr() % 16 or dst.data_ptr() % 16 or not src.is_contiguous() or not dst.is_contiguous():
+        dst.copy_(src)
+        return dst
+    _lib.check(_lib.lib().tdist_p2p_copy(src.data_ptr(), dst.data_ptr(), n, 0, min(64, max(1, n // 65536)), 512, 0,
+                                         _status_ptr(), default_timeout_ns(), _stream_ptr(src.device, stream)), "tdist_p2p_copy")
+    return dst
+
+
+def add_continuous(lhs: torch.Tensor, rhs: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``out = lhs + rhs`` with fp32 accumulation (reference reduce_scatter.py:186-225 ``add_continuous_kernel``): the
+    two-source case of :func:`ring_reduce`."""
+    stacked = torch.stack([lhs.reshape(-1, lhs.shape[-1]), rhs.reshape(-1, rhs.shape[-1])]).reshape(-1, lhs.shape[-1])
+    o = out if out is not None else torch.empty_like(lhs)
+    return ring_reduce(stacked, o.view(-1, lhs.shape[-1]), 0, 2).view_as(lhs)

@@ -155,6 +155,9 @@ def gqa_fwd_batch_decode(q, k_cache, v_cache, workspace=None, q_lens=None, kv_le
 
 
 gqa_fwd_batch_decode_persistent = gqa_fwd_batch_decode
+# The reference's AOT-compiled entry points (flash_decode.py `*_aot`): kernels here are always compiled ahead of time.
+gqa_fwd_batch_decode_aot = gqa_fwd_batch_decode
+gqa_fwd_batch_decode_persistent_aot = gqa_fwd_batch_decode
 
 
 def gqa_fwd_batch_decode_intra_rank(q, k_cache, v_cache, workspace=None, q_lens=None, kv_lens=None, block_table=None,

@@ -287,3 +287,48 @@ def _gemm_rs_cpu(a, b, ctx):
     dist.all_reduce(partial, group=ctx.group)
     out.copy_(partial[ctx.rank * out.shape[0]:(ctx.rank + 1) * out.shape[0]])
     return out.to(a.dtype)
+
+
+# ---------------------------------------------------------------------------- reference names kept for source compatibility
+def create_ag_gemm_inter_node_context(tensor_A, tensor_B, rank, num_ranks, num_local_ranks: int = 8, max_M: int = 2 ** 14,
+                                      **kw) -> AllGatherGEMMTensorParallelContext:
+    """The reference's multi-node constructor (kernels/nvidia/allgather_gemm.py:885-935). One NVSwitch node is one
+    level, so this is the intra-node context; more than one node is refused rather than silently mis-served."""
+    if num_ranks > num_local_ranks:
+        raise NotImplementedError("multi-node AG-GEMM is not built: one NVSwitch node (up to 8 ranks) is the target")
+    return create_ag_gemm_intra_node_context(tensor_A, tensor_B, rank, num_ranks, max_M=max_M, **kw)
+
+
+ag_gemm_inter_node = ag_gemm_intra_node  # reference allgather_gemm.py:938-975, same single-level kernel here
+
+
+def padded_to_BLOCK_M(x: torch.Tensor, world_size: int, BLOCK_SIZE_M: int = BLOCK_M) -> torch.Tensor:
+    """Pad every rank's row block of ``x [M, K]`` to a multiple of ``BLOCK_SIZE_M`` rows (reference
+    gemm_reduce_scatter.py:468-479). The sm_100a kernels take ragged blocks (TMA clips them), so nothing here
+    needs the padding; kept for callers that build padded layouts."""
+    M = x.shape[0]
+    mpr = M // world_size
+    pad = (mpr + BLOCK_SIZE_M - 1) // BLOCK_SIZE_M * BLOCK_SIZE_M
+    if pad == mpr:
+        return x
+    out = x.new_zeros((world_size, pad) + tuple(x.shape[1:]))
+    out[:, :mpr].copy_(x.view(world_size, mpr, *x.shape[1:]))
+    return out.view(world_size * pad, *x.shape[1:])
+
+
+def gemm_rs_op(a: torch.Tensor, b: torch.Tensor, ctx: GEMMReduceScatterTensorParallelContext, persistent: bool = True,
+               fuse_scatter: bool = True, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """reference gemm_reduce_scatter.py:482-521; the scatter is always fused into the GEMM epilogue here."""
+    return gemm_rs(a, b, ctx, persistent=persistent, out=out)
+
+
+def local_copy_and_barrier_all(local_data: torch.Tensor, ctx: AllGatherGEMMTensorParallelContext) -> None:
+    """reference allgather_gemm.py:99-114: stage this rank's shard in its own workspace slot and barrier. The fused
+    kernel reads the own shard in place and orders calls by number, so this is only needed by code that drives
+    the copy-engine producer (``cp_engine_producer_all_gather_intra_node``) against ``ctx.workspace`` itself."""
+    from .collectives import barrier_all_on_stream
+    if ctx.workspace is not None:
+        mpr, K = local_data.shape
+        ws = ctx.workspace.local[(ctx.epoch + 1) & 1][: ctx.world * mpr * K].view(ctx.world, mpr, K)
+        ws[ctx.rank].copy_(local_data)
+        barrier_all_on_stream()

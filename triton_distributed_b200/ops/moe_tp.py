@@ -282,3 +282,14 @@ def moe_reduce_rs(rank: int, world_size: int, local_world_size: int, a: torch.Te
     if debug_sync:
         torch.cuda.synchronize()
     return out
+
+
+# reference names of the multi-node variants (allgather_group_gemm.py:694-823): one NVSwitch node is one level
+def create_ag_group_gemm_inter_node_context(tp_pg, A, B, full_topk_ids, num_experts, **kw):
+    world = kw.get("num_ranks") or dist.get_world_size(tp_pg)
+    if world > 8:
+        raise NotImplementedError("multi-node AG + GroupGEMM is not built: one NVSwitch node (up to 8 ranks) is the target")
+    return create_ag_group_gemm_intra_node_context(tp_pg, A, B, full_topk_ids, num_experts, **kw)
+
+
+ag_group_gemm_inter_node = ag_group_gemm_intra_node

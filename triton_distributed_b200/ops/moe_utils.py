@@ -157,3 +157,18 @@ def full_moe_align_block_size(topk_ids: torch.Tensor, block_size: int, num_exper
         base += int(padded.sum())
     post_pad = torch.tensor([base], dtype=torch.int32, device=dev)
     return sorted_ids, expert_ids, barrier_ids, rank_block_num, post_pad
+
+
+def bincount(exp_indices: torch.Tensor, num_experts: int) -> torch.Tensor:
+    """Tokens per expert, int32 ``[num_experts]`` (reference kernels/nvidia/ep_a2a.py:309-321 ``kernel_bincount``): the
+    ``splits`` of :func:`route`."""
+    ids = exp_indices.reshape(-1, 1)
+    return route(ids, num_experts).splits
+
+
+def calc_gather_index(topk_ids: torch.Tensor, num_experts: int) -> Tuple[torch.Tensor, torch.Tensor]:
+    """``(gather_index, scatter_index)`` of the expert-sorted layout: row ``i`` of the sorted activations is token
+    ``gather_index[i]``, and pair ``(t, k)`` sits at row ``scatter_index[t * topk + k]`` (the reference builds these
+    with torch argsort in its MoE tests, test/nvidia/test_ag_moe.py)."""
+    r = route(topk_ids, num_experts)
+    return r.sorted_token, r.slot_of
