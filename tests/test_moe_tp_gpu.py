@@ -60,7 +60,11 @@ def test_ag_group_gemm(cuda_device, world, tpr, E, K, N, topk):
 
 
 @pytest.mark.parametrize("world,M,E,Kl,N,topk", [(1, 256, 8, 256, 256, 2), (2, 512, 16, 128, 512, 2), (4, 256, 32, 256, 1024, 4)])
-def test_moe_reduce_rs(cuda_device, world, M, E, Kl, N, topk):
+@pytest.mark.parametrize("fused", [True, False], ids=["fused_topk_rs", "staged"])
+def test_moe_reduce_rs(cuda_device, monkeypatch, world, M, E, Kl, N, topk, fused):
+    """`fused`: the top-k weighted reduce happens inside the reduce-scatter kernel (the [M, N] partial is never
+    written); staged: separate top-k reduce kernel, then the plain reduce-scatter."""
+    monkeypatch.setattr(MT, "FUSED_TOPK_RS", fused)
     torch.manual_seed(world * 11 + M)
     lw = LocalWorld(world, cuda_device)
     ids = torch.randint(0, E, (M, topk), dtype=torch.int32, device=cuda_device)
@@ -69,11 +73,14 @@ def test_moe_reduce_rs(cuda_device, world, M, E, Kl, N, topk):
     b = [(torch.randn(E, Kl, N, device=cuda_device) * (Kl * world) ** -0.5).to(torch.bfloat16) for _ in range(world)]
     ctxs = [MT.create_moe_rs_context(None, r, world, world, M, N, E, topk, torch.bfloat16, torch.bfloat16, cuda_device,
                                      full_topk_ids=ids, full_topk_weight=w, heap=lw.heap(r)) for r in range(world)]
-    for r in range(world):
-        MT.moe_reduce_rs(r, world, world, a[r], b[r], ctxs[r], phase=1)
-    outs = [MT.moe_reduce_rs(r, world, world, a[r], b[r], ctxs[r], phase=2) for r in range(world)]
-    check_status()
-    total = sum((_expert_matmul(a[r], ids.reshape(-1), b[r]).view(M, topk, N) * w.view(M, topk, 1)).sum(1) for r in range(world))
-    mpr = M // world
-    for r in range(world):
-        torch.testing.assert_close(outs[r].float(), total[r * mpr:(r + 1) * mpr], atol=6e-2, rtol=3e-2)
+    for it in range(2):   # two calls: both staging parities
+        if it == 1:
+            a = [torch.randn(M * topk, Kl, device=cuda_device).to(torch.bfloat16) for _ in range(world)]
+        for r in range(world):
+            MT.moe_reduce_rs(r, world, world, a[r], b[r], ctxs[r], phase=1)
+        outs = [MT.moe_reduce_rs(r, world, world, a[r], b[r], ctxs[r], phase=2) for r in range(world)]
+        check_status()
+        total = sum((_expert_matmul(a[r], ids.reshape(-1), b[r]).view(M, topk, N) * w.view(M, topk, 1)).sum(1) for r in range(world))
+        mpr = M // world
+        for r in range(world):
+            torch.testing.assert_close(outs[r].float(), total[r * mpr:(r + 1) * mpr], atol=6e-2, rtol=3e-2)

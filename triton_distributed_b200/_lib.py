@@ -103,6 +103,7 @@ class CollArgs(C.Structure):
         ("status", C.c_void_p),
         ("timeout_ns", C.c_uint64),
         ("stream", C.c_void_p),
+        ("pos_of", C.c_void_p), ("topk_w", C.c_void_p), ("topk", C.c_int), ("row_bytes", C.c_int),
     ]
 
 

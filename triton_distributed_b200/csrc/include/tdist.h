@@ -137,6 +137,13 @@ typedef struct TdistCollArgs {
     void* status;
     uint64_t timeout_ns;
     void* stream;
+    /* reduce-scatter, optional fused top-k reduce (MoE): with topk > 0, `input` is the expert-sorted bf16 output
+     * [rows, row_bytes] of a grouped GEMM and logical row t of the [world * seg_bytes] input is
+     * sum_k topk_w[t*topk+k] * input_row[pos_of[t*topk+k]] (topk_w may be NULL = 1). */
+    const void* pos_of;
+    const void* topk_w;
+    int topk;
+    int row_bytes;
 } TdistCollArgs;
 
 int tdist_allgather(const TdistCollArgs* args);

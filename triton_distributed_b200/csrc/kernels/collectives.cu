@@ -30,6 +30,11 @@ struct CollParams {
     size_t seg_bytes;
     int world, rank, mode, phase, ctas_per_peer, dtype;
     uint64_t epoch;
+    // fused top-k reduce (reduce-scatter of MoE outputs): row t of the logical input is
+    // sum_k topk_w[t*topk+k] * input_row[pos_of[t*topk+k]], computed on the fly (bf16 only); topk == 0 = plain input
+    const int* pos_of;
+    const float* topk_w;
+    int topk, row_bytes;
     WaitCtx wctx;
 };
 
@@ -120,6 +125,36 @@ __global__ void __launch_bounds__(kCollThreads) allgather_kernel(const CollParam
     }
 }
 
+// 8 bf16 columns (vector c) of logical row t in top-k mode: sum_k w * gathered row, fp32.
+__device__ __forceinline__ void topk_vec(const CollParams& p, size_t t, size_t c, float (&acc)[8]) {
+    const size_t vpr = static_cast<size_t>(p.row_bytes) / 16;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) acc[j] = 0.f;
+    for (int k0 = 0; k0 < p.topk; k0 += 8) {
+        uint4 q[8];
+        float w[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            w[j] = 0.f;
+            q[j] = make_uint4(0, 0, 0, 0);
+            if (k0 + j < p.topk) {
+                const size_t pair = t * p.topk + k0 + j;
+                w[j] = p.topk_w ? p.topk_w[pair] : 1.f;
+                q[j] = ld_nc_v4(p.input + (static_cast<size_t>(p.pos_of[pair]) * vpr + c) * 16);
+            }
+        }
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            const uint32_t u[4] = {q[j].x, q[j].y, q[j].z, q[j].w};
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                acc[2 * i] += w[j] * __uint_as_float(u[i] << 16);
+                acc[2 * i + 1] += w[j] * __uint_as_float(u[i] & 0xffff0000u);
+            }
+        }
+    }
+}
+
 // out[i] = sum over sources of (staging[src][i] | own input rows), 16 bytes per thread per step.
 template <typename T, typename Acc>
 __device__ __forceinline__ void reduce_sources(const CollParams& p, size_t first, size_t step) {
@@ -129,7 +164,19 @@ __device__ __forceinline__ void reduce_sources(const CollParams& p, size_t first
     const char* own = p.input + static_cast<size_t>(p.rank) * p.seg_bytes;
     for (size_t i = first; i < nvec; i += step) {
         Acc acc[V];
-        {
+        bool own_done = false;
+        if constexpr (sizeof(T) == 2 && sizeof(Acc) == 4) {
+            if (p.topk > 0) {  // bf16 only (checked on the host)
+                const size_t vpr = static_cast<size_t>(p.row_bytes) / 16;
+                const size_t mpr = p.seg_bytes / p.row_bytes;
+                float a8[8];
+                topk_vec(p, static_cast<size_t>(p.rank) * mpr + i / vpr, i % vpr, a8);
+#pragma unroll
+                for (int j = 0; j < V; ++j) acc[j] = static_cast<Acc>(a8[j]);
+                own_done = true;
+            }
+        }
+        if (!own_done) {
             const uint4 q = ld_nc_v4(own + i * 16);
             const T* e = reinterpret_cast<const T*>(&q);
 #pragma unroll
@@ -159,7 +206,24 @@ __global__ void __launch_bounds__(kCollThreads) reduce_scatter_kernel(const Coll
         size_t b0, b1;
         slice_range(seg, slice, p.ctas_per_peer, &b0, &b1);
         char* dst = p.buf_peer[peer] + static_cast<size_t>(p.rank) * seg;
-        copy_coop(dst + b0, p.input + static_cast<size_t>(peer) * seg + b0, b1 - b0, threadIdx.x, blockDim.x);
+        if (p.topk > 0) {
+            // the peer's rows do not exist anywhere yet: reduce the top-k expert outputs of each token straight
+            // into the peer's staging
+            const size_t vpr = static_cast<size_t>(p.row_bytes) / 16;
+            const size_t mpr = seg / p.row_bytes;
+            for (size_t v = b0 / 16 + threadIdx.x; v < b1 / 16; v += blockDim.x) {
+                float a8[8];
+                topk_vec(p, static_cast<size_t>(peer) * mpr + v / vpr, v % vpr, a8);
+                uint4 o;
+                o.x = pack_bf16x2(a8[0], a8[1]);
+                o.y = pack_bf16x2(a8[2], a8[3]);
+                o.z = pack_bf16x2(a8[4], a8[5]);
+                o.w = pack_bf16x2(a8[6], a8[7]);
+                st_v4(dst + v * 16, o);
+            }
+        } else {
+            copy_coop(dst + b0, p.input + static_cast<size_t>(peer) * seg + b0, b1 - b0, threadIdx.x, blockDim.x);
+        }
         group_signal(p, peer);
     }
     if (!(p.phase & 2)) return;
@@ -240,6 +304,10 @@ static int fill_params(const TdistCollArgs* a, CollParams* p) {
     p->phase = a->phase ? a->phase : 3;
     p->dtype = a->dtype;
     p->epoch = a->epoch;
+    p->pos_of = static_cast<const int*>(a->pos_of);
+    p->topk_w = static_cast<const float*>(a->topk_w);
+    p->topk = a->topk;
+    p->row_bytes = a->row_bytes;
     p->ctas_per_peer = a->ctas_per_peer > 0 ? a->ctas_per_peer : 4;
     if (p->ctas_per_peer > 16) p->ctas_per_peer = 16;
     p->wctx.status = static_cast<Status*>(a->status);
@@ -274,6 +342,12 @@ extern "C" int tdist_reduce_scatter(const TdistCollArgs* a) {
     if (a->seg_bytes % 16 != 0) return fail(TDIST_EINVAL, "reduce-scatter needs a segment size that is a multiple of 16 bytes");
     if (a->input == nullptr || a->output == nullptr) return fail(TDIST_EINVAL, "reduce-scatter: null input/output");
     if (a->dtype < TDIST_BF16 || a->dtype > TDIST_I32) return fail(TDIST_EINVAL, "reduce-scatter: bad dtype");
+    if (a->topk < 0 || a->topk > 64) return fail(TDIST_EINVAL, "reduce-scatter: topk out of range");
+    if (a->topk > 0) {
+        if (a->dtype != TDIST_BF16) return fail(TDIST_EINVAL, "reduce-scatter with top-k reduce takes bf16");
+        if (a->pos_of == nullptr || a->row_bytes <= 0 || a->row_bytes % 16 != 0 || a->seg_bytes % a->row_bytes != 0)
+            return fail(TDIST_EINVAL, "reduce-scatter with top-k reduce needs pos_of and a row size that is a multiple of 16 bytes and divides the segment");
+    }
     const int grid = 1 + (a->world - 1) * p.ctas_per_peer;
     reduce_scatter_kernel<<<grid, kCollThreads, 0, static_cast<cudaStream_t>(a->stream)>>>(p);
     TDIST_CUDA_OK(cudaGetLastError());

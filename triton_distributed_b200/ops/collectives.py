@@ -313,6 +313,55 @@ def reduce_scatter_2d_op(input: torch.Tensor, ctx: ReduceScatter2DContext, out: 
     return o
 
 
+def topk_reduce_scatter(y_sorted: torch.Tensor, pos_of: torch.Tensor, weights: Optional[torch.Tensor], ntok: int, topk: int,
+                        ctx: ReduceScatter2DContext, out: Optional[torch.Tensor] = None, phase: int = 3, stream=None) -> torch.Tensor:
+    """Fused MoE tail: ``out[M/ws, N] = rows of this rank of sum_ranks P_r`` with
+    ``P_r[t] = sum_k weights[t,k] * y_sorted_r[pos_of[t*topk+k]]``. ``P_r`` is never materialised: the kernel reduces
+    the top-k expert outputs of each token straight into the owning rank's staging, signals, then sums the
+    sources in fp32 (reference kernels/nvidia/moe_reduce_rs.py:471-546, the kernel that stores into peers from
+    inside the reduction)."""
+    global launch_count
+    N = y_sorted.shape[1]
+    if ntok % ctx.world:
+        raise ValueError("the token count must be divisible by the world size")
+    mpr = ntok // ctx.world
+    if y_sorted.device.type != "cuda" or y_sorted.dtype != torch.bfloat16:
+        rows = y_sorted[pos_of.long()].float().view(ntok, topk, N)
+        w = weights.float().view(ntok, topk, 1) if weights is not None else 1.0
+        return reduce_scatter_2d_op((rows * w).sum(1).to(y_sorted.dtype), ctx, out=out, phase=phase, stream=stream)
+    if not y_sorted.is_contiguous() or (N * 2) % 16:
+        raise ValueError("y_sorted must be contiguous with N a multiple of 8")
+    if ntok * N > ctx.max_M * ctx.N:
+        raise ValueError("problem exceeds the context's staging")
+    o = out if out is not None else torch.empty((mpr, N), dtype=y_sorted.dtype, device=y_sorted.device)
+    a = _lib.CollArgs()
+    half = (ctx.epoch + (1 if phase != 2 else 0)) & 1
+    a.buf_peer = ctx.staging.half_ptr_arrays()[half]
+    a.sig_peer = ctx.signal.cached_ptr_array()
+    a.counters = ctx.counters.data_ptr()
+    a.input = y_sorted.data_ptr()
+    a.output = o.data_ptr()
+    a.seg_bytes = mpr * N * 2
+    a.world, a.rank = ctx.world, ctx.rank
+    a.phase = phase
+    a.dtype = _lib.DT_BF16
+    a.ctas_per_peer = ctx.ctas_per_peer or (1 if a.seg_bytes <= (64 << 10) else (4 if a.seg_bytes <= (4 << 20) else 16))
+    pos = pos_of if pos_of.dtype == torch.int32 else pos_of.to(torch.int32)
+    w = weights.float().contiguous() if weights is not None else None
+    a.pos_of = pos.contiguous().data_ptr()
+    a.topk_w = w.data_ptr() if w is not None else None
+    a.topk, a.row_bytes = topk, N * 2
+    if phase != 2:
+        ctx.epoch += 1
+    a.epoch = ctx.epoch
+    a.status = _status_ptr()
+    a.timeout_ns = default_timeout_ns()
+    a.stream = _stream_ptr(y_sorted.device, stream)
+    _lib.check(_lib.lib().tdist_reduce_scatter(C.byref(a)), "tdist_reduce_scatter")
+    launch_count += 1
+    return o
+
+
 def ring_reduce(input: torch.Tensor, output: torch.Tensor, begin_idx: int, num_splits: int, num_sms: int = -1) -> torch.Tensor:
     """Sum the ``num_splits`` row blocks of ``input`` (starting the rotation at ``begin_idx``) into
     ``output``; accumulation in fp32 (reference kernels/nvidia/reduce_scatter.py:752-763)."""

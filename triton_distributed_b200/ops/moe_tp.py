@@ -14,8 +14,8 @@ Public surface (names of the reference):
 Pipeline on CUDA (each stage one hand-written kernel): all-gather of the token shards (push kernel
 over NVLink) -> block-aligned expert sort (``moe_align_block_size``) -> row gather into the sorted,
 128-row-padded layout -> grouped GEMM (the persistent tcgen05 kernel picking B[expert] per 128-row
-block) -> un-permute / top-k weighted reduce -> reduce-scatter kernel. The stages are not yet fused
-across the collective the way AG-GEMM and GEMM-RS are.
+block) -> top-k weighted reduce fused into the reduce-scatter kernel (each token's expert outputs are reduced
+straight into the owning rank's staging). The all-gather and the grouped GEMM are separate launches.
 
 CPU tensors run a torch restatement (masked per-expert matmul, the reference's own oracle:
 test/nvidia/test_ag_moe.py:24-39).
@@ -36,6 +36,7 @@ from . import gemm as G
 from . import moe_utils as MU
 
 GROUP_BLOCK_M = 128
+FUSED_TOPK_RS = True   # False: separate top-k reduce kernel, then the plain reduce-scatter (for A/B checks)
 launch_count = 0
 
 
@@ -276,9 +277,13 @@ def moe_reduce_rs(rank: int, world_size: int, local_world_size: int, a: torch.Te
         a_sorted, pos_of = gather_rows(a, ctx.sorted_ids, 1, numel, want_inverse=True)
         if ctx.b_nk is None:
             ctx.b_nk = b.transpose(1, 2).contiguous()
-        y_sorted = group_gemm(a_sorted, ctx.b_nk, ctx.expert_ids, ctx.num_blocks)
-        ctx._partial = topk_reduce(y_sorted, pos_of, ctx.full_topk_weight, M, ctx.topk)
-    out = CO.reduce_scatter_2d_op(ctx._partial, ctx.rs_ctx, phase=phase)
+        ctx._partial = (group_gemm(a_sorted, ctx.b_nk, ctx.expert_ids, ctx.num_blocks), pos_of)
+    y_sorted, pos_of = ctx._partial
+    if FUSED_TOPK_RS and y_sorted.dtype == torch.bfloat16 and M % world_size == 0:
+        # top-k weighted reduce and reduce-scatter in one kernel: the [M, N] partial is never written
+        out = CO.topk_reduce_scatter(y_sorted, pos_of, ctx.full_topk_weight, M, ctx.topk, ctx.rs_ctx, phase=phase)
+    else:
+        out = CO.reduce_scatter_2d_op(topk_reduce(y_sorted, pos_of, ctx.full_topk_weight, M, ctx.topk), ctx.rs_ctx, phase=phase)
     if debug_sync:
         torch.cuda.synchronize()
     return out
