@@ -40,13 +40,19 @@ def run(group, rank, world, dev):
     ctx.source.copy_(torch.full((4096,), rank + 1, dtype=torch.uint8, device=dev))
     torch.cuda.synchronize()
     dist.barrier(group)
+    left = (rank - 1) % world
     for it in range(1, 4):
-        P.run_primitive(ctx, "ring_put", value=it)        # put into rank+1's slot `rank`, notify, wait for rank-1
+        # putmem_signal: copy my block into rank+1's slot `rank`, then set its signal word to `it`; my own kernel
+        # then waits until MY signal word has been set by rank-1 and reports whether the wait succeeded
+        P.run_primitive(ctx, "put_signal", value=it, scope="block")
+        torch.cuda.synchronize()
         check_status()                                    # raises if a wait ran out
-        left = (rank - 1) % world
-        if world > 1:
-            assert int(ctx.slot(left)[0]) == left + 1
-    dist_print(f"rank {rank}: ring put + notify/wait ok", allowed_ranks="all")
+        assert int(ctx.result[0]) == 1
+        assert int(ctx.slot(left)[0]) == left + 1 and int(ctx.slot(left)[-1]) == left + 1
+        # This demo kernel waits for EQUALITY with `it`, so no rank may run a round ahead: keep them in step. (The
+        # fused ops avoid the host barrier by waiting for >= a call number that only grows.)
+        dist.barrier(group)
+    dist_print(f"rank {rank}: putmem_signal ring + bounded wait ok", allowed_ranks="all")
 
 
 if __name__ == "__main__":
