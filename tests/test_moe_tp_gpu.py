@@ -38,7 +38,11 @@ def test_group_gemm_blocks_pick_their_expert(cuda_device, T, E, K, N, topk):
 
 
 @pytest.mark.parametrize("world,tpr,E,K,N,topk", [(1, 256, 8, 256, 256, 2), (4, 128, 16, 512, 264, 2), (8, 64, 32, 256, 512, 4)])
-def test_ag_group_gemm(cuda_device, world, tpr, E, K, N, topk):
+@pytest.mark.parametrize("fused", [True, False], ids=["gather_in_gemm", "staged"])
+def test_ag_group_gemm(cuda_device, monkeypatch, world, tpr, E, K, N, topk, fused):
+    """`fused`: the all-gather only sends; the grouped GEMM gathers its A rows itself (cp.async by index) and waits
+    per 128-row block for the arrival flag of the rank the block's tokens come from."""
+    monkeypatch.setattr(MT, "FUSED_AG_GROUP_GEMM", fused)
     torch.manual_seed(world * 7 + tpr)
     lw = LocalWorld(world, cuda_device)
     M = world * tpr
@@ -47,16 +51,19 @@ def test_ag_group_gemm(cuda_device, world, tpr, E, K, N, topk):
     ids = torch.randint(0, E, (M, topk), dtype=torch.int32, device=cuda_device)
     ctxs = [MT.create_ag_group_gemm_intra_node_context(None, shards[r], bs[r], ids, E, max_M=M, rank=r, num_ranks=world,
                                                        heap=lw.heap(r)) for r in range(world)]
-    if world > 1:
+    for it in range(2):   # two calls: both gather buffers
+        if it == 1:
+            shards = [torch.randn(tpr, K, device=cuda_device).to(torch.bfloat16) for _ in range(world)]
+        if world > 1:
+            for r in range(world):
+                MT.ag_group_gemm_intra_node(shards[r], bs[r], ctxs[r], phase=1)
+        outs = [MT.ag_group_gemm_intra_node(shards[r], bs[r], ctxs[r], phase=2 if world > 1 else 3) for r in range(world)]
+        check_status()
+        full = torch.cat(shards)
+        rows = full[torch.arange(M * topk, device=cuda_device) // topk]
         for r in range(world):
-            MT.ag_group_gemm_intra_node(shards[r], bs[r], ctxs[r], phase=1)
-    outs = [MT.ag_group_gemm_intra_node(shards[r], bs[r], ctxs[r], phase=2 if world > 1 else 3) for r in range(world)]
-    check_status()
-    full = torch.cat(shards)
-    rows = full[torch.arange(M * topk, device=cuda_device) // topk]
-    for r in range(world):
-        ref = _expert_matmul(rows, ids.reshape(-1), bs[r])
-        torch.testing.assert_close(outs[r].float(), ref, atol=3e-2, rtol=3e-2)
+            ref = _expert_matmul(rows, ids.reshape(-1), bs[r])
+            torch.testing.assert_close(outs[r].float(), ref, atol=3e-2, rtol=3e-2)
 
 
 @pytest.mark.parametrize("world,M,E,Kl,N,topk", [(1, 256, 8, 256, 256, 2), (2, 512, 16, 128, 512, 2), (4, 256, 32, 256, 1024, 4)])
@@ -84,3 +91,23 @@ def test_moe_reduce_rs(cuda_device, monkeypatch, world, M, E, Kl, N, topk, fused
         mpr = M // world
         for r in range(world):
             torch.testing.assert_close(outs[r].float(), total[r * mpr:(r + 1) * mpr], atol=6e-2, rtol=3e-2)
+
+
+@pytest.mark.parametrize("T,E,K,N,topk", [(300, 8, 264, 520, 2), (128, 4, 64, 256, 1), (777, 16, 1024, 384, 3)])
+def test_group_gemm_gathers_rows_in_kernel(cuda_device, T, E, K, N, topk):
+    """The cp.async row-gathering producer against the staged path (row gather kernel + TMA-fed grouped GEMM):
+    same sorted layout, ragged K (not a multiple of the 64-wide K block), padding rows."""
+    torch.manual_seed(T + K)
+    x = torch.randn(T, K, device=cuda_device).to(torch.bfloat16)
+    b = (torch.randn(E, N, K, device=cuda_device) * K ** -0.5).to(torch.bfloat16)
+    ids = torch.randint(0, E, (T, topk), dtype=torch.int32, device=cuda_device)
+    sorted_ids, expert_ids, _, _, post_pad = MU.sort_topk_ids_align_block_size(ids, E, 1, T, 128)
+    n = int(post_pad)
+    sid = sorted_ids[:n].contiguous()
+    nb = (post_pad // 128).to(torch.int32)
+    a_sorted, _ = MT.gather_rows(x, sid, topk, T * topk)
+    want = MT.group_gemm(a_sorted, b, expert_ids, nb)
+    row_index = torch.div(sid, topk, rounding_mode="floor").to(torch.int32)
+    got = MT.group_gemm_gather(x, row_index, b, expert_ids, nb)
+    check_status()
+    assert torch.equal(got, want)

@@ -55,6 +55,8 @@ class GemmArgs(C.Structure):
         ("trace", C.c_void_p),
         ("expert_ids", C.c_void_p), ("num_m_blocks", C.c_void_p), ("num_experts", C.c_int),
         ("a_ws_mc", C.c_void_p),
+        ("a_gather", C.c_void_p), ("a_gather_rows", C.c_int), ("block_src", C.c_void_p), ("src_flags", C.c_void_p),
+        ("src_epoch", C.c_uint64), ("src_rank", C.c_int), ("src_world", C.c_int),
     ]
 
 

@@ -79,6 +79,18 @@ typedef struct TdistGemmArgs {
     /* AG, optional: multicast alias of `a_ws` (a heap bound to an NVSwitch multicast object). When set, the
      * pushers store every block once with multimem.st instead of once per peer. */
     void* a_ws_mc;
+    /* PLAIN, optional row-gathering A: row r of the logical A [m_per_rank, K] is row a_gather[r] (device int32) of
+     * the matrix at `a` ([a_gather_rows, K]); indices outside [0, a_gather_rows) read as zeros. One CTA per tile;
+     * the producer warp copies the rows with cp.async. With block_src (device int32 per 128-row block) the rows of
+     * a block belong to rank block_src[b]'s segment of an all-gather in flight: before loading them the kernel waits
+     * (bounded) until src_flags[block_src[b]] >= src_epoch (64-bit words, the all-gather's arrival flags); blocks
+     * of src_rank itself are not waited for. */
+    const void* a_gather;
+    int a_gather_rows;
+    const void* block_src;
+    const void* src_flags;
+    uint64_t src_epoch;
+    int src_rank, src_world;
 } TdistGemmArgs;
 
 int tdist_gemm_run(const TdistGemmArgs* args);

@@ -97,8 +97,28 @@ struct GemmParams {
     unsigned long long* trace;  // optional timeline (see tdist.h), nullptr = off
     const int* expert_ids;      // grouped GEMM: expert (slice of B) of every 128-row block, nullptr = plain
     const int* num_m_blocks;    // grouped GEMM: device count of live 128-row blocks (rest is padding)
+    // Row-gathering A operand (PLAIN, one CTA per tile): row r of the logical A is row a_gather[r] of the matrix
+    // at a_raw ([a_gather_rows, K], K contiguous); indices >= a_gather_rows read as zeros. With block_src set,
+    // the rows of 128-row block b come from rank block_src[b]'s segment of an all-gather in flight: the
+    // producer waits until src_flags[block_src[b]] >= src_epoch before it loads them.
+    const int* a_gather;
+    const char* a_raw;
+    int a_gather_rows;
+    const int* block_src;
+    const uint64_t* src_flags;
+    uint64_t src_epoch;
+    int src_rank, src_world;    // this rank and the size of the all-gather's group
     WaitCtx wctx;
 };
+
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src, int src_bytes) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(src_bytes) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() {
+    asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
+}
 
 struct TileCoord {
     int seg, m_in_seg, n_tile;
@@ -353,7 +373,8 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_sm100_kernel(const __grid_con
         prefetch_tensormap(&p.tm_b);
         if (MODE == TDIST_GEMM_AG) prefetch_tensormap(&p.tm_a_own);
         for (int s = 0; s < STAGES; ++s) {
-            mbar_init(bar_full(s), 1);
+            // gather mode: the 32 producer lanes each arrive once their cp.async rows have landed, plus lane 0's expect_tx
+            mbar_init(bar_full(s), p.a_gather != nullptr ? 33 : 1);
             mbar_init(bar_empty(s), 1);
         }
         for (int b = 0; b < 2; ++b) {
@@ -377,7 +398,76 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_sm100_kernel(const __grid_con
     tc_fence_after();
     const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(tmem_slot);
 
-    if (warp == 0) {
+    if (warp == 0 && MODE == TDIST_GEMM_PLAIN && CTAS == 1 && p.a_gather != nullptr) {
+        // ===================== gathering producer: A rows by index with cp.async, B with TMA ==========
+        // All 32 lanes copy: lane l owns rows l, l+32, l+64, l+96 of the tile, 8 chunks of 16 bytes per row and K
+        // block, written in the 128-byte-swizzled layout the MMA descriptors expect. Completion is lagged: the
+        // arrival for stage i is made when stage i + LAG has been issued (cp.async.wait_group), after a proxy fence
+        // that makes the generic-proxy writes visible to the tensor core's async-proxy reads.
+        constexpr int LAG = STAGES - 1;
+        uint32_t it = 0, signaled = 0;
+        const int live_blocks = p.num_m_blocks ? *p.num_m_blocks : 0x7fffffff;
+        auto drain = [&]() {
+            cp_async_wait<0>();
+            fence_proxy_async();
+            while (signaled < it) {
+                mbar_arrive(bar_full(signaled % STAGES));
+                ++signaled;
+            }
+        };
+        for (int t = unit; t < p.num_tiles; t += num_units) {
+            const TileCoord tc = decode_tile(t, first_seg, p.world, p.seg_m_tiles, p.n_tiles, p.group_m);
+            const int block = tc.m_in_seg;
+            if (block >= live_blocks) continue;
+            const int bz = p.expert_ids ? p.expert_ids[block] : 0;
+            if (p.block_src != nullptr) {
+                const int src = p.block_src[block];
+                if (src != p.src_rank && src >= 0 && src < p.src_world) {
+                    drain();  // do not leave the MMA side waiting for stages that are already in shared memory
+                    if (lane == 0) signal_wait_until(p.src_flags + src, kCmpGe, p.src_epoch, p.wctx, src, 8);
+                    __syncwarp();
+                }
+            }
+            const char* rowp[4];
+            bool valid[4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const int r = block * BM + lane + 32 * j;
+                const int idx = r < p.m_per_rank ? p.a_gather[r] : p.a_gather_rows;
+                valid[j] = idx >= 0 && idx < p.a_gather_rows;
+                rowp[j] = p.a_raw + (valid[j] ? static_cast<size_t>(idx) * p.k * 2 : 0);
+            }
+            const int col = tc.n_tile * BN;
+            for (int kb = 0; kb < p.k_blocks; ++kb, ++it) {
+                const uint32_t s = it % STAGES;
+                mbar_wait(bar_empty(s), ((it / STAGES) & 1u) ^ 1u, p.wctx, 2);
+                const uint32_t sa = smem_u32(smem + s * STAGE_BYTES);
+                if (lane == 0) {
+                    mbar_expect_tx(bar_full(s), T::B_BYTES);
+                    tma_load_3d(sa + A_BYTES, &p.tm_b, bar_full(s), kb * BK, col, bz);
+                }
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    const int r = lane + 32 * j;
+#pragma unroll
+                    for (int c = 0; c < 8; ++c) {
+                        const int kcol = kb * BK + c * 8;
+                        const int nbytes = (valid[j] && kcol < p.k) ? 16 : 0;  // K % 8 == 0: a chunk is whole or absent
+                        cp_async16(sa + r * 128 + ((c ^ (r & 7)) << 4), rowp[j] + (nbytes ? static_cast<size_t>(kcol) * 2 : 0), nbytes);
+                    }
+                }
+                cp_async_commit();
+                if (it + 1 - signaled > LAG) {
+                    cp_async_wait<LAG>();
+                    fence_proxy_async();
+                    mbar_arrive(bar_full(signaled % STAGES));
+                    ++signaled;
+                }
+            }
+        }
+        drain();
+        __syncwarp();
+    } else if (warp == 0) {
         // ===================== TMA producer (every CTA loads its own A rows and B rows) ==========
         if (lane == 0) {
             uint32_t it = 0;
@@ -597,7 +687,7 @@ using namespace tdist;
 using tdist_host::fail;
 
 static bool use_pair(const TdistGemmArgs* a) {
-    if (a->expert_ids != nullptr) return false;  // one expert per 128-row block
+    if (a->expert_ids != nullptr || a->a_gather != nullptr) return false;  // one expert / one source per 128-row block
     if (a->cta_pair == 0) return false;
     if (a->cta_pair > 0) return true;
     return a->m_per_rank > BM;  // a second CTA would only compute padding otherwise
@@ -718,6 +808,12 @@ extern "C" int tdist_gemm_run(const TdistGemmArgs* a) {
     if (a->mode < TDIST_GEMM_PLAIN || a->mode > TDIST_GEMM_RS) return fail(TDIST_EINVAL, "bad mode");
     if (a->expert_ids != nullptr && (a->mode != TDIST_GEMM_PLAIN || a->world != 1))
         return fail(TDIST_EINVAL, "grouped GEMM (expert_ids) is a single-rank plain-mode feature");
+    if (a->a_gather != nullptr) {
+        if (a->mode != TDIST_GEMM_PLAIN || a->world != 1) return fail(TDIST_EINVAL, "row-gathering A is a plain-mode feature (world = 1 in the GEMM's own terms)");
+        if (a->a_gather_rows < 1) return fail(TDIST_EINVAL, "row-gathering A needs the number of source rows");
+        if (a->block_src != nullptr && (a->src_flags == nullptr || a->src_world < 1 || a->src_world > TDIST_MAX_RANKS || a->src_rank < 0 || a->src_rank >= a->src_world))
+            return fail(TDIST_EINVAL, "block_src needs src_flags and a valid (src_rank, src_world)");
+    }
 
     const GridPlan plan = plan_grid(a);
     const int ctas = plan.ctas_per_tile;
@@ -768,6 +864,14 @@ extern "C" int tdist_gemm_run(const TdistGemmArgs* a) {
         p.a_ws_peer[r] = static_cast<char*>(a->a_ws_peer[r]);
         p.flags_peer[r] = a->flags_peer[r];
     }
+    p.a_gather = static_cast<const int*>(a->a_gather);
+    p.a_raw = static_cast<const char*>(a->a);
+    p.a_gather_rows = a->a_gather_rows;
+    p.block_src = static_cast<const int*>(a->block_src);
+    p.src_flags = static_cast<const uint64_t*>(a->src_flags);
+    p.src_epoch = a->src_epoch;
+    p.src_rank = a->src_rank;
+    p.src_world = a->src_world;
     p.stage_local = static_cast<const char*>(a->c_stage_peer[a->rank]);
     p.a_ws_mc = (a->mode == TDIST_GEMM_AG && a->world > 1) ? static_cast<char*>(a->a_ws_mc) : nullptr;
     p.rs_out = a->rs_out;

@@ -36,6 +36,7 @@ from . import gemm as G
 from . import moe_utils as MU
 
 GROUP_BLOCK_M = 128
+FUSED_AG_GROUP_GEMM = True   # False: all-gather (waits for every rank), row-gather kernel, then the grouped GEMM
 FUSED_TOPK_RS = True   # False: separate top-k reduce kernel, then the plain reduce-scatter (for A/B checks)
 launch_count = 0
 
@@ -126,6 +127,44 @@ def group_gemm(a_sorted: torch.Tensor, b: torch.Tensor, expert_ids: torch.Tensor
     return c
 
 
+def group_gemm_gather(a: torch.Tensor, row_index: torch.Tensor, b: torch.Tensor, expert_ids: torch.Tensor,
+                      num_blocks: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None,
+                      block_src: Optional[torch.Tensor] = None, src_flags: Optional[torch.Tensor] = None, src_epoch: int = 0,
+                      src_rank: int = 0, src_world: int = 1) -> torch.Tensor:
+    """Grouped GEMM whose A rows are gathered inside the kernel: ``out[r] = a[row_index[r]] @ b[expert_ids[r // 128]].T``
+    (rows with ``row_index >= a.shape[0]`` are padding and read as zeros). With ``block_src`` the rows of 128-row
+    block ``i`` come from rank ``block_src[i]``'s segment of an all-gather that may still be in flight: the kernel
+    waits for that rank's arrival flag (``src_flags[rank] >= src_epoch``) before loading them, so blocks of ranks
+    that have arrived compute while later segments are still on the wire."""
+    rows = row_index.shape[0]
+    E, N, K = b.shape
+    if rows % GROUP_BLOCK_M:
+        raise ValueError("grouped GEMM rows must be a multiple of 128")
+    if a.device.type != "cuda":
+        padded = torch.cat([a, a.new_zeros((1, K))])
+        return group_gemm(padded[row_index.long().clamp(max=a.shape[0])], b, expert_ids, num_blocks, out)
+    G._check_operands(a, b.view(E * N, K))
+    c = out if out is not None else torch.empty((rows, N), dtype=a.dtype, device=a.device)
+    g = G._base_args(a, b.view(E * N, K), 1, 0, _lib.GEMM_PLAIN)
+    g.n = N
+    g.c = c.data_ptr()
+    g.m_per_rank = rows
+    g.epoch = 1
+    g.expert_ids = expert_ids.data_ptr()
+    g.num_m_blocks = num_blocks.data_ptr() if num_blocks is not None else None
+    g.num_experts = E
+    g.cta_pair = 0
+    g.a_gather = row_index.data_ptr()
+    g.a_gather_rows = a.shape[0]
+    if block_src is not None:
+        g.block_src = block_src.data_ptr()
+        g.src_flags = src_flags.data_ptr()
+        g.src_epoch = src_epoch
+        g.src_rank, g.src_world = src_rank, src_world
+    G._launch(g)
+    return c
+
+
 # ---------------------------------------------------------------------------- AG + GroupGEMM
 @dataclass
 class MoEAllGatherGroupGEMMTensorParallelContext:
@@ -145,6 +184,9 @@ class MoEAllGatherGroupGEMMTensorParallelContext:
     rank_block_num: Optional[torch.Tensor] = None
     num_blocks: Optional[torch.Tensor] = None    # int32 [1]: live 128-row blocks
     b_nk: Optional[torch.Tensor] = None          # [E, N, K] copy of the weights (K contiguous)
+    row_index: Optional[torch.Tensor] = None     # int32 [sorted rows]: token of every sorted row (padding = M)
+    pos_of: Optional[torch.Tensor] = None        # int32 [M * topk]: sorted row of every (token, k) pair
+    calls: int = 0
 
 
 def sort_topk_ids_align_block_size(topk_ids, num_experts, num_ranks, num_tokens_per_rank, block_size, moe_stream=None):
@@ -172,9 +214,16 @@ def create_ag_group_gemm_intra_node_context(tp_pg, A: torch.Tensor, B: torch.Ten
     ctx.sorted_ids = sorted_ids[: int(post_pad)].contiguous()
     ctx.num_blocks = (post_pad // GROUP_BLOCK_M).to(torch.int32)
     ctx.b_nk = B.transpose(1, 2).contiguous()
+    # static routing: the gather index of the fused kernel and the inverse permutation of its output
+    numel = M * topk
+    ctx.row_index = torch.div(ctx.sorted_ids, topk, rounding_mode="floor").to(torch.int32).contiguous()   # padding numel -> M
+    valid = ctx.sorted_ids < numel
+    ctx.pos_of = torch.zeros(numel, dtype=torch.int32, device=ctx.sorted_ids.device)
+    ctx.pos_of[ctx.sorted_ids[valid].long()] = torch.arange(ctx.sorted_ids.numel(), dtype=torch.int32, device=ctx.sorted_ids.device)[valid]
     if A.device.type == "cuda" and world > 1:
         heap = heap or symm_heap(tp_pg)
-        ctx.gather_buf = heap.empty((ctx.max_M, K), A.dtype)
+        # two gather buffers, alternated per call: a rank that is one call ahead pushes into the other one
+        ctx.gather_buf = heap.empty((2, ctx.max_M, K), A.dtype)
         ctx.ag_ctx = CO.create_fast_allgather_context(rank, 0, world, 1, max_buffer_size=ctx.max_M * K * A.element_size(),
                                                       heap=heap, group=tp_pg, device=A.device)
     return ctx
@@ -198,18 +247,38 @@ def ag_group_gemm_intra_node(a: torch.Tensor, b: torch.Tensor, ctx: MoEAllGather
             m = ids == e
             out[m] = (rows[m] @ b[e].float()).to(a.dtype)
         return out
+    b_nk = ctx.b_nk if ctx.b_nk is not None else b.transpose(1, 2).contiguous()
     if ctx.world > 1:
-        buf = ctx.gather_buf.view_as((M, K), a.dtype)
+        if phase != 2:
+            ctx.calls += 1
+        half = ctx.calls & 1
+        nbytes = M * K * a.element_size()
+        buf = ctx.gather_buf.view_as((M, K), a.dtype, offset_bytes=half * ctx.max_M * K * a.element_size())
         if phase != 2:
             buf.local[ctx.rank * mpr:(ctx.rank + 1) * mpr].copy_(a)
+        if FUSED_AG_GROUP_GEMM:
+            # send half of the all-gather only; the grouped GEMM gathers its A rows itself and waits, block by
+            # block, for the arrival flag of the rank the block's tokens come from
+            if phase != 2:
+                CO.fast_allgather(buf, ctx.ag_ctx, mode="push", phase=1)
+            if phase == 1:
+                return None
+            c_sorted = group_gemm_gather(buf.local, ctx.row_index, b_nk, ctx.expert_ids, ctx.num_blocks,
+                                         block_src=ctx.block_barrier_ids, src_flags=ctx.ag_ctx.signal.local,
+                                         src_epoch=ctx.ag_ctx.epoch, src_rank=ctx.rank, src_world=ctx.world)
+            out, _ = gather_rows(c_sorted, ctx.pos_of, 1, c_sorted.shape[0])
+            return out
         CO.fast_allgather(buf, ctx.ag_ctx, mode="push", phase=phase)
         if phase == 1:
             return None
         full = buf.local
     else:
         full = a
+    if FUSED_AG_GROUP_GEMM:
+        c_sorted = group_gemm_gather(full, ctx.row_index, b_nk, ctx.expert_ids, ctx.num_blocks)
+        out, _ = gather_rows(c_sorted, ctx.pos_of, 1, c_sorted.shape[0])
+        return out
     a_sorted, pos_of = gather_rows(full, ctx.sorted_ids, ctx.topk, numel, want_inverse=True)
-    b_nk = ctx.b_nk if ctx.b_nk is not None else b.transpose(1, 2).contiguous()
     c_sorted = group_gemm(a_sorted, b_nk, ctx.expert_ids, ctx.num_blocks)
     out, _ = gather_rows(c_sorted, pos_of, 1, c_sorted.shape[0])
     return out
