@@ -320,6 +320,35 @@ def _bench_nvls(args, world, rank, group, dev, dtype, pk, row):
         row.update({"nccl_us": round(base, 2), "speedup_vs_nccl": round(base / us, 3)})
 
 
+def _bench_moe_tp(args, world, rank, group, dev, dtype, pk, row):
+    """Tensor-parallel MoE (Mixtral-like by default: 8192 tokens, hidden 4096, intermediate 14336, 8 experts, top-2):
+    AllGather + GroupGEMM and GroupGEMM + top-k reduce + ReduceScatter, fused against staged."""
+    from .ops import moe_tp as MT
+    M, H, I, E, topk = args.m, args.k, args.n, args.experts, args.topk
+    mpr = M // world
+    row.update({"tokens": M, "hidden": H, "intermediate": I, "experts": E, "topk": topk})
+    gen = torch.Generator(device=dev).manual_seed(0)
+    ids = torch.randint(0, E, (M, topk), device=dev, generator=gen).to(torch.int32)
+    if world > 1:
+        dist.broadcast(ids, 0, group=group)
+    w = torch.rand(M, topk, device=dev, generator=gen)
+    a = torch.randn(mpr, H, device=dev, dtype=dtype)
+    b1 = (torch.randn(E, H, I // world, device=dev) * H ** -0.5).to(dtype)
+    ctx1 = MT.create_ag_group_gemm_intra_node_context(group, a, b1, ids, E, max_M=M, rank=rank, num_ranks=world)
+    h = torch.randn(M * topk, I // world, device=dev, dtype=dtype)
+    b2 = (torch.randn(E, I // world, H, device=dev) * I ** -0.5).to(dtype)
+    ctx2 = MT.create_moe_rs_context(group, rank, world, world, M, H, E, topk, dtype, dtype, dev, full_topk_ids=ids, full_topk_weight=w)
+    flops1 = 2.0 * M * topk * (I // world) * H
+    for name, flag in (("fused", True), ("staged", False)):
+        MT.FUSED_AG_GROUP_GEMM = flag
+        MT.FUSED_TOPK_RS = flag
+        us1 = timed_us(lambda: MT.ag_group_gemm_intra_node(a, b1, ctx1), args.iters, args.warmup, world, group)
+        us2 = timed_us(lambda: MT.moe_reduce_rs(rank, world, world, h, b2, ctx2), args.iters, args.warmup, world, group)
+        row.update({f"ag_group_gemm_{name}_us": round(us1, 1), f"moe_reduce_rs_{name}_us": round(us2, 1),
+                    f"ag_group_gemm_{name}_tflops": round(flops1 / us1 / 1e6, 1), f"moe_reduce_rs_{name}_tflops": round(flops1 / us2 / 1e6, 1)})
+    MT.FUSED_AG_GROUP_GEMM = MT.FUSED_TOPK_RS = True
+
+
 def _run_suite(args, world, rank, group, dev, dtype, pk):
     """Every headline configuration in one process (one NCCL / heap bring-up): the two tensor-parallel
     GEMMs on the m8192 n49152 k12288 problem, MoE dispatch+combine (128 tokens, hidden 7168, 256 experts,
@@ -373,7 +402,7 @@ def _run_suite(args, world, rank, group, dev, dtype, pk):
 
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser()
-    ap.add_argument("--op", required=True, choices=["gemm", "ag_gemm", "gemm_rs", "gemm_fp8", "ag_gemm_fp8", "decode", "sp_decode", "a2a", "allgather", "nvls", "nvls_suite", "suite"])
+    ap.add_argument("--op", required=True, choices=["gemm", "ag_gemm", "gemm_rs", "gemm_fp8", "ag_gemm_fp8", "decode", "sp_decode", "a2a", "allgather", "nvls", "nvls_suite", "moe_tp", "suite"])
     ap.add_argument("--shape", default="", help="MxNxK in one argument (torchrun swallows a bare --m)")
     ap.add_argument("--m", type=int, default=8192)
     ap.add_argument("--n", type=int, default=6144)
@@ -402,7 +431,7 @@ def main(argv=None) -> int:
     if args.shape:
         args.m, args.n, args.k = (int(v) for v in args.shape.lower().split("x"))
     if args.presleep_ms < 0:
-        args.presleep_ms = 0.0 if args.op in ("gemm", "ag_gemm", "gemm_rs", "gemm_fp8", "ag_gemm_fp8") else 30.0
+        args.presleep_ms = 0.0 if args.op in ("gemm", "ag_gemm", "gemm_rs", "gemm_fp8", "ag_gemm_fp8", "moe_tp") else 30.0
     PRESLEEP_CYCLES = int(args.presleep_ms * 1.9e6)
 
     from .runtime import check_status, finalize_distributed, initialize_distributed
@@ -447,6 +476,10 @@ def main(argv=None) -> int:
         _bench_a2a(args, world, rank, group, dev, dtype, pk, row)
     elif args.op == "nvls":
         _bench_nvls(args, world, rank, group, dev, dtype, pk, row)
+    elif args.op == "moe_tp":
+        if args.experts == 256 and args.topk == 8 and args.n == 6144 and args.k == 12288:   # untouched defaults: Mixtral-like
+            args.n, args.k, args.experts, args.topk = 14336, 4096, 8, 2
+        _bench_moe_tp(args, world, rank, group, dev, dtype, pk, row)
     else:
         _bench_allgather(args, world, rank, group, dev, dtype, pk, row)
     check_status()
