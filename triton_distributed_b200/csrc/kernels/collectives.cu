@@ -309,7 +309,8 @@ static int fill_params(const TdistCollArgs* a, CollParams* p) {
     p->topk = a->topk;
     p->row_bytes = a->row_bytes;
     p->ctas_per_peer = a->ctas_per_peer > 0 ? a->ctas_per_peer : 4;
-    if (p->ctas_per_peer > 16) p->ctas_per_peer = 16;
+    // plain copies saturate NVLink with a few CTAs per peer; the fused top-k reduce is compute and wants the whole GPU
+    if (p->ctas_per_peer > (a->topk > 0 ? 144 : 16)) p->ctas_per_peer = a->topk > 0 ? 144 : 16;
     p->wctx.status = static_cast<Status*>(a->status);
     p->wctx.timeout_ns = a->timeout_ns;
     p->wctx.kernel_id = kKernelColl;

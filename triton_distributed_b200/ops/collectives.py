@@ -345,7 +345,8 @@ def topk_reduce_scatter(y_sorted: torch.Tensor, pos_of: torch.Tensor, weights: O
     a.world, a.rank = ctx.world, ctx.rank
     a.phase = phase
     a.dtype = _lib.DT_BF16
-    a.ctas_per_peer = ctx.ctas_per_peer or (1 if a.seg_bytes <= (64 << 10) else (4 if a.seg_bytes <= (4 << 20) else 16))
+    # the send half computes the top-k sums of the peers' rows: spread it over the whole GPU
+    a.ctas_per_peer = ctx.ctas_per_peer or max(1, min(128, 144 // max(1, ctx.world - 1)))
     pos = pos_of if pos_of.dtype == torch.int32 else pos_of.to(torch.int32)
     w = weights.float().contiguous() if weights is not None else None
     a.pos_of = pos.contiguous().data_ptr()
