@@ -323,8 +323,11 @@ __device__ __forceinline__ void rs_reduce_tile(const GemmParams& p, int block, i
     }
 }
 
-template <int MODE, int CTAS>
-__global__ void __launch_bounds__(THREADS, 1) gemm_sm100_kernel(const __grid_constant__ GemmParams p) {
+// GATHER (PLAIN, one CTA per tile): four extra warps (threads 192..319) copy the A rows by index with cp.async,
+// warp 0 then only issues the TMA loads of B.
+constexpr int GATHER_THREADS = THREADS + 128;
+template <int MODE, int CTAS, bool GATHER = false>
+__global__ void __launch_bounds__(GATHER ? GATHER_THREADS : THREADS, 1) gemm_sm100_kernel(const __grid_constant__ GemmParams p) {
     using T = Tiling<CTAS>;
     constexpr int STAGES = T::STAGES;
     constexpr int STAGE_BYTES = T::STAGE_BYTES;
@@ -373,8 +376,8 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_sm100_kernel(const __grid_con
         prefetch_tensormap(&p.tm_b);
         if (MODE == TDIST_GEMM_AG) prefetch_tensormap(&p.tm_a_own);
         for (int s = 0; s < STAGES; ++s) {
-            // gather mode: the 32 producer lanes each arrive once their cp.async rows have landed, plus lane 0's expect_tx
-            mbar_init(bar_full(s), p.a_gather != nullptr ? 33 : 1);
+            // gather mode: the 128 producer threads each arrive once their cp.async rows have landed, plus warp 0's expect_tx
+            mbar_init(bar_full(s), GATHER ? 129 : 1);
             mbar_init(bar_empty(s), 1);
         }
         for (int b = 0; b < 2; ++b) {
@@ -398,13 +401,14 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_sm100_kernel(const __grid_con
     tc_fence_after();
     const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(tmem_slot);
 
-    if (warp == 0 && MODE == TDIST_GEMM_PLAIN && CTAS == 1 && p.a_gather != nullptr) {
-        // ===================== gathering producer: A rows by index with cp.async, B with TMA ==========
-        // All 32 lanes copy: lane l owns rows l, l+32, l+64, l+96 of the tile, 8 chunks of 16 bytes per row and K
-        // block, written in the 128-byte-swizzled layout the MMA descriptors expect. Completion is lagged: the
-        // arrival for stage i is made when stage i + LAG has been issued (cp.async.wait_group), after a proxy fence
-        // that makes the generic-proxy writes visible to the tensor core's async-proxy reads.
+    if (GATHER && warp >= THREADS / 32) {
+        // ===================== gathering producers: A rows by index with cp.async ==========
+        // Thread r of the 128 owns row r of the tile: 8 chunks of 16 bytes per K block, written in the 128-byte-swizzled
+        // layout the MMA descriptors expect. Completion is lagged: the arrival for stage i is made when stage i + LAG
+        // has been issued (cp.async.wait_group), after a proxy fence that makes the generic-proxy writes visible to the
+        // tensor core's async-proxy reads.
         constexpr int LAG = STAGES - 1;
+        const int r = static_cast<int>(threadIdx.x) - THREADS;
         uint32_t it = 0, signaled = 0;
         const int live_blocks = p.num_m_blocks ? *p.num_m_blocks : 0x7fffffff;
         auto drain = [&]() {
@@ -419,7 +423,6 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_sm100_kernel(const __grid_con
             const TileCoord tc = decode_tile(t, first_seg, p.world, p.seg_m_tiles, p.n_tiles, p.group_m);
             const int block = tc.m_in_seg;
             if (block >= live_blocks) continue;
-            const int bz = p.expert_ids ? p.expert_ids[block] : 0;
             if (p.block_src != nullptr) {
                 const int src = p.block_src[block];
                 if (src != p.src_rank && src >= 0 && src < p.src_world) {
@@ -428,33 +431,19 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_sm100_kernel(const __grid_con
                     __syncwarp();
                 }
             }
-            const char* rowp[4];
-            bool valid[4];
-#pragma unroll
-            for (int j = 0; j < 4; ++j) {
-                const int r = block * BM + lane + 32 * j;
-                const int idx = r < p.m_per_rank ? p.a_gather[r] : p.a_gather_rows;
-                valid[j] = idx >= 0 && idx < p.a_gather_rows;
-                rowp[j] = p.a_raw + (valid[j] ? static_cast<size_t>(idx) * p.k * 2 : 0);
-            }
-            const int col = tc.n_tile * BN;
+            const int row = block * BM + r;
+            const int idx = row < p.m_per_rank ? p.a_gather[row] : p.a_gather_rows;
+            const bool valid = idx >= 0 && idx < p.a_gather_rows;
+            const char* rowp = p.a_raw + (valid ? static_cast<size_t>(idx) * p.k * 2 : 0);
             for (int kb = 0; kb < p.k_blocks; ++kb, ++it) {
                 const uint32_t s = it % STAGES;
                 mbar_wait(bar_empty(s), ((it / STAGES) & 1u) ^ 1u, p.wctx, 2);
                 const uint32_t sa = smem_u32(smem + s * STAGE_BYTES);
-                if (lane == 0) {
-                    mbar_expect_tx(bar_full(s), T::B_BYTES);
-                    tma_load_3d(sa + A_BYTES, &p.tm_b, bar_full(s), kb * BK, col, bz);
-                }
 #pragma unroll
-                for (int j = 0; j < 4; ++j) {
-                    const int r = lane + 32 * j;
-#pragma unroll
-                    for (int c = 0; c < 8; ++c) {
-                        const int kcol = kb * BK + c * 8;
-                        const int nbytes = (valid[j] && kcol < p.k) ? 16 : 0;  // K % 8 == 0: a chunk is whole or absent
-                        cp_async16(sa + r * 128 + ((c ^ (r & 7)) << 4), rowp[j] + (nbytes ? static_cast<size_t>(kcol) * 2 : 0), nbytes);
-                    }
+                for (int c = 0; c < 8; ++c) {
+                    const int kcol = kb * BK + c * 8;
+                    const int nbytes = (valid && kcol < p.k) ? 16 : 0;  // K % 8 == 0: a chunk is whole or absent
+                    cp_async16(sa + r * 128 + ((c ^ (r & 7)) << 4), rowp + (nbytes ? static_cast<size_t>(kcol) * 2 : 0), nbytes);
                 }
                 cp_async_commit();
                 if (it + 1 - signaled > LAG) {
@@ -466,6 +455,26 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_sm100_kernel(const __grid_con
             }
         }
         drain();
+        __syncwarp();
+    } else if (GATHER && warp == 0) {
+        // ===================== B-only TMA producer of the gather variant ==========
+        if (lane == 0) {
+            uint32_t it = 0;
+            const int live_blocks = p.num_m_blocks ? *p.num_m_blocks : 0x7fffffff;
+            for (int t = unit; t < p.num_tiles; t += num_units) {
+                const TileCoord tc = decode_tile(t, first_seg, p.world, p.seg_m_tiles, p.n_tiles, p.group_m);
+                const int block = tc.m_in_seg;
+                if (block >= live_blocks) continue;
+                const int bz = p.expert_ids ? p.expert_ids[block] : 0;
+                const int col = tc.n_tile * BN;
+                for (int kb = 0; kb < p.k_blocks; ++kb, ++it) {
+                    const uint32_t s = it % STAGES;
+                    mbar_wait(bar_empty(s), ((it / STAGES) & 1u) ^ 1u, p.wctx, 2);
+                    mbar_expect_tx(bar_full(s), T::B_BYTES);
+                    tma_load_3d(smem_u32(smem + s * STAGE_BYTES) + A_BYTES, &p.tm_b, bar_full(s), kb * BK, col, bz);
+                }
+            }
+        }
         __syncwarp();
     } else if (warp == 0) {
         // ===================== TMA producer (every CTA loads its own A rows and B rows) ==========
@@ -913,11 +922,23 @@ extern "C" int tdist_gemm_run(const TdistGemmArgs* a) {
 
     cudaStream_t stream = static_cast<cudaStream_t>(a->stream);
     const void* fn = ctas == 2 ? kernel_for<2>(a->mode) : kernel_for<1>(a->mode);  // smem opt-in done by resident_ctas()
+    int block_threads = THREADS;
+    if (a->a_gather != nullptr) {
+        fn = reinterpret_cast<const void*>(&gemm_sm100_kernel<TDIST_GEMM_PLAIN, 1, true>);
+        block_threads = GATHER_THREADS;
+        static bool attr_set[64] = {};
+        int dev = 0;
+        TDIST_CUDA_OK(cudaGetDevice(&dev));
+        if (dev >= 0 && dev < 64 && !attr_set[dev]) {
+            TDIST_CUDA_OK(cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
+            attr_set[dev] = true;
+        }
+    }
     void* kargs[] = {&p};
     cudaLaunchConfig_t cfg;
     memset(&cfg, 0, sizeof(cfg));
     cfg.gridDim = dim3(plan.grid);
-    cfg.blockDim = dim3(THREADS);
+    cfg.blockDim = dim3(block_threads);
     cfg.dynamicSmemBytes = SMEM_BYTES;
     cfg.stream = stream;
     cudaLaunchAttribute attr[1];

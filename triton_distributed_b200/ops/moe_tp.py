@@ -36,10 +36,8 @@ from . import gemm as G
 from . import moe_utils as MU
 
 GROUP_BLOCK_M = 128
-# True: the all-gather only sends and the grouped GEMM gathers its A rows itself (one cp.async producer warp), waiting
-# per block for the source rank's flag. Measured slower than the staged path (tp2, 8192 tokens, hidden 4096,
-# intermediate 14336, 8 experts, top-2: 4.36 ms vs 1.00 ms: one warp cannot issue 1024 16-byte copies per K block
-# at the tensor core's pace, and the CTA-pair tiling is lost), so the staged path is the default.
+# True: the all-gather only sends and the grouped GEMM gathers its A rows itself (four cp.async producer warps),
+# waiting per 128-row block for the source rank's flag. False: all-gather, row-gather kernel, TMA-fed grouped GEMM.
 FUSED_AG_GROUP_GEMM = False
 FUSED_TOPK_RS = True   # False: separate top-k reduce kernel, then the plain reduce-scatter (for A/B checks)
 launch_count = 0
