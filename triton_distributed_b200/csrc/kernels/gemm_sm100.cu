@@ -403,11 +403,13 @@ __global__ void __launch_bounds__(GATHER ? GATHER_THREADS : THREADS, 1) gemm_sm1
 
     if (GATHER && warp >= THREADS / 32) {
         // ===================== gathering producers: A rows by index with cp.async ==========
-        // Thread r of the 128 owns row r of the tile: 8 chunks of 16 bytes per K block, written in the 128-byte-swizzled
-        // layout the MMA descriptors expect. Completion is lagged: the arrival for stage i is made when stage i + LAG
-        // has been issued (cp.async.wait_group), after a proxy fence that makes the generic-proxy writes visible to the
-        // tensor core's async-proxy reads.
-        constexpr int LAG = STAGES - 1;
+        // Eight consecutive threads copy the eight 16-byte chunks of one row and K block (one full 128-byte line per
+        // row, four rows per warp instruction); thread t does chunk t % 8 of rows t / 8 + 16 j, j < 8, written in the
+        // 128-byte-swizzled layout the MMA descriptors expect. Completion is lagged: before a thread waits for the next free slot it
+        // makes the arrivals of every stage that is more than LAG copy groups old (cp.async.wait_group), after a proxy
+        // fence that makes the generic-proxy writes visible to the tensor core's async-proxy reads. The arrival of
+        // stage i therefore never waits for the MMA of stage i - 1 to retire: the MMA queue stays one stage ahead.
+        constexpr int LAG = 2;
         const int r = static_cast<int>(threadIdx.x) - THREADS;
         uint32_t it = 0, signaled = 0;
         const int live_blocks = p.num_m_blocks ? *p.num_m_blocks : 0x7fffffff;
@@ -431,27 +433,35 @@ __global__ void __launch_bounds__(GATHER ? GATHER_THREADS : THREADS, 1) gemm_sm1
                     __syncwarp();
                 }
             }
-            const int row = block * BM + r;
-            const int idx = row < p.m_per_rank ? p.a_gather[row] : p.a_gather_rows;
-            const bool valid = idx >= 0 && idx < p.a_gather_rows;
-            const char* rowp = p.a_raw + (valid ? static_cast<size_t>(idx) * p.k * 2 : 0);
+            const int c = r & 7, r0 = r >> 3;
+            const char* rowp[8];
+            unsigned valid = 0;
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                const int row = block * BM + r0 + 16 * j;
+                const int idx = row < p.m_per_rank ? p.a_gather[row] : p.a_gather_rows;
+                const bool ok = idx >= 0 && idx < p.a_gather_rows;
+                valid |= ok ? (1u << j) : 0u;
+                rowp[j] = p.a_raw + (ok ? static_cast<size_t>(idx) * p.k * 2 : 0) + c * 16;
+            }
             for (int kb = 0; kb < p.k_blocks; ++kb, ++it) {
                 const uint32_t s = it % STAGES;
-                mbar_wait(bar_empty(s), ((it / STAGES) & 1u) ^ 1u, p.wctx, 2);
-                const uint32_t sa = smem_u32(smem + s * STAGE_BYTES);
-#pragma unroll
-                for (int c = 0; c < 8; ++c) {
-                    const int kcol = kb * BK + c * 8;
-                    const int nbytes = (valid && kcol < p.k) ? 16 : 0;  // K % 8 == 0: a chunk is whole or absent
-                    cp_async16(sa + r * 128 + ((c ^ (r & 7)) << 4), rowp + (nbytes ? static_cast<size_t>(kcol) * 2 : 0), nbytes);
-                }
-                cp_async_commit();
-                if (it + 1 - signaled > LAG) {
+                while (it - signaled > LAG) {   // `it` groups issued so far: all but the newest LAG have landed after this wait
                     cp_async_wait<LAG>();
                     fence_proxy_async();
                     mbar_arrive(bar_full(signaled % STAGES));
                     ++signaled;
                 }
+                mbar_wait(bar_empty(s), ((it / STAGES) & 1u) ^ 1u, p.wctx, 2);
+                const uint32_t sa = smem_u32(smem + s * STAGE_BYTES);
+                const bool in_k = kb * BK + c * 8 < p.k;  // K % 8 == 0: a chunk is whole or absent
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                    const int rr = r0 + 16 * j;
+                    const int nbytes = (in_k && ((valid >> j) & 1u)) ? 16 : 0;
+                    cp_async16(sa + rr * 128 + ((c ^ (rr & 7)) << 4), rowp[j] + (nbytes ? static_cast<size_t>(kb) * BK * 2 : 0), nbytes);
+                }
+                cp_async_commit();
             }
         }
         drain();

@@ -279,6 +279,11 @@ def reduce_scatter_2d_op(input: torch.Tensor, ctx: ReduceScatter2DContext, out: 
         if ctx.world > 1:
             dist.all_reduce(acc, group=ctx.group)
         return acc[ctx.rank * mpr:(ctx.rank + 1) * mpr].to(input.dtype)
+    if ctx.world == 1:   # one rank: the reduce-scatter of a single contribution is a copy
+        if out is not None:
+            out.copy_(input)
+            return out
+        return input.clone()
     if input.dtype not in _RS_DTYPES:
         raise TypeError(f"reduce-scatter supports {list(_RS_DTYPES)}, got {input.dtype}")
     if not input.is_contiguous():
@@ -329,6 +334,13 @@ def topk_reduce_scatter(y_sorted: torch.Tensor, pos_of: torch.Tensor, weights: O
         rows = y_sorted[pos_of.long()].float().view(ntok, topk, N)
         w = weights.float().view(ntok, topk, 1) if weights is not None else 1.0
         return reduce_scatter_2d_op((rows * w).sum(1).to(y_sorted.dtype), ctx, out=out, phase=phase, stream=stream)
+    if ctx.world == 1:   # nothing to scatter: the top-k reduce kernel on the whole GPU
+        from .moe_tp import topk_reduce
+        res = topk_reduce(y_sorted, pos_of, weights, ntok, topk)
+        if out is not None:
+            out.copy_(res)
+            return out
+        return res
     if not y_sorted.is_contiguous() or (N * 2) % 16:
         raise ValueError("y_sorted must be contiguous with N a multiple of 8")
     if ntok * N > ctx.max_M * ctx.N:

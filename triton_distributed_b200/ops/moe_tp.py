@@ -37,7 +37,8 @@ from . import moe_utils as MU
 
 GROUP_BLOCK_M = 128
 # True: the all-gather only sends and the grouped GEMM gathers its A rows itself (four cp.async producer warps),
-# waiting per 128-row block for the source rank's flag. False: all-gather, row-gather kernel, TMA-fed grouped GEMM.
+# waiting per 128-row block for the source rank's flag. False (default): all-gather, row-gather kernel, TMA-fed grouped
+# GEMM. The fused form measured 2.2x slower: sixteen-byte copies saturate the L2 request rate long before TMA does.
 FUSED_AG_GROUP_GEMM = False
 FUSED_TOPK_RS = True   # False: separate top-k reduce kernel, then the plain reduce-scatter (for A/B checks)
 launch_count = 0
