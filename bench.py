@@ -291,6 +291,25 @@ def main():
                             "torch_nccl_cublas_ms": trs_ms, "speedup_vs_torch": trs_ms / rs_ms,
                             "check_max_abs_err_vs_torch": rs_err}
 
+    if not args.no_extra:
+        # the block-scaled fp8 flavour of the headline op (e4m3, 1x128 / 128x128 fp32 scales), same shape
+        try:
+            from triton_distributed_b200.ops import gemm_fp8 as F8
+            a8, sa8 = F8.quantize_fp8_rowwise(a)
+            b8, sb8 = F8.quantize_fp8_blockwise(b)
+            ctx8 = F8.create_ag_gemm_fp8_context(M_TOTAL, K_TOTAL, rank, world, device=dev, group=group)
+            c8 = torch.empty(M_TOTAL, npr, device=dev, dtype=torch.bfloat16)
+            F8.ag_gemm_fp8(a8, sa8, b8, sb8, ctx8, out=c8)
+            check_status()
+            err8 = (c8[::257].float() - out[::257].float()).abs().max().item()   # against the bf16 result: quantisation noise only
+            f8_ms = timed(lambda: F8.ag_gemm_fp8(a8, sa8, b8, sb8, ctx8, out=c8), K_STEPS, W)
+            check_status()
+            extra["ag_gemm_fp8_blockscaled"] = {"ms_per_step": f8_ms, "tflops": flops / (f8_ms * 1e-3) / 1e12,
+                                                "max_abs_diff_vs_bf16_result": err8}
+            del a8, b8, c8
+        except Exception as e:  # noqa: BLE001 - a side measurement must not take the headline down
+            extra["ag_gemm_fp8_blockscaled"] = {"error": repr(e)[:200]}
+
     if rank == 0:
         line = {
             "metric": "AG-GEMM aggregate TFLOP/s (m8192 n49152 k12288, TP over N GPUs)",
