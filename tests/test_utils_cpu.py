@@ -127,3 +127,21 @@ def test_reference_names_resolve_on_cpu():
     assert G.ag_gemm_inter_node(a, w, ctx).shape == (4, 6)
     rs = G.create_gemm_rs_context(4, 6, 0, 1, output_dtype=torch.float32, device="cpu")
     assert G.gemm_rs_op(a, w, rs).shape == (4, 6)
+
+
+def test_config_catalogue_and_nvtx_decorator(monkeypatch):
+    from triton_distributed_b200.utils import Config, nvtx_range
+
+    c = Config.from_env({"TDIST_NVLS": "1", "TDIST_WAIT_TIMEOUT_MS": "250", "TDIST_GEMM_CTA_PAIR": "0", "TDIST_HEAP_BACKEND": "ipc"})
+    assert c.nvls is True and c.wait_timeout_ms == 250.0 and c.gemm_cta_pair == 0 and c.heap_backend == "ipc"
+    assert Config.from_env({}) == Config()
+    text = c.describe()
+    assert "TDIST_WAIT_TIMEOUT_MS" in text and "(default 4000.0)" in text and len(text.splitlines()) == len(Config.env_names())
+
+    def f(x):
+        return x + 1
+    monkeypatch.delenv("TDIST_NVTX", raising=False)
+    assert nvtx_range("t")(f) is f                      # off: the function is returned untouched
+    monkeypatch.setenv("TDIST_NVTX", "1")
+    g = nvtx_range("t")(f)
+    assert g is not f and g(1) == 2 and g.__name__ == "f"  # on: wrapped; without CUDA the range calls are skipped

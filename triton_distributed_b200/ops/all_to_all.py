@@ -24,6 +24,7 @@ import torch
 import torch.distributed as dist
 
 from .. import _lib
+from ..utils.profile import nvtx_range
 from ..runtime import SymmTensor, default_timeout_ns, global_status, symm_heap
 from . import moe_utils
 
@@ -99,6 +100,7 @@ def _launch(a: "_lib.A2AArgs") -> None:
     launch_count += 1
 
 
+@nvtx_range("tdist.fast_all_to_all")
 def fast_all_to_all(ctx: AllToAllContext, send_tensor: torch.Tensor, send_split_cumsum: torch.Tensor,
                     send_scale: Optional[torch.Tensor] = None, phase: int = 3, stream=None):
     """Rows ``[cumsum[e], cumsum[e+1])`` of ``send_tensor`` go to the rank owning expert ``e``.
@@ -204,6 +206,7 @@ def create_moe_dispatch_context(max_tokens: int, hidden: int, topk: int, num_exp
     return MoEDispatchContext(d, c, num_experts, topk, hidden)
 
 
+@nvtx_range("tdist.moe_dispatch")
 def moe_dispatch(ctx: MoEDispatchContext, x: torch.Tensor, topk_ids: torch.Tensor, topk_weights: torch.Tensor,
                  phase: int = 3, stream=None) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
     """Send every token to the ranks of its ``topk`` experts as fp8 e4m3 with per-128 fp32 scales.
@@ -239,6 +242,7 @@ def moe_dispatch(ctx: MoEDispatchContext, x: torch.Tensor, topk_ids: torch.Tenso
             d.split_recv_buf.local[half].view(d.WORLD_SIZE, d.experts_per_rank))
 
 
+@nvtx_range("tdist.moe_combine")
 def moe_combine(ctx: MoEDispatchContext, expert_out: torch.Tensor, recv_splits: torch.Tensor,
                 out: Optional[torch.Tensor] = None, phase: int = 3, stream=None) -> torch.Tensor:
     """Return the experts' outputs to their source ranks and reduce over ``topk`` with the gate

@@ -26,6 +26,7 @@ import torch
 import torch.distributed as dist
 
 from .. import _lib
+from ..utils.profile import nvtx_range
 from ..runtime import SymmTensor, default_timeout_ns, global_status, symm_heap
 
 launch_count = 0
@@ -172,6 +173,7 @@ def create_fast_allgather_context(rank: int, node: int = 0, num_ranks: int = 1, 
     return ctx
 
 
+@nvtx_range("tdist.fast_allgather")
 def fast_allgather(symm_buffer: SymmTensor, ctx: Optional[FastAllGatherContext] = None, rank: Optional[int] = None,
                    node: int = 0, num_ranks: Optional[int] = None, num_nodes: int = 1, mode: str = "pull",
                    phase: int = 3, stream=None) -> torch.Tensor:
@@ -265,6 +267,7 @@ def create_reduce_scater_2d_ctx(max_M: int, N: int, rank: int, world_size: int, 
 create_reduce_scatter_2d_ctx = create_reduce_scater_2d_ctx
 
 
+@nvtx_range("tdist.reduce_scatter_2d_op")
 def reduce_scatter_2d_op(input: torch.Tensor, ctx: ReduceScatter2DContext, out: Optional[torch.Tensor] = None,
                          phase: int = 3, stream=None) -> torch.Tensor:
     """``out[M/ws, N] = sum over ranks of input_r[rank*M/ws:(rank+1)*M/ws]`` (fp32 accumulation for

@@ -26,6 +26,7 @@ import torch
 import torch.distributed as dist
 
 from .. import _lib
+from ..utils.profile import nvtx_range
 from ..runtime import SymmTensor, default_timeout_ns, global_status, symm_heap
 
 launch_count = 0
@@ -143,6 +144,7 @@ def _launch(q, k_cache, v_cache, kv_lens, block_table, scale, soft_cap, out, mod
     return out
 
 
+@nvtx_range("tdist.gqa_fwd_batch_decode")
 def gqa_fwd_batch_decode(q, k_cache, v_cache, workspace=None, q_lens=None, kv_lens=None, block_table=None, scale=None,
                          soft_cap: float = 0.0, output_split=None, output_combine=None, kv_split: int = -1):
     """Decode attention of one query token per sequence. Returns ``[B, Hq, D]`` in q's dtype."""
@@ -221,6 +223,7 @@ def create_sp_decode_context(rank: int, world: int, max_batch: int, Hq: int, hea
     return ctx
 
 
+@nvtx_range("tdist.sp_gqa_fwd_batch_decode")
 def sp_gqa_fwd_batch_decode(ctx: SpDecodeContext, q, k_cache, v_cache, global_kv_lens, block_table, scale=None,
                             soft_cap: float = 0.0, kv_split: int = -1, out: Optional[torch.Tensor] = None,
                             phase: int = 3):

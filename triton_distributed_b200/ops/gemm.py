@@ -24,6 +24,7 @@ import torch
 import torch.distributed as dist
 
 from .. import _lib
+from ..utils.profile import nvtx_range
 from ..runtime import SymmTensor, default_timeout_ns, global_status, symm_heap
 
 BLOCK_M = 128
@@ -86,6 +87,7 @@ def _launch(g: "_lib.GemmArgs") -> None:
 
 
 # ---------------------------------------------------------------------------- plain GEMM
+@nvtx_range("tdist.gemm_persistent")
 def gemm_persistent(a: torch.Tensor, b: torch.Tensor, out: Optional[torch.Tensor] = None,
                     num_sms: int = 0) -> torch.Tensor:
     """``a[M,K] @ b[N,K].T`` with fp32 accumulation; output dtype = input dtype."""
@@ -158,6 +160,7 @@ def create_ag_gemm_intra_node_context(tensor_A: torch.Tensor, tensor_B: torch.Te
 
 
 
+@nvtx_range("tdist.ag_gemm_intra_node")
 def ag_gemm_intra_node(a: torch.Tensor, b: torch.Tensor, ctx: Optional[AllGatherGEMMTensorParallelContext] = None,
                        rank: Optional[int] = None, num_ranks: Optional[int] = None, persistent: bool = True,
                        out: Optional[torch.Tensor] = None) -> torch.Tensor:
@@ -246,6 +249,7 @@ def create_gemm_rs_context(max_M: int, N: int, rank: int, world_size: int, local
 
 
 
+@nvtx_range("tdist.gemm_rs")
 def gemm_rs(a: torch.Tensor, b: torch.Tensor, ctx: GEMMReduceScatterTensorParallelContext, persistent: bool = True,
             out: Optional[torch.Tensor] = None) -> torch.Tensor:
     """``reduce_scatter_rows(a @ b.T)``: ``a`` is ``[M, K/ws]``, ``b`` is ``[N, K/ws]``; returns this

@@ -25,6 +25,7 @@ import torch
 import torch.distributed as dist
 
 from .. import _lib
+from ..utils.profile import nvtx_range
 from ..runtime import SymmTensor, default_timeout_ns, global_status, symm_heap
 
 FP8 = torch.float8_e4m3fn
@@ -110,6 +111,7 @@ def _launch(g) -> None:
     launch_count += 1
 
 
+@nvtx_range("tdist.gemm_fp8_blockscaled")
 def gemm_fp8_blockscaled(a: torch.Tensor, sa: torch.Tensor, b: torch.Tensor, sb: torch.Tensor,
                          out: Optional[torch.Tensor] = None, num_sms: int = 0) -> torch.Tensor:
     if a.device.type != "cuda":
@@ -155,6 +157,7 @@ def create_ag_gemm_fp8_context(max_M: int, K: int, rank: int, num_ranks: int, de
     return ctx
 
 
+@nvtx_range("tdist.ag_gemm_fp8")
 def ag_gemm_fp8(a: torch.Tensor, sa: torch.Tensor, b: torch.Tensor, sb: torch.Tensor, ctx: AGGemmFp8Context,
                 out: Optional[torch.Tensor] = None) -> torch.Tensor:
     """``allgather(a) @ b.T`` with block scales: ``a`` / ``sa`` are this rank's ``[M/ws, K]`` rows and

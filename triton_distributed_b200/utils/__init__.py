@@ -8,10 +8,11 @@ probes) and ``python/triton_dist/autotuner.py`` (``contextual_autotune``).
 from .autotuner import contextual_autotune, tunable
 from .misc import (assert_allclose, check_p2p_native_atomic_supported, dist_print, generate_data, get_has_nvlink,
                    get_numa_world_size, p2p_bandwidth, perf_func, perf_func_max_over_ranks)
-from .profile import get_torch_prof_ctx, group_profile
+from .config import Config
+from .profile import get_torch_prof_ctx, group_profile, nvtx_range
 
 __all__ = [
     "contextual_autotune", "tunable", "assert_allclose", "check_p2p_native_atomic_supported", "dist_print",
     "generate_data", "get_has_nvlink", "get_numa_world_size", "p2p_bandwidth", "perf_func", "perf_func_max_over_ranks",
-    "get_torch_prof_ctx", "group_profile",
+    "get_torch_prof_ctx", "group_profile", "nvtx_range", "Config",
 ]

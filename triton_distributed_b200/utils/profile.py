@@ -16,6 +16,28 @@ import torch
 import torch.distributed as dist
 
 
+def nvtx_range(name: str):
+    """Decorator: run the function inside an NVTX range when TDIST_NVTX=1 (and CUDA is up), so that the ops show as
+    named spans in external timelines; otherwise the function is returned untouched (no per-call cost)."""
+    def decor(fn):
+        if os.environ.get("TDIST_NVTX", "0") != "1":
+            return fn
+
+        import functools
+
+        @functools.wraps(fn)
+        def wrapped(*a, **kw):
+            if not torch.cuda.is_available():
+                return fn(*a, **kw)
+            torch.cuda.nvtx.range_push(name)
+            try:
+                return fn(*a, **kw)
+            finally:
+                torch.cuda.nvtx.range_pop()
+        return wrapped
+    return decor
+
+
 def get_torch_prof_ctx(do_prof: bool):
     if not do_prof:
         return contextlib.nullcontext()
