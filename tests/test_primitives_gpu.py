@@ -120,3 +120,20 @@ def test_host_stream_ops_put_signal_wait(cuda_device):
         check_status()
     torch.cuda.synchronize()
     check_status()  # the record was cleared and the context still works
+
+
+@pytest.mark.parametrize("grid", [1, 7, 64])
+def test_scoped_loads_stores_atomics_and_warp_intrinsics(cuda_device, grid):
+    """red / atom / CAS at gpu and sys scope, release-acquire hand-over and the warp intrinsics, counted exactly
+    (the reference's test_language_extra.py checks the same helpers through Triton kernels)."""
+    lw = LocalWorld(1, cuda_device)
+    ctx = P.create_primitive_context(0, 1, 4096, heap=lw.heap(0))
+    ctx.slot(0).zero_()
+    ctx.result.zero_()
+    P.run_primitive(ctx, "scoped_ops", grid=grid)
+    torch.cuda.synchronize()
+    check_status()
+    w = ctx.slot(0).view(torch.int32)[:6].tolist()
+    threads = grid * 256
+    assert int(ctx.result[0]) == 0
+    assert w[0] == threads and w[1] == threads and w[2] == 0 and w[3] == grid and w[5] == threads // 32

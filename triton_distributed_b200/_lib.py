@@ -160,7 +160,7 @@ class PrimArgs(C.Structure):
 
 
 (PRIM_RING_PUT, PRIM_NOTIFY_WAIT, PRIM_NOTIFY_ADD, PRIM_PUT_SIGNAL, PRIM_PUT_QUIET_SIGNAL, PRIM_GET, PRIM_BROADCAST,
- PRIM_FCOLLECT, PRIM_GRID_BARRIER) = range(9)
+ PRIM_FCOLLECT, PRIM_GRID_BARRIER, PRIM_SCOPED_OPS) = range(10)
 GEMM_PLAIN, GEMM_AG, GEMM_RS = 0, 1, 2
 A2A_DISPATCH, A2A_COMBINE = 0, 1
 DT_BF16, DT_F16, DT_F32, DT_I32 = 0, 1, 2, 3

@@ -294,7 +294,7 @@ int tdist_lse_combine(const void* parts, int ranks, int heads, int head_dim, voi
 enum {
     TDIST_PRIM_RING_PUT = 0, TDIST_PRIM_NOTIFY_WAIT = 1, TDIST_PRIM_NOTIFY_ADD = 2, TDIST_PRIM_PUT_SIGNAL = 3,
     TDIST_PRIM_PUT_QUIET_SIGNAL = 4, TDIST_PRIM_GET = 5, TDIST_PRIM_BROADCAST = 6, TDIST_PRIM_FCOLLECT = 7,
-    TDIST_PRIM_GRID_BARRIER = 8
+    TDIST_PRIM_GRID_BARRIER = 8, TDIST_PRIM_SCOPED_OPS = 9
 };
 
 typedef struct TdistPrimArgs {

@@ -109,6 +109,37 @@ __global__ void prim_kernel(const PrimParams p) {
             }
             break;
         }
+        case TDIST_PRIM_SCOPED_OPS: {
+            // The scoped load / store / atomic helpers and warp intrinsics, in the spirit of the reference's
+            // test_language_extra.py: all counters live in slot 0 (uint32 words), zeroed by the host.
+            //   word 0: every thread adds 1 (red.release.gpu)           -> grid * block
+            //   word 1: lane 0 of every warp adds 32 (atom.acq_rel.gpu) -> grid * block
+            //   word 2: CAS lock (0 free / 1 taken); word 3: plain counter incremented under the lock by thread 0
+            //           of every CTA                                      -> grid
+            //   word 4: st.release.gpu / ld.acquire.gpu hand-over inside the CTA; word 5: warps whose ballot / shuffle
+            //           results were right                                -> grid * block / 32
+            uint32_t* w = reinterpret_cast<uint32_t*>(slot(p, 0));
+            red_release_gpu_add_u32(w + 0, 1u);
+            if ((threadIdx.x & 31) == 0) atom_add_acq_rel_gpu_u32(w + 1, 32u);
+            if (threadIdx.x == 0) {
+                bool got = false;
+                for (int spin = 0; spin < (1 << 22) && !got; ++spin) got = atom_cas_acq_rel_sys_u32(w + 2, 0u, 1u) == 0u;
+                if (got) {
+                    *reinterpret_cast<volatile uint32_t*>(w + 3) = *reinterpret_cast<volatile uint32_t*>(w + 3) + 1u;
+                    st_release_gpu_u32(w + 2, 0u);
+                } else {
+                    atomicAdd(p.result, 1);  // lock never obtained
+                }
+            }
+            const unsigned ballot = __ballot_sync(0xffffffffu, (threadIdx.x & 1) != 0);
+            int sum = static_cast<int>(threadIdx.x & 31);
+#pragma unroll
+            for (int o = 16; o >= 1; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+            const int up = __shfl_up_sync(0xffffffffu, static_cast<int>(threadIdx.x & 31), 1);
+            const bool warp_ok = ballot == 0xaaaaaaaau && sum == 496 && ((threadIdx.x & 31) == 0 || up == static_cast<int>(threadIdx.x & 31) - 1);
+            if (__all_sync(0xffffffffu, warp_ok) && (threadIdx.x & 31) == 0) red_release_gpu_add_u32(w + 5, 1u);
+            break;
+        }
         default: break;
     }
 }
@@ -120,7 +151,7 @@ using namespace tdist;
 extern "C" int tdist_primitive(const TdistPrimArgs* a) {
     if (a->world < 1 || a->world > TDIST_MAX_RANKS || a->rank < 0 || a->rank >= a->world)
         return tdist_host::fail(TDIST_EINVAL, "primitive: world/rank out of range");
-    if (a->op < 0 || a->op > TDIST_PRIM_GRID_BARRIER) return tdist_host::fail(TDIST_EINVAL, "primitive: unknown op");
+    if (a->op < 0 || a->op > TDIST_PRIM_SCOPED_OPS) return tdist_host::fail(TDIST_EINVAL, "primitive: unknown op");
     PrimParams p;
     memset(&p, 0, sizeof(p));
     for (int r = 0; r < a->world; ++r) {
@@ -145,7 +176,7 @@ extern "C" int tdist_primitive(const TdistPrimArgs* a) {
     p.wctx.timeout_ns = a->timeout_ns;
     p.wctx.kernel_id = kKernelPrim;
     p.wctx.rank = a->rank;
-    const int grid = a->op == TDIST_PRIM_GRID_BARRIER ? (a->grid > 0 ? a->grid : 64) : 1;
+    const int grid = (a->op == TDIST_PRIM_GRID_BARRIER || a->op == TDIST_PRIM_SCOPED_OPS) ? (a->grid > 0 ? a->grid : 64) : 1;
     prim_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(a->stream)>>>(p);
     TDIST_CUDA_OK(cudaGetLastError());
     return 0;

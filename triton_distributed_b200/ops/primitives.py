@@ -22,7 +22,7 @@ from ..runtime import SymmTensor, default_timeout_ns, global_status, symm_heap
 OPS = {
     "ring_put": _lib.PRIM_RING_PUT, "notify_wait": _lib.PRIM_NOTIFY_WAIT, "notify_add": _lib.PRIM_NOTIFY_ADD,
     "put_signal": _lib.PRIM_PUT_SIGNAL, "put_quiet_signal": _lib.PRIM_PUT_QUIET_SIGNAL, "get": _lib.PRIM_GET,
-    "broadcast": _lib.PRIM_BROADCAST, "fcollect": _lib.PRIM_FCOLLECT, "grid_barrier": _lib.PRIM_GRID_BARRIER,
+    "broadcast": _lib.PRIM_BROADCAST, "fcollect": _lib.PRIM_FCOLLECT, "grid_barrier": _lib.PRIM_GRID_BARRIER, "scoped_ops": _lib.PRIM_SCOPED_OPS,
 }
 SCOPES = {"thread": 0, "warp": 1, "block": 2}
 
