@@ -349,6 +349,62 @@ def _bench_moe_tp(args, world, rank, group, dev, dtype, pk, row):
     MT.FUSED_AG_GROUP_GEMM = MT.FUSED_TOPK_RS = True
 
 
+def _bench_fused_local(args, world, rank, group, dev, dtype, pk, row):
+    """One rank's fused AG-GEMM and GEMM-RS kernels on ONE GPU, against peer buffers prepared by the host (the
+    other ranks of a 2-rank world are emulated in the same process). The kernels run their real code paths: pusher
+    CTAs storing into the peer's workspace, flag waits, epilogue stores into the peer's staging, reduce tail. Meant
+    for single-process profilers; the timings are of this one launch, not of a collective step."""
+    from .ops import gemm as G
+    from .runtime import LocalWorld
+    W = 2
+    M, N, K = args.m, args.n, args.k
+    mpr = M // W
+    row.update({"m": M, "n": N, "k": K, "emulated_world": W})
+    lw = LocalWorld(W, dev)
+    A = [torch.randn(mpr, K, device=dev, dtype=dtype) for _ in range(W)]
+    B = [(torch.randn(N // W, K, device=dev) * K ** -0.5).to(dtype) for _ in range(W)]
+    ctxs = [G.create_ag_gemm_intra_node_context(A[r], B[r], r, W, max_M=M, heap=lw.heap(r)) for r in range(W)]
+    mt = (mpr + 127) // 128
+    times = {}
+    for it in range(args.warmup + 1):
+        ctx = ctxs[0]
+        half = (ctx.epoch + 1) & 1
+        ws = ctx.workspace.local[half][: W * mpr * K].view(W, mpr, K)
+        ws[1].copy_(A[1])                                    # rank 1's rows "arrive", with their flags
+        ctx.flags.local[half][: W * mt].view(W, mt)[1].fill_(ctx.epoch + 1)
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        c = G.ag_gemm_intra_node(A[0], B[0], ctx)
+        e1.record()
+        torch.cuda.synchronize()
+        times["ag_gemm_rank0_us"] = round(e0.elapsed_time(e1) * 1e3, 1)
+    ref = torch.cat(A).float() @ B[0].float().t()
+    row["ag_max_err"] = float((c.float() - ref).abs().max())
+    # GEMM-RS: rank 0's kernel; rank 1's partial tiles and flags are written by the host
+    kl = K // W
+    X = [torch.randn(M, kl, device=dev, dtype=dtype) for _ in range(W)]
+    V = [(torch.randn(N, kl, device=dev) * K ** -0.5).to(dtype) for _ in range(W)]
+    rctx = G.create_gemm_rs_context(M, N, 0, W, output_dtype=dtype, heap=lw.heap(0), device=dev)
+    G.create_gemm_rs_context(M, N, 1, W, output_dtype=dtype, heap=lw.heap(1), device=dev)   # the peer's half of the symmetric state
+    partial1 = (X[1].float() @ V[1].float().t())[:mpr].to(dtype)
+    tiles = mt * ((N + 255) // 256)
+    for it in range(args.warmup + 1):
+        half = (rctx.epoch + 1) & 1
+        rctx.staging.local[half][: W * mpr * N].view(W, mpr, N)[1].copy_(partial1)
+        rctx.flags.local[half][: tiles * W].view(tiles, W)[:, 1].fill_(rctx.epoch + 1)
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        o = G.gemm_rs(X[0], V[0], rctx)
+        e1.record()
+        torch.cuda.synchronize()
+        times["gemm_rs_rank0_us"] = round(e0.elapsed_time(e1) * 1e3, 1)
+    ref = (X[0].float() @ V[0].float().t() + X[1].float() @ V[1].float().t())[:mpr]
+    row["rs_max_err"] = float((o.float() - ref).abs().max())
+    row.update(times)
+
+
 def _run_suite(args, world, rank, group, dev, dtype, pk):
     """Every headline configuration in one process (one NCCL / heap bring-up): the two tensor-parallel
     GEMMs on the m8192 n49152 k12288 problem, MoE dispatch+combine (128 tokens, hidden 7168, 256 experts,
@@ -402,7 +458,7 @@ def _run_suite(args, world, rank, group, dev, dtype, pk):
 
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser()
-    ap.add_argument("--op", required=True, choices=["gemm", "ag_gemm", "gemm_rs", "gemm_fp8", "ag_gemm_fp8", "decode", "sp_decode", "a2a", "allgather", "nvls", "nvls_suite", "moe_tp", "suite"])
+    ap.add_argument("--op", required=True, choices=["gemm", "ag_gemm", "gemm_rs", "gemm_fp8", "ag_gemm_fp8", "decode", "sp_decode", "a2a", "allgather", "nvls", "nvls_suite", "moe_tp", "fused_local", "suite"])
     ap.add_argument("--shape", default="", help="MxNxK in one argument (torchrun swallows a bare --m)")
     ap.add_argument("--m", type=int, default=8192)
     ap.add_argument("--n", type=int, default=6144)
@@ -431,7 +487,7 @@ def main(argv=None) -> int:
     if args.shape:
         args.m, args.n, args.k = (int(v) for v in args.shape.lower().split("x"))
     if args.presleep_ms < 0:
-        args.presleep_ms = 0.0 if args.op in ("gemm", "ag_gemm", "gemm_rs", "gemm_fp8", "ag_gemm_fp8", "moe_tp") else 30.0
+        args.presleep_ms = 0.0 if args.op in ("gemm", "ag_gemm", "gemm_rs", "gemm_fp8", "ag_gemm_fp8", "moe_tp", "fused_local") else 30.0
     PRESLEEP_CYCLES = int(args.presleep_ms * 1.9e6)
 
     from .runtime import check_status, finalize_distributed, initialize_distributed
@@ -476,6 +532,8 @@ def main(argv=None) -> int:
         _bench_a2a(args, world, rank, group, dev, dtype, pk, row)
     elif args.op == "nvls":
         _bench_nvls(args, world, rank, group, dev, dtype, pk, row)
+    elif args.op == "fused_local":
+        _bench_fused_local(args, world, rank, group, dev, dtype, pk, row)
     elif args.op == "moe_tp":
         if args.experts == 256 and args.topk == 8 and args.n == 6144 and args.k == 12288:   # untouched defaults: Mixtral-like
             args.n, args.k, args.experts, args.topk = 14336, 4096, 8, 2
