@@ -1,12 +1,10 @@
 """`torch.ops.tdist.*` registrations: every op is reachable through the dispatcher, runs on CPU
 tensors (the torch restatement path) and has a fake implementation that yields the right shapes."""
-import math
 
 import torch
 from torch._subclasses.fake_tensor import FakeTensorMode
 
 import triton_distributed_b200.torch_ops as T
-from triton_distributed_b200.ops import flash_decode as FD
 from triton_distributed_b200.ops import gemm as G
 
 

@@ -2,7 +2,6 @@
 random per-rank delays before each call (the reference's test_common_ops.py jitter idiom)."""
 import json
 import random
-import time
 
 import torch
 import torch.distributed as dist

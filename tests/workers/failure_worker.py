@@ -2,7 +2,6 @@
 short process-group timeout on their next collective and report instead of waiting forever."""
 import json
 import os
-import sys
 import time
 
 import torch

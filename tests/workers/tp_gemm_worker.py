@@ -6,7 +6,6 @@ Follows the reference's test_ag_gemm_intra_node.py:129-149 and test_gemm_rs.py:4
 fresh random inputs every iteration, non-tile-aligned M, stale-workspace poisoning.
 """
 import json
-import os
 import sys
 
 import torch

@@ -1,7 +1,6 @@
 """Model blocks built from the fused ops: the units the end-to-end benchmark and the smoke test drive."""
 from __future__ import annotations
 
-from typing import Optional
 
 import torch
 import torch.nn.functional as F

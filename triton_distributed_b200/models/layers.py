@@ -3,10 +3,8 @@ constructor arguments and methods (reference layers/nvidia/low_latency_allgather
 ep_a2a_layer.py:40-240, sp_flash_decode_layer.py:43-184), built on this package's kernels."""
 from __future__ import annotations
 
-from typing import Optional
 
 import torch
-import torch.distributed as dist
 
 from ..ops import all_to_all as A
 from ..ops import collectives as CO

@@ -22,7 +22,6 @@ test/nvidia/test_ag_moe.py:24-39).
 """
 from __future__ import annotations
 
-import ctypes as C
 from dataclasses import dataclass
 from typing import Optional, Tuple
 

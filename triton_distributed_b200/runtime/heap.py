@@ -21,7 +21,7 @@ import atexit
 import ctypes as C
 import math
 import os
-from dataclasses import dataclass, field
+from dataclasses import dataclass
 from typing import List, Optional, Sequence
 
 import torch

@@ -7,8 +7,7 @@ library writing through the peer mapping, signals are 8-byte words in symmetric 
 """
 from __future__ import annotations
 
-import ctypes as C
-from typing import List, Optional, Sequence
+from typing import List, Sequence
 
 import torch
 import torch.distributed as dist

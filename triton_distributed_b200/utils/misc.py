@@ -2,9 +2,8 @@
 from __future__ import annotations
 
 import ctypes as C
-import os
 import sys
-from typing import Callable, Iterable, List, Optional, Sequence, Tuple
+from typing import Callable, Iterable, Optional, Sequence, Tuple
 
 import torch
 import torch.distributed as dist
