@@ -145,3 +145,35 @@ def test_config_catalogue_and_nvtx_decorator(monkeypatch):
     monkeypatch.setenv("TDIST_NVTX", "1")
     g = nvtx_range("t")(f)
     assert g is not f and g(1) == 2 and g.__name__ == "f"  # on: wrapped; without CUDA the range calls are skipped
+
+
+def test_top_level_namespace_and_remaining_reference_names():
+    """`import triton_distributed_b200 as tdist` exposes the reference's public names; the EP helper functions and the
+    pynvshmem-style host names exist and behave on CPU."""
+    import torch
+    import triton_distributed_b200 as tdist
+    from triton_distributed_b200.ops import collectives as CO, flash_decode as FD
+    from triton_distributed_b200.runtime import shmem_host as SH
+    from triton_distributed_b200.utils import aot_compile_spaces, aot_spaces, get_triton_combine_kv_algo_info, p2p_native_atomic_required
+
+    for name in ("ag_gemm_intra_node", "gemm_rs", "fast_allgather", "fast_all_to_all", "moe_dispatch", "gqa_fwd_batch_decode",
+                 "sp_gqa_fwd_batch_decode", "ag_group_gemm_intra_node", "moe_reduce_rs", "select_experts", "AllGatherLayer",
+                 "EPAll2AllLayer", "SpGQAFlashDecodeAttention", "initialize_distributed", "nvshmem_create_tensor",
+                 "contextual_autotune", "group_profile", "nvls_allreduce", "ag_gemm_fp8"):
+        assert hasattr(tdist, name), name
+    recv_splits, recv_offset, n = tdist.get_ag_splits_and_recv_offset_for_dispatch(torch.tensor([3, 0, 2, 1], dtype=torch.int32), 1, 4)
+    assert recv_splits.tolist() == [[3, 0, 2, 1]] and recv_offset.view(-1).tolist() == [0, 3, 3, 5] and n == 6
+    reqs = tdist.get_dispatch_send_reqs_for_target_node(torch.tensor([0, 0, 1, 0, 0, 0, 1]), 0)
+    assert reqs.tolist() == [[0, 2], [3, 6]]
+    assert tdist.get_dispatch_send_reqs_for_target_node(torch.tensor([1, 1]), 0).shape == (0, 2)
+    assert SH.nvshmem_my_pe() == 0 and SH.nvshmem_n_pes() == 1 and SH.nvshmem_team_n_pes(SH.NVSHMEMX_TEAM_NODE) == 1
+    assert SH.NVSHMEM_SIGNAL_SET == 9 and SH.NVSHMEM_SIGNAL_ADD == 10 and SH.NVSHMEM_CMP_GE == 5
+    assert CO.reduce_scatter_ring_push_1d_intra_node_sm is CO.reduce_scatter_ring_push_1d_intra_node_kernel
+    assert FD.kernel_inter_rank_gqa_fwd_batch_decode_combine_kv is FD.inter_rank_combine
+    assert get_triton_combine_kv_algo_info(32, 128)["BLOCK_DV"] == 128
+
+    @aot_compile_spaces({"decode_bf16_d128": {"signature": "*bf16, *bf16, i32", "grid": ["B", "Hkv", "splits"]}})
+    def kernel():
+        return 7
+    assert kernel() == 7 and aot_spaces()["decode_bf16_d128"]["function"] == "kernel"
+    assert p2p_native_atomic_required(lambda: 5)() == 5

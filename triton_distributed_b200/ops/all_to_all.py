@@ -324,3 +324,37 @@ def _moe_combine_cpu(ctx, expert_out, recv_splits):
     row = er * mm + (r.slot_of.long() - r.cumsum.long()[er * epr])
     vals = back[row].float() * ctx.topk_weights.reshape(-1, 1)
     return vals.view(T, K, -1).sum(1).to(torch.bfloat16)
+
+
+# ---------------------------------------------------------------------------- helpers of the reference's EP layer
+def get_ag_splits_and_recv_offset_for_dispatch(send_splits: torch.Tensor, world_size: int, experts_per_rank: int, group=None):
+    """From this rank's per-expert send counts ``[num_experts]`` build what the dispatch needs (reference
+    kernels/nvidia/ep_a2a.py:352-387): ``recv_splits [world, experts_per_rank]`` (rows each source sends to my experts),
+    ``recv_offset [experts_per_rank, world]`` (exclusive prefix sum in (expert, source) order = where each (expert,
+    source) group starts in the regrouped receive layout) and ``num_recv`` (rows I receive in total). A set-up
+    collective (NCCL / gloo all-gather), not a hot path: the fused dispatch kernel carries the splits itself."""
+    splits = send_splits.to(torch.int32).contiguous()
+    if world_size > 1:
+        gathered = torch.empty((world_size, splits.numel()), dtype=torch.int32, device=splits.device)
+        dist.all_gather_into_tensor(gathered, splits, group=group)
+        rank = dist.get_rank(group)
+    else:
+        gathered, rank = splits.view(1, -1), 0
+    recv_splits = gathered[:, rank * experts_per_rank:(rank + 1) * experts_per_rank].contiguous()     # [src, e]
+    by_expert = recv_splits.t().contiguous()                                                            # [e, src]
+    flat = by_expert.reshape(-1).to(torch.int64)
+    recv_offset = (torch.cumsum(flat, 0) - flat).view(experts_per_rank, world_size).to(torch.int32)
+    return recv_splits, recv_offset, int(flat.sum())
+
+
+def get_dispatch_send_reqs_for_target_node(token_node_idx: torch.Tensor, traget_node_id: int, index_type=torch.int32):
+    """Contiguous ``[start, end)`` ranges of tokens bound for one node (reference ep_a2a.py:338-350; the spelling of the
+    second argument is the reference's). With a single NVSwitch node every token's node is 0 and the answer is one range."""
+    hit = (token_node_idx == traget_node_id).any(dim=-1) if token_node_idx.dim() > 1 else (token_node_idx == traget_node_id)
+    idx = torch.nonzero(hit, as_tuple=False).flatten()
+    if idx.numel() == 0:
+        return torch.empty((0, 2), dtype=index_type, device=token_node_idx.device)
+    breaks = torch.nonzero(idx[1:] != idx[:-1] + 1, as_tuple=False).flatten()
+    starts = torch.cat([idx[:1], idx[breaks + 1]])
+    ends = torch.cat([idx[breaks], idx[-1:]]) + 1
+    return torch.stack([starts, ends], dim=1).to(index_type)

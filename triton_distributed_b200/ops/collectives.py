@@ -414,6 +414,7 @@ def reduce_scatter_ring_push_1d_intra_node_kernel(input: torch.Tensor, ctx: Redu
 
 
 reduce_scatter_ring_push_1d_intra_node_ce = reduce_scatter_ring_push_1d_intra_node_kernel  # reference :289-341
+reduce_scatter_ring_push_1d_intra_node_sm = reduce_scatter_ring_push_1d_intra_node_kernel
 
 
 def copy_continuous(src: torch.Tensor, dst: torch.Tensor, stream=None) -> torch.Tensor:

@@ -260,3 +260,6 @@ def sp_gqa_fwd_batch_decode(ctx: SpDecodeContext, q, k_cache, v_cache, global_kv
                    max_kv=int(block_table.shape[1]) * k_cache.shape[1],
                    ll_ptrs=ctx.gather.half_ptr_arrays()[half], world=ctx.world, rank=ctx.rank, epoch=ctx.epoch,
                    push_only=(phase == 1))
+
+
+kernel_inter_rank_gqa_fwd_batch_decode_combine_kv = inter_rank_combine   # the reference's name of the cross-rank merge

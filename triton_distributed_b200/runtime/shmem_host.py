@@ -118,3 +118,46 @@ class _null:
 
     def __exit__(self, *a):
         return False
+
+
+# ---------------------------------------------------------------------------- the remaining pynvshmem names
+NVSHMEM_TEAM_WORLD, NVSHMEMX_TEAM_NODE = 0, 2
+
+
+def nvshmem_team_my_pe(team: int = NVSHMEM_TEAM_WORLD) -> int:
+    """One NVSwitch node: the node team is the world team."""
+    return nvshmem_my_pe()
+
+
+def nvshmem_team_n_pes(team: int = NVSHMEM_TEAM_WORLD) -> int:
+    return nvshmem_n_pes()
+
+
+def nvshmemx_mc_ptr(team: int, t: SymmTensor) -> int:
+    """Address of the multicast alias of ``t`` (0 when the heap was not bound to a multicast object, TDIST_NVLS=1)."""
+    return 0 if t.mc is None else t.mc.data_ptr()
+
+
+def nvshmemx_barrier_all_on_stream(stream=None) -> None:
+    from ..ops.collectives import barrier_all_on_stream
+    barrier_all_on_stream(stream)
+
+
+nvshmemx_putmem_on_stream = putmem_on_stream
+nvshmemx_putmem_signal_on_stream = putmem_signal_on_stream
+
+
+def nvshmem_putmem(dst: SymmTensor, src: torch.Tensor, pe: int) -> None:
+    """Blocking put: returns when the data is at ``pe``."""
+    putmem_on_stream(dst, src, pe)
+    torch.cuda.current_stream(src.device).synchronize()
+
+
+def nvshmem_getmem(dst: torch.Tensor, src: SymmTensor, pe: int) -> None:
+    getmem_on_stream(dst, src, pe)
+    torch.cuda.current_stream(dst.device).synchronize()
+
+
+def nvshmem_p(t: SymmTensor, index: int, value, pe: int) -> None:
+    """Typed single-element put (``nvshmem_<type>_p``): element ``index`` of rank ``pe``'s copy := value."""
+    t.peers[pe].reshape(-1)[index] = value

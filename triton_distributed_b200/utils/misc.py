@@ -158,3 +158,18 @@ def p2p_bandwidth(nbytes: int = 64 << 20, mode: int = 0, ctas: int = 32, threads
     _, ms = perf_func_max_over_ranks(run, iters, 2, group)
     heap.barrier()
     return nbytes / ms / 1e6
+
+
+def p2p_native_atomic_required(fn):
+    """Decorator of the reference's tests (utils.py): skip a function on systems whose peer links have no native
+    atomics. NVLink always has them; the check runs only when two GPUs are visible."""
+    import functools
+
+    @functools.wraps(fn)
+    def wrapped(*a, **kw):
+        import torch
+        if torch.cuda.is_available() and torch.cuda.device_count() >= 2 and not check_p2p_native_atomic_supported(0, 1):
+            print(f"skipping {fn.__name__}: peer atomics are not native on this system")
+            return None
+        return fn(*a, **kw)
+    return wrapped
