@@ -10,6 +10,7 @@
 // every rank first, so that no launch ever waits for a launch that has not run.
 #include <cuda_runtime.h>
 
+#include "../device/language_extra.cuh"
 #include "../device/shmem.cuh"
 #include "../include/tdist.h"
 #include "../runtime/host_common.h"
@@ -120,7 +121,7 @@ __global__ void prim_kernel(const PrimParams p) {
             //           results were right                                -> grid * block / 32
             uint32_t* w = reinterpret_cast<uint32_t*>(slot(p, 0));
             red_release_gpu_add_u32(w + 0, 1u);
-            if ((threadIdx.x & 31) == 0) atom_add_acq_rel_gpu_u32(w + 1, 32u);
+            language_extra::atomic_add_per_warp(w + 1, 32u, language_extra::kScopeGpu);  // lane 0 adds for its warp
             if (threadIdx.x == 0) {
                 bool got = false;
                 for (int spin = 0; spin < (1 << 22) && !got; ++spin) got = atom_cas_acq_rel_sys_u32(w + 2, 0u, 1u) == 0u;
@@ -142,6 +143,27 @@ __global__ void prim_kernel(const PrimParams p) {
         }
         default: break;
     }
+}
+
+// Never launched: instantiates every helper of language_extra.cuh so that ptxas checks their PTX at build time.
+__global__ void language_extra_compile_check(uint32_t* a, uint64_t* b, void* mc, WaitCtx w) {
+    namespace le = language_extra;
+    uint32_t acc = le::tid(0) + le::ntid(0) + le::laneid();
+    le::fence_sc(le::kScopeGpu);
+    le::fence_sc(le::kScopeSys);
+    acc += le::ld(a, le::kScopeSys, le::kAcquire) + le::ld_acquire(a, le::kScopeGpu) + static_cast<uint32_t>(le::ld(b, le::kScopeGpu, le::kRelaxed));
+    le::st(a, acc, le::kScopeSys, le::kRelease);
+    le::st(b, acc, le::kScopeGpu, le::kRelaxed);
+    acc += le::atomic_add(a, 1u, le::kScopeSys) + le::atomic_cas(a, 0u, 1u) + le::atomic_add_per_warp(a, 1u, le::kScopeGpu);
+    le::red_release(a, 1u, le::kScopeSys);
+    le::arrive_inc(a, 0, 1u, le::kScopeGpu);
+    acc += le::wait_eq(b, 1, w) ? 1u : 0u;
+    const uint4 v4 = le::load_v4_u32(a);
+    const ulonglong2 v2 = le::load_v2_b64(b);
+    le::store_v2_u32(a, v4.x + static_cast<uint32_t>(v2.x), acc);
+    le::multimem_st_b32(mc, acc);
+    le::multimem_st_b64(mc, v2.y);
+    le::multimem_st_v2_b32(mc, v4.y, v4.z);
 }
 
 }  // namespace tdist
