@@ -192,4 +192,67 @@ __device__ __forceinline__ void fcollect_block(const SymmWindow& w, void* dst, c
     }
 }
 
+// ---- the same collectives at warp and thread scope, and the remaining names of the reference's device library
+__device__ __forceinline__ void getmem_nbi(const SymmWindow& w, void* dst, const void* src, size_t bytes, int pe) {
+    getmem(w, dst, src, bytes, pe);
+}
+__device__ __forceinline__ void broadcast_warp(const SymmWindow& w, void* dst, const void* src, size_t bytes, int root) {
+    if (w.rank != root) return;
+    for (int pe = 0; pe < w.world; ++pe) putmem_warp(w, dst, src, bytes, pe);
+}
+__device__ __forceinline__ void broadcast(const SymmWindow& w, void* dst, const void* src, size_t bytes, int root) {
+    if (w.rank != root) return;
+    for (int pe = 0; pe < w.world; ++pe) putmem(w, dst, src, bytes, pe);
+}
+__device__ __forceinline__ void broadcastmem_block(const SymmWindow& w, void* dst, const void* src, size_t bytes, int root) {
+    broadcast_block(w, dst, src, bytes, root);
+}
+__device__ __forceinline__ void fcollect_warp(const SymmWindow& w, void* dst, const void* src, size_t bytes) {
+    for (int i = 0; i < w.world; ++i) {
+        int pe = w.rank + i;
+        if (pe >= w.world) pe -= w.world;
+        putmem_warp(w, static_cast<char*>(dst) + static_cast<size_t>(w.rank) * bytes, src, bytes, pe);
+    }
+}
+__device__ __forceinline__ void fcollect(const SymmWindow& w, void* dst, const void* src, size_t bytes) {
+    for (int i = 0; i < w.world; ++i) {
+        int pe = w.rank + i;
+        if (pe >= w.world) pe -= w.world;
+        putmem(w, static_cast<char*>(dst) + static_cast<size_t>(w.rank) * bytes, src, bytes, pe);
+    }
+}
+// Barrier called by ONE warp (at least n_pes lanes take part) or ONE thread: same flags and epoch as the block form.
+__device__ __forceinline__ bool barrier_all_warp(const SymmWindow& w, const BarrierState& b, const WaitCtx& wc) {
+    __syncwarp();
+    const uint64_t target = *reinterpret_cast<volatile uint64_t*>(b.epoch) + 1;
+    bool ok = true;
+    const int lane = static_cast<int>(lane_id());
+    if (lane < w.world) {
+        fence_acq_rel_sys();
+        st_release_sys_u64(symm_at(w, b.flags, lane) + w.rank, target);
+        ok = signal_wait_until(b.flags + lane, kCmpGe, target, wc, lane, 101);
+    }
+    ok = __all_sync(0xffffffffu, ok);
+    if (lane == 0) *reinterpret_cast<volatile uint64_t*>(b.epoch) = target;
+    __syncwarp();
+    return ok;
+}
+__device__ __forceinline__ bool barrier_all(const SymmWindow& w, const BarrierState& b, const WaitCtx& wc) {
+    const uint64_t target = *reinterpret_cast<volatile uint64_t*>(b.epoch) + 1;
+    bool ok = true;
+    fence_acq_rel_sys();
+    for (int pe = 0; pe < w.world; ++pe) st_release_sys_u64(symm_at(w, b.flags, pe) + w.rank, target);
+    for (int pe = 0; pe < w.world; ++pe) ok = signal_wait_until(b.flags + pe, kCmpGe, target, wc, pe, 102) && ok;
+    *reinterpret_cast<volatile uint64_t*>(b.epoch) = target;
+    return ok;
+}
+__device__ __forceinline__ bool sync_all_warp(const SymmWindow& w, const BarrierState& b, const WaitCtx& wc) { return barrier_all_warp(w, b, wc); }
+__device__ __forceinline__ bool sync_all(const SymmWindow& w, const BarrierState& b, const WaitCtx& wc) { return barrier_all(w, b, wc); }
+// Address of `local` inside the multicast alias of its buffer (`mc_base` = SymmTensor.mc of the same object): what
+// multimem.st / multimem.ld_reduce take (reference libshmem_device.remote_mc_ptr).
+template <typename T>
+__device__ __forceinline__ T* remote_mc_ptr(const SymmWindow& w, char* mc_base, T* local) {
+    return reinterpret_cast<T*>(mc_base + (reinterpret_cast<char*>(local) - w.base[w.rank]));
+}
+
 }  // namespace tdist

@@ -165,6 +165,17 @@ __global__ void language_extra_compile_check(uint32_t* a, uint64_t* b, void* mc,
     le::multimem_st_b64(mc, v2.y);
     le::multimem_st_v2_b32(mc, v4.y, v4.z);
 }
+// Likewise for the warp- and thread-scope forms of shmem.cuh that no test op launches.
+__global__ void shmem_scopes_compile_check(SymmWindow win, BarrierState st, char* mc_base, char* buf, size_t bytes, WaitCtx w) {
+    getmem_nbi(win, buf, buf + bytes, bytes, 0);
+    broadcast_warp(win, buf, buf + bytes, bytes, 0);
+    broadcast(win, buf, buf + bytes, bytes, 0);
+    broadcastmem_block(win, buf, buf + bytes, bytes, 0);
+    fcollect_warp(win, buf, buf + bytes, bytes);
+    fcollect(win, buf, buf + bytes, bytes);
+    bool ok = barrier_all_warp(win, st, w) && barrier_all(win, st, w) && sync_all_warp(win, st, w) && sync_all(win, st, w);
+    if (ok) language_extra::multimem_st_b32(remote_mc_ptr(win, mc_base, reinterpret_cast<int*>(buf)), 0u);
+}
 
 }  // namespace tdist
 
