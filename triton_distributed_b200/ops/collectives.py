@@ -438,3 +438,16 @@ def add_continuous(lhs: torch.Tensor, rhs: torch.Tensor, out: Optional[torch.Ten
     stacked = torch.stack([lhs.reshape(-1, lhs.shape[-1]), rhs.reshape(-1, rhs.shape[-1])]).reshape(-1, lhs.shape[-1])
     o = out if out is not None else torch.empty_like(lhs)
     return ring_reduce(stacked, o.view(-1, lhs.shape[-1]), 0, 2).view_as(lhs)
+
+
+def barrier_all_intra_node_non_atomic(local_world_size: int = 0, rank: int = 0, num_ranks: int = 0, symm_flags=None, target_value: int = 0,
+                                      stream=None) -> None:
+    """reference common_ops.py:104-159 (monotonic target values written to peers, then an acquire spin): exactly the
+    protocol of the barrier kernel here, which keeps its own flags and target."""
+    barrier_all_on_stream(stream)
+
+
+barrier_all_intra_node_non_atomic_block = barrier_all_intra_node_non_atomic
+# reference common_ops.py:88-101: CAS 0 -> 1 on the peers, then 1 -> 0 on the own flags. The monotonic barrier needs no
+# reset phase and works over links without native atomics, so both names run it.
+barrier_all_intra_node_atomic_cas_block = barrier_all_intra_node_non_atomic
