@@ -126,3 +126,40 @@ def test_abandoned_wait_reports_timeout_and_leaves_the_context_usable(cuda_devic
     c = G.gemm_persistent(a, b)
     check_status()
     torch.testing.assert_close(c.float(), a.float() @ b.float().t(), atol=2e-2, rtol=2e-2)
+
+
+def test_consumer_blocks_until_the_host_sets_the_flags(cuda_device):
+    """The fused AG-GEMM of one emulated rank is launched while the peer's rows are in the workspace but their flags
+    are not set; the host sets them a moment later with stream write-values (no kernel involved). The kernel must
+    wait, then finish with the right result (the reference's test_distributed_wait.py `correctness` case)."""
+    import time
+
+    from triton_distributed_b200.ops import collectives as CO
+
+    torch.manual_seed(5)
+    dtype = torch.bfloat16
+    world, mpr, N, K = 2, 256, 512, 256
+    lw = LocalWorld(world, cuda_device)
+    A = [_rand((mpr, K), dtype, cuda_device) for _ in range(world)]
+    B = _rand((N, K), dtype, cuda_device, K ** -0.5)
+    ctxs = [G.create_ag_gemm_intra_node_context(A[r], B, r, world, max_M=world * mpr, heap=lw.heap(r)) for r in range(world)]
+    ctx = ctxs[0]
+    half = (ctx.epoch + 1) & 1
+    mt = (mpr + 127) // 128
+    ws = ctx.workspace.local[half][: world * mpr * K].view(world, mpr, K)
+    flags = ctx.flags.local[half][: world * mt].view(world, mt)
+    ws[1].copy_(A[1])
+    assert int(flags[1].abs().sum()) == 0          # nothing has announced rank 1's blocks
+    torch.cuda.synchronize()
+    side = torch.cuda.Stream()
+    t0 = time.time()
+    c = G.ag_gemm_intra_node(A[0], B, ctx)         # asynchronous: the kernel now spins on rank 1's flags
+    time.sleep(0.3)
+    for b in range(mt):
+        CO.set_signal(flags[1, b:b + 1].data_ptr(), ctx.epoch, stream=side)
+    torch.cuda.synchronize()
+    took = time.time() - t0
+    check_status()
+    assert took >= 0.3                               # it really waited for the host
+    ref = torch.cat(A).float() @ B.float().t()
+    torch.testing.assert_close(c.float(), ref, atol=2e-2, rtol=2e-2)
