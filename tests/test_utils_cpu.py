@@ -177,3 +177,19 @@ def test_top_level_namespace_and_remaining_reference_names():
         return 7
     assert kernel() == 7 and aot_spaces()["decode_bf16_d128"]["function"] == "kernel"
     assert p2p_native_atomic_required(lambda: 5)() == 5
+
+
+def test_bench_reference_arm_reports_unavailable():
+    """`bench.py --impl reference` must print one JSON line and exit 0 even without a GPU: the reference cannot be
+    installed offline, and the line says so."""
+    import json
+    import os
+    import subprocess
+    import sys
+
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    r = subprocess.run([sys.executable, os.path.join(root, "bench.py"), "--impl", "reference", "--gpus", "1", "--steps", "2", "--warmup", "3"],
+                       capture_output=True, text=True, timeout=120, env=dict(os.environ, CUDA_VISIBLE_DEVICES=""))
+    assert r.returncode == 0, r.stderr[-1000:]
+    line = json.loads(r.stdout.strip().splitlines()[-1])
+    assert line["impl"] == "reference" and "unavailable" in line and len(line["unavailable"]) > 10
