@@ -55,3 +55,22 @@ def test_fake_implementations_propagate_shapes():
         ids, w = torch.ops.tdist.moe_topk_softmax(torch.empty(5, 16), 2, False)
         assert ids.shape == (5, 2) and w.dtype == torch.float32
     T.release_context(h)
+
+
+def test_fp8_ops_through_the_dispatcher_on_cpu():
+    from triton_distributed_b200.ops import gemm_fp8 as F8
+
+    torch.manual_seed(2)
+    x, w = torch.randn(16, 256), torch.randn(24, 256) * 256 ** -0.5
+    a, sa = F8.quantize_fp8_rowwise(x)
+    b, sb = F8.quantize_fp8_blockwise(w)
+    ref = F8.gemm_fp8_reference(a, sa, b, sb)
+    torch.testing.assert_close(torch.ops.tdist.gemm_fp8(a, sa, b, sb), ref)
+    h = T.register_context(F8.create_ag_gemm_fp8_context(16, 256, 0, 1, device="cpu"))
+    torch.testing.assert_close(torch.ops.tdist.ag_gemm_fp8(a, sa, b, sb, h), ref)
+    assert (ref.float() - x @ w.t()).abs().max() < 0.1 * (x @ w.t()).abs().max()     # the quantisation itself is sane
+    with FakeTensorMode():
+        fa, fb = torch.empty(16, 256, dtype=F8.FP8), torch.empty(24, 256, dtype=F8.FP8)
+        out = torch.ops.tdist.gemm_fp8(fa, torch.empty(16, 2), fb, torch.empty(1, 2))
+        assert out.shape == (16, 24) and out.dtype == torch.bfloat16
+    T.release_context(h)
