@@ -160,4 +160,9 @@ def nvshmem_getmem(dst: torch.Tensor, src: SymmTensor, pe: int) -> None:
 
 def nvshmem_p(t: SymmTensor, index: int, value, pe: int) -> None:
     """Typed single-element put (``nvshmem_<type>_p``): element ``index`` of rank ``pe``'s copy := value."""
-    t.peers[pe].reshape(-1)[index] = value
+    if t.local.device.type != "cuda":
+        t.peers[pe].reshape(-1)[index] = value
+        return
+    # a device-to-device memcpy of one element (copy engine): no library kernel is handed the peer's memory
+    src = torch.tensor([value], dtype=t.local.dtype, device=t.local.device)
+    t.peers[pe].reshape(-1)[index:index + 1].copy_(src)
