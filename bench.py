@@ -1,4 +1,4 @@
-"""Headline benchmark: tensor-parallel AllGather-GEMM on the BASELINE shape.
+"""Headline benchmark: tensor-parallel AllGather-GEMM on the headline shape (m8192 n49152 k12288).
 
     python bench.py --gpus N --steps K --warmup W           (N=1)
     python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 \
@@ -265,7 +265,7 @@ def main():
         extra["ag_gemm_speedup_vs_torch"] = tb_ms / ms
         extra["reference_published_speedup_vs_torch_h800"] = REFERENCE_PUBLISHED_SPEEDUP
         del gathered
-        # GEMM-RS on the BASELINE shape: A [8192, 49152/N], B [12288, 49152/N] -> [8192/N, 12288]
+        # GEMM-RS on the transposed headline shape: A [8192, 49152/N], B [12288, 49152/N] -> [8192/N, 12288]
         kl = N_TOTAL // world
         x = torch.randn(M_TOTAL, kl, device=dev, dtype=torch.bfloat16, generator=gen)
         v = (torch.randn(K_TOTAL, kl, device=dev, dtype=torch.float32, generator=gen) * N_TOTAL ** -0.5).to(torch.bfloat16)

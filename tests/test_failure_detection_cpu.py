@@ -48,3 +48,16 @@ def test_descriptor_exchange_round_trip_single_process():
             os.close(fd)
         a.close()
         b.close()
+
+
+def test_heap_setup_keeps_ranks_in_step_when_one_rank_cannot_map():
+    """A failure after the first agreement (exchange / import / map) on one rank: every rank runs the same
+    collectives, all give the segment up, and each releases its handles and address range."""
+    res, out = run_workers("heap_agreement_worker.py", 2, env={"CUDA_VISIBLE_DEVICES": ""}, timeout=120)
+    assert res is not None, out[-2000:]
+    assert all(r["none"] for r in res), res
+    assert res[0]["calls"] == res[1]["calls"] and res[0]["calls"], res
+    assert "map" in res[1]["err"] and "another rank" in res[0]["err"], res
+    for r in res:
+        assert r["released"] == 2 and r["freed"] == 1, res      # own + imported handle, the reserved range
+    assert res[0]["unmapped"] == 2 and res[1]["unmapped"] == 0, res

@@ -123,3 +123,55 @@ def test_fused_dispatch_combine_roundtrip(cuda_device, world, T, E, K, H):
             deq = (q.float().view(T, H // 128, 128) * sc.unsqueeze(-1)).view(T, H).to(torch.bfloat16).float()
             ref = deq * routed[r][1].sum(-1, keepdim=True)
             torch.testing.assert_close(outs[r].float(), ref, atol=2e-2, rtol=2e-2)
+
+
+def test_route_rejects_out_of_range_expert_ids(cuda_device):
+    """An id of -1 (a dropped pair) or E must not index shared memory: the pair is left out, its slot is -1, and the
+    status block carries a bad-argument record that check_status() raises."""
+    from triton_distributed_b200._lib import TdistError
+    T, E, K = 64, 16, 2
+    torch.manual_seed(5)
+    ids = torch.randint(0, E, (T, K), dtype=torch.int32, device=cuda_device)
+    ids[3, 1] = -1
+    ids[40, 0] = E
+    r = MU.route(ids, E)
+    with pytest.raises(TdistError, match="bad argument"):
+        check_status()
+    ref = MU.route(ids.cpu(), E)
+    assert int(r.splits.sum()) == T * K - 2
+    assert torch.equal(r.splits.cpu(), ref.splits) and torch.equal(r.cumsum.cpu(), ref.cumsum)
+    assert torch.equal(r.slot_of.cpu(), ref.slot_of)
+    assert int(r.slot_of[3 * K + 1]) == -1 and int(r.slot_of[40 * K]) == -1
+    live = T * K - 2
+    assert torch.equal(r.sorted_token[:live].cpu(), ref.sorted_token[:live])
+    # the aligned sort drops the same pairs: no sorted entry names them
+    got = MU.sort_topk_ids_align_block_size(ids, E, 1, T, 16)
+    with pytest.raises(TdistError, match="bad argument"):
+        check_status()
+    named = got[0][got[0] < T * K]
+    assert named.numel() == live and (3 * K + 1) not in named.tolist() and (40 * K) not in named.tolist()
+    # a clean call afterwards reports nothing
+    MU.route(torch.randint(0, E, (T, K), dtype=torch.int32, device=cuda_device), E)
+    check_status()
+
+
+def test_fast_all_to_all_reports_a_destination_overflow(cuda_device):
+    """More than max_m rows for one destination: max_m rows are sent, the published splits say so, and the status
+    block records the bad argument instead of rows spilling into the next source's slot."""
+    from triton_distributed_b200._lib import TdistError
+    world, E, H, max_m = 2, 4, 256, 8
+    lw = LocalWorld(world, cuda_device)
+    epr = E // world
+    ctxs = [A.create_all_to_all_context(max_m, H, r, E, world, epr, heap=lw.heap(r), device=cuda_device) for r in range(world)]
+    # rank 0 sends 12 rows to rank 1's experts (2 and 3): 7 + 5 > max_m
+    cums = torch.tensor([0, 1, 2, 9, 14], dtype=torch.int32, device=cuda_device)
+    send = torch.randn(14, H, device=cuda_device).to(torch.bfloat16)
+    A.fast_all_to_all(ctxs[0], send, cums, None, phase=1)
+    with pytest.raises(TdistError, match="bad argument"):
+        check_status()
+    empty = torch.zeros(E + 1, dtype=torch.int32, device=cuda_device)
+    A.fast_all_to_all(ctxs[1], send[:0], empty, None, phase=1)
+    splits, recv, _ = A.fast_all_to_all(ctxs[1], send[:0], empty, None, phase=2)
+    check_status()
+    assert splits[:epr].tolist() == [7, 1]          # clamped to the 8 rows that were sent
+    assert torch.equal(recv[:max_m], send[2:2 + max_m])

@@ -1,7 +1,7 @@
 """Multi-rank check of the symmetric heap and the fused AG-GEMM / GEMM-RS ops.
 
 Runs under torchrun on CUDA (NCCL oracle: all_gather_into_tensor + matmul, matmul +
-reduce_scatter_tensor) or on CPU (gloo; BASELINE plumbing config: fp32, seed 0, rtol 1e-5).
+reduce_scatter_tensor) or on CPU (gloo plumbing config: fp32, seed 0, rtol 1e-5).
 Follows the reference's test_ag_gemm_intra_node.py:129-149 and test_gemm_rs.py:43-115:
 fresh random inputs every iteration, non-tile-aligned M, stale-workspace poisoning.
 """

@@ -239,11 +239,13 @@ int tdist_a2a(const TdistA2AArgs* args);
 int tdist_dequant_fp8(const void* x, const void* scale, void* out_bf16, int rows, int hidden, void* stream);
 
 /* ------------------------------------------------------------------ MoE routing */
+/* An expert id outside [0, num_experts) (e.g. -1 for a dropped pair) is left out of the counts and of the sort
+   (slot_of = -1 / no sorted entry) and reported once through `status` (may be NULL) as a bad argument. */
 int tdist_moe_route(const void* ids, int n, int topk, int num_experts, void* splits, void* cumsum,
-                    void* sorted_token, void* slot_of, void* stream);
+                    void* sorted_token, void* slot_of, void* status, void* stream);
 int tdist_moe_align_block_size(const void* ids, int numel_per_rank, int num_experts, int num_ranks, int block_size,
                                void* sorted_ids, int sorted_cap, void* expert_ids, void* block_barrier_ids,
-                               void* rank_block_num, void* num_tokens_post_pad, void* stream);
+                               void* rank_block_num, void* num_tokens_post_pad, void* status, void* stream);
 /* dst[p] = src[index[p] / div] (zeros where index[p] is outside [0, limit)); pos_of (optional) gets the inverse map */
 int tdist_gather_rows(const void* src, const void* index, int rows_out, int div, int limit, int row_bytes,
                       void* dst, void* pos_of, void* stream);

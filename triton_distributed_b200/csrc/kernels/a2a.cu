@@ -138,7 +138,12 @@ __global__ void __launch_bounds__(kA2AThreads, 2) a2a_kernel(const A2AParams p) 
             count = 0;
             for (int e = 0; e < p.epr; ++e) count += p.counts[dest * p.epr + e];
         }
-        count = min(count, p.max_m);
+        if (count > p.max_m) {
+            // A destination's slot for this source holds max_m rows: the surplus is not sent, the splits published
+            // below are clamped to what was sent, and the host learns of it through the status block.
+            if (slice == 0 && threadIdx.x == 0) report_timeout(p.wctx, kStatusBadArgument, dest, p.max_m, p.max_m, count, 3);
+            count = p.max_m;
+        }
         char* rbase = p.recv_peer[dest] + static_cast<size_t>(p.rank) * p.max_m * p.row_bytes_out;
         float* sbase = p.scale_peer[dest] ? p.scale_peer[dest] + static_cast<size_t>(p.rank) * p.max_m * p.scale_cols : nullptr;
         const int segs = p.quant ? (p.hidden / 128 + kSegGroups - 1) / kSegGroups : (p.row_bytes_in + kSegBytes - 1) / kSegBytes;
@@ -159,7 +164,8 @@ __global__ void __launch_bounds__(kA2AThreads, 2) a2a_kernel(const A2AParams p) 
         }
         if (p.mode == TDIST_A2A_DISPATCH && slice == 0 && static_cast<int>(threadIdx.x) < p.epr) {
             const int e = dest * p.epr + threadIdx.x;
-            p.splits_peer[dest][p.rank * p.epr + threadIdx.x] = p.counts[e + 1] - p.counts[e];
+            const int lo = min(p.counts[e] - first, p.max_m), hi = min(p.counts[e + 1] - first, p.max_m);
+            p.splits_peer[dest][p.rank * p.epr + threadIdx.x] = hi - lo;   // rows of this expert that were sent
         }
         // Publish: the last CTA of the group raises this source's flag on the destination. Only one
         // thread per CTA fences: the CTA barrier orders every thread's stores before thread 0's

@@ -21,6 +21,9 @@
 #include <cuda_runtime.h>
 #include <math_constants.h>
 
+#include <mutex>
+#include <string>
+
 #include "../device/ll.cuh"
 #include "../device/signal.cuh"
 #include "../include/tdist.h"
@@ -509,6 +512,8 @@ static int flash_decode_impl(const TdistDecodeArgs* a) {
     if (a->head_dim != 64 && a->head_dim != 128 && a->head_dim != 256) return fail(TDIST_EINVAL, "decode: head_dim must be 64, 128 or 256");
     if (a->stride_token % 8 || a->stride_block % 8 || a->stride_head % 8) return fail(TDIST_EINVAL, "decode: cache strides must be multiples of 8 elements");
     if (a->mode < 0 || a->mode > 2) return fail(TDIST_EINVAL, "decode: bad mode");
+    if (a->page_size < 1 || a->max_blocks < 1) return fail(TDIST_EINVAL, "decode: page_size and max_blocks must be at least 1");
+    if (static_cast<long long>(a->B) * a->Hkv * a->splits > 0x7fffffffLL) return fail(TDIST_ELIMIT, "decode: B * Hkv * splits exceeds the grid limit");
     DecodeParams p;
     memset(&p, 0, sizeof(p));
     p.q = a->q;
@@ -586,6 +591,13 @@ extern "C" int tdist_flash_decode_static(const TdistDecodeArgs* a) {
         return fail(TDIST_EINVAL, "decode(static): only modes 0 and 1 (the sequence-parallel mode needs caller-owned symmetric memory)");
     if (a->B < 1 || a->Hq < 1 || a->Hkv < 1 || a->splits < 1 || a->head_dim < 1)
         return fail(TDIST_EINVAL, "decode(static): bad sizes");
+    // the cheap range checks of the regular path come first: nothing is enqueued for a call that will be refused,
+    // and the size product below cannot overflow
+    if (a->splits > 256) return fail(TDIST_EINVAL, "decode: splits must be in [1, 256]");
+    if (a->head_dim != 64 && a->head_dim != 128 && a->head_dim != 256) return fail(TDIST_EINVAL, "decode: head_dim must be 64, 128 or 256");
+    if (a->Hq % a->Hkv || a->Hq / a->Hkv > 16) return fail(TDIST_EINVAL, "decode: bad head counts");
+    if (a->page_size < 1 || a->max_blocks < 1) return fail(TDIST_EINVAL, "decode: page_size and max_blocks must be at least 1");
+    if (static_cast<long long>(a->B) * a->Hq > (1LL << 24)) return fail(TDIST_ELIMIT, "decode(static): B * Hq beyond the built-in scratch");
     const size_t counters_bytes = (static_cast<size_t>(a->B) * a->Hkv * sizeof(unsigned) + 255) / 256 * 256;
     const size_t partial_bytes = static_cast<size_t>(a->B) * a->Hq * a->splits * (a->head_dim + 2) * sizeof(float);
     if (counters_bytes + partial_bytes > TDIST_DECODE_STATIC_SCRATCH_BYTES)
@@ -594,16 +606,21 @@ extern "C" int tdist_flash_decode_static(const TdistDecodeArgs* a) {
                                       std::to_string(TDIST_DECODE_STATIC_SCRATCH_BYTES) + " bytes; use fewer splits or tdist_flash_decode");
     // once per device, with that device current: resolve the array's device address
     static unsigned char* scratch_of_device[64] = {};
+    static std::mutex setup_lock;   // two host threads may make the first call on one device at once
     int dev = 0;
     TDIST_CUDA_OK(cudaGetDevice(&dev));
     if (dev < 0 || dev >= 64) return fail(TDIST_EINVAL, "decode(static): device ordinal out of range");
-    if (scratch_of_device[dev] == nullptr) {
-        unsigned char* ptr = nullptr;
-        TDIST_CUDA_OK(cudaGetSymbolAddress(reinterpret_cast<void**>(&ptr), g_decode_static_scratch));
-        if (ptr == nullptr) return fail(TDIST_EDRIVER, "decode(static): cudaGetSymbolAddress returned a null address");
-        scratch_of_device[dev] = ptr;
+    unsigned char* base = nullptr;
+    {
+        std::lock_guard<std::mutex> guard(setup_lock);
+        if (scratch_of_device[dev] == nullptr) {
+            unsigned char* ptr = nullptr;
+            TDIST_CUDA_OK(cudaGetSymbolAddress(reinterpret_cast<void**>(&ptr), g_decode_static_scratch));
+            if (ptr == nullptr) return fail(TDIST_EDRIVER, "decode(static): cudaGetSymbolAddress returned a null address");
+            scratch_of_device[dev] = ptr;
+        }
+        base = scratch_of_device[dev];
     }
-    unsigned char* base = scratch_of_device[dev];
     // the counters must start at zero whatever the previous call left behind
     TDIST_CUDA_OK(cudaMemsetAsync(base, 0, counters_bytes, static_cast<cudaStream_t>(a->stream)));
     TdistDecodeArgs b = *a;

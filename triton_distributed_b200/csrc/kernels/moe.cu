@@ -10,11 +10,13 @@
 #include <cuda_runtime.h>
 #include <math_constants.h>
 
+#include "../device/signal.cuh"
 #include "../include/tdist.h"
 #include "../runtime/host_common.h"
 
 namespace tdist {
 
+constexpr int kKernelMoe = 6;
 constexpr int kMoeThreads = 512;
 constexpr int kMoeWarps = kMoeThreads / 32;
 
@@ -24,20 +26,33 @@ __device__ __forceinline__ unsigned lanemask_lt() {
     return m;
 }
 
+// An expert id outside [0, E) (a dropped or padded pair, e.g. -1) never indexes shared memory: the pair is
+// left out of the histogram and of the sort, and the first such id is recorded in the status block
+// (kStatusBadArgument: index = position of the pair, seen = the id, expected = E) for the host to raise.
+__device__ __forceinline__ bool expert_in_range(int e, int E) { return e >= 0 && e < E; }
+__device__ __forceinline__ void report_bad_expert(const WaitCtx& w, int i, int e, int E, int where) {
+    report_timeout(w, kStatusBadArgument, -1, i, E, e, where);
+}
+
 // CTA-wide stable counting-sort positions. `running[e]` (smem) holds the next free position of
 // expert e and is advanced; `cnt` is smem scratch of kMoeWarps * E ints. emit(i, pos) is called
-// once per element in [0, n).
+// once per element in [0, n) whose id is a valid expert; the others get emit(i, -1).
 template <typename F>
-__device__ __forceinline__ void stable_positions(const int* ids, int n, int E, int* running, int* cnt, F emit) {
+__device__ __forceinline__ void stable_positions(const int* ids, int n, int E, int* running, int* cnt, const WaitCtx& w,
+                                                 F emit) {
     const int tid = static_cast<int>(threadIdx.x);
     const int warp = tid >> 5;
     for (int base = 0; base < n; base += kMoeThreads) {
         for (int j = tid; j < kMoeWarps * E; j += kMoeThreads) cnt[j] = 0;
         __syncthreads();
         const int i = base + tid;
-        const bool valid = i < n;
-        const int e = valid ? ids[i] : 0;
-        const int key = valid ? e : E + (tid & 31);  // idle lanes never match anybody
+        const int e = i < n ? ids[i] : 0;
+        const bool valid = i < n && expert_in_range(e, E);
+        if (i < n && !valid) {
+            report_bad_expert(w, i, e, E, 2);
+            emit(i, -1);
+        }
+        const int key = valid ? e : E + (tid & 31);  // idle lanes and rejected ids never match anybody
         const unsigned mask = __match_any_sync(0xffffffffu, key);
         const int rank_in_warp = __popc(mask & lanemask_lt());
         if (valid && rank_in_warp == 0) cnt[warp * E + e] = __popc(mask);
@@ -57,10 +72,14 @@ __device__ __forceinline__ void stable_positions(const int* ids, int n, int E, i
     }
 }
 
-__device__ __forceinline__ void histogram(const int* ids, int n, int E, int* hist) {
+__device__ __forceinline__ void histogram(const int* ids, int n, int E, int* hist, const WaitCtx& w) {
     for (int x = threadIdx.x; x < E; x += kMoeThreads) hist[x] = 0;
     __syncthreads();
-    for (int i = threadIdx.x; i < n; i += kMoeThreads) atomicAdd(&hist[ids[i]], 1);
+    for (int i = threadIdx.x; i < n; i += kMoeThreads) {
+        const int e = ids[i];
+        if (expert_in_range(e, E)) atomicAdd(&hist[e], 1);
+        else report_bad_expert(w, i, e, E, 1);
+    }
     __syncthreads();
 }
 
@@ -68,12 +87,13 @@ __device__ __forceinline__ void histogram(const int* ids, int n, int E, int* his
 // ids[n] (n = tokens * topk, token-major) -> splits[E], cumsum[E+1], sorted_token[n] (token of the
 // pair at each sorted position), slot_of[n] (sorted position of each pair). One CTA.
 __global__ void __launch_bounds__(kMoeThreads) moe_route_kernel(const int* ids, int n, int topk, int E, int* splits,
-                                                                int* cumsum, int* sorted_token, int* slot_of) {
+                                                                int* cumsum, int* sorted_token, int* slot_of,
+                                                                WaitCtx w) {
     extern __shared__ int sm[];
     int* hist = sm;
     int* running = sm + E;
     int* cnt = sm + 2 * E;
-    histogram(ids, n, E, hist);
+    histogram(ids, n, E, hist, w);
     if (threadIdx.x < 32) {
         // exclusive scan of the histogram by one warp: a contiguous chunk of experts per lane
         const int lane = threadIdx.x;
@@ -97,9 +117,9 @@ __global__ void __launch_bounds__(kMoeThreads) moe_route_kernel(const int* ids, 
         if (lane == 31) cumsum[E] = incl;
     }
     __syncthreads();
-    stable_positions(ids, n, E, running, cnt, [&](int i, int pos) {
-        slot_of[i] = pos;
-        sorted_token[pos] = i / topk;
+    stable_positions(ids, n, E, running, cnt, w, [&](int i, int pos) {
+        slot_of[i] = pos;   // -1 for a pair whose expert id was rejected
+        if (pos >= 0) sorted_token[pos] = i / topk;
     });
 }
 
@@ -108,7 +128,8 @@ __global__ void __launch_bounds__(kMoeThreads) moe_route_kernel(const int* ids, 
 __global__ void __launch_bounds__(kMoeThreads) moe_align_kernel(const int* ids, int numel_per_rank, int E, int num_ranks,
                                                                 int block_size, int* sorted_ids, int sorted_cap,
                                                                 int* expert_ids, int* block_barrier_ids,
-                                                                int* rank_block_num, int* num_tokens_post_pad) {
+                                                                int* rank_block_num, int* num_tokens_post_pad,
+                                                                WaitCtx w) {
     extern __shared__ int sm[];
     int* hist = sm;
     int* running = sm + E;
@@ -119,7 +140,7 @@ __global__ void __launch_bounds__(kMoeThreads) moe_align_kernel(const int* ids, 
     if (threadIdx.x == 0) base_s = 0;
     // padded sizes of the earlier ranks give this rank's base offset
     for (int q = 0; q <= r; ++q) {
-        histogram(ids + static_cast<size_t>(q) * numel_per_rank, numel_per_rank, E, hist);
+        histogram(ids + static_cast<size_t>(q) * numel_per_rank, numel_per_rank, E, hist, w);
         if (threadIdx.x == 0) {
             int acc = 0;
             for (int e = 0; e < E; ++e) {
@@ -149,8 +170,9 @@ __global__ void __launch_bounds__(kMoeThreads) moe_align_kernel(const int* ids, 
     for (int i = base + threadIdx.x; i < fill_end; i += kMoeThreads) sorted_ids[i] = pad_value;
     __syncthreads();
     const int* my = ids + static_cast<size_t>(r) * numel_per_rank;
-    stable_positions(my, numel_per_rank, E, running, cnt,
-                     [&](int i, int pos) { sorted_ids[base + pos] = i + r * numel_per_rank; });
+    stable_positions(my, numel_per_rank, E, running, cnt, w, [&](int i, int pos) {
+        if (pos >= 0) sorted_ids[base + pos] = i + r * numel_per_rank;
+    });
 }
 
 // ---------------------------------------------------------------------------- softmax + top-k
@@ -245,8 +267,10 @@ __global__ void topk_reduce_kernel(const uint4* y, const int* pos_of, const floa
         for (int c = lane; c < vec_per_row; c += 32) {
             float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
             for (int k = 0; k < topk; ++k) {
+                const int pos = pos_of[t * topk + k];
+                if (pos < 0) continue;   // a pair that routing rejected contributes nothing
                 const float wk = w ? w[t * topk + k] : 1.f;
-                const uint4 q = y[static_cast<size_t>(pos_of[t * topk + k]) * vec_per_row + c];
+                const uint4 q = y[static_cast<size_t>(pos) * vec_per_row + c];
                 const uint32_t u[4] = {q.x, q.y, q.z, q.w};
 #pragma unroll
                 for (int i = 0; i < 4; ++i) {
@@ -280,8 +304,17 @@ static int ensure_smem(K kernel, int bytes) {
     return 0;
 }
 
+static WaitCtx moe_wctx(void* status) {
+    WaitCtx w;
+    w.status = static_cast<Status*>(status);
+    w.timeout_ns = 0;
+    w.kernel_id = kKernelMoe;
+    w.rank = 0;
+    return w;
+}
+
 extern "C" int tdist_moe_route(const void* ids, int n, int topk, int num_experts, void* splits, void* cumsum,
-                               void* sorted_token, void* slot_of, void* stream) {
+                               void* sorted_token, void* slot_of, void* status, void* stream) {
     if (num_experts < 1 || num_experts > 2048) return fail(TDIST_ELIMIT, "moe_route: at most 2048 experts");
     if (topk < 1 || n < 0) return fail(TDIST_EINVAL, "moe_route: bad sizes");
     const int smem = moe_smem_bytes(num_experts);
@@ -289,7 +322,7 @@ extern "C" int tdist_moe_route(const void* ids, int n, int topk, int num_experts
     if (rc) return rc;
     moe_route_kernel<<<1, kMoeThreads, smem, static_cast<cudaStream_t>(stream)>>>(
         static_cast<const int*>(ids), n, topk, num_experts, static_cast<int*>(splits), static_cast<int*>(cumsum),
-        static_cast<int*>(sorted_token), static_cast<int*>(slot_of));
+        static_cast<int*>(sorted_token), static_cast<int*>(slot_of), moe_wctx(status));
     TDIST_CUDA_OK(cudaGetLastError());
     return 0;
 }
@@ -297,7 +330,7 @@ extern "C" int tdist_moe_route(const void* ids, int n, int topk, int num_experts
 extern "C" int tdist_moe_align_block_size(const void* ids, int numel_per_rank, int num_experts, int num_ranks,
                                           int block_size, void* sorted_ids, int sorted_cap, void* expert_ids,
                                           void* block_barrier_ids, void* rank_block_num, void* num_tokens_post_pad,
-                                          void* stream) {
+                                          void* status, void* stream) {
     if (num_experts < 1 || num_experts > 2048) return fail(TDIST_ELIMIT, "moe_align: at most 2048 experts");
     if (block_size < 1 || num_ranks < 1) return fail(TDIST_EINVAL, "moe_align: bad sizes");
     const int smem = moe_smem_bytes(num_experts);
@@ -306,7 +339,7 @@ extern "C" int tdist_moe_align_block_size(const void* ids, int numel_per_rank, i
     moe_align_kernel<<<num_ranks, kMoeThreads, smem, static_cast<cudaStream_t>(stream)>>>(
         static_cast<const int*>(ids), numel_per_rank, num_experts, num_ranks, block_size, static_cast<int*>(sorted_ids),
         sorted_cap, static_cast<int*>(expert_ids), static_cast<int*>(block_barrier_ids), static_cast<int*>(rank_block_num),
-        static_cast<int*>(num_tokens_post_pad));
+        static_cast<int*>(num_tokens_post_pad), moe_wctx(status));
     TDIST_CUDA_OK(cudaGetLastError());
     return 0;
 }

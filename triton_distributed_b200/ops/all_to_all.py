@@ -106,7 +106,10 @@ def fast_all_to_all(ctx: AllToAllContext, send_tensor: torch.Tensor, send_split_
     """Rows ``[cumsum[e], cumsum[e+1])`` of ``send_tensor`` go to the rank owning expert ``e``.
     Returns views into this call's half of the receive buffers: ``(recv_splits[G] int32 laid out
     [source rank, local expert], recv[ws*max_m, hidden], recv_scale[ws*max_m, scale_cols] | None)``.
-    The views stay valid until the call after next."""
+    The views are valid only for work enqueued before the next call on this context: a peer may start
+    the call after next as soon as this rank's next call has pushed, and then overwrites this half.
+    A destination that would get more than ``max_m`` rows from this rank receives ``max_m`` (its splits say so)
+    and the status block records a bad argument, which ``check_status()`` raises."""
     ntok = send_tensor.shape[0]
     # one destination never gets more than max_m rows from one source; the sender as a whole may hold
     # up to world * max_m rows (the combine direction sends back everything it received)

@@ -121,7 +121,9 @@ def _launch(q, k_cache, v_cache, kv_lens, block_table, scale, soft_cap, out, mod
     a.q, a.k_cache, a.v_cache = q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr()
     bt = block_table if block_table.dtype == torch.int32 else block_table.to(torch.int32)
     kl = kv_lens if kv_lens.dtype == torch.int32 else kv_lens.to(torch.int32)
-    a.block_table, a.kv_lens = bt.contiguous().data_ptr(), kl.contiguous().data_ptr()
+    # named locals: the (possibly copied) index tensors must outlive the launch call below
+    bt_c, kl_c = bt.contiguous(), kl.contiguous()
+    a.block_table, a.kv_lens = bt_c.data_ptr(), kl_c.data_ptr()
     a.partial, a.counters, a.out = partial.data_ptr(), counters.data_ptr(), out.data_ptr()
     a.B, a.Hq, a.Hkv, a.head_dim, a.page_size = B, Hq, Hkv, D, page
     a.max_blocks, a.splits = bt.shape[1], splits
@@ -139,6 +141,14 @@ def _launch(q, k_cache, v_cache, kv_lens, block_table, scale, soft_cap, out, mod
     a.status = st.device_ptr if st is not None else None
     a.timeout_ns = default_timeout_ns()
     a.stream = (stream or torch.cuda.current_stream(q.device)).cuda_stream
+    if stream is not None:
+        # copies made on the current stream are read on `stream`: order the two, and keep the allocator from
+        # handing the copies' memory out again before `stream` is done with them
+        cur = torch.cuda.current_stream(q.device)
+        if stream != cur and (bt_c is not block_table or kl_c is not kv_lens):
+            stream.wait_stream(cur)
+        for t in (bt_c, kl_c):
+            t.record_stream(stream)
     _lib.check(_lib.lib().tdist_flash_decode(C.byref(a)), "tdist_flash_decode")
     launch_count += 1
     return out

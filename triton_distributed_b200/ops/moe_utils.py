@@ -27,6 +27,12 @@ def _stream(t: torch.Tensor, stream=None):
     return (stream or torch.cuda.current_stream(t.device)).cuda_stream
 
 
+def _status_ptr():
+    from ..runtime.status import global_status
+    st = global_status()
+    return st.device_ptr if st is not None else None
+
+
 class Routing(NamedTuple):
     splits: torch.Tensor        # int32 [E]   pairs per expert
     cumsum: torch.Tensor        # int32 [E+1] exclusive prefix sum
@@ -57,7 +63,11 @@ def topk_softmax(logits: torch.Tensor, topk: int, renormalize: bool = False) -> 
 
 
 def route(topk_ids: torch.Tensor, num_experts: int, out: Optional[Routing] = None) -> Routing:
-    """Stable expert sort of the ``T*topk`` (token, k) pairs."""
+    """Stable expert sort of the ``T*topk`` (token, k) pairs.
+
+    An id outside ``[0, num_experts)`` (``-1`` for a dropped pair) is not counted and not sorted: its ``slot_of`` is
+    ``-1``, and on CUDA the first such id is recorded as a bad argument in the status block, which
+    ``check_status()`` raises."""
     global launch_count
     T, K = topk_ids.shape
     n = T * K
@@ -68,19 +78,24 @@ def route(topk_ids: torch.Tensor, num_experts: int, out: Optional[Routing] = Non
                       torch.empty(n, dtype=torch.int32, device=dev), torch.empty(n, dtype=torch.int32, device=dev))
     if dev.type != "cuda":
         flat = topk_ids.reshape(-1).long()
-        splits = torch.bincount(flat, minlength=num_experts)
-        order = torch.sort(flat, stable=True).indices
+        ok = (flat >= 0) & (flat < num_experts)
+        key = torch.where(ok, flat, torch.full_like(flat, num_experts))      # rejected ids sort last
+        splits = torch.bincount(key, minlength=num_experts + 1)[:num_experts]
+        order = torch.sort(key, stable=True).indices
+        live = int(ok.sum())
         out.splits.copy_(splits)
         out.cumsum[0] = 0
         out.cumsum[1:].copy_(torch.cumsum(splits, 0))
-        out.sorted_token.copy_(order // K)
-        out.slot_of[order] = torch.arange(n, dtype=torch.int32)
+        out.sorted_token[:live].copy_(order[:live] // K)
+        out.slot_of.fill_(-1)
+        out.slot_of[order[:live]] = torch.arange(live, dtype=torch.int32)
         return out
     ids = topk_ids.contiguous()
     if ids.dtype != torch.int32:
         ids = ids.to(torch.int32)
     _lib.check(_lib.lib().tdist_moe_route(ids.data_ptr(), n, K, num_experts, out.splits.data_ptr(), out.cumsum.data_ptr(),
-                                          out.sorted_token.data_ptr(), out.slot_of.data_ptr(), _stream(ids)), "tdist_moe_route")
+                                          out.sorted_token.data_ptr(), out.slot_of.data_ptr(), _status_ptr(), _stream(ids)),
+               "tdist_moe_route")
     launch_count += 1
     return out
 
@@ -119,7 +134,7 @@ def sort_topk_ids_align_block_size(topk_ids: torch.Tensor, num_experts: int, num
     _lib.check(_lib.lib().tdist_moe_align_block_size(ids.data_ptr(), numel, num_experts, num_ranks, block_size,
                                                      sorted_ids.data_ptr(), sorted_cap, expert_ids.data_ptr(),
                                                      barrier_ids.data_ptr(), rank_block_num.data_ptr(),
-                                                     post_pad.data_ptr(), _stream(ids, moe_stream)),
+                                                     post_pad.data_ptr(), _status_ptr(), _stream(ids, moe_stream)),
                "tdist_moe_align_block_size")
     launch_count += 1
     return sorted_ids, expert_ids, barrier_ids, rank_block_num, post_pad

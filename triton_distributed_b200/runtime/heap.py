@@ -225,7 +225,7 @@ class SymmetricHeap:
 
     def _try_vmm(self, nbytes: int):
         lib = _lib.lib()
-        dev = self.device.index if self.device.index is not None else torch.cuda.current_device()
+        dev = self.device.index if self.device.index is not None else (torch.cuda.current_device() if self.device.type == "cuda" else 0)
         stage = "caps"
         handles: List[int] = [0] * self.world
         va = C.c_uint64(0)
@@ -275,7 +275,26 @@ class SymmetricHeap:
                 _lib.check(lib.tdist_symm_map(C.c_uint64(va.value + r * seg_bytes), C.c_size_t(seg_bytes), C.c_uint64(handles[r]), dev), "map")
                 mapped.append(r)
         except Exception as e:  # noqa: BLE001 - every rank must reach the agreement step
-            return None, f"{stage}: {e}"
+            map_err = f"{stage}: {e}"
+        else:
+            map_err = ""
+        # Agree again after exchange / import / map: a rank that failed here must not go on to the fallback's
+        # collectives while the others enter the multicast set-up's. Every rank runs this one all-reduce; if any
+        # rank failed, all of them undo what they built and return None together.
+        all_mapped = not map_err
+        if self.world > 1:
+            t = torch.tensor([1 if all_mapped else 0], device=self.device, dtype=torch.int32)
+            dist.all_reduce(t, op=dist.ReduceOp.MIN, group=self.group)
+            all_mapped = int(t.item()) == 1
+        if not all_mapped:
+            for r in mapped:
+                lib.tdist_symm_unmap(C.c_uint64(va.value + r * seg_bytes), C.c_size_t(seg_bytes))
+            if va.value:
+                lib.tdist_symm_address_free(C.c_uint64(va.value), C.c_size_t(seg_bytes * self.world))
+            for hdl in handles:
+                if hdl:
+                    lib.tdist_symm_release(C.c_uint64(hdl))
+            return None, map_err or "another rank could not exchange, import or map the segments"
 
         # Optional NVLS alias: rank 0 creates a multicast object, every rank adds its device and binds its
         # own segment, then maps the object. Every step is followed by an agreement so that a rank that

@@ -55,15 +55,31 @@ def nvshmem_ptr(t: SymmTensor, pe: int) -> int:
     return t.ptrs[pe]
 
 
+def _order_after_current(device, stream) -> None:
+    """Make ``stream`` wait for what the current stream has queued (a staging copy made there)."""
+    cur = torch.cuda.current_stream(device)
+    if stream is not None and stream != cur:
+        ev = torch.cuda.Event()
+        ev.record(cur)
+        stream.wait_event(ev)
+
+
 def putmem_on_stream(dst: SymmTensor, src: torch.Tensor, pe: int, stream=None) -> None:
-    """Copy ``src`` (local) into rank ``pe``'s copy of ``dst``, stream-ordered."""
+    """Copy ``src`` (local) into rank ``pe``'s copy of ``dst``, stream-ordered.
+
+    A non-contiguous ``src`` is first packed on the current stream; ``stream`` is then ordered after that copy."""
     target = dst.peers[pe].reshape(-1).view(torch.uint8)
-    flat = src.contiguous().reshape(-1).view(torch.uint8)
-    n = flat.numel()
-    if n > target.numel():
+    if src.numel() * src.element_size() > target.numel():
         raise ValueError("source larger than the symmetric destination")
     if src.device.type != "cuda":
         raise ValueError("putmem_on_stream moves device memory; on CPU use torch.distributed")
+    staged = not src.is_contiguous()
+    flat = src.contiguous().reshape(-1).view(torch.uint8)
+    n = flat.numel()
+    if staged:
+        _order_after_current(src.device, stream)
+        if stream is not None:
+            flat.record_stream(stream)
     if n % 16 == 0 and flat.data_ptr() % 16 == 0 and target.data_ptr() % 16 == 0:
         st = global_status()
         _lib.check(_lib.lib().tdist_p2p_copy(flat.data_ptr(), target.data_ptr(), n, 0, min(64, max(1, n // 65536)), 512, 0,
@@ -75,10 +91,18 @@ def putmem_on_stream(dst: SymmTensor, src: torch.Tensor, pe: int, stream=None) -
 
 
 def getmem_on_stream(dst: torch.Tensor, src: SymmTensor, pe: int, stream=None) -> None:
-    """Copy rank ``pe``'s copy of ``src`` into the local tensor ``dst``, stream-ordered."""
+    """Copy rank ``pe``'s copy of ``src`` into the local tensor ``dst``, stream-ordered. ``dst`` must be contiguous
+    (a reshaped copy would silently drop the data) and no larger than ``src`` (the read would run past the peer
+    mapping)."""
+    if not dst.is_contiguous():
+        raise ValueError("getmem_on_stream needs a contiguous destination")
     source = src.peers[pe].reshape(-1).view(torch.uint8)
     flat = dst.reshape(-1).view(torch.uint8)
     n = flat.numel()
+    if n > source.numel():
+        raise ValueError("destination larger than the symmetric source")
+    if dst.device.type != "cuda":
+        raise ValueError("getmem_on_stream moves device memory; on CPU use torch.distributed")
     if n % 16 == 0 and flat.data_ptr() % 16 == 0 and source.data_ptr() % 16 == 0:
         st = global_status()
         _lib.check(_lib.lib().tdist_p2p_copy(source.data_ptr(), flat.data_ptr(), n, 0, min(64, max(1, n // 65536)), 512, 0,
