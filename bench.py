@@ -11,17 +11,24 @@ TFLOP/s of the whole job: 2*8192*49152*12288 FLOP / (max-over-ranks device time 
 
 One step = one call of the public op `ag_gemm_intra_node` = ONE fused kernel launch (the gather
 is done inside the kernel over NVLink). Timing: CUDA events on the launching stream around K
-back-to-back steps, barrier + synchronize on both sides, max over ranks. The operands of a step
-(B shard >= 151 MB, plus A and C) exceed the 126 MB L2, so no explicit flush is needed.
+back-to-back steps, barrier + synchronize on both sides, max over ranks. One such K-step region
+lasts only 20-150 ms, which is too short against clock and power transients, so the region is
+repeated (at least 5 times and until about one second of device time has been measured); the
+reported time per step is the MEDIAN over the repeats, with the fastest and slowest repeat beside
+it. The operands of a step (B shard >= 151 MB, plus A and C) exceed the 126 MB L2, so no explicit
+flush is needed.
 
 Extra keys: `e2e` repeats the measurement with, every step, the host->device copy of the step's
-A shard from pinned memory and a device->host read of a slice of the result; `torch_baseline` is
-the non-overlapped NCCL all_gather + cuBLAS matmul on the same box; `extra` holds GEMM-RS.
+A shard from pinned memory and the device->host copy of this rank's own [M/N, 49152/N] block of
+the result (both on a copy stream, double-buffered, as a serving loop would overlap them);
+`extra.torch_nccl_cublas_ag_gemm` is the non-overlapped NCCL all_gather + cuBLAS matmul on the
+same box; `extra` also holds GEMM-RS and the fp8 flavour.
 """
 from __future__ import annotations
 
 import argparse
 import json
+import math
 import os
 import statistics
 import subprocess
@@ -40,9 +47,10 @@ class ClockSampler:
     nvidia-smi; read-only queries) from the benchmark's own thread.
 
     Every NVML query costs milliseconds and briefly stalls work on the GPU it touches, and one
-    stalled rank stalls every rank of a fused collective kernel, so sampling is sparse: one
-    sample as soon as the timed launches are queued (the GPU is then inside the timed region),
-    then one every 250 ms until the region's closing event has fired.
+    stalled rank stalls every rank of a fused collective kernel. The timed region is therefore
+    repeated and only every third repeat is sampled (densely: one query every 10 ms while that
+    repeat's closing event is pending). All samples lie inside timed repeats, and because the
+    sampled repeats are a minority the median over repeats is a time that no query disturbed.
     BENCH_SAMPLER=off disables sampling; =smi shells out to nvidia-smi per sample instead."""
 
     REASONS = {"hw_slowdown": 0x8, "hw_thermal_slowdown": 0x40, "sw_thermal_slowdown": 0x20, "sw_power_cap": 0x4}
@@ -89,7 +97,7 @@ class ClockSampler:
         except Exception:  # noqa: BLE001 - a failed sample is just missing
             pass
 
-    def watch(self, done_event) -> None:
+    def watch(self, done_event, period_s: float = 0.01) -> None:
         """Sample while `done_event` (a CUDA event recorded after the timed launches) is pending."""
         if self.kind == "off":
             return
@@ -97,10 +105,9 @@ class ClockSampler:
             self.sample()
             if done_event.query():
                 return
-            for _ in range(25):
-                time.sleep(0.01)
-                if done_event.query():
-                    return
+            time.sleep(period_s)
+            if done_event.query():
+                return
 
     def summary(self) -> dict:
         if not self.samples:
@@ -109,7 +116,12 @@ class ClockSampler:
         for x in self.samples:
             mask |= x[2]
         reasons = sorted(n for n, bit in self.REASONS.items() if mask & bit)
+        bins = {}
+        for x in self.samples:   # samples binned by SM clock (100 MHz bins)
+            key = f"{int(x[0] // 100 * 100)}"
+            bins[key] = bins.get(key, 0) + 1
         return {"sm_mhz": statistics.median(x[0] for x in self.samples), "sm_max_mhz": self.max_mhz,
+                "sm_mhz_min": min(x[0] for x in self.samples), "sm_mhz_bins": bins,
                 "power_w_max": max(x[1] for x in self.samples), "samples": len(self.samples),
                 "reasons": reasons, "source": self.kind}
 
@@ -163,22 +175,40 @@ def main():
             dist.barrier(group)
             torch.cuda.synchronize()
 
-    def timed(fn, steps, warmup, sampler=None):
+    MIN_REPEATS, TARGET_MS = 5, 1000.0
+
+    def timed(fn, steps, warmup, sampler=None, finish=None):
+        """Median (over repeats) of the max-over-ranks device time per step of a `steps`-step region.
+        Returns (median_ms, {"repeats", "ms_min", "ms_max", "timed_ms_total"}). Every third repeat is sampled
+        by `sampler` while it runs (see ClockSampler)."""
         for _ in range(warmup):
             fn()
         sync()
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e0.record()
-        for _ in range(steps):
-            fn()
-        e1.record()
-        if sampler is not None:
-            sampler.watch(e1)  # the launches above are asynchronous: the GPU is inside the region now
-        sync()
-        ms = torch.tensor([e0.elapsed_time(e1) / steps], device=dev)
-        if world > 1:
-            dist.all_reduce(ms, op=dist.ReduceOp.MAX, group=group)
-        return float(ms.item())
+        per_step = []
+        repeats = MIN_REPEATS
+        r = 0
+        while r < repeats:
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for _ in range(steps):
+                fn()
+            if finish is not None:
+                finish()   # work the steps left on other streams joins the timed stream before the closing event
+            e1.record()
+            if sampler is not None and r % 3 == 1:
+                sampler.watch(e1)  # the launches above are asynchronous: the GPU is inside the region now
+            sync()
+            ms = torch.tensor([e0.elapsed_time(e1) / steps], device=dev)
+            if world > 1:
+                dist.all_reduce(ms, op=dist.ReduceOp.MAX, group=group)
+            per_step.append(float(ms.item()))
+            if r == 0:
+                # every rank derives the same count from the same max-over-ranks time
+                repeats = max(MIN_REPEATS, min(200, math.ceil(TARGET_MS / max(per_step[0] * steps, 1e-3))))
+            r += 1
+        med = statistics.median(per_step)
+        return med, {"repeats": len(per_step), "ms_min": min(per_step), "ms_max": max(per_step),
+                     "timed_ms_total": sum(per_step) * steps}
 
     # ---- correctness guard (one step against torch) so a wrong kernel never reports a number
     out = G.ag_gemm_intra_node(a, b, ctx, out=c)
@@ -196,60 +226,65 @@ def main():
 
     # ---- headline: device-timed fused op
     sampler = ClockSampler(torch.cuda.current_device()) if rank == 0 else None
-    ms = timed(lambda: G.ag_gemm_intra_node(a, b, ctx, out=c), K_STEPS, W, sampler)
+    ms, spread = timed(lambda: G.ag_gemm_intra_node(a, b, ctx, out=c), K_STEPS, W, sampler)
     clocks = sampler.summary() if rank == 0 else None
+    if clocks is not None and clocks.get("sm_mhz"):
+        clocks["ms_times_median_mhz"] = ms * clocks["sm_mhz"]   # clock-normalised time (compare runs at different clocks)
     check_status()
-    # The timed region is too short for more than one or two NVML samples (each query costs milliseconds and
-    # perturbs the coupled ranks), so the same launches are repeated for ~0.4 s, untimed, while rank 0 samples
-    # every 50 ms: the clock and power the kernel settles at under sustained load.
-    probe_steps = max(K_STEPS, int(400.0 / max(ms, 1e-3)))
-    probe = ClockSampler(torch.cuda.current_device()) if rank == 0 else None
-    for _ in range(probe_steps):
-        G.ag_gemm_intra_node(a, b, ctx, out=c)
-    if probe is not None and probe.kind != "off":
-        e_probe = torch.cuda.Event()
-        e_probe.record()
-        while not e_probe.query():
-            probe.sample()
-            time.sleep(0.05)
-        clocks["sustained_probe"] = probe.summary()
-        clocks["sustained_probe"]["steps"] = probe_steps
-    sync()
-    check_status()
-    launches = K_STEPS  # one fused kernel per step
+    launches = K_STEPS  # one fused kernel per step, counted for one K-step region
     value = flops / (ms * 1e-3) / 1e12
 
-    # ---- end to end through the public API: H2D of the step's input, op, D2H of a result slice
+    # ---- end to end through the public API: H2D of the step's input, op, D2H of this rank's block of the result
     a_host = torch.empty(mpr, K_TOTAL, dtype=torch.bfloat16).pin_memory()
     a_host.copy_(a)
-    probe_host = torch.empty(npr, dtype=torch.bfloat16).pin_memory()
-    a_dev = torch.empty_like(a)
+    # this rank's own rows of its output shard: [M/N, 49152/N] (at N = 1 that is all of C)
+    out_host = [torch.empty(mpr, npr, dtype=torch.bfloat16).pin_memory() for _ in range(2)]
 
-    # Two input buffers and a copy stream: the H2D copy of step i+1 runs while step i computes (what a serving
-    # loop does); every step still copies its own input and reads its own result back.
-    a_bufs = [a_dev, torch.empty_like(a)]
-    copy_stream = torch.cuda.Stream()
+    # Two input buffers, two result buffers and a copy stream per direction: the H2D copy of step i+1 and the D2H
+    # copy of step i-1 run while step i computes (what a serving loop does); every step still copies its own
+    # input in and its own result out, and the region only ends when the last result has landed on the host.
+    a_bufs = [torch.empty_like(a), torch.empty_like(a)]
+    c_bufs = [c, torch.empty_like(c)]
+    h2d_stream, d2h_stream = torch.cuda.Stream(), torch.cuda.Stream()
     ev_in = [torch.cuda.Event() for _ in range(2)]
     ev_free = [torch.cuda.Event() for _ in range(2)]
+    ev_out = [torch.cuda.Event() for _ in range(2)]
+    ev_read = [torch.cuda.Event() for _ in range(2)]
     step_no = [0]
 
     def e2e_step():
         i = step_no[0] & 1
         step_no[0] += 1
         cur = torch.cuda.current_stream()
-        with torch.cuda.stream(copy_stream):
-            copy_stream.wait_event(ev_free[i])            # the op that last read this buffer is done
+        with torch.cuda.stream(h2d_stream):
+            h2d_stream.wait_event(ev_free[i])             # the op that last read this input buffer is done
             a_bufs[i].copy_(a_host, non_blocking=True)
-            ev_in[i].record(copy_stream)
+            ev_in[i].record(h2d_stream)
         cur.wait_event(ev_in[i])
-        o = G.ag_gemm_intra_node(a_bufs[i], b, ctx, out=c)
+        cur.wait_event(ev_read[i])                        # the copy-out that last read this result buffer is done
+        o = G.ag_gemm_intra_node(a_bufs[i], b, ctx, out=c_bufs[i])
         ev_free[i].record(cur)
-        probe_host.copy_(o[rank * mpr], non_blocking=True)
+        ev_out[i].record(cur)
+        with torch.cuda.stream(d2h_stream):
+            d2h_stream.wait_event(ev_out[i])
+            out_host[i].copy_(o[rank * mpr:(rank + 1) * mpr], non_blocking=True)
+            ev_read[i].record(d2h_stream)
+        cur.wait_event(ev_read[i ^ 1])                    # the timed stream trails the copy-out of the step before
 
-    e2e_ms = timed(e2e_step, K_STEPS, W)
+    def e2e_finish():
+        for ev in ev_read:
+            torch.cuda.current_stream().wait_event(ev)    # the last results are on the host when the region closes
+
+    e2e_ms, e2e_spread = timed(e2e_step, K_STEPS, W, finish=e2e_finish)
+    torch.cuda.synchronize()
     check_status()
+    e2e_err = (out_host[(step_no[0] - 1) & 1][::61].float() - out[rank * mpr:(rank + 1) * mpr:61].float()).abs().max().item()
+    if not (e2e_err < 1e-3):
+        raise SystemExit(f"the result copied back to the host differs from the device result ({e2e_err})")
     e2e = {"value": flops / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOP/s", "ms_per_step": e2e_ms,
-           "h2d_bytes_per_step": a_host.numel() * 2, "d2h_bytes_per_step": probe_host.numel() * 2}
+           "h2d_bytes_per_step": a_host.numel() * 2, "d2h_bytes_per_step": out_host[0].numel() * 2,
+           "d2h": f"this rank's own [M/{world}, N/{world}] block of C, every step", **e2e_spread}
+    del a_bufs, c_bufs[1:], out_host
 
     extra = {}
     if not args.no_extra:
@@ -260,8 +295,8 @@ def main():
                 torch.matmul(gathered, b.t(), out=c)
             else:
                 torch.matmul(a, b.t(), out=c)
-        tb_ms = timed(torch_step, K_STEPS, W)
-        extra["torch_nccl_cublas_ag_gemm"] = {"ms_per_step": tb_ms, "tflops": flops / (tb_ms * 1e-3) / 1e12}
+        tb_ms, tb_spread = timed(torch_step, K_STEPS, W)
+        extra["torch_nccl_cublas_ag_gemm"] = {"ms_per_step": tb_ms, "tflops": flops / (tb_ms * 1e-3) / 1e12, **tb_spread}
         extra["ag_gemm_speedup_vs_torch"] = tb_ms / ms
         extra["reference_published_speedup_vs_torch_h800"] = REFERENCE_PUBLISHED_SPEEDUP
         del gathered
@@ -271,7 +306,7 @@ def main():
         v = (torch.randn(K_TOTAL, kl, device=dev, dtype=torch.float32, generator=gen) * N_TOTAL ** -0.5).to(torch.bfloat16)
         rctx = G.create_gemm_rs_context(M_TOTAL, K_TOTAL, rank, world, output_dtype=torch.bfloat16, group=group, device=dev)
         ro = torch.empty(mpr, K_TOTAL, device=dev, dtype=torch.bfloat16)
-        rs_ms = timed(lambda: G.gemm_rs(x, v, rctx, out=ro), K_STEPS, W)
+        rs_ms, rs_spread = timed(lambda: G.gemm_rs(x, v, rctx, out=ro), K_STEPS, W)
         check_status()
         full = torch.empty(M_TOTAL, K_TOTAL, device=dev, dtype=torch.bfloat16)
 
@@ -279,8 +314,8 @@ def main():
             torch.matmul(x, v.t(), out=full)
             if world > 1:
                 dist.reduce_scatter_tensor(ro, full, group=group)
-        trs_ms = timed(torch_rs, K_STEPS, W)
-        ref_out = ro.clone()                       # torch result of the last baseline step
+        trs_ms, _ = timed(torch_rs, K_STEPS, W)
+        ref_out = ro.clone() if world > 1 else full[:mpr].clone()   # torch result of the last baseline step
         G.gemm_rs(x, v, rctx, out=ro)
         check_status()
         rs_err = (ro.float() - ref_out.float()).abs().max().item()
@@ -288,7 +323,8 @@ def main():
             raise SystemExit(f"gemm_rs result is wrong (max abs err {rs_err})")
         extra["gemm_rs"] = {"ms_per_step": rs_ms, "tflops": flops / (rs_ms * 1e-3) / 1e12,
                             "torch_nccl_cublas_ms": trs_ms, "speedup_vs_torch": trs_ms / rs_ms,
-                            "check_max_abs_err_vs_torch": rs_err}
+                            "check_max_abs_err_vs_torch": rs_err, **rs_spread}
+        del full, x, v, ro, ref_out
 
     if not args.no_extra:
         # the block-scaled fp8 flavour of the headline op (e4m3, 1x128 / 128x128 fp32 scales), same shape
@@ -300,8 +336,9 @@ def main():
             c8 = torch.empty(M_TOTAL, npr, device=dev, dtype=torch.bfloat16)
             F8.ag_gemm_fp8(a8, sa8, b8, sb8, ctx8, out=c8)
             check_status()
+            out = G.ag_gemm_intra_node(a, b, ctx, out=c)
             err8 = (c8[::257].float() - out[::257].float()).abs().max().item()   # against the bf16 result: quantisation noise only
-            f8_ms = timed(lambda: F8.ag_gemm_fp8(a8, sa8, b8, sb8, ctx8, out=c8), K_STEPS, W)
+            f8_ms, _ = timed(lambda: F8.ag_gemm_fp8(a8, sa8, b8, sb8, ctx8, out=c8), K_STEPS, W)
             check_status()
             extra["ag_gemm_fp8_blockscaled"] = {"ms_per_step": f8_ms, "tflops": flops / (f8_ms * 1e-3) / 1e12,
                                                 "max_abs_diff_vs_bf16_result": err8}
@@ -313,12 +350,16 @@ def main():
         line = {
             "metric": "AG-GEMM aggregate TFLOP/s (m8192 n49152 k12288, TP over N GPUs)",
             "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": K_STEPS, "warmup": W,
-            "ms_per_step": ms, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+            "ms_per_step": ms, "ms_per_step_min": spread["ms_min"], "ms_per_step_max": spread["ms_max"],
+            "repeats": spread["repeats"], "timed_ms_total": spread["timed_ms_total"],
+            "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
             "dtype": "bf16", "data": "synthetic (random-init weights and activations of the named shape)",
             "config": {"model": "TP AllGather-GEMM A[8192,12288] x B[12288,49152]", "global_batch": M_TOTAL,
                        "seq_len": K_TOTAL, "parallelism": f"tp{world}",
                        "l2": "operands of one step exceed the 126 MB L2 (no explicit flush)",
-                       "timing": "CUDA events, max over ranks"},
+                       "timing": "CUDA events around `steps` back-to-back steps, max over ranks; that region is repeated "
+                                 "`repeats` times (>= 5 and >= 1 s in total) and ms_per_step is the median repeat",
+                       "e2e_d2h": "this rank's own [M/N, 49152/N] block of C every step (all of C at N = 1)"},
             "clocks": clocks, "e2e": e2e, "gpu_launches": launches, "impl": "ours", "extra": extra,
             "check_max_abs_err": err,
         }

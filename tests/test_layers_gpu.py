@@ -39,8 +39,7 @@ def test_ep_moe_single_rank(cuda_device):
     check_status()
     from triton_distributed_b200.ops import moe_utils as MU
     ids, w = MU.topk_softmax(x.float() @ gate.float().t(), K, renormalize=True)
-    q, sc = A.quant_fp8_reference(x)
-    xd = (q.float().view(T, H // 128, 128) * sc.unsqueeze(-1)).view(T, H).to(torch.bfloat16).float()
+    xd = x.float()          # rows travel as bf16
     ref = torch.zeros(T, H, device=cuda_device)
     for t in range(T):
         for k in range(K):
@@ -58,9 +57,10 @@ def test_ep_all2all_layer_emulated(cuda_device, world):
     layers = [EPAll2AllLayer(None, T, H, K, r, E, world, world, heap=lw.heap(r), device=cuda_device) for r in range(world)]
     xs = [torch.randn(T, H, device=cuda_device).to(torch.bfloat16) for _ in range(world)]
     ids = [torch.randint(0, E, (T, K), dtype=torch.int32, device=cuda_device) for _ in range(world)]
-    for r in range(world):
-        layers[r].dispatch(xs[r], ids[r], phase=1)
-    recv = [layers[r].dispatch(xs[r], ids[r], phase=2) for r in range(world)]
+    for phase in (1, 2):        # every rank publishes its counts, then every rank sends
+        for r in range(world):
+            layers[r].dispatch(xs[r], ids[r], phase=phase)
+    recv = [layers[r].dispatch(xs[r], ids[r], phase=4) for r in range(world)]
     check_status()
     epr = E // world
     for d in range(world):
@@ -70,7 +70,14 @@ def test_ep_all2all_layer_emulated(cuda_device, world):
             for s in range(world):
                 pairs = (ids[s].reshape(-1) == e).nonzero().flatten()
                 want.append(xs[s][pairs // K])
-        assert torch.equal(recv[d], torch.cat(want))
+        want = torch.cat(want)
+        assert int(layers[d].num_recv) == want.shape[0]
+        assert torch.equal(recv[d][: want.shape[0]], want)
+        # the group table matches: splits [source, expert] and the start row of every (expert, source) group
+        sp = torch.stack([torch.bincount(ids[s].reshape(-1).long(), minlength=E)[d * epr:(d + 1) * epr] for s in range(world)])
+        assert torch.equal(layers[d].recv_splits.long(), sp)
+        flat = sp.t().reshape(-1)
+        assert torch.equal(layers[d].recv_offset.long().reshape(-1), torch.cumsum(flat, 0) - flat)
     for r in range(world):
         layers[r].combine(recv[r], phase=1)
     outs = [layers[r].combine(recv[r], phase=2) for r in range(world)]

@@ -101,17 +101,26 @@ def test_fused_dispatch_combine_roundtrip(cuda_device, world, T, E, K, H):
             A.moe_dispatch(ctxs[r], xs[r], routed[r][0], routed[r][1], phase=1)
         recvs = [A.moe_dispatch(ctxs[r], xs[r], routed[r][0], routed[r][1], phase=2) for r in range(world)]
         check_status()
+        for r in range(world):   # per-source splits as the receiver sees them
+            want = torch.stack([torch.bincount(routed[s][0].reshape(-1).long(), minlength=E)[r * (E // world):(r + 1) * (E // world)]
+                                for s in range(world)])
+            assert torch.equal(recvs[r][2].long(), want)
         # quantisation matches the torch statement on what rank 0 received from rank 1 (or itself)
         d, s = 0, world - 1
         rx, rs, splits = recvs[d]
         n = int(splits[s].sum())
-        rows = ctxs[s].routing.sorted_token.long()[int(ctxs[s].routing.cumsum[0]): int(ctxs[s].routing.cumsum[E // world])]
+        rt = MU.route(routed[s][0], E)
+        rows = rt.sorted_token.long()[int(rt.cumsum[0]): int(rt.cumsum[E // world])]
         q_ref, s_ref = A.quant_fp8_reference(xs[s][rows])
         mm = T * K
         torch.testing.assert_close(rs[s * mm: s * mm + n], s_ref, rtol=1e-6, atol=0)
         assert (rx[s * mm: s * mm + n].view(torch.uint8).int() - q_ref.view(torch.uint8).int()).abs().max() <= 1
         # identity experts
-        ys = [A.dequant_fp8(recvs[r][0], recvs[r][1]) for r in range(world)]
+        # identity experts: odd iterations write straight into the symmetric output buffer, even ones pass a tensor
+        if it & 1:
+            ys = [A.dequant_fp8(recvs[r][0], recvs[r][1], out=A.moe_expert_out_buffer(ctxs[r])) for r in range(world)]
+        else:
+            ys = [A.dequant_fp8(recvs[r][0], recvs[r][1]) for r in range(world)]
         outs = [None] * world
         for r in range(world):
             A.moe_combine(ctxs[r], ys[r], recvs[r][2], phase=1)
@@ -169,9 +178,59 @@ def test_fast_all_to_all_reports_a_destination_overflow(cuda_device):
     A.fast_all_to_all(ctxs[0], send, cums, None, phase=1)
     with pytest.raises(TdistError, match="bad argument"):
         check_status()
-    empty = torch.zeros(E + 1, dtype=torch.int32, device=cuda_device)
-    A.fast_all_to_all(ctxs[1], send[:0], empty, None, phase=1)
-    splits, recv, _ = A.fast_all_to_all(ctxs[1], send[:0], empty, None, phase=2)
+    empty = torch.zeros(E + 1, dtype=torch.int32, device=cuda_device)   # rank 1 sends nothing
+    A.fast_all_to_all(ctxs[1], send[:1], empty, None, phase=1)
+    splits, recv, _ = A.fast_all_to_all(ctxs[1], send[:1], empty, None, phase=2)
     check_status()
     assert splits[:epr].tolist() == [7, 1]          # clamped to the 8 rows that were sent
     assert torch.equal(recv[:max_m], send[2:2 + max_m])
+
+
+@pytest.mark.parametrize("world,T,E,K,H,align", [(2, 33, 8, 2, 256, 1), (4, 64, 32, 4, 512, 128), (8, 128, 256, 8, 1024, 128), (1, 50, 4, 3, 128, 16)])
+def test_ep_dispatch_compact_layout_and_pull_combine(cuda_device, world, T, E, K, H, align):
+    """Compact (expert-major) receive layout with block-aligned groups: every rank's rows sit where the gathered
+    counts say, the block -> expert table covers them, and the pull combine returns K x the input (identity
+    experts, plain sum). The (token, k) pairs of rank 1 include a dropped pair (id -1)."""
+    from triton_distributed_b200._lib import TdistError
+    from triton_distributed_b200.ops import moe_ep as EP
+    torch.manual_seed(world * 11 + T)
+    lw = LocalWorld(world, cuda_device)
+    ctxs = [EP.create_ep_context(T, H, K, E, r, world, quant=False, compact=True, align=align, heap=lw.heap(r), device=cuda_device)
+            for r in range(world)]
+    epr = E // world
+    for it in range(3):
+        xs = [torch.randn(T, H, device=cuda_device).to(torch.bfloat16) for _ in range(world)]
+        ids = [torch.randint(0, E, (T, K), dtype=torch.int32, device=cuda_device) for _ in range(world)]
+        dropped = world > 1 and it == 1
+        if dropped:
+            ids[1][5, 0] = -1
+        for phase in (1, 2):
+            for r in range(world):
+                EP.ep_dispatch(ctxs[r], xs[r], ids[r], None, phase=phase)
+        recv = [EP.ep_dispatch(ctxs[r], xs[r], ids[r], None, phase=4) for r in range(world)]
+        if dropped:
+            with pytest.raises(TdistError, match="bad argument"):
+                check_status()
+        else:
+            check_status()
+        for d in range(world):
+            rows, _, splits, num_recv = recv[d]
+            off, total = 0, 0
+            for le in range(epr):
+                e = d * epr + le
+                group = torch.cat([xs[s][(ids[s].reshape(-1) == e).nonzero().flatten() // K] for s in range(world)])
+                n = group.shape[0]
+                assert torch.equal(rows[off: off + n], group), (it, d, le)
+                nb = (n + align - 1) // align
+                assert (ctxs[d].block_expert[off // align: off // align + nb] == le).all()
+                off += nb * align
+                total += n
+            assert int(num_recv) == total and int(ctxs[d].num_blocks) == off // align
+        for r in range(world):
+            EP.expert_out_buffer(ctxs[r]).copy_(recv[r][0])     # identity experts, written in place
+            EP.ep_combine(ctxs[r], None, weighted=False, phase=1)
+        outs = [EP.ep_combine(ctxs[r], None, weighted=False, phase=2) for r in range(world)]
+        check_status()
+        for r in range(world):
+            live = (ids[r] >= 0).sum(-1, keepdim=True).float()
+            torch.testing.assert_close(outs[r].float(), xs[r].float() * live, atol=2e-2, rtol=2e-2)

@@ -16,6 +16,9 @@ from triton_distributed_b200.ops import gemm_fp8 as F8
 from triton_distributed_b200.runtime import check_status, finalize_distributed, initialize_distributed, symm_heap
 
 
+ITERS = 20   # fresh-data iterations per small shape (one context reused, as in serving)
+
+
 def main():
     group = initialize_distributed(seed=0)
     rank, world = dist.get_rank(), dist.get_world_size()
@@ -35,14 +38,16 @@ def main():
         heap.barrier()
 
     # ---------------- AG-GEMM ----------------
+    # on GPUs: tile-aligned, ragged (8-column partial tile, rows no multiple of 128), and two K >= 4096 problems that the
+    # launcher runs with the wide (256 x 512) pair tiling, one of them with a 200-column partial tile
     shapes = [(128, 256, 256), (999, 264, 520)] if cuda else [(128, 256, 256)]
     if cuda:
-        shapes.append((1024, 1024, 2048))
+        shapes += [(1024, 1024, 2048), (520, 1224, 4096), (256, 2048, 4160)]
     ag_err = 0.0
     for (mpr, n_per, K) in shapes:
         gen = torch.Generator(device="cpu").manual_seed(0)
         ctx = None
-        for it in range(3 if cuda else 1):
+        for it in range((ITERS if mpr * K <= 1 << 21 else 3) if cuda else 1):
             A_full = torch.randn(world * mpr, K, generator=gen)
             W_full = torch.randn(world * n_per, K, generator=gen) * (0.02 if not cuda else K ** -0.5)
             a = A_full[rank * mpr:(rank + 1) * mpr].to(dev, dtype).contiguous()
@@ -71,13 +76,13 @@ def main():
     res["ag_multicast_pusher"] = bool(cuda and ctx is not None and ctx.workspace is not None and ctx.workspace.mc is not None and (G.AG_NVLS == 2 or world >= 4))
 
     # ---------------- GEMM-RS ----------------
-    shapes = [(128, 256, 128), (250, 520, 264), (1024, 2048, 1024)] if cuda else [(128, 256, 128)]
+    shapes = [(128, 256, 128), (250, 520, 264), (1024, 2048, 1024), (300, 1224, 4096)] if cuda else [(128, 256, 128)]
     rs_err = 0.0
     for (mpr, N, k_loc) in shapes:
         gen = torch.Generator(device="cpu").manual_seed(0)
         M = world * mpr
         ctx = G.create_gemm_rs_context(M, N, rank, world, output_dtype=dtype, group=group, device=dev)
-        for it in range(3 if cuda else 1):
+        for it in range((ITERS if M * k_loc <= 1 << 21 else 3) if cuda else 1):
             X_full = torch.randn(M, world * k_loc, generator=gen)
             V_full = torch.randn(N, world * k_loc, generator=gen) * (0.02 if not cuda else (world * k_loc) ** -0.5)
             x = X_full[:, rank * k_loc:(rank + 1) * k_loc].to(dev, dtype).contiguous()

@@ -128,6 +128,35 @@ class A2AArgs(C.Structure):
     ]
 
 
+class MoeDispatchArgs(C.Structure):
+    _fields_ = [
+        ("x", C.c_void_p), ("topk_ids", C.c_void_p), ("slot_of", C.c_void_p), ("cumsum", C.c_void_p),
+        ("recv_peer", C.c_void_p * MAX_RANKS), ("scale_peer", C.c_void_p * MAX_RANKS),
+        ("counts_peer", C.c_void_p * MAX_RANKS), ("sig_peer", C.c_void_p * MAX_RANKS),
+        ("counters", C.c_void_p), ("pair_row", C.c_void_p), ("send_splits", C.c_void_p), ("recv_splits", C.c_void_p),
+        ("recv_offset", C.c_void_p), ("num_recv", C.c_void_p), ("block_expert", C.c_void_p), ("num_blocks", C.c_void_p),
+        ("ntok", C.c_int), ("topk", C.c_int), ("hidden", C.c_int), ("num_experts", C.c_int), ("world", C.c_int), ("rank", C.c_int),
+        ("max_m", C.c_int), ("quant", C.c_int), ("compact", C.c_int), ("align", C.c_int), ("phase", C.c_int), ("num_ctas", C.c_int),
+        ("epoch", C.c_uint64),
+        ("status", C.c_void_p),
+        ("timeout_ns", C.c_uint64),
+        ("stream", C.c_void_p),
+    ]
+
+
+class MoeCombineArgs(C.Structure):
+    _fields_ = [
+        ("buf_peer", C.c_void_p * MAX_RANKS), ("sig_peer", C.c_void_p * MAX_RANKS),
+        ("topk_ids", C.c_void_p), ("topk_w", C.c_void_p), ("pair_row", C.c_void_p), ("out", C.c_void_p),
+        ("ntok", C.c_int), ("topk", C.c_int), ("hidden", C.c_int), ("epr", C.c_int), ("world", C.c_int), ("rank", C.c_int),
+        ("phase", C.c_int), ("num_ctas", C.c_int),
+        ("epoch", C.c_uint64),
+        ("status", C.c_void_p),
+        ("timeout_ns", C.c_uint64),
+        ("stream", C.c_void_p),
+    ]
+
+
 class DecodeArgs(C.Structure):
     _fields_ = [
         ("q", C.c_void_p), ("k_cache", C.c_void_p), ("v_cache", C.c_void_p), ("block_table", C.c_void_p),
@@ -193,6 +222,8 @@ def _declare(lib):
     lib.tdist_p2p_copy.argtypes = [C.c_void_p, C.c_void_p, C.c_size_t, C.c_int, C.c_int, C.c_int, C.c_int,
                                    C.c_void_p, C.c_uint64, C.c_void_p]
     lib.tdist_a2a.argtypes = [C.POINTER(A2AArgs)]
+    lib.tdist_moe_dispatch.argtypes = [C.POINTER(MoeDispatchArgs)]
+    lib.tdist_moe_combine.argtypes = [C.POINTER(MoeCombineArgs)]
     lib.tdist_signal_op_on_stream.argtypes = [C.c_void_p, C.c_uint64, C.c_int, C.c_void_p]
     lib.tdist_signal_wait_on_stream.argtypes = [C.c_void_p, C.c_int, C.c_uint64, C.c_void_p, C.c_uint64, C.c_void_p]
     lib.tdist_primitive.argtypes = [C.POINTER(PrimArgs)]

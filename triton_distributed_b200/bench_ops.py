@@ -84,6 +84,16 @@ def _bench_gemm_family(args, world, rank, group, dev, dtype, pk, row):
         b = (torch.randn(npr, K, device=dev) * K ** -0.5).to(dtype)
         c = torch.empty(M, npr, device=dev, dtype=dtype)
         ctx = G.create_ag_gemm_intra_node_context(a, b, rank, world, max_M=M, group=group)
+        if getattr(args, "sweep_comm", ""):
+            # pusher-CTA count x tiling in one process (one heap and NCCL bring-up): extra rows before the default one
+            for pair in (1, 2):
+                for nc in (int(x) for x in args.sweep_comm.split(",")):
+                    G.CTA_PAIR, ctx.num_comm_sms = pair, nc
+                    t = timed_us(lambda: G.ag_gemm_intra_node(a, b, ctx, out=c), args.iters, args.warmup, world, group)
+                    if rank == 0:
+                        print(json.dumps({"op": "ag_gemm_sweep", "world": world, "m": M, "n": N, "k": K, "cta_pair": pair,
+                                          "num_comm_sms": nc, "us": round(t, 2)}), flush=True)
+            G.CTA_PAIR, ctx.num_comm_sms = args.cta_pair, 0
         us = timed_us(lambda: G.ag_gemm_intra_node(a, b, ctx, out=c), args.iters, args.warmup, world, group)
         flops = 2.0 * M * npr * K
         link_us = (world - 1) * mpr * K * 2 / (NVLINK_GBS * 1e3)
@@ -480,6 +490,7 @@ def main(argv=None) -> int:
     ap.add_argument("--dtype", default="bf16", choices=["bf16", "fp16"])
     ap.add_argument("--cta-pair", type=int, default=-1)
     ap.add_argument("--no-baseline", action="store_true")
+    ap.add_argument("--sweep-comm", default="", help="ag_gemm: comma-separated pusher-CTA counts to time under both pair tilings")
     ap.add_argument("--presleep-ms", type=float, default=-1.0,
                     help="spin the GPU this long before each timed loop (default: 30 ms for the latency ops, 0 for GEMMs)")
     args = ap.parse_args(argv)

@@ -63,7 +63,7 @@ typedef struct TdistGemmArgs {
     int num_comm_sms;  /* AG: CTAs that only push this rank's shard to the peers */
     int debug_delay_ns;/* AG: the pusher sleeps this long before every block (race hunting) */
     int group_m;       /* row-tiles per raster group (0 = default 8) */
-    int cta_pair;      /* -1 auto, 0 = one CTA per 128x256 tile, 1 = CTA pair per 256x256 tile */
+    int cta_pair;      /* -1 auto, 0 = one CTA per 128x256 tile, 1 = CTA pair per 256x256 tile, 2 = CTA pair per 256x512 tile */
     void* status;      /* device pointer of a TdistStatus, may be NULL */
     uint64_t timeout_ns;
     void* stream;
@@ -237,6 +237,58 @@ typedef struct TdistA2AArgs {
 
 int tdist_a2a(const TdistA2AArgs* args);
 int tdist_dequant_fp8(const void* x, const void* scale, void* out_bf16, int rows, int hidden, void* stream);
+
+/* ------------------------------------------------------------------ expert-parallel dispatch / combine (moe_ep.cu) */
+#define TDIST_MOE_ROUTE_IN_PLACE_MAX 8192   /* most (token, k) pairs the dispatch kernel routes by itself */
+
+typedef struct TdistMoeDispatchArgs {
+    const void* x;            /* [ntok, hidden] bf16 */
+    const void* topk_ids;     /* int32 [ntok * topk]; an id outside [0, num_experts) drops the pair and is reported */
+    const void* slot_of;      /* optional routing done beforehand (tdist_moe_route), for more pairs than the kernel */
+    const void* cumsum;       /*   routes in place: sorted position of each pair, prefix sum of the counts [E + 1] */
+    void* recv_peer[TDIST_MAX_RANKS];    /* receive rows of every rank as mapped here (this call's parity) */
+    void* scale_peer[TDIST_MAX_RANKS];   /* quant: fp32 [rows, hidden / 128] beside them */
+    void* counts_peer[TDIST_MAX_RANKS];  /* int32 [world(src)][num_experts], this call's parity */
+    void* sig_peer[TDIST_MAX_RANKS];     /* uint64 [2 * world]: data flags [0, world), count flags [world, 2 world) */
+    void* counters;           /* uint32 [2], local, zero before the first call */
+    void* pair_row;           /* out int32 [ntok * topk]: row of each pair in its destination's buffer, -1 = dropped */
+    void* send_splits;        /* out int32 [num_experts]: pairs of this rank per expert */
+    void* recv_splits;        /* out int32 [world, experts_per_rank]: rows each source sent to my experts */
+    void* recv_offset;        /* out int32 [experts_per_rank, world] (compact): first row of each (expert, source) group */
+    void* num_recv;           /* out int32 [1]: rows received in all */
+    void* block_expert;       /* out int32 [max_m / align], optional (compact): local expert of each block of `align` rows */
+    void* num_blocks;         /* out int32 [1], optional (compact): blocks in use */
+    int ntok, topk, hidden, num_experts, world, rank;
+    int max_m;     /* slots: rows per source slot; compact: capacity of the receive buffer in rows */
+    int quant;     /* 1 = rows travel as fp8 e4m3 with one fp32 scale per 128 values, 0 = as bf16 */
+    int compact;   /* 0 = per-source slots [world][max_m], 1 = rows grouped by (local expert, source) back to back */
+    int align;     /* compact: every expert's group starts on a multiple of this many rows (0/1 = dense, 128 = grouped GEMM) */
+    int phase;     /* bit 0 publish counts (compact), bit 1 route + send + flag, bit 2 wait for every source; 0 = all */
+    int num_ctas;  /* 0 = sized from the work */
+    uint64_t epoch;           /* call number, > 0, the same on every rank */
+    void* status;
+    uint64_t timeout_ns;
+    void* stream;
+} TdistMoeDispatchArgs;
+
+typedef struct TdistMoeCombineArgs {
+    void* buf_peer[TDIST_MAX_RANKS];   /* expert outputs [rows, hidden] bf16 of every rank as mapped here */
+    void* sig_peer[TDIST_MAX_RANKS];   /* uint64 [world]: "my outputs are in place" flags */
+    const void* topk_ids;     /* int32 [ntok * topk] */
+    const void* topk_w;       /* fp32 [ntok * topk] or NULL (plain sum) */
+    const void* pair_row;     /* from the matching dispatch */
+    void* out;                /* [ntok, hidden] bf16 */
+    int ntok, topk, hidden, epr, world, rank;
+    int phase;                /* bit 0 announce, bit 1 wait + gather; 0 = both */
+    int num_ctas;
+    uint64_t epoch;
+    void* status;
+    uint64_t timeout_ns;
+    void* stream;
+} TdistMoeCombineArgs;
+
+int tdist_moe_dispatch(const TdistMoeDispatchArgs* args);
+int tdist_moe_combine(const TdistMoeCombineArgs* args);
 
 /* ------------------------------------------------------------------ MoE routing */
 /* An expert id outside [0, num_experts) (e.g. -1 for a dropped pair) is left out of the counts and of the sort

@@ -15,14 +15,22 @@
 //          (python/triton_dist/kernels/nvidia/gemm_reduce_scatter.py:104-232,482-538 and
 //          reduce_scatter.py:527-685), where scatter and reduction are separate streams.
 //
-// Two tilings of the same kernel body:
-//   CTAS = 1  one CTA computes a 128 x 256 tile (tcgen05.mma cta_group::1), 4 TMA stages of 48 KB.
-//   CTAS = 2  a cluster of two CTAs computes a 256 x 256 tile (cta_group::2): each CTA loads its own
-//             128 rows of A and its own half (128 rows) of the B tile, the leader CTA issues the MMAs
-//             for both, 6 stages of 32 KB per CTA. B is read from L2 once per pair, which is what
-//             lifts the kernel to library-GEMM speed. No TMA load here uses cluster multicast.
-// In both, K advances 64 elements per stage and the fp32 accumulators are double-buffered in TMEM
-// (2 x 256 columns) so the epilogue of tile i overlaps the main loop of tile i+1.
+// Three tilings of the same kernel body:
+//   CTAS = 1        one CTA computes a 128 x 256 tile (tcgen05.mma cta_group::1), 4 TMA stages of 48 KB.
+//   CTAS = 2        a cluster of two CTAs computes a 256 x 256 tile (cta_group::2): each CTA loads its own
+//                   128 rows of A and its own half (128 rows) of the B tile, the leader CTA issues the MMAs
+//                   for both, 6 stages of 32 KB per CTA. B is read from L2 once per pair.
+//   CTAS = 2, WIDE  the pair computes a 256 x 512 tile as two 256 x 256 halves that share the A rows: per
+//                   K block each CTA loads 16 KB of A and 2 x 16 KB of B (4 stages of 48 KB) for twice the
+//                   MMA work, so a quarter less operand traffic from L2 into shared memory per FLOP and a
+//                   quarter less shared-memory write bandwidth beside the tensor core's own operand reads.
+//                   The two halves fill all 512 TMEM columns: the epilogue of a tile overlaps the next main
+//                   loop only half by half (each half has its own full / empty barrier), which long-K
+//                   problems do not notice. When the last round of tiles would leave at least half of the
+//                   CTA pairs idle, its tiles are split into their 256 x 256 halves.
+// No TMA load here uses cluster multicast. K advances 64 elements per stage; the fp32 accumulators live in two
+// TMEM slots of 256 columns: narrow tiles alternate between them so that the epilogue of tile i overlaps the
+// main loop of tile i+1, a wide tile takes both.
 // Warp roles (192 threads): warp 0 = TMA producer, warp 1 = MMA issuer and TMEM owner,
 // warps 2..5 = epilogue (TMEM -> registers -> swizzled smem -> TMA store).
 #include <cuda.h>
@@ -54,12 +62,14 @@ constexpr int TMEM_COLS = 512;
 constexpr int DEFAULT_GROUP_M = 8;
 constexpr int MAX_STAGES = 6;
 
-template <int CTAS>
+template <int CTAS, bool WIDE = false>
 struct Tiling {
-    static constexpr int B_ROWS = BN / CTAS;              // rows of the B tile this CTA loads
+    static_assert(!WIDE || CTAS == 2, "the wide tiling is a CTA-pair tiling");
+    static constexpr int HALVES = WIDE ? 2 : 1;           // 256-column halves of a tile
+    static constexpr int B_ROWS = BN / CTAS;              // rows of one half of the B tile this CTA loads
     static constexpr int B_BYTES = B_ROWS * BK * 2;
-    static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
-    static constexpr int STAGES = PIPE_BYTES / STAGE_BYTES;  // 4 or 6
+    static constexpr int STAGE_BYTES = A_BYTES + HALVES * B_BYTES;
+    static constexpr int STAGES = PIPE_BYTES / STAGE_BYTES;  // 4, 6 or 4
     static_assert(STAGES <= MAX_STAGES, "barrier area too small");
 };
 
@@ -88,7 +98,8 @@ struct GemmParams {
     int world, rank;
     int seg_m_tiles, n_tiles, k_blocks;
     int seg_blocks;  // 128-row blocks per segment (flag granularity)
-    int num_tiles;
+    int num_tiles;   // work items of the schedule: 256-column tiles, or 512-column tiles (wide tiling)
+    int n_pairs;     // wide tiling: 512-column tiles per row of tiles = ceil(n_tiles / 2)
     int num_comm;
     int group_m;
     int is_f16;
@@ -143,6 +154,60 @@ __device__ __forceinline__ TileCoord decode_tile(int t, int first_seg, int world
     c.n_tile = r / gsize;
     c.m_in_seg = first_m + (r - c.n_tile * gsize);
     return c;
+}
+
+// One unit of work of a CTA (CTAS == 1) or a CTA pair: `halves` neighbouring 256-column tiles of one row of tiles.
+struct Work {
+    int seg, m_in_seg, n_tile, halves;
+};
+
+// Static schedule: unit u of num_units takes item u + round * num_units. Narrow tilings: an item is one 256-column
+// tile. Wide tiling: an item is a pair of neighbouring 256-column tiles (the odd last tile of a row stands alone);
+// when the last, partial round holds at most num_units / 2 items, each of them is split into its halves, which go to
+// two units, so that the round takes half as long. Returns false once the unit has nothing left.
+template <bool WIDE>
+__device__ __forceinline__ bool get_work(const GemmParams& p, int unit, int num_units, int round, int first_seg, Work& w) {
+    if (!WIDE) {
+        const int t = unit + round * num_units;
+        if (t >= p.num_tiles) return false;
+        const TileCoord tc = decode_tile(t, first_seg, p.world, p.seg_m_tiles, p.n_tiles, p.group_m);
+        w.seg = tc.seg;
+        w.m_in_seg = tc.m_in_seg;
+        w.n_tile = tc.n_tile;
+        w.halves = 1;
+        return true;
+    }
+    const int full_rounds = p.num_tiles / num_units;
+    const int rem = p.num_tiles - full_rounds * num_units;
+    int t, half = -1;
+    if (round < full_rounds) {
+        t = unit + round * num_units;
+    } else if (round > full_rounds || rem == 0) {
+        return false;
+    } else if (2 * rem <= num_units) {
+        if (unit >= 2 * rem) return false;
+        t = full_rounds * num_units + (unit >> 1);
+        half = unit & 1;
+    } else {
+        if (unit >= rem) return false;
+        t = full_rounds * num_units + unit;
+    }
+    const TileCoord tc = decode_tile(t, first_seg, p.world, p.seg_m_tiles, p.n_pairs, p.group_m);
+    w.seg = tc.seg;
+    w.m_in_seg = tc.m_in_seg;
+    w.n_tile = 2 * tc.n_tile;
+    w.halves = (w.n_tile + 1 < p.n_tiles) ? 2 : 1;
+    if (half >= 0) {
+        if (half >= w.halves) return false;
+        w.n_tile += half;
+        w.halves = 1;
+    }
+    return true;
+}
+
+// TMEM slot (256 accumulator columns) of half `h` of a work item: a wide item takes both slots, narrow items alternate.
+__device__ __forceinline__ uint32_t slot_of_half(const Work& w, int h, uint32_t next_narrow) {
+    return w.halves == 2 ? static_cast<uint32_t>(h) : next_narrow;
 }
 
 // ------------------------------------------------------------------------------------------
@@ -326,9 +391,10 @@ __device__ __forceinline__ void rs_reduce_tile(const GemmParams& p, int block, i
 // GATHER (PLAIN, one CTA per tile): four extra warps (threads 192..319) copy the A rows by index with cp.async,
 // warp 0 then only issues the TMA loads of B.
 constexpr int GATHER_THREADS = THREADS + 128;
-template <int MODE, int CTAS, bool GATHER = false>
+template <int MODE, int CTAS, bool GATHER = false, bool WIDE = false>
 __global__ void __launch_bounds__(GATHER ? GATHER_THREADS : THREADS, 1) gemm_sm100_kernel(const __grid_constant__ GemmParams p) {
-    using T = Tiling<CTAS>;
+    using T = Tiling<CTAS, WIDE>;
+    static_assert(!(GATHER && WIDE), "the row-gathering producer feeds narrow tiles");
     constexpr int STAGES = T::STAGES;
     constexpr int STAGE_BYTES = T::STAGE_BYTES;
     extern __shared__ uint8_t smem_raw[];
@@ -494,8 +560,8 @@ __global__ void __launch_bounds__(GATHER ? GATHER_THREADS : THREADS, 1) gemm_sm1
             unsigned long long waited = 0, blocked = 0;
             if (tr) tr[0] = globaltimer_ns();
             const int live_blocks = p.num_m_blocks ? *p.num_m_blocks : 0x7fffffff;
-            for (int t = unit; t < p.num_tiles; t += num_units) {
-                const TileCoord tc = decode_tile(t, first_seg, p.world, p.seg_m_tiles, p.n_tiles, p.group_m);
+            Work tc;
+            for (int round = 0; get_work<WIDE>(p, unit, num_units, round, first_seg, tc); ++round) {
                 if (tc.m_in_seg * CTAS >= live_blocks) continue;  // padding tile of a grouped GEMM: every role skips it
                 const int block = tc.m_in_seg * CTAS + cta_rank;  // 128-row block inside the segment
                 const int bz = p.expert_ids ? p.expert_ids[block] : 0;
@@ -518,6 +584,7 @@ __global__ void __launch_bounds__(GATHER ? GATHER_THREADS : THREADS, 1) gemm_sm1
                 }
                 const int row = block * BM;
                 const int col = tc.n_tile * BN + cta_rank * T::B_ROWS;
+                const uint32_t stage_tx = A_BYTES + tc.halves * T::B_BYTES;
                 for (int kb = 0; kb < p.k_blocks; ++kb, ++it) {
                     const uint32_t s = it % STAGES;
                     mbar_wait(bar_empty(s), ((it / STAGES) & 1u) ^ 1u, p.wctx, 2);
@@ -528,10 +595,12 @@ __global__ void __launch_bounds__(GATHER ? GATHER_THREADS : THREADS, 1) gemm_sm1
                         tma_load_3d(sa + A_BYTES, &p.tm_b, bar_full(s), kb * BK, col, bz);
                     } else {
                         // both CTAs' bytes are counted on the leader's barrier
-                        if (cta_rank == 0) mbar_expect_tx(bar_full(s), 2 * STAGE_BYTES);
+                        if (cta_rank == 0) mbar_expect_tx(bar_full(s), 2 * stage_tx);
                         const uint32_t leader_full = mapa_u32(bar_full(s), 0);
                         tma_load_3d_pair(sa, am, leader_full, kb * BK, row, az);
                         tma_load_3d_pair(sa + A_BYTES, &p.tm_b, leader_full, kb * BK, col, bz);
+                        if (WIDE && tc.halves == 2)
+                            tma_load_3d_pair(sa + A_BYTES + T::B_BYTES, &p.tm_b, leader_full, kb * BK, col + BN, bz);
                     }
                 }
             }
@@ -547,35 +616,47 @@ __global__ void __launch_bounds__(GATHER ? GATHER_THREADS : THREADS, 1) gemm_sm1
         if (lane == 0 && cta_rank == 0) {
             const uint32_t idesc = umma_idesc(p.is_f16 ? 0u : 1u, p.is_f16 ? 0u : 1u, BM * CTAS, BN);
             uint32_t it = 0;
-            uint32_t local_tile = 0;
+            uint32_t uses0 = 0, uses1 = 0, next_narrow = 0;   // per-slot use counts give the barrier phases
             const int live_blocks = p.num_m_blocks ? *p.num_m_blocks : 0x7fffffff;
-            for (int t = unit; t < p.num_tiles; t += num_units) {
-                if (p.num_m_blocks != nullptr &&
-                    decode_tile(t, first_seg, p.world, p.seg_m_tiles, p.n_tiles, p.group_m).m_in_seg * CTAS >= live_blocks)
-                    continue;
-                const uint32_t buf = local_tile & 1u;
-                mbar_wait(bar_tempty(buf), ((local_tile >> 1) & 1u) ^ 1u, p.wctx, 3);
-                tc_fence_after();
-                const uint32_t d_tmem = tmem_base + buf * BN;
+            Work tc;
+            for (int round = 0; get_work<WIDE>(p, unit, num_units, round, first_seg, tc); ++round) {
+                if (tc.m_in_seg * CTAS >= live_blocks) continue;
                 for (int kb = 0; kb < p.k_blocks; ++kb, ++it) {
                     const uint32_t s = it % STAGES;
                     mbar_wait(bar_full(s), (it / STAGES) & 1u, p.wctx, 4);
                     tc_fence_after();
                     const uint32_t sa = smem_u32(smem + s * STAGE_BYTES);
                     const uint64_t adesc = umma_desc_k_sw128(sa);
-                    const uint64_t bdesc = umma_desc_k_sw128(sa + A_BYTES);
 #pragma unroll
-                    for (int k = 0; k < BK / UMMA_K; ++k) {
-                        // 16 elements of K = 32 bytes = 2 descriptor address units
-                        umma_bf16<CTAS>(d_tmem, adesc + 2 * k, bdesc + 2 * k, idesc, (kb | k) != 0 ? 1u : 0u);
+                    for (int h = 0; h < T::HALVES; ++h) {
+                        if (h < tc.halves) {
+                            const uint32_t slot = slot_of_half(tc, h, next_narrow);
+                            if (kb == 0) {
+                                // the epilogue has drained this slot's previous accumulator
+                                mbar_wait(bar_tempty(slot), (((slot ? uses1 : uses0)) & 1u) ^ 1u, p.wctx, 3);
+                                tc_fence_after();
+                            }
+                            const uint32_t d_tmem = tmem_base + slot * BN;
+                            const uint64_t bdesc = umma_desc_k_sw128(sa + A_BYTES + h * T::B_BYTES);
+#pragma unroll
+                            for (int k = 0; k < BK / UMMA_K; ++k) {
+                                // 16 elements of K = 32 bytes = 2 descriptor address units
+                                umma_bf16<CTAS>(d_tmem, adesc + 2 * k, bdesc + 2 * k, idesc, (kb | k) != 0 ? 1u : 0u);
+                            }
+                        }
                     }
                     // frees the smem stage (in both CTAs) when the MMAs retire
                     if (CTAS == 1) umma_commit(bar_empty(s));
                     else umma_commit_pair(bar_empty(s), 3);
                 }
-                if (CTAS == 1) umma_commit(bar_tfull(buf));  // accumulator ready
-                else umma_commit_pair(bar_tfull(buf), 3);
-                ++local_tile;
+                for (int h = 0; h < tc.halves; ++h) {
+                    const uint32_t slot = slot_of_half(tc, h, next_narrow);
+                    if (CTAS == 1) umma_commit(bar_tfull(slot));  // accumulator ready
+                    else umma_commit_pair(bar_tfull(slot), 3);
+                    if (slot) ++uses1;
+                    else ++uses0;
+                }
+                if (tc.halves == 1) next_narrow ^= 1u;
             }
         }
         __syncwarp();
@@ -585,85 +666,108 @@ __global__ void __launch_bounds__(GATHER ? GATHER_THREADS : THREADS, 1) gemm_sm1
         const int row_in_tile = q * 32 + lane;
         const bool issuer = (warp == 2 && lane == 0);
         uint8_t* cstage = smem + PIPE_BYTES;
-        uint32_t local_tile = 0;
+        uint32_t uses0 = 0, uses1 = 0, next_narrow = 0;   // same slot bookkeeping as the MMA issuer
+        // RS: the flag of a 256-column partial tile may only be raised once its stores have completed at the owner.
+        // Waiting for that right after issuing them would stall the epilogue for an NVLink round trip per tile, so
+        // the flag of a tile is published two tiles later, when `cp.async.bulk.wait_group 8` (all but the newest
+        // eight groups, i.e. the two younger tiles' four chunks each, are complete) costs nothing.
+        uint32_t* pend0 = nullptr;   // older
+        uint32_t* pend1 = nullptr;   // younger
         const int live_blocks = p.num_m_blocks ? *p.num_m_blocks : 0x7fffffff;
-        for (int t = unit; t < p.num_tiles; t += num_units) {
-            const TileCoord tc = decode_tile(t, first_seg, p.world, p.seg_m_tiles, p.n_tiles, p.group_m);
+        Work tc;
+        for (int round = 0; get_work<WIDE>(p, unit, num_units, round, first_seg, tc); ++round) {
             if (tc.m_in_seg * CTAS >= live_blocks) continue;
-            const uint32_t buf = local_tile & 1u;
-            mbar_wait(bar_tfull(buf), (local_tile >> 1) & 1u, p.wctx, 5);
-            tc_fence_after();
             const CUtensorMap* cm = (MODE == TDIST_GEMM_RS) ? &p.tm_c[tc.seg] : &p.tm_c[0];
             const int cz = (MODE == TDIST_GEMM_RS) ? p.rank : tc.seg;
             const int block = tc.m_in_seg * CTAS + cta_rank;
             const int row = block * BM;
-            const int col = tc.n_tile * BN;
+            for (int h = 0; h < tc.halves; ++h) {
+                const uint32_t buf = slot_of_half(tc, h, next_narrow);
+                mbar_wait(bar_tfull(buf), (buf ? uses1 : uses0) & 1u, p.wctx, 5);
+                tc_fence_after();
+                if (buf) ++uses1;
+                else ++uses0;
+                const int col = (tc.n_tile + h) * BN;
 #pragma unroll 1
-            for (int c = 0; c < BN / EPI_COLS; ++c) {
-                uint32_t r0[32], r1[32];
-                const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + buf * BN + c * EPI_COLS;
-                tmem_ld_32x32(taddr, r0);
-                tmem_ld_32x32(taddr + 32, r1);
-                tmem_ld_wait();
-                if (c == BN / EPI_COLS - 1) {
-                    // accumulator fully read: hand the TMEM buffer back to the MMA issuer
-                    tc_fence_before();
-                    __syncwarp();
-                    if (lane == 0) {
-                        if (CTAS == 1) mbar_arrive(bar_tempty(buf));
-                        else mbar_arrive_cluster(bar_tempty(buf), 0);
+                for (int c = 0; c < BN / EPI_COLS; ++c) {
+                    uint32_t r0[32], r1[32];
+                    const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + buf * BN + c * EPI_COLS;
+                    tmem_ld_32x32(taddr, r0);
+                    tmem_ld_32x32(taddr + 32, r1);
+                    tmem_ld_wait();
+                    if (c == BN / EPI_COLS - 1) {
+                        // accumulator fully read: hand the TMEM slot back to the MMA issuer
+                        tc_fence_before();
+                        __syncwarp();
+                        if (lane == 0) {
+                            if (CTAS == 1) mbar_arrive(bar_tempty(buf));
+                            else mbar_arrive_cluster(bar_tempty(buf), 0);
+                        }
                     }
-                }
-                uint8_t* cs = cstage + (c & 1) * EPI_BYTES;
-                named_barrier(1, 128);  // the store that last read this buffer has drained
-                uint8_t* rowp = cs + row_in_tile * 128;
-                const int sw = row_in_tile & 7;
+                    uint8_t* cs = cstage + (c & 1) * EPI_BYTES;
+                    named_barrier(1, 128);  // the store that last read this buffer has drained
+                    uint8_t* rowp = cs + row_in_tile * 128;
+                    const int sw = row_in_tile & 7;
 #pragma unroll
-                for (int j = 0; j < 4; ++j) {
-                    uint4 v0, v1;
-                    if (p.is_f16) {
-                        v0.x = pack_f16x2(__uint_as_float(r0[8 * j + 0]), __uint_as_float(r0[8 * j + 1]));
-                        v0.y = pack_f16x2(__uint_as_float(r0[8 * j + 2]), __uint_as_float(r0[8 * j + 3]));
-                        v0.z = pack_f16x2(__uint_as_float(r0[8 * j + 4]), __uint_as_float(r0[8 * j + 5]));
-                        v0.w = pack_f16x2(__uint_as_float(r0[8 * j + 6]), __uint_as_float(r0[8 * j + 7]));
-                        v1.x = pack_f16x2(__uint_as_float(r1[8 * j + 0]), __uint_as_float(r1[8 * j + 1]));
-                        v1.y = pack_f16x2(__uint_as_float(r1[8 * j + 2]), __uint_as_float(r1[8 * j + 3]));
-                        v1.z = pack_f16x2(__uint_as_float(r1[8 * j + 4]), __uint_as_float(r1[8 * j + 5]));
-                        v1.w = pack_f16x2(__uint_as_float(r1[8 * j + 6]), __uint_as_float(r1[8 * j + 7]));
-                    } else {
-                        v0.x = pack_bf16x2(__uint_as_float(r0[8 * j + 0]), __uint_as_float(r0[8 * j + 1]));
-                        v0.y = pack_bf16x2(__uint_as_float(r0[8 * j + 2]), __uint_as_float(r0[8 * j + 3]));
-                        v0.z = pack_bf16x2(__uint_as_float(r0[8 * j + 4]), __uint_as_float(r0[8 * j + 5]));
-                        v0.w = pack_bf16x2(__uint_as_float(r0[8 * j + 6]), __uint_as_float(r0[8 * j + 7]));
-                        v1.x = pack_bf16x2(__uint_as_float(r1[8 * j + 0]), __uint_as_float(r1[8 * j + 1]));
-                        v1.y = pack_bf16x2(__uint_as_float(r1[8 * j + 2]), __uint_as_float(r1[8 * j + 3]));
-                        v1.z = pack_bf16x2(__uint_as_float(r1[8 * j + 4]), __uint_as_float(r1[8 * j + 5]));
-                        v1.w = pack_bf16x2(__uint_as_float(r1[8 * j + 6]), __uint_as_float(r1[8 * j + 7]));
+                    for (int j = 0; j < 4; ++j) {
+                        uint4 v0, v1;
+                        if (p.is_f16) {
+                            v0.x = pack_f16x2(__uint_as_float(r0[8 * j + 0]), __uint_as_float(r0[8 * j + 1]));
+                            v0.y = pack_f16x2(__uint_as_float(r0[8 * j + 2]), __uint_as_float(r0[8 * j + 3]));
+                            v0.z = pack_f16x2(__uint_as_float(r0[8 * j + 4]), __uint_as_float(r0[8 * j + 5]));
+                            v0.w = pack_f16x2(__uint_as_float(r0[8 * j + 6]), __uint_as_float(r0[8 * j + 7]));
+                            v1.x = pack_f16x2(__uint_as_float(r1[8 * j + 0]), __uint_as_float(r1[8 * j + 1]));
+                            v1.y = pack_f16x2(__uint_as_float(r1[8 * j + 2]), __uint_as_float(r1[8 * j + 3]));
+                            v1.z = pack_f16x2(__uint_as_float(r1[8 * j + 4]), __uint_as_float(r1[8 * j + 5]));
+                            v1.w = pack_f16x2(__uint_as_float(r1[8 * j + 6]), __uint_as_float(r1[8 * j + 7]));
+                        } else {
+                            v0.x = pack_bf16x2(__uint_as_float(r0[8 * j + 0]), __uint_as_float(r0[8 * j + 1]));
+                            v0.y = pack_bf16x2(__uint_as_float(r0[8 * j + 2]), __uint_as_float(r0[8 * j + 3]));
+                            v0.z = pack_bf16x2(__uint_as_float(r0[8 * j + 4]), __uint_as_float(r0[8 * j + 5]));
+                            v0.w = pack_bf16x2(__uint_as_float(r0[8 * j + 6]), __uint_as_float(r0[8 * j + 7]));
+                            v1.x = pack_bf16x2(__uint_as_float(r1[8 * j + 0]), __uint_as_float(r1[8 * j + 1]));
+                            v1.y = pack_bf16x2(__uint_as_float(r1[8 * j + 2]), __uint_as_float(r1[8 * j + 3]));
+                            v1.z = pack_bf16x2(__uint_as_float(r1[8 * j + 4]), __uint_as_float(r1[8 * j + 5]));
+                            v1.w = pack_bf16x2(__uint_as_float(r1[8 * j + 6]), __uint_as_float(r1[8 * j + 7]));
+                        }
+                        // 16-byte chunk index inside the 128-byte row, XOR-swizzled with the row
+                        *reinterpret_cast<uint4*>(rowp + ((j ^ sw) << 4)) = v0;
+                        *reinterpret_cast<uint4*>(rowp + (((4 + j) ^ sw) << 4)) = v1;
                     }
-                    // 16-byte chunk index inside the 128-byte row, XOR-swizzled with the row
-                    *reinterpret_cast<uint4*>(rowp + ((j ^ sw) << 4)) = v0;
-                    *reinterpret_cast<uint4*>(rowp + (((4 + j) ^ sw) << 4)) = v1;
+                    fence_proxy_async_smem();
+                    named_barrier(1, 128);  // the staging buffer is complete
+                    if (issuer) {
+                        if (col + c * EPI_COLS < p.n && row < p.m_per_rank)
+                            tma_store_3d(cm, smem_u32(cs), col + c * EPI_COLS, row, cz);
+                        // One group per chunk even when the chunk lies outside the matrix and stores
+                        // nothing: "at most one group pending" below then always means that the store
+                        // which last read the OTHER staging buffer (two chunks back) has drained, and the
+                        // flag scheme below can count four groups per 256-column tile.
+                        bulk_commit();
+                        bulk_wait_read<1>();
+                    }
                 }
-                fence_proxy_async_smem();
-                named_barrier(1, 128);  // the staging buffer is complete
-                if (issuer) {
-                    if (col + c * EPI_COLS < p.n && row < p.m_per_rank)
-                        tma_store_3d(cm, smem_u32(cs), col + c * EPI_COLS, row, cz);
-                    // One group per chunk even when the chunk lies outside the matrix and stores
-                    // nothing: "at most one group pending" below then always means that the store
-                    // which last read the OTHER staging buffer (two chunks back) has drained.
-                    bulk_commit();
-                    bulk_wait_read<1>();
+                if (MODE == TDIST_GEMM_RS && issuer) {
+                    if (pend0 != nullptr) {
+                        // the tile two back is complete at its owner: order its (async-proxy) writes before the
+                        // system-scope release store of its flag
+                        bulk_wait<2 * (BN / EPI_COLS)>();
+                        fence_proxy_async();
+                        fence_acq_rel_sys();
+                        st_release_sys_u32(pend0, p.epoch);
+                    }
+                    pend0 = pend1;
+                    pend1 = p.flags_peer[tc.seg] + (block * p.n_tiles + tc.n_tile + h) * p.world + p.rank;
                 }
             }
-            if (MODE == TDIST_GEMM_RS && issuer) {
-                // The partial tile has to be complete at its owner before the flag is.
-                bulk_wait<0>();
-                fence_proxy_async();
-                fence_acq_rel_sys();
-                st_release_sys_u32(p.flags_peer[tc.seg] + (block * p.n_tiles + tc.n_tile) * p.world + p.rank, p.epoch);
-            }
-            ++local_tile;
+            if (tc.halves == 1) next_narrow ^= 1u;
+        }
+        if (MODE == TDIST_GEMM_RS && issuer && (pend0 != nullptr || pend1 != nullptr)) {
+            bulk_wait<0>();
+            fence_proxy_async();
+            fence_acq_rel_sys();
+            if (pend0 != nullptr) st_release_sys_u32(pend0, p.epoch);
+            if (pend1 != nullptr) st_release_sys_u32(pend1, p.epoch);
         }
         if (issuer) bulk_wait<0>();
         __syncwarp();
@@ -712,28 +816,41 @@ static bool use_pair(const TdistGemmArgs* a) {
     return a->m_per_rank > BM;  // a second CTA would only compute padding otherwise
 }
 
+// The wide tiling pays when the main loop of a 256 x 512 tile is long against its epilogue, which only
+// overlaps the next tile half by half: from K = 4096 on, and only where a row of tiles has a pair to form.
+static bool use_wide(const TdistGemmArgs* a) {
+    if (!use_pair(a)) return false;
+    if (a->cta_pair == 2) return true;
+    if (a->cta_pair == 1) return false;
+    return a->k >= 4096 && a->n > BN;
+}
+
 struct GridPlan {
-    int ctas_per_tile, num_comm, num_tiles, grid;
+    int ctas_per_tile, wide, num_comm, num_tiles, grid;
 };
 
-template <int CTAS>
+template <int CTAS, bool WIDE>
 static const void* kernel_for(int mode) {
     switch (mode) {
-        case TDIST_GEMM_PLAIN: return reinterpret_cast<const void*>(&gemm_sm100_kernel<TDIST_GEMM_PLAIN, CTAS>);
-        case TDIST_GEMM_AG: return reinterpret_cast<const void*>(&gemm_sm100_kernel<TDIST_GEMM_AG, CTAS>);
-        default: return reinterpret_cast<const void*>(&gemm_sm100_kernel<TDIST_GEMM_RS, CTAS>);
+        case TDIST_GEMM_PLAIN: return reinterpret_cast<const void*>(&gemm_sm100_kernel<TDIST_GEMM_PLAIN, CTAS, false, WIDE>);
+        case TDIST_GEMM_AG: return reinterpret_cast<const void*>(&gemm_sm100_kernel<TDIST_GEMM_AG, CTAS, false, WIDE>);
+        default: return reinterpret_cast<const void*>(&gemm_sm100_kernel<TDIST_GEMM_RS, CTAS, false, WIDE>);
     }
+}
+static const void* kernel_of(int ctas, int wide, int mode) {
+    if (ctas == 1) return kernel_for<1, false>(mode);
+    return wide ? kernel_for<2, true>(mode) : kernel_for<2, false>(mode);
 }
 
 // CTAs of this kernel that can be resident at once on the current device (all of them wait on
 // one another through flags, so the grid must never exceed this). Cached per device/variant.
-static int resident_ctas(int ctas, int mode) {
-    static int cache[64][2][3] = {};
+static int resident_ctas(int ctas, int wide, int mode) {
+    static int cache[64][3][3] = {};
     int dev = 0;
     if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return tdist_host::sm_count();
-    int& slot = cache[dev][ctas - 1][mode];
+    int& slot = cache[dev][ctas - 1 + wide][mode];
     if (slot > 0) return slot;
-    const void* fn = ctas == 2 ? kernel_for<2>(mode) : kernel_for<1>(mode);
+    const void* fn = kernel_of(ctas, wide, mode);
     int result = 0;
     if (cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES) == cudaSuccess) {
         if (ctas == 2) {
@@ -763,13 +880,21 @@ static int resident_ctas(int ctas, int mode) {
     return result;
 }
 
+// Length of the schedule in rounds of 256-column tiles (a round of wide items counts two): what get_work() deals out.
+static int schedule_cost(int items, int units, int wide) {
+    if (!wide) return (items + units - 1) / units;
+    const int full = items / units, rem = items - full * units;
+    return 2 * full + (rem == 0 ? 0 : (2 * rem <= units ? 1 : 2));
+}
+
 static GridPlan plan_grid(const TdistGemmArgs* a) {
     GridPlan g;
     g.ctas_per_tile = use_pair(a) ? 2 : 1;
+    g.wide = use_wide(a) ? 1 : 0;
     const int seg_m_tiles = (a->m_per_rank + BM * g.ctas_per_tile - 1) / (BM * g.ctas_per_tile);
     const int n_tiles = (a->n + BN - 1) / BN;
-    g.num_tiles = seg_m_tiles * n_tiles * a->world;
-    const int capacity = resident_ctas(g.ctas_per_tile, a->mode);
+    g.num_tiles = seg_m_tiles * (g.wide ? (n_tiles + 1) / 2 : n_tiles) * a->world;
+    const int capacity = resident_ctas(g.ctas_per_tile, g.wide, a->mode);
     int sms = a->num_sms > 0 ? a->num_sms : capacity;
     if (sms > capacity) sms = capacity;
     if (g.ctas_per_tile == 2) sms &= ~1;
@@ -791,14 +916,14 @@ static GridPlan plan_grid(const TdistGemmArgs* a) {
             need = (need + 1) & ~1;
             if (need < 2) need = 2;
             if (need > 18) need = 18;
-            // then the count in [need, need + 8] that leaves the GEMM side the fewest waves (the smallest such)
-            int best = need, best_waves = 1 << 30;
+            // then the count in [need, need + 8] that leaves the GEMM side the shortest schedule (the smallest such)
+            int best = need, best_cost = 1 << 30;
             for (int c = need; c <= need + 8; c += 2) {
                 const int units = (sms - c) / g.ctas_per_tile;
                 if (units < 1) break;
-                const int waves = (g.num_tiles + units - 1) / units;
-                if (waves < best_waves) {
-                    best_waves = waves;
+                const int cost = schedule_cost(g.num_tiles, units, g.wide);
+                if (cost < best_cost) {
+                    best_cost = cost;
                     best = c;
                 }
             }
@@ -809,7 +934,9 @@ static GridPlan plan_grid(const TdistGemmArgs* a) {
         if (g.num_comm < g.ctas_per_tile) g.num_comm = g.ctas_per_tile;
     }
     int units = (sms - g.num_comm) / g.ctas_per_tile;
-    if (units > g.num_tiles) units = g.num_tiles;
+    // a wide schedule may split its last round in two: allow up to twice the items
+    const int most = g.wide ? 2 * g.num_tiles : g.num_tiles;
+    if (units > most) units = most;
     if (units < 1) units = 1;
     g.grid = units * g.ctas_per_tile + g.num_comm;
     return g;
@@ -903,6 +1030,7 @@ extern "C" int tdist_gemm_run(const TdistGemmArgs* a) {
     p.seg_blocks = (a->m_per_rank + BM - 1) / BM;
     p.seg_m_tiles = (a->m_per_rank + BM * ctas - 1) / (BM * ctas);
     p.n_tiles = (a->n + BN - 1) / BN;
+    p.n_pairs = (p.n_tiles + 1) / 2;
     p.k_blocks = (a->k + BK - 1) / BK;
     p.is_f16 = a->dtype == TDIST_F16;
     p.epoch = a->epoch;
@@ -931,7 +1059,7 @@ extern "C" int tdist_gemm_run(const TdistGemmArgs* a) {
     }
 
     cudaStream_t stream = static_cast<cudaStream_t>(a->stream);
-    const void* fn = ctas == 2 ? kernel_for<2>(a->mode) : kernel_for<1>(a->mode);  // smem opt-in done by resident_ctas()
+    const void* fn = kernel_of(ctas, plan.wide, a->mode);  // smem opt-in done by resident_ctas()
     int block_threads = THREADS;
     if (a->a_gather != nullptr) {
         fn = reinterpret_cast<const void*>(&gemm_sm100_kernel<TDIST_GEMM_PLAIN, 1, true>);

@@ -5,8 +5,8 @@ from __future__ import annotations
 import torch
 import torch.nn.functional as F
 
-from ..ops import all_to_all as A
 from ..ops import gemm as G
+from ..ops import moe_ep as EP
 from ..ops import moe_tp as MT
 from ..ops import moe_utils as MU
 
@@ -43,9 +43,14 @@ class TPMLP:
 
 
 class EPMoE:
-    """Expert-parallel MoE feed-forward: route -> fp8 dispatch -> per-expert ``act(x W1^T) W2^T`` as two
-    grouped tcgen05 GEMMs over the received rows -> weighted combine. ``w1`` ``[E/ws, ffn, hidden]``,
-    ``w2`` ``[E/ws, hidden, ffn]`` are this rank's experts; ``gate`` ``[E, hidden]`` is replicated."""
+    """Expert-parallel MoE feed-forward: gate -> softmax top-k -> dispatch -> per-expert ``act(x W1^T) W2^T`` as two
+    grouped tcgen05 GEMMs -> weighted combine. ``w1`` ``[E/ws, ffn, hidden]``, ``w2`` ``[E/ws, hidden, ffn]`` are this
+    rank's experts; ``gate`` ``[E, hidden]`` is replicated.
+
+    The dispatch kernel writes the received rows grouped by local expert with every group starting on a 128-row
+    boundary, together with the expert of every 128-row block, so the receive buffer is the A operand of the
+    grouped GEMM as it stands; the second GEMM writes into the symmetric buffer the combine kernels of the source
+    ranks read. Five launches (top-k, dispatch, GEMM, activation, GEMM) + combine, no host synchronisation."""
 
     def __init__(self, gate: torch.Tensor, w1: torch.Tensor, w2: torch.Tensor, topk: int, rank: int, world: int, max_tokens: int,
                  group=None, heap=None):
@@ -53,51 +58,35 @@ class EPMoE:
         self.E = gate.shape[0]
         self.epr = self.E // world
         self.hidden = gate.shape[1]
-        self.ctx = A.create_moe_dispatch_context(max_tokens, self.hidden, topk, self.E, rank, world, heap=heap, group=group,
-                                                 device=gate.device)
+        self.ctx = EP.create_ep_context(max_tokens, self.hidden, topk, self.E, rank, world, quant=False, compact=True,
+                                        align=MT.GROUP_BLOCK_M, heap=heap, group=group, device=gate.device)
 
-    def experts(self, rx: torch.Tensor, rs: torch.Tensor, splits: torch.Tensor) -> torch.Tensor:
-        """Run this rank's experts over the receive layout ``[ws*max_m, hidden]`` (rows of source s sorted
-        by local expert inside slot s) and return outputs in the same layout."""
-        W, mm = self.world, self.ctx.dispatch.max_m
-        x = A.dequant_fp8(rx, rs)
-        # every (source, local expert) run of rows is one group; pad groups to 128 rows for the grouped GEMM
-        sp = splits.reshape(W, self.epr)
-        ids = torch.full((W * mm,), -1, dtype=torch.int32, device=x.device)
-        live_rows, expert_of_row = [], []
-        counts = sp.tolist()
-        for s in range(W):
-            off = s * mm
-            for e in range(self.epr):
-                n = counts[s][e]
-                if n:
-                    live_rows.append(torch.arange(off, off + n, device=x.device))
-                    expert_of_row.append(torch.full((n,), e, dtype=torch.int32, device=x.device))
-                    off += n
-        if not live_rows:
-            return torch.zeros_like(x)
-        rows = torch.cat(live_rows)
-        eids = torch.cat(expert_of_row).view(-1, 1)
-        sorted_ids, expert_ids, _, _, post_pad = MU.sort_topk_ids_align_block_size(eids, self.epr, 1, eids.shape[0], 128)
-        n = int(post_pad)
-        index = sorted_ids[:n].clone()
-        live = index < rows.shape[0]
-        index[live] = rows[index[live].long()].to(torch.int32)
-        index[~live] = -1
-        a_sorted, _ = MT.gather_rows(x, index, 1, W * mm)
-        nb = (post_pad // 128).to(torch.int32)
-        h = MT.group_gemm(a_sorted, self.w1, expert_ids, nb)
-        h = F.silu(h)
-        y_sorted = MT.group_gemm(h, self.w2, expert_ids, nb)
-        out = torch.zeros_like(x)
-        out[index[live].long()] = y_sorted[live]
-        return out
+    def experts(self, rows: torch.Tensor, out: torch.Tensor = None) -> torch.Tensor:
+        """This rank's experts over the dispatched rows (``[capacity, hidden]``, block-aligned groups)."""
+        h = MT.group_gemm(rows, self.w1, self.ctx.block_expert, self.ctx.num_blocks)
+        return MT.group_gemm(F.silu(h), self.w2, self.ctx.block_expert, self.ctx.num_blocks, out=out)
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         logits = x.float() @ self.gate.float().t()
         ids, w = MU.topk_softmax(logits, self.topk, renormalize=True)
-        rx, rs, splits = A.moe_dispatch(self.ctx, x, ids, w)
-        y = self.experts(rx, rs, splits)
-        return A.moe_combine(self.ctx, y, splits)
+        rows, _, _, _ = EP.ep_dispatch(self.ctx, x, ids, w)
+        if x.device.type != "cuda":
+            return EP.ep_combine(self.ctx, self._experts_cpu(rows), weighted=True)
+        self.experts(rows, out=EP.expert_out_buffer(self.ctx))
+        return EP.ep_combine(self.ctx, None, weighted=True)
+
+    def _experts_cpu(self, rows: torch.Tensor) -> torch.Tensor:
+        # CPU ranks (gloo): the same block-aligned layout, block by block
+        al = self.ctx.align
+        counts = self.ctx.recv_splits.sum(0)
+        out = torch.zeros_like(rows)
+        off = 0
+        for le in range(self.epr):
+            n = int(counts[le])
+            blk = slice(off, off + n)
+            hmid = F.silu((rows[blk].float() @ self.w1[le].float().t()).to(rows.dtype))
+            out[blk] = (hmid.float() @ self.w2[le].float().t()).to(rows.dtype)
+            off += (n + al - 1) // al * al
+        return out
 
     __call__ = forward

@@ -6,10 +6,9 @@ from __future__ import annotations
 
 import torch
 
-from ..ops import all_to_all as A
 from ..ops import collectives as CO
 from ..ops import flash_decode as FD
-from ..ops import moe_utils as MU
+from ..ops import moe_ep as EP
 from ..runtime import symm_heap
 
 
@@ -56,68 +55,56 @@ class AllGatherLayer:
 
 
 class EPAll2AllLayer:
-    """Expert-parallel token exchange: ``dispatch(input[T,hidden], exp_indices[T,topk])`` returns the
-    rows this rank's experts have to process, grouped by local expert and, inside an expert, by
-    source rank; ``combine(x)`` sends the processed rows back and sums each token's ``topk`` copies."""
+    """Expert-parallel token exchange (reference layers/nvidia/ep_a2a_layer.py:40-240).
+
+    ``dispatch(input[T,hidden], exp_indices[T,topk])`` returns the rows this rank's experts have to process, grouped
+    by local expert and, inside an expert, by source rank (each group in the source's token order);
+    ``combine(x)`` reads the processed rows back from their owners and sums each token's ``topk`` copies. Both are
+    one kernel launch (``csrc/kernels/moe_ep.cu``) and neither synchronises with the host: the receive buffer is
+    returned at its full capacity, ``num_recv`` (device int32 ``[1]``) says how many leading rows are live,
+    ``recv_splits`` ``[world, experts_per_rank]`` and ``recv_offset`` ``[experts_per_rank, world]`` describe the
+    groups. ``dispatch(..., exact=True)`` reads the count back and returns exactly ``[num_recv, hidden]`` like the
+    reference (one host synchronisation)."""
 
     def __init__(self, ep_group, max_tokens: int, hidden: int, topk: int, rank: int, num_tot_experts: int,
-                 local_world_size: int, world_size: int, dtype=torch.bfloat16, num_sm: int = 20, heap=None, device=None):
+                 local_world_size: int, world_size: int, dtype=torch.bfloat16, num_sm: int = 20, heap=None, device=None,
+                 capacity=None, align: int = 1):
+        if dtype != torch.bfloat16:
+            raise ValueError("the expert-parallel exchange moves bf16 rows")
         self.group, self.rank, self.world_size = ep_group, rank, world_size
         self.hidden, self.topk, self.num_experts = hidden, topk, num_tot_experts
         self.epr = num_tot_experts // world_size
-        self.max_m = max_tokens * topk
-        self.dtype = dtype
-        self.d_ctx = A.create_all_to_all_context(self.max_m, hidden, rank, num_tot_experts, world_size, self.epr, dtype=dtype,
-                                                 heap=heap, group=ep_group, device=device)
-        self.c_ctx = A.create_all_to_all_context(self.max_m, hidden, rank, num_tot_experts, world_size, self.epr, dtype=dtype,
-                                                 heap=heap, group=ep_group, device=device)
-        self._routing = None
-        self._ids = None
-        self._perm = None
-        self._splits = None
-        self._ntok = 0
+        self.ctx = EP.create_ep_context(max_tokens, hidden, topk, num_tot_experts, rank, world_size, quant=False, compact=True,
+                                        align=align, capacity=capacity, heap=heap, group=ep_group, device=device)
 
-    def dispatch(self, input: torch.Tensor, exp_indices: torch.Tensor, phase: int = 3):
-        T = input.shape[0]
-        if phase != 2:
-            self._ids = exp_indices.to(torch.int32).contiguous()
-            self._routing = MU.route(self._ids, self.num_experts)
-            self._ntok = T
-            self._send = input[self._routing.sorted_token.long()].contiguous()
-        splits, recv, _ = A.fast_all_to_all(self.d_ctx, self._send, self._routing.cumsum, None, phase=phase)
-        if phase == 1:
-            return None
-        # receive layout is [source rank][local expert]; regroup to [local expert][source rank]
-        W, epr, mm = self.world_size, self.epr, self.max_m
-        sp = splits.view(W, epr).long()
-        start_in_src = torch.cumsum(sp, 1) - sp                              # [W, epr] offset inside the source's slot
-        src_base = (torch.arange(W, device=sp.device) * mm).unsqueeze(1)
-        counts = sp.t().reshape(-1)                                          # (expert, src) order
-        starts = (src_base + start_in_src).t().reshape(-1)
-        total = int(counts.sum())
-        seg = torch.repeat_interleave(torch.arange(W * epr, device=sp.device), counts, output_size=total)
-        first = torch.cumsum(counts, 0) - counts
-        self._perm = starts[seg] + (torch.arange(total, device=sp.device) - first[seg])
-        self._splits = splits
-        return recv[self._perm]
+    @property
+    def num_recv(self) -> torch.Tensor:
+        return self.ctx.num_recv
 
-    def combine(self, x: torch.Tensor, phase: int = 3) -> torch.Tensor:
-        W, mm = self.world_size, self.max_m
-        if phase != 2:
-            # back to the receive layout, compacted source by source for the return trip
-            slots = torch.zeros((W * mm, self.hidden), dtype=x.dtype, device=x.device)
-            slots[self._perm] = x
-            per_src = self._splits.view(W, self.epr).sum(1).tolist()
-            self._back = torch.cat([slots[s * mm: s * mm + n] for s, n in enumerate(per_src)]) if sum(per_src) else slots[:0]
-            self._back_cums = torch.zeros(self.num_experts + 1, dtype=torch.int32, device=x.device)
-            self._back_cums[1:] = torch.cumsum(self._splits.reshape(-1), 0)
-        _s, back, _ = A.fast_all_to_all(self.c_ctx, self._back.contiguous(), self._back_cums, None, phase=phase)
-        if phase == 1:
+    @property
+    def recv_splits(self) -> torch.Tensor:
+        return self.ctx.recv_splits
+
+    @property
+    def recv_offset(self) -> torch.Tensor:
+        return self.ctx.recv_offset
+
+    def dispatch(self, input: torch.Tensor, exp_indices: torch.Tensor, phase: int = 7, exact: bool = False):
+        """``phase`` bits (emulated ranks run them one after the other): 1 publish counts, 2 send, 4 wait."""
+        recv, _, _, num_recv = EP.ep_dispatch(self.ctx, input, exp_indices, None, phase=phase)
+        if not (phase & 4):
             return None
-        r = self._routing
-        er = self._ids.reshape(-1).long() // self.epr
-        row = er * mm + (r.slot_of.long() - r.cumsum.long()[er * self.epr])
-        return back[row].float().view(self._ntok, self.topk, self.hidden).sum(1).to(x.dtype)
+        return recv[: int(num_recv)] if exact else recv
+
+    def output_buffer(self) -> torch.Tensor:
+        """Symmetric buffer ``[capacity, hidden]`` for the processed rows of the call in flight: write row ``i`` of the
+        experts' output where row ``i`` of the dispatched rows was, then call ``combine()`` without an argument."""
+        return EP.expert_out_buffer(self.ctx)
+
+    def combine(self, x=None, phase: int = 3) -> torch.Tensor:
+        """Sum of each token's ``topk`` processed copies, ``[T, hidden]``. ``x`` is ``output_buffer()`` (or nothing), or
+        any ``[rows, hidden]`` bf16 tensor in the dispatched row order, which is first copied there."""
+        return EP.ep_combine(self.ctx, x, weighted=False, phase=phase)
 
 
 class SpGQAFlashDecodeAttention:

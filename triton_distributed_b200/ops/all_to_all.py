@@ -184,108 +184,77 @@ def _fast_all_to_all_cpu(ctx, send, cumsum, scale):
 # ---------------------------------------------------------------------------- fused MoE pair
 @dataclass
 class MoEDispatchContext:
-    """State of the fused dispatch/combine pair: one all-to-all context per direction (fp8 rows
-    with hidden/128 scales out, bf16 rows back) and the routing of the call in flight."""
+    """State of the fused dispatch / combine pair for the serving layout: fp8 rows with hidden/128 scales out
+    (per-source slots, routing done inside the dispatch kernel), bf16 expert outputs pulled back by the combine.
+    ``ep`` is the underlying expert-parallel context (``ops/moe_ep.py``)."""
 
-    dispatch: AllToAllContext
-    combine: AllToAllContext
+    ep: "object"
     num_experts: int
     topk: int
     hidden: int
-    routing: Optional[moe_utils.Routing] = None
-    topk_ids: Optional[torch.Tensor] = None
-    topk_weights: Optional[torch.Tensor] = None
-    ntok: int = 0
+
+    @property
+    def max_m(self) -> int:
+        return self.ep.max_m
+
+    @property
+    def ntok(self) -> int:
+        return self.ep.ntok
 
 
 def create_moe_dispatch_context(max_tokens: int, hidden: int, topk: int, num_experts: int, rank: int, world_size: int,
                                 heap=None, group=None, device=None) -> MoEDispatchContext:
-    epr = num_experts // world_size
-    max_m = max_tokens * topk
-    d = create_all_to_all_context(max_m, hidden, rank, num_experts, world_size, epr, dtype=torch.float8_e4m3fn,
-                                  scale_cols=hidden // 128, heap=heap, group=group, device=device)
-    c = create_all_to_all_context(max_m, hidden, rank, num_experts, world_size, epr, dtype=torch.bfloat16,
+    from . import moe_ep
+    ep = moe_ep.create_ep_context(max_tokens, hidden, topk, num_experts, rank, world_size, quant=True, compact=False,
                                   heap=heap, group=group, device=device)
-    return MoEDispatchContext(d, c, num_experts, topk, hidden)
+    return MoEDispatchContext(ep, num_experts, topk, hidden)
 
 
 @nvtx_range("tdist.moe_dispatch")
 def moe_dispatch(ctx: MoEDispatchContext, x: torch.Tensor, topk_ids: torch.Tensor, topk_weights: torch.Tensor,
                  phase: int = 3, stream=None) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
-    """Send every token to the ranks of its ``topk`` experts as fp8 e4m3 with per-128 fp32 scales.
+    """Send every token to the ranks of its ``topk`` experts as fp8 e4m3 with per-128 fp32 scales: one launch that
+    sorts the (token, k) pairs by expert, quantises each token once and stores it into every owner's slot.
 
     ``x`` bf16 ``[T, hidden]``, ``topk_ids`` int32 ``[T, topk]``. Returns views into the receive
     buffers: ``(recv_x fp8 [ws*max_m, hidden], recv_scale fp32 [ws*max_m, hidden/128], recv_splits
     int32 [ws, experts_per_rank])``; source ``s`` occupies rows ``[s*max_m, s*max_m + sum(splits[s]))``
-    sorted by local expert."""
-    T = x.shape[0]
-    d = ctx.dispatch
-    if T * ctx.topk > d.max_m:
-        raise ValueError("more tokens than the context was built for")
-    if x.device.type != "cuda":
-        return _moe_dispatch_cpu(ctx, x, topk_ids, topk_weights)
-    if x.dtype != torch.bfloat16 or not x.is_contiguous():
-        raise ValueError("x must be contiguous bf16")
-    if phase != 2:
-        ctx.routing = moe_utils.route(topk_ids, ctx.num_experts, ctx.routing if ctx.ntok == T else None)
-        ctx.topk_ids = topk_ids.to(torch.int32).contiguous()
-        ctx.topk_weights = topk_weights.to(torch.float32).contiguous()
-        ctx.ntok = T
-    half = _next_call(d, phase)
-    a = _lib.A2AArgs()
-    a.send = x.data_ptr()
-    a.src_index = ctx.routing.sorted_token.data_ptr()
-    a.counts = ctx.routing.cumsum.data_ptr()
-    a.row_bytes_in, a.row_bytes_out = ctx.hidden * 2, ctx.hidden
-    a.scale_cols, a.hidden = ctx.hidden // 128, ctx.hidden
-    a.mode, a.quant = _lib.A2A_DISPATCH, 1
-    _fill_common(a, d, half, phase, x.device, stream)
-    _launch(a)
-    return (d.recv_buf.local[half], d.scale_recv_buf.local[half],
-            d.split_recv_buf.local[half].view(d.WORLD_SIZE, d.experts_per_rank))
+    sorted by local expert. ``phase`` 1 = send only, 2 = wait only (emulated ranks), 3 = both."""
+    from . import moe_ep
+    rx, rs, splits, _ = moe_ep.ep_dispatch(ctx.ep, x, topk_ids, topk_weights, phase=(phase & 3) << 1, stream=stream)
+    return rx, rs, splits
+
+
+def moe_expert_out_buffer(ctx: MoEDispatchContext) -> torch.Tensor:
+    """Where the experts of the call in flight write their bf16 outputs (``[ws*max_m, hidden]``, receive layout) for
+    :func:`moe_combine` to read in place."""
+    from . import moe_ep
+    return moe_ep.expert_out_buffer(ctx.ep)
 
 
 @nvtx_range("tdist.moe_combine")
-def moe_combine(ctx: MoEDispatchContext, expert_out: torch.Tensor, recv_splits: torch.Tensor,
+def moe_combine(ctx: MoEDispatchContext, expert_out: Optional[torch.Tensor] = None, recv_splits: Optional[torch.Tensor] = None,
                 out: Optional[torch.Tensor] = None, phase: int = 3, stream=None) -> torch.Tensor:
-    """Return the experts' outputs to their source ranks and reduce over ``topk`` with the gate
-    weights of the matching ``moe_dispatch``.
+    """Bring the experts' outputs back to their source ranks and reduce over ``topk`` with the gate
+    weights of the matching ``moe_dispatch``: every rank reads the rows of its tokens straight from the owners'
+    buffers (peer loads) and sums them in fp32.
 
     ``expert_out`` bf16 ``[ws*max_m, hidden]`` in the receive layout of ``moe_dispatch`` (row i of
-    the output corresponds to row i of ``recv_x``). Returns bf16 ``[T, hidden]``."""
-    c = ctx.combine
-    if expert_out.device.type != "cuda":
-        return _moe_combine_cpu(ctx, expert_out, recv_splits)
-    if expert_out.dtype != torch.bfloat16 or not expert_out.is_contiguous():
-        raise ValueError("expert_out must be contiguous bf16")
-    T = ctx.ntok
-    o = out if out is not None else torch.empty((T, ctx.hidden), dtype=torch.bfloat16, device=expert_out.device)
-    half = _next_call(c, phase)
-    a = _lib.A2AArgs()
-    a.send = expert_out.data_ptr()
-    a.counts = recv_splits.contiguous().data_ptr()
-    a.row_bytes_in = a.row_bytes_out = ctx.hidden * 2
-    a.scale_cols, a.hidden = 1, ctx.hidden
-    a.mode, a.reduce = _lib.A2A_COMBINE, 1
-    a.slot_of = ctx.routing.slot_of.data_ptr()
-    a.cumsum = ctx.routing.cumsum.data_ptr()
-    a.topk_ids = ctx.topk_ids.data_ptr()
-    a.topk_w = ctx.topk_weights.data_ptr()
-    a.out = o.data_ptr()
-    a.ntok, a.topk = T, ctx.topk
-    _fill_common(a, c, half, phase, expert_out.device, stream)
-    _launch(a)
-    return o
+    the output corresponds to row i of ``recv_x``); pass :func:`moe_expert_out_buffer` (or nothing) when the
+    experts wrote there, any other tensor is copied there first. Returns bf16 ``[T, hidden]``."""
+    from . import moe_ep
+    return moe_ep.ep_combine(ctx.ep, expert_out, weighted=True, out=out, phase=phase, stream=stream)
 
 
-def dequant_fp8(x: torch.Tensor, scale: torch.Tensor, rows: Optional[int] = None) -> torch.Tensor:
-    """fp8 e4m3 ``[R, hidden]`` with fp32 scales ``[R, hidden/128]`` -> bf16 ``[R, hidden]``."""
+def dequant_fp8(x: torch.Tensor, scale: torch.Tensor, rows: Optional[int] = None, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """fp8 e4m3 ``[R, hidden]`` with fp32 scales ``[R, hidden/128]`` -> bf16 ``[R, hidden]`` (into ``out`` when given)."""
     global launch_count
     R = x.shape[0] if rows is None else rows
     hidden = x.shape[1]
     if x.device.type != "cuda":
         return (x[:R].float().view(R, hidden // 128, 128) * scale[:R].float().unsqueeze(-1)).view(R, hidden).to(torch.bfloat16)
-    out = torch.empty((x.shape[0], hidden), dtype=torch.bfloat16, device=x.device)
+    if out is None:
+        out = torch.empty((x.shape[0], hidden), dtype=torch.bfloat16, device=x.device)
     _lib.check(_lib.lib().tdist_dequant_fp8(x.data_ptr(), scale.data_ptr(), out.data_ptr(), R, hidden,
                                             torch.cuda.current_stream(x.device).cuda_stream), "tdist_dequant_fp8")
     launch_count += 1
@@ -300,33 +269,6 @@ def quant_fp8_reference(x: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
     scale = g.abs().amax(-1).clamp_min(1e-10) / 448.0
     q = (g / scale.unsqueeze(-1)).view(R, H).to(torch.float8_e4m3fn)
     return q, scale
-
-
-def _moe_dispatch_cpu(ctx, x, topk_ids, topk_weights):
-    ctx.routing = moe_utils.route(topk_ids, ctx.num_experts)
-    ctx.topk_ids, ctx.topk_weights, ctx.ntok = topk_ids.to(torch.int32), topk_weights.float(), x.shape[0]
-    q, scale = quant_fp8_reference(x)
-    rows = ctx.routing.sorted_token.long()
-    d = ctx.dispatch
-    # fp8 tensors do not travel through gloo: ship the bytes
-    splits, recv, rscale = _fast_all_to_all_cpu(d, q[rows].view(torch.uint8), ctx.routing.cumsum, scale[rows])
-    return recv.view(torch.float8_e4m3fn), rscale, splits.view(d.WORLD_SIZE, d.experts_per_rank)
-
-
-def _moe_combine_cpu(ctx, expert_out, recv_splits):
-    c = ctx.combine
-    W, epr, mm = c.WORLD_SIZE, c.experts_per_rank, c.max_m
-    per_src = recv_splits.reshape(W, epr).sum(1)
-    compact = torch.cat([expert_out[s * mm: s * mm + int(per_src[s])] for s in range(W)])
-    cums = torch.zeros(W * epr + 1, dtype=torch.int32)
-    cums[1:] = torch.cumsum(recv_splits.reshape(-1), 0)
-    _splits, back, _ = _fast_all_to_all_cpu(c, compact, cums, None)
-    r = ctx.routing
-    T, K = ctx.ntok, ctx.topk
-    er = (ctx.topk_ids.reshape(-1).long() // epr)
-    row = er * mm + (r.slot_of.long() - r.cumsum.long()[er * epr])
-    vals = back[row].float() * ctx.topk_weights.reshape(-1, 1)
-    return vals.view(T, K, -1).sum(1).to(torch.bfloat16)
 
 
 # ---------------------------------------------------------------------------- helpers of the reference's EP layer

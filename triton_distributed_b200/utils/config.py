@@ -21,7 +21,7 @@ class Config:
     heap_backend: str = "auto"           # TDIST_HEAP_BACKEND: auto | vmm (cuMem + fd export) | ipc (cudaIpc) | host
     nvls: bool = False                   # TDIST_NVLS: bind heap segments to an NVSwitch multicast object (multimem ops)
     ag_gemm_nvls: int = 0                # TDIST_AG_GEMM_NVLS: AG-GEMM pushers use multimem.st (0 never, 1 from 4 ranks, 2 always)
-    gemm_cta_pair: int = -1              # TDIST_GEMM_CTA_PAIR: -1 automatic, 0 one CTA per 128x256 tile, 1 CTA pair per 256x256
+    gemm_cta_pair: int = -1              # TDIST_GEMM_CTA_PAIR: -1 automatic, 0 one CTA per 128x256 tile, 1 CTA pair per 256x256, 2 CTA pair per 256x512
     gemm_group_m: int = 0                # TDIST_GEMM_GROUP_M: row-tiles per raster group, 0 = kernel default (8)
     nvtx: bool = False                   # TDIST_NVTX: wrap the ops in NVTX ranges (timelines of external profilers)
     nvcc: str = ""                       # TDIST_NVCC: compiler used by the build, empty = search PATH and /usr/local/cuda
