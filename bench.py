@@ -278,7 +278,7 @@ def main():
     e2e_ms, e2e_spread = timed(e2e_step, K_STEPS, W, finish=e2e_finish)
     torch.cuda.synchronize()
     check_status()
-    e2e_err = (out_host[(step_no[0] - 1) & 1][::61].float() - out[rank * mpr:(rank + 1) * mpr:61].float()).abs().max().item()
+    e2e_err = (out_host[(step_no[0] - 1) & 1][::61].float() - out[rank * mpr:(rank + 1) * mpr:61].float().cpu()).abs().max().item()
     if not (e2e_err < 1e-3):
         raise SystemExit(f"the result copied back to the host differs from the device result ({e2e_err})")
     e2e = {"value": flops / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOP/s", "ms_per_step": e2e_ms,

@@ -7,7 +7,7 @@ from _mp import run_workers
 
 def test_cpu_gloo_world2():
     res, _ = run_workers("moe_decode_worker.py", 2, env={"CUDA_VISIBLE_DEVICES": ""})
-    assert res["ranks_ok"] == 2 and res["fast_all_to_all"] == "ok"
+    assert res["ranks_ok"] == 2 and res["fast_all_to_all"] == "ok" and res["ep_layer"] == "ok"
     assert res["fused_moe_err"] < 3e-2 and res["sp_decode_err"] < 1e-4
 
 

@@ -38,11 +38,12 @@ def test_group_gemm_blocks_pick_their_expert(cuda_device, T, E, K, N, topk):
 
 
 @pytest.mark.parametrize("world,tpr,E,K,N,topk", [(1, 256, 8, 256, 256, 2), (4, 128, 16, 512, 264, 2), (8, 64, 32, 256, 512, 4)])
-@pytest.mark.parametrize("fused", [True, False], ids=["gather_in_gemm", "staged"])
-def test_ag_group_gemm(cuda_device, monkeypatch, world, tpr, E, K, N, topk, fused):
-    """`fused`: the all-gather only sends; the grouped GEMM gathers its A rows itself (cp.async by index) and waits
-    per 128-row block for the arrival flag of the rank the block's tokens come from."""
-    monkeypatch.setattr(MT, "FUSED_AG_GROUP_GEMM", fused)
+@pytest.mark.parametrize("mode", ["fused", "cp_async", "staged"])
+def test_ag_group_gemm(cuda_device, monkeypatch, world, tpr, E, K, N, topk, mode):
+    """`fused`: the all-gather only sends; one grouped-GEMM launch stages the rows block by block as the source
+    rank's segment arrives, feeds the MMAs by TMA from this rank's own blocks on, and stores every row at its
+    (token, k) position. `cp_async`: the producer warps gather by index. `staged`: four separate launches."""
+    monkeypatch.setattr(MT, "AG_GROUP_GEMM_MODE", mode)
     torch.manual_seed(world * 7 + tpr)
     lw = LocalWorld(world, cuda_device)
     M = world * tpr
@@ -69,9 +70,11 @@ def test_ag_group_gemm(cuda_device, monkeypatch, world, tpr, E, K, N, topk, fuse
 @pytest.mark.parametrize("world,M,E,Kl,N,topk", [(1, 256, 8, 256, 256, 2), (2, 512, 16, 128, 512, 2), (4, 256, 32, 256, 1024, 4)])
 @pytest.mark.parametrize("fused", [True, False], ids=["fused_topk_rs", "staged"])
 def test_moe_reduce_rs(cuda_device, monkeypatch, world, M, E, Kl, N, topk, fused):
-    """`fused`: the top-k weighted reduce happens inside the reduce-scatter kernel (the [M, N] partial is never
-    written); staged: separate top-k reduce kernel, then the plain reduce-scatter."""
+    """`fused`: the rows are sorted by expert inside the grouped-GEMM launch and the top-k weighted reduce happens
+    inside the reduce-scatter kernel (the [M, N] partial is never written); staged: row-gather kernel, grouped GEMM,
+    top-k reduce kernel, plain reduce-scatter."""
     monkeypatch.setattr(MT, "FUSED_TOPK_RS", fused)
+    monkeypatch.setattr(MT, "AG_GROUP_GEMM_MODE", "fused" if fused else "staged")
     torch.manual_seed(world * 11 + M)
     lw = LocalWorld(world, cuda_device)
     ids = torch.randint(0, E, (M, topk), dtype=torch.int32, device=cuda_device)
@@ -111,3 +114,34 @@ def test_group_gemm_gathers_rows_in_kernel(cuda_device, T, E, K, N, topk):
     got = MT.group_gemm_gather(x, row_index, b, expert_ids, nb)
     check_status()
     assert torch.equal(got, want)
+
+
+@pytest.mark.parametrize("T,E,K,N,topk,rot", [(300, 8, 264, 520, 2, 0), (1500, 16, 512, 776, 3, 7), (128, 4, 64, 256, 1, 1)])
+def test_group_gemm_staged_gather_rotation_and_scatter(cuda_device, T, E, K, N, topk, rot):
+    """Gatherer CTAs + TMA-fed MMAs + scattering epilogue in one launch against the four-launch path, over several
+    calls with fresh data (the per-block flags carry the call number), starting the schedule at block `rot`."""
+    torch.manual_seed(T + K)
+    b = (torch.randn(E, N, K, device=cuda_device) * K ** -0.5).to(torch.bfloat16)
+    ids = torch.randint(0, E, (T, topk), dtype=torch.int32, device=cuda_device)
+    sorted_ids, expert_ids, _, _, post_pad = MU.sort_topk_ids_align_block_size(ids, E, 1, T, 128)
+    n = int(post_pad)
+    sid = sorted_ids[:n].contiguous()
+    nb = (post_pad // 128).to(torch.int32)
+    row_index = torch.div(sid, topk, rounding_mode="floor").to(torch.int32)
+    staging = torch.full((n, K), float("nan"), device=cuda_device, dtype=torch.bfloat16)
+    ready = torch.zeros(n // 128 + 1, dtype=torch.int32, device=cuda_device)   # per-block flags + the prologue's counter
+    rot_t = torch.tensor([min(rot, n // 128 - 1)], dtype=torch.int32, device=cuda_device)
+    for call in range(1, 4):
+        x = torch.randn(T, K, device=cuda_device).to(torch.bfloat16)
+        a_sorted, pos_of = MT.gather_rows(x, sid, topk, T * topk, want_inverse=True)
+        want_sorted = MT.group_gemm(a_sorted, b, expert_ids, nb)
+        want, _ = MT.gather_rows(want_sorted, pos_of, 1, n)
+        got_sorted = MT.group_gemm_gather(x, row_index, b, expert_ids, nb, staging=staging, block_ready=ready, epoch=2 * call - 1,
+                                          block_rot=rot_t, num_gather_ctas=3 + call)
+        staging.fill_(float("nan"))    # the second launch must stage the rows again, not reuse what is there
+        got = MT.group_gemm_gather(x, row_index, b, expert_ids, nb, staging=staging, block_ready=ready, epoch=2 * call,
+                                   block_rot=rot_t, c_scatter=sid, c_rows=T * topk)
+        check_status()
+        live = sid < T * topk
+        assert torch.equal(got_sorted[live], want_sorted[live])
+        assert torch.equal(got, want)

@@ -69,14 +69,44 @@ def test_put_quiet_signal_add_and_get(ring):
         assert torch.equal(c.slot(prev), ring[prev].source)
 
 
-def test_broadcast_and_fcollect(ring):
-    _both_phases(ring, "broadcast")
+@pytest.mark.parametrize("scope", ["thread", "warp", "block"])
+def test_broadcast_and_fcollect(ring, scope):
+    """broadcast / fcollect at thread, warp and block scope (the thread and warp forms are what a kernel calls from a
+    single lane or warp of a busy CTA)."""
+    _both_phases(ring, "broadcast", scope=scope)
     for c in ring:
         assert torch.equal(c.slot(0), ring[0].source)
-    _both_phases(ring, "fcollect")
+    for c in ring:
+        for s in range(len(ring)):
+            c.slot(s).zero_()
+    _both_phases(ring, "fcollect", scope=scope)
     for c in ring:
         for s in range(len(ring)):
             assert torch.equal(c.slot(s), ring[s].source)
+
+
+@pytest.mark.parametrize("scope", ["thread", "warp"])
+def test_getmem_nbi_thread_and_warp_scope(ring, scope):
+    for c in ring:
+        for s in range(len(ring)):
+            c.slot(s).zero_()
+    _both_phases(ring, "get", scope=scope)
+    for r, c in enumerate(ring):
+        prev = (r - 1) % len(ring)
+        assert torch.equal(c.slot(prev), ring[prev].source)
+
+
+@pytest.mark.parametrize("scope", ["thread", "warp", "block"])
+def test_barrier_all_scopes_single_rank(cuda_device, scope):
+    """barrier_all / barrier_all_warp / barrier_all_block over 200 rounds on a one-rank world (ranks of one GPU must
+    not wait for each other across launches): every round publishes the next epoch into this rank's own flag word
+    and waits for it; the epoch counter must have advanced by exactly the number of rounds and no wait may fail."""
+    lw = LocalWorld(1, cuda_device)
+    ctx = P.create_primitive_context(0, 1, 256, heap=lw.heap(0))
+    P.run_primitive(ctx, "barrier", value=200, scope=scope)
+    check_status()
+    assert int(ctx.result[0]) == 0
+    assert int(ctx.barrier_epoch[0]) == 200 and int(ctx.sig.local[8]) == 200
 
 
 def test_grid_barrier_random_grids(cuda_device):

@@ -77,6 +77,49 @@ def main():
         assert torch.allclose(out.float(), ref, atol=3e-2, rtol=3e-2), ("fused", it, err)
     res["fused_moe_err"] = err
 
+    # ---------------- expert-parallel layer: dispatched rows against all_to_all_single, exactly
+    # (the reference's check: test/nvidia/test_ep_a2a.py:206-264)
+    from triton_distributed_b200.models import EPAll2AllLayer
+    T, H, K = (96, 512, 4) if cuda else (8, 64, 2)
+    E = 8 * world
+    epr = E // world
+    layer = EPAll2AllLayer(group, T, H, K, rank, E, world, world, device=dev)
+    for it in range(3):
+        x = torch.randn(T, H, device=dev).to(torch.bfloat16)
+        ids = torch.randint(0, E, (T, K), dtype=torch.int32, device=dev)
+        rows = layer.dispatch(x, ids)
+        if cuda:
+            check_status()
+        n = int(layer.num_recv)
+        # oracle: expert-sorted rows, exchanged with the collective, then regrouped from (source, expert) to (expert, source)
+        rt = MU.route(ids, E)
+        send = x[rt.sorted_token.long()].contiguous()
+        counts = torch.stack(gather_list(rt.splits, group, world)).long()                 # [source, expert]
+        mine = counts[:, rank * epr:(rank + 1) * epr]                                    # [source, local expert]
+        in_splits = [int(v) for v in counts[rank].view(world, epr).sum(1)]
+        out_splits = [int(v) for v in mine.sum(1)]
+        got = torch.empty((sum(out_splits), H), dtype=send.dtype, device=dev)
+        if cuda:
+            dist.all_to_all_single(got, send, out_splits, in_splits, group=group)
+        else:   # gloo has no all_to_all_single on every build: gather everything and cut
+            every = gather_list(torch.cat([send, send.new_zeros((T * K - send.shape[0], H))]), group, world)
+            every_cum = gather_list(rt.cumsum, group, world)
+            got = torch.cat([every[s][int(every_cum[s][rank * epr]): int(every_cum[s][(rank + 1) * epr])] for s in range(world)])
+        per_src = torch.split(got, out_splits)
+        want = []
+        for le in range(epr):
+            for s_ in range(world):
+                lo = int(mine[s_, :le].sum())
+                want.append(per_src[s_][lo: lo + int(mine[s_, le])])
+        want = torch.cat(want)
+        assert n == want.shape[0], ("ep rows", it, n, want.shape[0])
+        assert torch.equal(rows[:n], want), ("ep dispatch", it)
+        out = layer.combine(rows)
+        if cuda:
+            check_status()
+        assert torch.allclose(out.float(), x.float() * K, atol=2e-2, rtol=2e-2), ("ep combine", it)
+    res["ep_layer"] = "ok"
+
     # ---------------- sequence-parallel decode
     B, Hq, Hkv, D, page = (4, 32, 8, 128, 16) if cuda else (2, 8, 2, 64, 4)
     dtype = torch.bfloat16 if cuda else torch.float32

@@ -23,6 +23,10 @@ CSRC = PKG_DIR / "csrc"
 OUT_DIR = PKG_DIR / "_C"
 OBJ_DIR = OUT_DIR / "obj"
 LIB_PATH = OUT_DIR / "libtdist.so"
+# the same sources with -DTDIST_BOUNDS_CHECK: every symmetric-address translation checks peer and span, records the
+# first violation and skips the access (csrc/device/signal.cuh); loaded instead of the above with TDIST_BOUNDS_CHECK=1
+CHECK_OBJ_DIR = OUT_DIR / "obj_check"
+CHECK_LIB_PATH = OUT_DIR / "libtdist_check.so"
 
 ARCH_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a"]
 NVCC_FLAGS = [
@@ -46,61 +50,68 @@ def sources() -> list[Path]:
     return out
 
 
-def _headers_digest() -> str:
+def _headers_digest(extra_flags=()) -> str:
     h = hashlib.sha256()
     for p in sorted(CSRC.rglob("*")):
         if p.suffix in (".h", ".cuh", ".hpp"):
             h.update(p.name.encode())
             h.update(p.read_bytes())
-    h.update(" ".join(ARCH_FLAGS + NVCC_FLAGS).encode())
+    h.update(" ".join([*ARCH_FLAGS, *NVCC_FLAGS, *extra_flags]).encode())
     return h.hexdigest()
 
 
-def _compile_one(nvcc: str, src: Path, hdr_digest: str, verbose: bool) -> tuple[Path, bool, str]:
-    obj = OBJ_DIR / (src.stem + ".o")
-    stamp = OBJ_DIR / (src.stem + ".sha")
+def _compile_one(nvcc: str, src: Path, hdr_digest: str, verbose: bool, obj_dir: Path = OBJ_DIR, extra_flags=()) -> tuple[Path, bool, str]:
+    obj = obj_dir / (src.stem + ".o")
+    stamp = obj_dir / (src.stem + ".sha")
     digest = hashlib.sha256(src.read_bytes() + hdr_digest.encode()).hexdigest()
     if obj.exists() and stamp.exists() and stamp.read_text() == digest:
         return obj, False, ""
-    cmd = [nvcc, *ARCH_FLAGS, *NVCC_FLAGS, "-x", "cu", "-c", str(src), "-o", str(obj)]
+    cmd = [nvcc, *ARCH_FLAGS, *NVCC_FLAGS, *extra_flags, "-x", "cu", "-c", str(src), "-o", str(obj)]
     proc = subprocess.run(cmd, capture_output=True, text=True)
     log = proc.stdout + proc.stderr
     if proc.returncode != 0:
         raise RuntimeError(f"nvcc failed for {src.name}:\n{log}")
-    (OBJ_DIR / (src.stem + ".ptxas.txt")).write_text(log)
+    (obj_dir / (src.stem + ".ptxas.txt")).write_text(log)
     stamp.write_text(digest)
     if verbose:
-        print(f"[tdist build] compiled {src.name}", file=sys.stderr)
+        print(f"[tdist build] compiled {src.name}" + (f" ({' '.join(extra_flags)})" if extra_flags else ""), file=sys.stderr)
     return obj, True, log
 
 
-def build(verbose: bool = False, force: bool = False) -> Path:
-    """Compile every source for sm_100a and link ``libtdist.so``. Returns its path."""
+def _build_variant(lib_path: Path, obj_dir: Path, extra_flags, verbose: bool, force: bool) -> Path:
     nvcc = _nvcc()
-    OBJ_DIR.mkdir(parents=True, exist_ok=True)
+    obj_dir.mkdir(parents=True, exist_ok=True)
     if force:
-        for p in OBJ_DIR.glob("*.sha"):
+        for p in obj_dir.glob("*.sha"):
             p.unlink()
-    hdr = _headers_digest()
+    hdr = _headers_digest(extra_flags)
     srcs = sources()
     with ThreadPoolExecutor(max_workers=min(8, max(1, len(srcs)))) as ex:
-        results = list(ex.map(lambda s: _compile_one(nvcc, s, hdr, verbose), srcs))
+        results = list(ex.map(lambda s: _compile_one(nvcc, s, hdr, verbose, obj_dir, extra_flags), srcs))
     objs = [r[0] for r in results]
     changed = any(r[1] for r in results)
     # drop objects whose source disappeared
     keep = {o.name for o in objs}
-    for o in OBJ_DIR.glob("*.o"):
+    for o in obj_dir.glob("*.o"):
         if o.name not in keep:
             o.unlink()
             changed = True
-    if changed or not LIB_PATH.exists():
-        cmd = [nvcc, *ARCH_FLAGS, "-shared", "-o", str(LIB_PATH), *map(str, objs), "-ldl", "-lpthread"]
+    if changed or not lib_path.exists():
+        cmd = [nvcc, *ARCH_FLAGS, "-shared", "-o", str(lib_path), *map(str, objs), "-ldl", "-lpthread"]
         proc = subprocess.run(cmd, capture_output=True, text=True)
         if proc.returncode != 0:
             raise RuntimeError(f"link failed:\n{proc.stdout}{proc.stderr}")
         if verbose:
-            print(f"[tdist build] linked {LIB_PATH}", file=sys.stderr)
-    return LIB_PATH
+            print(f"[tdist build] linked {lib_path}", file=sys.stderr)
+    return lib_path
+
+
+def build(verbose: bool = False, force: bool = False) -> Path:
+    """Compile every source for sm_100a and link ``libtdist.so`` (and its bounds-checked twin
+    ``libtdist_check.so``). Returns the path of the former."""
+    path = _build_variant(LIB_PATH, OBJ_DIR, (), verbose, force)
+    _build_variant(CHECK_LIB_PATH, CHECK_OBJ_DIR, ("-DTDIST_BOUNDS_CHECK",), verbose, force)
+    return path
 
 
 def ptxas_report() -> str:

@@ -57,6 +57,8 @@ class GemmArgs(C.Structure):
         ("a_ws_mc", C.c_void_p),
         ("a_gather", C.c_void_p), ("a_gather_rows", C.c_int), ("block_src", C.c_void_p), ("src_flags", C.c_void_p),
         ("src_epoch", C.c_uint64), ("src_rank", C.c_int), ("src_world", C.c_int),
+        ("gather_dst", C.c_void_p), ("block_ready", C.c_void_p), ("gather_counter", C.c_void_p), ("block_rot", C.c_void_p),
+        ("c_scatter", C.c_void_p), ("c_rows", C.c_int),
     ]
 
 
@@ -172,6 +174,7 @@ class DecodeArgs(C.Structure):
         ("timeout_ns", C.c_uint64),
         ("stream", C.c_void_p),
         ("epoch_ptr", C.c_void_p), ("epoch_done", C.c_void_p), ("ll_peer_alt", C.c_void_p * MAX_RANKS),
+        ("ll_mc", C.c_void_p), ("ll_mc_alt", C.c_void_p),
     ]
 
 
@@ -189,15 +192,21 @@ class PrimArgs(C.Structure):
 
 
 (PRIM_RING_PUT, PRIM_NOTIFY_WAIT, PRIM_NOTIFY_ADD, PRIM_PUT_SIGNAL, PRIM_PUT_QUIET_SIGNAL, PRIM_GET, PRIM_BROADCAST,
- PRIM_FCOLLECT, PRIM_GRID_BARRIER, PRIM_SCOPED_OPS) = range(10)
+ PRIM_FCOLLECT, PRIM_GRID_BARRIER, PRIM_SCOPED_OPS, PRIM_BARRIER, PRIM_BOUNDS_PROBE) = range(12)
 GEMM_PLAIN, GEMM_AG, GEMM_RS = 0, 1, 2
 A2A_DISPATCH, A2A_COMBINE = 0, 1
 DT_BF16, DT_F16, DT_F32, DT_I32 = 0, 1, 2, 3
 AG_PULL, AG_PUSH, AG_LL = 0, 1, 2
 
 
+def bounds_checked() -> bool:
+    """True when ``TDIST_BOUNDS_CHECK=1`` selects the library whose symmetric-address translation checks peer and
+    span, records the first violation in the status block and skips the access (read once, at load time)."""
+    return os.environ.get("TDIST_BOUNDS_CHECK", "0") == "1"
+
+
 def lib_path() -> Path:
-    return Path(__file__).resolve().parent / "_C" / "libtdist.so"
+    return Path(__file__).resolve().parent / "_C" / ("libtdist_check.so" if bounds_checked() else "libtdist.so")
 
 
 def available() -> bool:
@@ -227,6 +236,7 @@ def _declare(lib):
     lib.tdist_signal_op_on_stream.argtypes = [C.c_void_p, C.c_uint64, C.c_int, C.c_void_p]
     lib.tdist_signal_wait_on_stream.argtypes = [C.c_void_p, C.c_int, C.c_uint64, C.c_void_p, C.c_uint64, C.c_void_p]
     lib.tdist_primitive.argtypes = [C.POINTER(PrimArgs)]
+    lib.tdist_bounds_checked.argtypes = []
     lib.tdist_flash_decode.argtypes = [C.POINTER(DecodeArgs)]
     lib.tdist_lse_combine.argtypes = [C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_int, C.c_void_p]
     lib.tdist_dequant_fp8.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_void_p]

@@ -248,15 +248,30 @@ def _bench_a2a(args, world, rank, group, dev, dtype, pk, row):
         state["recv"] = A.moe_dispatch(ctx, x, ids, w)
 
     def both():
+        # identity experts: the fp8 rows are dequantised straight into the symmetric buffer the combine reads
         rx, rs, splits = A.moe_dispatch(ctx, x, ids, w)
-        y = A.dequant_fp8(rx, rs)
-        A.moe_combine(ctx, y, splits)
+        A.dequant_fp8(rx, rs, out=A.moe_expert_out_buffer(ctx))
+        A.moe_combine(ctx, None, splits)
 
     dispatch()
-    y = A.dequant_fp8(*state["recv"][:2])
+    A.dequant_fp8(*state["recv"][:2], out=A.moe_expert_out_buffer(ctx))
     us_d = timed_us(dispatch, args.iters, args.warmup, world, group)
-    us_c = timed_us(lambda: A.moe_combine(ctx, y, state["recv"][2]), args.iters, args.warmup, world, group)
+    A.dequant_fp8(*state["recv"][:2], out=A.moe_expert_out_buffer(ctx))
+    us_c = timed_us(lambda: A.moe_combine(ctx, None, state["recv"][2]), args.iters, args.warmup, world, group)
     us_b = timed_us(both, args.iters, args.warmup, world, group)
+    # the expert-parallel layer on the same problem: bf16 rows into the expert-major compact layout, plain-sum combine
+    from .models import EPAll2AllLayer
+    layer = EPAll2AllLayer(group, T, H, K, rank, E, world, world, device=dev)
+
+    def ep_both():
+        rows = layer.dispatch(x, ids)
+        layer.output_buffer().copy_(rows)     # identity experts
+        layer.combine()
+    layer.dispatch(x, ids)
+    us_ed = timed_us(lambda: layer.dispatch(x, ids), args.iters, args.warmup, world, group)
+    us_ec = timed_us(lambda: layer.combine(), args.iters, args.warmup, world, group)
+    row.update({"ep_layer_dispatch_us": round(us_ed, 2), "ep_layer_combine_us": round(us_ec, 2)})
+    del ep_both
     out_bytes = T * K * (H + H // 128 * 4) * (world - 1) / world
     back_bytes = T * K * H * 2 * (world - 1) / world
     link_us = (out_bytes + back_bytes) / (NVLINK_GBS * 1e3)
@@ -349,14 +364,19 @@ def _bench_moe_tp(args, world, rank, group, dev, dtype, pk, row):
     b2 = (torch.randn(E, I // world, H, device=dev) * I ** -0.5).to(dtype)
     ctx2 = MT.create_moe_rs_context(group, rank, world, world, M, H, E, topk, dtype, dtype, dev, full_topk_ids=ids, full_topk_weight=w)
     flops1 = 2.0 * M * topk * (I // world) * H
-    for name, flag in (("fused", True), ("staged", False)):
-        MT.FUSED_AG_GROUP_GEMM = flag
+    # fused: one grouped-GEMM launch that stages its rows block by block (gatherer CTAs), waits per block for the
+    # all-gather, stores every row at its final position; top-k reduce inside the reduce-scatter.
+    # staged: all-gather, row-gather, grouped GEMM, un-sort, top-k reduce, reduce-scatter as separate launches.
+    for name, mode, flag in (("fused", "fused", True), ("staged", "staged", False)):
+        MT.AG_GROUP_GEMM_MODE = mode
         MT.FUSED_TOPK_RS = flag
         us1 = timed_us(lambda: MT.ag_group_gemm_intra_node(a, b1, ctx1), args.iters, args.warmup, world, group)
         us2 = timed_us(lambda: MT.moe_reduce_rs(rank, world, world, h, b2, ctx2), args.iters, args.warmup, world, group)
         row.update({f"ag_group_gemm_{name}_us": round(us1, 1), f"moe_reduce_rs_{name}_us": round(us2, 1),
                     f"ag_group_gemm_{name}_tflops": round(flops1 / us1 / 1e6, 1), f"moe_reduce_rs_{name}_tflops": round(flops1 / us2 / 1e6, 1)})
-    MT.FUSED_AG_GROUP_GEMM = MT.FUSED_TOPK_RS = True
+    MT.AG_GROUP_GEMM_MODE, MT.FUSED_TOPK_RS = "fused", True
+    row["ag_group_gemm_fused_over_staged"] = round(row["ag_group_gemm_staged_us"] / row["ag_group_gemm_fused_us"], 3)
+    row["moe_reduce_rs_fused_over_staged"] = round(row["moe_reduce_rs_staged_us"] / row["moe_reduce_rs_fused_us"], 3)
 
 
 def _bench_fused_local(args, world, rank, group, dev, dtype, pk, row):

@@ -14,6 +14,14 @@ __device__ __forceinline__ void ll_store(void* packet, uint64_t payload, uint32_
                  : "memory");
 }
 
+// The same packet through an NVSwitch multicast address: the switch replicates the store to every device bound to
+// the multicast object (reference low_latency_allgather.py:570-697 `_recv_ll_and_multimem_st*`, multimem.st.b64).
+__device__ __forceinline__ void ll_store_multimem(void* mc_packet, uint64_t payload, uint32_t flag) {
+    asm volatile("multimem.st.weak.global.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(mc_packet),
+                 "r"(static_cast<uint32_t>(payload)), "r"(flag), "r"(static_cast<uint32_t>(payload >> 32)), "r"(flag)
+                 : "memory");
+}
+
 // Spins until both flag copies of the packet equal `flag`; bounded like every other wait.
 __device__ __forceinline__ bool ll_load(const void* packet, uint32_t flag, uint64_t* payload, const WaitCtx& w,
                                         int peer, int index) {

@@ -64,13 +64,19 @@ __device__ __forceinline__ void copy_coop(void* dst, const void* src, size_t byt
 
 // ---- put / get: `dst` and `src` are LOCAL symmetric addresses; the remote side is `pe`'s copy.
 __device__ __forceinline__ void putmem_block(const SymmWindow& w, void* dst, const void* src, size_t bytes, int pe) {
-    copy_coop(symm_at(w, static_cast<char*>(dst), pe), src, bytes, threadIdx.x, blockDim.x);
+    char* remote = symm_span(w, static_cast<char*>(dst), bytes, pe, 201);
+    TDIST_SKIP_IF_NULL(remote);
+    copy_coop(remote, src, bytes, threadIdx.x, blockDim.x);
 }
 __device__ __forceinline__ void putmem_warp(const SymmWindow& w, void* dst, const void* src, size_t bytes, int pe) {
-    copy_coop(symm_at(w, static_cast<char*>(dst), pe), src, bytes, lane_id(), 32);
+    char* remote = symm_span(w, static_cast<char*>(dst), bytes, pe, 202);
+    TDIST_SKIP_IF_NULL(remote);
+    copy_coop(remote, src, bytes, lane_id(), 32);
 }
 __device__ __forceinline__ void putmem(const SymmWindow& w, void* dst, const void* src, size_t bytes, int pe) {
-    copy_coop(symm_at(w, static_cast<char*>(dst), pe), src, bytes, 0, 1);
+    char* remote = symm_span(w, static_cast<char*>(dst), bytes, pe, 203);
+    TDIST_SKIP_IF_NULL(remote);
+    copy_coop(remote, src, bytes, 0, 1);
 }
 // The *_nbi forms are the same code: stores to peer memory never block the issuing thread.
 __device__ __forceinline__ void putmem_nbi_block(const SymmWindow& w, void* dst, const void* src, size_t bytes, int pe) {
@@ -83,13 +89,19 @@ __device__ __forceinline__ void putmem_nbi(const SymmWindow& w, void* dst, const
     putmem(w, dst, src, bytes, pe);
 }
 __device__ __forceinline__ void getmem_block(const SymmWindow& w, void* dst, const void* src, size_t bytes, int pe) {
-    copy_coop(dst, symm_at(w, const_cast<char*>(static_cast<const char*>(src)), pe), bytes, threadIdx.x, blockDim.x);
+    const char* remote = symm_span(w, const_cast<char*>(static_cast<const char*>(src)), bytes, pe, 204);
+    TDIST_SKIP_IF_NULL(remote);
+    copy_coop(dst, remote, bytes, threadIdx.x, blockDim.x);
 }
 __device__ __forceinline__ void getmem_warp(const SymmWindow& w, void* dst, const void* src, size_t bytes, int pe) {
-    copy_coop(dst, symm_at(w, const_cast<char*>(static_cast<const char*>(src)), pe), bytes, lane_id(), 32);
+    const char* remote = symm_span(w, const_cast<char*>(static_cast<const char*>(src)), bytes, pe, 205);
+    TDIST_SKIP_IF_NULL(remote);
+    copy_coop(dst, remote, bytes, lane_id(), 32);
 }
 __device__ __forceinline__ void getmem(const SymmWindow& w, void* dst, const void* src, size_t bytes, int pe) {
-    copy_coop(dst, symm_at(w, const_cast<char*>(static_cast<const char*>(src)), pe), bytes, 0, 1);
+    const char* remote = symm_span(w, const_cast<char*>(static_cast<const char*>(src)), bytes, pe, 206);
+    TDIST_SKIP_IF_NULL(remote);
+    copy_coop(dst, remote, bytes, 0, 1);
 }
 __device__ __forceinline__ void getmem_nbi_block(const SymmWindow& w, void* dst, const void* src, size_t bytes, int pe) {
     getmem_block(w, dst, src, bytes, pe);
@@ -98,12 +110,15 @@ __device__ __forceinline__ void getmem_nbi_warp(const SymmWindow& w, void* dst, 
     getmem_warp(w, dst, src, bytes, pe);
 }
 __device__ __forceinline__ void int_p(const SymmWindow& w, int* dst, int value, int pe) {
-    *reinterpret_cast<volatile int*>(symm_at(w, dst, pe)) = value;
+    int* remote = symm_at(w, dst, pe);
+    TDIST_SKIP_IF_NULL(remote);
+    *reinterpret_cast<volatile int*>(remote) = value;
 }
 
 // ---- signals
 __device__ __forceinline__ void signal_op(const SymmWindow& w, uint64_t* sig, uint64_t value, int sig_op, int pe) {
     uint64_t* remote = symm_at(w, sig, pe);
+    TDIST_SKIP_IF_NULL(remote);
     if (sig_op == kSignalAdd) red_release_sys_add_u64(remote, value);
     else st_release_sys_u64(remote, value);
 }
@@ -164,7 +179,8 @@ __device__ __forceinline__ bool barrier_all_block(const SymmWindow& w, const Bar
     __syncthreads();
     if (static_cast<int>(threadIdx.x) < w.world) {
         fence_acq_rel_sys();
-        st_release_sys_u64(symm_at(w, b.flags, threadIdx.x) + w.rank, target);
+        uint64_t* peer_flags = symm_span(w, b.flags, static_cast<size_t>(w.world) * 8, threadIdx.x, 207);
+        if (peer_flags != nullptr) st_release_sys_u64(peer_flags + w.rank, target);
         if (!signal_wait_until(b.flags + threadIdx.x, kCmpGe, target, wc, threadIdx.x, 100)) ok_s = 0;
     }
     __syncthreads();
@@ -229,7 +245,8 @@ __device__ __forceinline__ bool barrier_all_warp(const SymmWindow& w, const Barr
     const int lane = static_cast<int>(lane_id());
     if (lane < w.world) {
         fence_acq_rel_sys();
-        st_release_sys_u64(symm_at(w, b.flags, lane) + w.rank, target);
+        uint64_t* peer_flags = symm_span(w, b.flags, static_cast<size_t>(w.world) * 8, lane, 208);
+        if (peer_flags != nullptr) st_release_sys_u64(peer_flags + w.rank, target);
         ok = signal_wait_until(b.flags + lane, kCmpGe, target, wc, lane, 101);
     }
     ok = __all_sync(0xffffffffu, ok);
@@ -241,7 +258,10 @@ __device__ __forceinline__ bool barrier_all(const SymmWindow& w, const BarrierSt
     const uint64_t target = *reinterpret_cast<volatile uint64_t*>(b.epoch) + 1;
     bool ok = true;
     fence_acq_rel_sys();
-    for (int pe = 0; pe < w.world; ++pe) st_release_sys_u64(symm_at(w, b.flags, pe) + w.rank, target);
+    for (int pe = 0; pe < w.world; ++pe) {
+        uint64_t* peer_flags = symm_span(w, b.flags, static_cast<size_t>(w.world) * 8, pe, 209);
+        if (peer_flags != nullptr) st_release_sys_u64(peer_flags + w.rank, target);
+    }
     for (int pe = 0; pe < w.world; ++pe) ok = signal_wait_until(b.flags + pe, kCmpGe, target, wc, pe, 102) && ok;
     *reinterpret_cast<volatile uint64_t*>(b.epoch) = target;
     return ok;

@@ -294,14 +294,66 @@ struct SymmWindow {
     char* base[kMaxRanks];
     int rank;
     int world;
+    size_t bytes;   // size of the symmetric object (0 = not known: spans are then not checked)
+    Status* dbg;    // where the bounds-checked build records a violation (may be nullptr)
 };
+
+// Bounds-checked build (-DTDIST_BOUNDS_CHECK, `TDIST_BOUNDS_CHECK=1` selects that library at load time): every
+// translation of a symmetric address checks that the peer exists and that the span [offset, offset + len) lies inside
+// the symmetric object. The first violation is recorded in the status block (kStatusBadArgument: peer, index = byte
+// offset, expected = object size, seen = end of the span) and the access is SKIPPED: the translation returns nullptr
+// and every helper of shmem.cuh returns without touching memory. Nothing traps, the context stays usable. This is the
+// stand-in for running the kernels under a memory checker, which is not available where these kernels are developed.
+constexpr int kKernelBounds = 8;
+#ifdef TDIST_BOUNDS_CHECK
+#define TDIST_SKIP_IF_NULL(ptr) \
+    do {                        \
+        if ((ptr) == nullptr) return; \
+    } while (0)
+#define TDIST_SKIP_IF_NULL_RET(ptr, value) \
+    do {                                   \
+        if ((ptr) == nullptr) return (value); \
+    } while (0)
+static __device__ __noinline__ void report_bounds(const SymmWindow& win, int peer, long long off, long long end, int where) {
+    WaitCtx w;
+    w.status = win.dbg;
+    w.timeout_ns = 0;
+    w.kernel_id = kKernelBounds;
+    w.rank = win.rank;
+    report_timeout(w, kStatusBadArgument, peer, static_cast<int>(off), static_cast<long long>(win.bytes), end, where);
+}
+template <typename T>
+__device__ __forceinline__ T* symm_span(const SymmWindow& win, T* local_ptr, size_t len, int peer, int where = 0) {
+    const ptrdiff_t off = reinterpret_cast<char*>(local_ptr) - win.base[win.rank];
+    const bool bad_peer = peer < 0 || peer >= win.world;
+    const bool bad_span = win.bytes != 0 && (off < 0 || static_cast<size_t>(off) + len > win.bytes);
+    if (bad_peer || bad_span) {
+        report_bounds(win, peer, off, off + static_cast<long long>(len), where);
+        return nullptr;
+    }
+    return reinterpret_cast<T*>(win.base[peer] + off);
+}
+#else
+#define TDIST_SKIP_IF_NULL(ptr) \
+    do {                        \
+    } while (0)
+#define TDIST_SKIP_IF_NULL_RET(ptr, value) \
+    do {                                   \
+    } while (0)
+template <typename T>
+__device__ __forceinline__ T* symm_span(const SymmWindow& win, T* local_ptr, size_t len, int peer, int where = 0) {
+    (void)len;
+    (void)where;
+    const ptrdiff_t off = reinterpret_cast<char*>(local_ptr) - win.base[win.rank];
+    return reinterpret_cast<T*>(win.base[peer] + off);
+}
+#endif
 
 // symm_at: translate a local symmetric address to the same offset in `peer`'s copy
 // (reference language.py:96-100; lowering DistributedOpToLLVM.cpp:342-421).
 template <typename T>
 __device__ __forceinline__ T* symm_at(const SymmWindow& win, T* local_ptr, int peer) {
-    const ptrdiff_t off = reinterpret_cast<char*>(local_ptr) - win.base[win.rank];
-    return reinterpret_cast<T*>(win.base[peer] + off);
+    return symm_span(win, local_ptr, sizeof(T), peer, 200);
 }
 __device__ __forceinline__ int rank(const SymmWindow& win) { return win.rank; }
 __device__ __forceinline__ int num_ranks(const SymmWindow& win) { return win.world; }
@@ -315,6 +367,7 @@ enum : int { kSignalSet = 9, kSignalAdd = 10 };  // reference NVSHMEM_SIGNAL_SET
 __device__ __forceinline__ void notify(const SymmWindow& win, uint64_t* local_sig, int peer,
                                        uint64_t value, int sig_op) {
     uint64_t* remote = symm_at(win, local_sig, peer);
+    TDIST_SKIP_IF_NULL(remote);
     fence_acq_rel_sys();
     if (sig_op == kSignalAdd) red_release_sys_add_u64(remote, value);
     else st_release_sys_u64(remote, value);

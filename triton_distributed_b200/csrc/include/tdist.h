@@ -91,6 +91,24 @@ typedef struct TdistGemmArgs {
     const void* src_flags;
     uint64_t src_epoch;
     int src_rank, src_world;
+    /* Row-gathering A through a staging matrix (preferred form of the above): with gather_dst set ([m_per_rank, K]
+     * workspace), `num_comm_sms` CTAs of the grid (default 8) copy the rows block by block into gather_dst, in the
+     * order the GEMM consumes them, and raise block_ready[b] = epoch (device uint32 per 128-row block, zero before
+     * the first call, epochs strictly increasing); the GEMM CTAs feed on gather_dst with TMA and wait per block. The
+     * copy of one block overlaps the MMAs of the blocks before it, and with block_src the all-gather in flight. */
+    void* gather_dst;
+    void* block_ready;
+    /* device uint32, zero before the first call, may be NULL: with it, ALL CTAs of the grid first stage the blocks
+     * the first wave of tiles needs (ld/st copies, a warp per row) so the MMAs do not wait for the few gatherer CTAs
+     * to get ahead; without it the gatherer CTAs stage every block */
+    void* gather_counter;
+    /* device int32, may be NULL: 128-row block the schedule starts at (blocks are visited cyclically from there),
+     * e.g. the first block of this rank's own tokens */
+    const void* block_rot;
+    /* Scattering epilogue (PLAIN, one CTA per tile), optional: row r of the product goes to row c_scatter[r] (device
+     * int32) of the matrix at `c` ([c_rows, N]); rows whose index is outside [0, c_rows) are dropped (padding). */
+    const void* c_scatter;
+    int c_rows;
 } TdistGemmArgs;
 
 int tdist_gemm_run(const TdistGemmArgs* args);
@@ -338,6 +356,11 @@ typedef struct TdistDecodeArgs {
     void* epoch_ptr;
     void* epoch_done;
     void* ll_peer_alt[TDIST_MAX_RANKS];
+    /* mode 2, optional: multicast alias (heap bound to an NVSwitch multicast object) of this call's parity of the
+     * gather buffer; the exchange then takes one multimem.st per packet instead of one store per rank.
+     * ll_mc_alt = the odd-call parity, needed with epoch_ptr. */
+    void* ll_mc;
+    void* ll_mc_alt;
 } TdistDecodeArgs;
 
 int tdist_flash_decode(const TdistDecodeArgs* args);
@@ -348,7 +371,8 @@ int tdist_lse_combine(const void* parts, int ranks, int heads, int head_dim, voi
 enum {
     TDIST_PRIM_RING_PUT = 0, TDIST_PRIM_NOTIFY_WAIT = 1, TDIST_PRIM_NOTIFY_ADD = 2, TDIST_PRIM_PUT_SIGNAL = 3,
     TDIST_PRIM_PUT_QUIET_SIGNAL = 4, TDIST_PRIM_GET = 5, TDIST_PRIM_BROADCAST = 6, TDIST_PRIM_FCOLLECT = 7,
-    TDIST_PRIM_GRID_BARRIER = 8, TDIST_PRIM_SCOPED_OPS = 9
+    TDIST_PRIM_GRID_BARRIER = 8, TDIST_PRIM_SCOPED_OPS = 9, TDIST_PRIM_BARRIER = 10,
+    TDIST_PRIM_BOUNDS_PROBE = 11   /* only in the bounds-checked build: accesses that must be recorded and skipped */
 };
 
 typedef struct TdistPrimArgs {
@@ -366,6 +390,8 @@ typedef struct TdistPrimArgs {
     void* stream;
 } TdistPrimArgs;
 
+/* 1 when this library was compiled with -DTDIST_BOUNDS_CHECK (checked symmetric-address translation), else 0 */
+int tdist_bounds_checked(void);
 int tdist_primitive(const TdistPrimArgs* args);
 
 #ifdef __cplusplus

@@ -363,6 +363,8 @@ extern "C" int tdist_barrier_all(void* const* flags_peer, void* epoch_local, int
     for (int r = 0; r < world; ++r) win.base[r] = static_cast<char*>(flags_peer[r]);
     win.rank = rank;
     win.world = world;
+    win.bytes = 0;   // the caller passes bare pointers: the size of the flag object is not known here
+    win.dbg = static_cast<Status*>(status);
     BarrierState st;
     st.flags = static_cast<uint64_t*>(flags_peer[rank]);
     st.epoch = static_cast<uint64_t*>(epoch_local);

@@ -57,6 +57,8 @@ struct DecodeParams {
     unsigned* epoch_ptr;    // SP, optional: device-resident call number (see TdistDecodeArgs)
     unsigned* epoch_done;
     char* ll_peer_alt[kMaxRanks];
+    char* ll_mc;            // SP, optional: multicast alias of this call's parity of the gather buffer: one
+    char* ll_mc_alt;        // multimem.st per packet reaches every rank (alt = odd call numbers, device-resident epoch)
     WaitCtx wctx;
 };
 
@@ -411,8 +413,16 @@ __global__ void __launch_bounds__(kDecodeThreads, (D <= 128 ? 2 : 1)) flash_deco
     const int npk = G * W2 / 2;                                        // packets of this head group
     const size_t pk0 = (static_cast<size_t>(b) * p.Hq + kvh * G) * W2 / 2;  // first packet in a rank slot
     const size_t slot = static_cast<size_t>(p.B) * p.Hq * W2 / 2;      // packets per source rank
+    char* mc = p.ll_mc;
+    if (p.epoch_ptr != nullptr && (epoch & 1u)) mc = p.ll_mc_alt;
     for (int i = tid; i < npk; i += kDecodeThreads) {
         const uint64_t payload = *reinterpret_cast<const uint64_t*>(merged + 2 * i);
+        if (mc != nullptr) {
+            // one store into the NVSwitch multicast alias lands in every rank's buffer (this rank's included). Each
+            // 8-byte half of the packet carries its own flag copy, so a packet split on the way is still detected.
+            ll_store_multimem(mc + (static_cast<size_t>(p.rank) * slot + pk0 + i) * 16, payload, epoch);
+            continue;
+        }
         for (int r = 0; r < p.world; ++r) {
             int peer = p.rank + r;
             if (peer >= p.world) peer -= p.world;
@@ -551,6 +561,10 @@ static int flash_decode_impl(const TdistDecodeArgs* a) {
         if (a->epoch == 0 && a->epoch_ptr == nullptr) return fail(TDIST_EINVAL, "decode: the epoch of a sequence-parallel call must be non-zero");
         if (a->epoch_ptr != nullptr && a->epoch_done == nullptr) return fail(TDIST_EINVAL, "decode: epoch_ptr needs epoch_done");
         p.epoch_ptr = static_cast<unsigned*>(a->epoch_ptr);
+        p.ll_mc = a->world > 1 ? static_cast<char*>(a->ll_mc) : nullptr;
+        p.ll_mc_alt = a->world > 1 ? static_cast<char*>(a->ll_mc_alt) : nullptr;
+        if (a->epoch_ptr != nullptr && (p.ll_mc != nullptr) != (p.ll_mc_alt != nullptr))
+            return fail(TDIST_EINVAL, "decode: a device-resident call number needs both multicast aliases or none");
         p.epoch_done = static_cast<unsigned*>(a->epoch_done);
         for (int r = 0; r < a->world && a->epoch_ptr != nullptr; ++r) {
             p.ll_peer_alt[r] = static_cast<char*>(a->ll_peer_alt[r]);

@@ -119,8 +119,25 @@ struct GemmParams {
     const uint64_t* src_flags;
     uint64_t src_epoch;
     int src_rank, src_world;    // this rank and the size of the all-gather's group
+    // Staged row gather (PLAIN): the first num_comm CTAs copy the rows of block b into gather_dst (the matrix tm_a
+    // describes) and raise block_ready[b] = epoch; the TMA producers wait per block.
+    char* gather_dst;
+    uint32_t* block_ready;
+    uint32_t* gather_counter;   // arrival counter of the all-CTA prologue (zero between launches)
+    int gather_pro_blocks;      // blocks the prologue stages
+    const int* block_rot;       // device scalar: block the schedule starts at (cyclic), nullptr = 0
+    // Scattering epilogue (PLAIN, one CTA per tile): row r of the product goes to row c_scatter[r] of c_out.
+    const int* c_scatter;
+    char* c_out;
+    int c_rows;
     WaitCtx wctx;
 };
+
+// Block the schedule visits i-th when it starts at block `rot` and wraps around after `live` blocks.
+__device__ __forceinline__ int rotate_block(int i, int rot, int live) {
+    int b = i + rot;
+    return b >= live ? b - live : b;
+}
 
 __device__ __forceinline__ void cp_async16(uint32_t dst, const void* src, int src_bytes) {
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(src_bytes) : "memory");
@@ -334,6 +351,126 @@ __device__ void ag_pusher_nvls(const GemmParams& p, uint8_t* smem, uint64_t* bar
 }
 
 // ------------------------------------------------------------------------------------------
+// Local gatherer (grouped GEMM over rows picked by index): the comm CTAs copy the rows of one 128-row block after
+// the other into the staging matrix the TMA producers read, in the order the GEMM visits the blocks, and publish
+// one flag per block. With block_src the rows of a block come from another rank's segment of an all-gather that may
+// still be in flight: the gatherer waits for that rank's arrival flag first, so the MMAs of the blocks that are
+// already here run while the later segments are still on the wire. Plays the role of the reference's
+// `kernel_consumer_m_parallel_scatter_group_gemm` gathering A rows by `sorted_token_ids` behind a per-rank barrier
+// (kernels/nvidia/allgather_group_gemm.py:229-314).
+// ------------------------------------------------------------------------------------------
+// Blocks (in schedule order) that every CTA of the grid helps to stage before the MMAs start: what the first wave of
+// tiles touches, cut short at the first block whose rows belong to another rank's segment (those may not be here yet).
+__device__ __forceinline__ int gather_prologue_blocks(const GemmParams& p, int live, int rot) {
+    int pro = min(live, p.gather_pro_blocks);
+    if (p.block_src != nullptr) {
+        for (int i = 0; i < pro; ++i) {
+            const int src = p.block_src[rotate_block(i, rot, live)];
+            if (src != p.src_rank && src >= 0 && src < p.src_world) return i;
+        }
+    }
+    return pro;
+}
+
+// All CTAs, all threads: copy the rows of the first `pro` blocks (a warp per row, rows dealt round-robin over the grid);
+// the last CTA to finish publishes their flags.
+__device__ void gather_prologue(const GemmParams& p, int pro, int live, int rot) {
+    const int tid = static_cast<int>(threadIdx.x);
+    const int warp = tid >> 5, lane = tid & 31;
+    const int nwarps = static_cast<int>(blockDim.x) >> 5;
+    const size_t row_bytes = static_cast<size_t>(p.k) * 2;
+    for (int g = static_cast<int>(blockIdx.x) * nwarps + warp; g < pro * BM; g += static_cast<int>(gridDim.x) * nwarps) {
+        const int row = rotate_block(g / BM, rot, live) * BM + (g % BM);
+        if (row >= p.m_per_rank) continue;
+        const int idx = p.a_gather[row];
+        if (idx < 0 || idx >= p.a_gather_rows) continue;   // padding row: its product is never used
+        const char* src = p.a_raw + static_cast<size_t>(idx) * row_bytes;
+        char* dst = p.gather_dst + static_cast<size_t>(row) * row_bytes;
+        for (size_t off = static_cast<size_t>(lane) * 16; off < row_bytes; off += 8 * 512) {
+            uint4 q[8];
+#pragma unroll
+            for (int u = 0; u < 8; ++u)
+                if (off + u * 512 < row_bytes) q[u] = *reinterpret_cast<const uint4*>(src + off + u * 512);
+#pragma unroll
+            for (int u = 0; u < 8; ++u)
+                if (off + u * 512 < row_bytes) *reinterpret_cast<uint4*>(dst + off + u * 512) = q[u];
+        }
+    }
+    // the CTA barrier orders every thread's stores before thread 0's arrival (gpu scope, acq_rel): the last CTA to
+    // arrive has every CTA's rows behind it when it raises the flags
+    __syncthreads();
+    if (tid == 0) {
+        const uint32_t old = atom_add_acq_rel_gpu_u32(p.gather_counter, 1);
+        if (old == gridDim.x - 1) {
+            *p.gather_counter = 0;
+            fence_acq_rel_gpu();
+            for (int i = 0; i < pro; ++i) st_release_gpu_u32(p.block_ready + rotate_block(i, rot, live), p.epoch);
+        }
+    }
+}
+
+// The remaining blocks: one thread per gatherer CTA streams the rows through shared memory with bulk-async copies
+// (the same ring as the AG pusher: loads run PUSH_AHEAD chunks ahead of the stores), a row (or a 32 KB piece of a
+// longer row) per chunk, and raises the block's flag once its stores have completed.
+__device__ void local_gatherer(const GemmParams& p, uint8_t* smem, uint64_t* bars, int pro, int live, int rot) {
+    if (threadIdx.x != 0) return;
+    const size_t row_bytes = static_cast<size_t>(p.k) * 2;
+    const int cpr = static_cast<int>((row_bytes + PUSH_CHUNK - 1) / PUSH_CHUNK);   // chunks per row
+    uint32_t it_load = 0, it_store = 0;
+    // chunk j of block b: false when its row is padding
+    auto chunk = [&](int b, int j, const char** src, char** dst, uint32_t* sz) -> bool {
+        const int r = j / cpr, c = j - r * cpr;
+        const int row = b * BM + r;
+        if (row >= p.m_per_rank) return false;
+        const int idx = p.a_gather[row];
+        if (idx < 0 || idx >= p.a_gather_rows) return false;
+        const size_t off = static_cast<size_t>(c) * PUSH_CHUNK;
+        *src = p.a_raw + static_cast<size_t>(idx) * row_bytes + off;
+        *dst = p.gather_dst + static_cast<size_t>(row) * row_bytes + off;
+        *sz = static_cast<uint32_t>(min(static_cast<size_t>(PUSH_CHUNK), row_bytes - off));
+        return true;
+    };
+    for (int i = pro + static_cast<int>(blockIdx.x); i < live; i += p.num_comm) {
+        const int b = rotate_block(i, rot, live);
+        if (p.block_src != nullptr) {
+            const int srcr = p.block_src[b];
+            if (srcr != p.src_rank && srcr >= 0 && srcr < p.src_world) {
+                signal_wait_until(p.src_flags + srcr, kCmpGe, p.src_epoch, p.wctx, srcr, 8);
+                fence_proxy_async();   // the segment was written by a peer's stores, the bulk loads below read it
+            }
+        }
+        if (p.debug_delay_ns > 0) __nanosleep(p.debug_delay_ns);
+        const int nchunks = BM * cpr;
+        for (int j = 0; j < nchunks + PUSH_AHEAD; ++j) {
+            const char* src;
+            char* dst;
+            uint32_t sz;
+            if (j < nchunks && chunk(b, j, &src, &dst, &sz)) {
+                const uint32_t s = it_load % PUSH_STAGES;
+                // the store that last used this buffer was issued at least PUSH_STAGES - PUSH_AHEAD chunks ago
+                if (it_load >= PUSH_STAGES) bulk_wait_read<PUSH_STAGES - PUSH_AHEAD - 1>();
+                mbar_expect_tx(smem_u32(&bars[s]), sz);
+                bulk_load(smem_u32(smem + s * PUSH_CHUNK), src, sz, smem_u32(&bars[s]));
+                ++it_load;
+            }
+            if (j >= PUSH_AHEAD && chunk(b, j - PUSH_AHEAD, &src, &dst, &sz)) {
+                const uint32_t s = it_store % PUSH_STAGES;
+                mbar_wait(smem_u32(&bars[s]), (it_store / PUSH_STAGES) & 1u, p.wctx, 12);
+                bulk_store(dst, smem_u32(smem + s * PUSH_CHUNK), sz);
+                bulk_commit();
+                ++it_store;
+            }
+        }
+        // the rows are complete in the staging matrix before the flag: wait for the writes themselves, then order
+        // them (async proxy) before the release store (generic proxy)
+        bulk_wait<0>();
+        fence_proxy_async();
+        fence_acq_rel_gpu();
+        st_release_gpu_u32(p.block_ready + b, p.epoch);
+    }
+}
+
+// ------------------------------------------------------------------------------------------
 // RS reduce: sum the `world` partial copies of one owned tile in fp32, write bf16/f16.
 // ------------------------------------------------------------------------------------------
 __device__ __forceinline__ void rs_reduce_tile(const GemmParams& p, int block, int n_tile) {
@@ -416,6 +553,23 @@ __global__ void __launch_bounds__(GATHER ? GATHER_THREADS : THREADS, 1) gemm_sm1
         if (p.a_ws_mc != nullptr) ag_pusher_nvls(p, smem, bars);
         else ag_pusher(p, smem, bars);
         return;
+    }
+
+    // ---------------- gatherer CTAs (grouped GEMM with a staged row gather) ----------------
+    if (MODE == TDIST_GEMM_PLAIN && CTAS == 1 && !GATHER && p.gather_dst != nullptr) {
+        const int live = min(p.seg_blocks, p.num_m_blocks ? *p.num_m_blocks : p.seg_blocks);
+        const int rot = p.block_rot ? min(max(*p.block_rot, 0), max(live - 1, 0)) : 0;
+        const int pro = gather_prologue_blocks(p, live, rot);
+        if (pro > 0) gather_prologue(p, pro, live, rot);
+        if (static_cast<int>(blockIdx.x) < p.num_comm) {
+            if (threadIdx.x == 0) {
+                for (int s = 0; s < PUSH_STAGES; ++s) mbar_init(smem_u32(&bars[s]), 1);
+                fence_mbar_init();
+            }
+            __syncthreads();
+            local_gatherer(p, smem, bars, pro, live, rot);
+            return;
+        }
     }
 
     // `unit` = the CTA (CTAS == 1) or the CTA pair (CTAS == 2) that owns a tile.
@@ -560,13 +714,21 @@ __global__ void __launch_bounds__(GATHER ? GATHER_THREADS : THREADS, 1) gemm_sm1
             unsigned long long waited = 0, blocked = 0;
             if (tr) tr[0] = globaltimer_ns();
             const int live_blocks = p.num_m_blocks ? *p.num_m_blocks : 0x7fffffff;
+            const int block_rot = p.block_rot ? min(max(*p.block_rot, 0), max(min(live_blocks, p.seg_m_tiles) - 1, 0)) : 0;
             Work tc;
             for (int round = 0; get_work<WIDE>(p, unit, num_units, round, first_seg, tc); ++round) {
                 if (tc.m_in_seg * CTAS >= live_blocks) continue;  // padding tile of a grouped GEMM: every role skips it
-                const int block = tc.m_in_seg * CTAS + cta_rank;  // 128-row block inside the segment
+                int block = tc.m_in_seg * CTAS + cta_rank;  // 128-row block inside the segment
+                if (MODE == TDIST_GEMM_PLAIN && CTAS == 1 && p.block_rot != nullptr)
+                    block = rotate_block(block, block_rot, min(live_blocks, p.seg_m_tiles));
                 const int bz = p.expert_ids ? p.expert_ids[block] : 0;
                 const CUtensorMap* am = &p.tm_a;
                 int az = tc.seg;
+                if (MODE == TDIST_GEMM_PLAIN && CTAS == 1 && p.block_ready != nullptr) {
+                    // the gatherer CTAs have copied this block's rows (generic-proxy stores, read next by TMA)
+                    wait_flag_ge_gpu(p.block_ready + block, p.epoch, p.wctx, -1, block, 7);
+                    fence_proxy_async();
+                }
                 if (MODE == TDIST_GEMM_AG) {
                     if (tc.seg == p.rank) {
                         am = &p.tm_a_own;
@@ -621,33 +783,35 @@ __global__ void __launch_bounds__(GATHER ? GATHER_THREADS : THREADS, 1) gemm_sm1
             Work tc;
             for (int round = 0; get_work<WIDE>(p, unit, num_units, round, first_seg, tc); ++round) {
                 if (tc.m_in_seg * CTAS >= live_blocks) continue;
+                // the four MMAs of one 256-column half over one K block (stage `s`, K block `kb` of the tile)
+                auto issue_half = [&](int h, int kb, uint32_t s) {
+                    const uint32_t slot = slot_of_half(tc, h, next_narrow);
+                    if (kb == 0) {
+                        // the epilogue has drained this slot's previous accumulator
+                        mbar_wait(bar_tempty(slot), ((slot ? uses1 : uses0) & 1u) ^ 1u, p.wctx, 3);
+                        tc_fence_after();
+                    }
+                    const uint32_t sa = smem_u32(smem + s * STAGE_BYTES);
+                    const uint32_t d_tmem = tmem_base + slot * BN;
+                    const uint64_t adesc = umma_desc_k_sw128(sa);
+                    const uint64_t bdesc = umma_desc_k_sw128(sa + A_BYTES + h * T::B_BYTES);
+#pragma unroll
+                    for (int k = 0; k < BK / UMMA_K; ++k) {
+                        // 16 elements of K = 32 bytes = 2 descriptor address units
+                        umma_bf16<CTAS>(d_tmem, adesc + 2 * k, bdesc + 2 * k, idesc, (kb | k) != 0 ? 1u : 0u);
+                    }
+                };
+                auto release_stage = [&](uint32_t s) {
+                    // frees the smem stage (in both CTAs) when the MMAs retire
+                    if (CTAS == 1) umma_commit(bar_empty(s));
+                    else umma_commit_pair(bar_empty(s), 3);
+                };
                 for (int kb = 0; kb < p.k_blocks; ++kb, ++it) {
                     const uint32_t s = it % STAGES;
                     mbar_wait(bar_full(s), (it / STAGES) & 1u, p.wctx, 4);
                     tc_fence_after();
-                    const uint32_t sa = smem_u32(smem + s * STAGE_BYTES);
-                    const uint64_t adesc = umma_desc_k_sw128(sa);
-#pragma unroll
-                    for (int h = 0; h < T::HALVES; ++h) {
-                        if (h < tc.halves) {
-                            const uint32_t slot = slot_of_half(tc, h, next_narrow);
-                            if (kb == 0) {
-                                // the epilogue has drained this slot's previous accumulator
-                                mbar_wait(bar_tempty(slot), (((slot ? uses1 : uses0)) & 1u) ^ 1u, p.wctx, 3);
-                                tc_fence_after();
-                            }
-                            const uint32_t d_tmem = tmem_base + slot * BN;
-                            const uint64_t bdesc = umma_desc_k_sw128(sa + A_BYTES + h * T::B_BYTES);
-#pragma unroll
-                            for (int k = 0; k < BK / UMMA_K; ++k) {
-                                // 16 elements of K = 32 bytes = 2 descriptor address units
-                                umma_bf16<CTAS>(d_tmem, adesc + 2 * k, bdesc + 2 * k, idesc, (kb | k) != 0 ? 1u : 0u);
-                            }
-                        }
-                    }
-                    // frees the smem stage (in both CTAs) when the MMAs retire
-                    if (CTAS == 1) umma_commit(bar_empty(s));
-                    else umma_commit_pair(bar_empty(s), 3);
+                    for (int h = 0; h < tc.halves; ++h) issue_half(h, kb, s);
+                    release_stage(s);
                 }
                 for (int h = 0; h < tc.halves; ++h) {
                     const uint32_t slot = slot_of_half(tc, h, next_narrow);
@@ -674,13 +838,23 @@ __global__ void __launch_bounds__(GATHER ? GATHER_THREADS : THREADS, 1) gemm_sm1
         uint32_t* pend0 = nullptr;   // older
         uint32_t* pend1 = nullptr;   // younger
         const int live_blocks = p.num_m_blocks ? *p.num_m_blocks : 0x7fffffff;
+        const int block_rot = p.block_rot ? min(max(*p.block_rot, 0), max(min(live_blocks, p.seg_m_tiles) - 1, 0)) : 0;
+        const bool scatter = MODE == TDIST_GEMM_PLAIN && CTAS == 1 && p.c_scatter != nullptr;
         Work tc;
         for (int round = 0; get_work<WIDE>(p, unit, num_units, round, first_seg, tc); ++round) {
             if (tc.m_in_seg * CTAS >= live_blocks) continue;
             const CUtensorMap* cm = (MODE == TDIST_GEMM_RS) ? &p.tm_c[tc.seg] : &p.tm_c[0];
             const int cz = (MODE == TDIST_GEMM_RS) ? p.rank : tc.seg;
-            const int block = tc.m_in_seg * CTAS + cta_rank;
+            int block = tc.m_in_seg * CTAS + cta_rank;
+            if (MODE == TDIST_GEMM_PLAIN && CTAS == 1 && p.block_rot != nullptr)
+                block = rotate_block(block, block_rot, min(live_blocks, p.seg_m_tiles));
             const int row = block * BM;
+            // scattering epilogue: the output row of this thread's row of the tile (-1 = padding, dropped)
+            int out_row = -1;
+            if (scatter && row + row_in_tile < p.m_per_rank) {
+                out_row = p.c_scatter[row + row_in_tile];
+                if (out_row >= p.c_rows) out_row = -1;
+            }
             for (int h = 0; h < tc.halves; ++h) {
                 const uint32_t buf = slot_of_half(tc, h, next_narrow);
                 mbar_wait(bar_tfull(buf), (buf ? uses1 : uses0) & 1u, p.wctx, 5);
@@ -703,6 +877,32 @@ __global__ void __launch_bounds__(GATHER ? GATHER_THREADS : THREADS, 1) gemm_sm1
                             if (CTAS == 1) mbar_arrive(bar_tempty(buf));
                             else mbar_arrive_cluster(bar_tempty(buf), 0);
                         }
+                    }
+                    if (scatter) {
+                        // every thread owns one row of the tile: 64 columns = 128 contiguous bytes of its output row
+                        if (out_row >= 0) {
+                            char* orow = p.c_out + (static_cast<size_t>(out_row) * p.n + col + c * EPI_COLS) * 2;
+#pragma unroll
+                            for (int j = 0; j < 8; ++j) {
+                                const uint32_t* r = j < 4 ? r0 + 8 * j : r1 + 8 * (j - 4);
+                                if (col + c * EPI_COLS + j * 8 < p.n) {
+                                    uint4 v;
+                                    if (p.is_f16) {
+                                        v.x = pack_f16x2(__uint_as_float(r[0]), __uint_as_float(r[1]));
+                                        v.y = pack_f16x2(__uint_as_float(r[2]), __uint_as_float(r[3]));
+                                        v.z = pack_f16x2(__uint_as_float(r[4]), __uint_as_float(r[5]));
+                                        v.w = pack_f16x2(__uint_as_float(r[6]), __uint_as_float(r[7]));
+                                    } else {
+                                        v.x = pack_bf16x2(__uint_as_float(r[0]), __uint_as_float(r[1]));
+                                        v.y = pack_bf16x2(__uint_as_float(r[2]), __uint_as_float(r[3]));
+                                        v.z = pack_bf16x2(__uint_as_float(r[4]), __uint_as_float(r[5]));
+                                        v.w = pack_bf16x2(__uint_as_float(r[6]), __uint_as_float(r[7]));
+                                    }
+                                    *reinterpret_cast<uint4*>(orow + j * 16) = v;
+                                }
+                            }
+                        }
+                        continue;
                     }
                     uint8_t* cs = cstage + (c & 1) * EPI_BYTES;
                     named_barrier(1, 128);  // the store that last read this buffer has drained
@@ -810,7 +1010,8 @@ using namespace tdist;
 using tdist_host::fail;
 
 static bool use_pair(const TdistGemmArgs* a) {
-    if (a->expert_ids != nullptr || a->a_gather != nullptr) return false;  // one expert / one source per 128-row block
+    if (a->expert_ids != nullptr || a->a_gather != nullptr || a->c_scatter != nullptr || a->block_rot != nullptr)
+        return false;  // one expert / one source / one output row per 128-row block and thread
     if (a->cta_pair == 0) return false;
     if (a->cta_pair > 0) return true;
     return a->m_per_rank > BM;  // a second CTA would only compute padding otherwise
@@ -933,6 +1134,12 @@ static GridPlan plan_grid(const TdistGemmArgs* a) {
         if (g.num_comm > sms - g.ctas_per_tile) g.num_comm = sms - g.ctas_per_tile;
         if (g.num_comm < g.ctas_per_tile) g.num_comm = g.ctas_per_tile;
     }
+    if (a->mode == TDIST_GEMM_PLAIN && a->gather_dst != nullptr) {
+        // gatherer CTAs: a CTA copies ~100 GB/s; the rows have to be in place a block ahead of the MMAs
+        g.num_comm = a->num_comm_sms > 0 ? a->num_comm_sms : 8;
+        if (g.num_comm > sms / 2) g.num_comm = sms / 2;
+        if (g.num_comm < 1) g.num_comm = 1;
+    }
     int units = (sms - g.num_comm) / g.ctas_per_tile;
     // a wide schedule may split its last round in two: allow up to twice the items
     const int most = g.wide ? 2 * g.num_tiles : g.num_tiles;
@@ -954,6 +1161,10 @@ extern "C" int tdist_gemm_run(const TdistGemmArgs* a) {
     if (a->mode < TDIST_GEMM_PLAIN || a->mode > TDIST_GEMM_RS) return fail(TDIST_EINVAL, "bad mode");
     if (a->expert_ids != nullptr && (a->mode != TDIST_GEMM_PLAIN || a->world != 1))
         return fail(TDIST_EINVAL, "grouped GEMM (expert_ids) is a single-rank plain-mode feature");
+    if ((a->gather_dst != nullptr) != (a->block_ready != nullptr) || (a->gather_dst != nullptr && a->a_gather == nullptr))
+        return fail(TDIST_EINVAL, "the staged row gather needs a_gather, gather_dst and block_ready together");
+    if ((a->c_scatter != nullptr || a->block_rot != nullptr) && (a->mode != TDIST_GEMM_PLAIN || a->world != 1 || a->cta_pair > 0))
+        return fail(TDIST_EINVAL, "c_scatter / block_rot are plain-mode, one-CTA-per-tile features");
     if (a->a_gather != nullptr) {
         if (a->mode != TDIST_GEMM_PLAIN || a->world != 1) return fail(TDIST_EINVAL, "row-gathering A is a plain-mode feature (world = 1 in the GEMM's own terms)");
         if (a->a_gather_rows < 1) return fail(TDIST_EINVAL, "row-gathering A needs the number of source rows");
@@ -972,6 +1183,7 @@ extern "C" int tdist_gemm_run(const TdistGemmArgs* a) {
         // A (or the gather workspace): {K, m_per_rank, world}
         const void* base = a->mode == TDIST_GEMM_AG ? a->a_ws : a->a;
         if (a->mode == TDIST_GEMM_AG && a->world == 1) base = a->a;
+        if (a->gather_dst != nullptr) base = a->gather_dst;   // the gatherer CTAs fill it, TMA reads it
         if (base == nullptr) return fail(TDIST_EINVAL, "A / workspace pointer is null");
         uint64_t dims[3] = {K, MPR, W};
         uint64_t strides[2] = {K * 2, MPR * K * 2};
@@ -1000,9 +1212,11 @@ extern "C" int tdist_gemm_run(const TdistGemmArgs* a) {
                 if (a->c_stage_peer[r] == nullptr) return fail(TDIST_EINVAL, "RS staging pointer is null");
                 if ((rc = tdist_host::encode_tmap(&p.tm_c[r], dt, 2, 3, a->c_stage_peer[r], dims, strides, box, tdist_host::Swizzle::B128))) return rc;
             }
-        } else {
+        } else if (a->c_scatter == nullptr) {
             if (a->c == nullptr) return fail(TDIST_EINVAL, "C pointer is null");
             if ((rc = tdist_host::encode_tmap(&p.tm_c[0], dt, 2, 3, a->c, dims, strides, box, tdist_host::Swizzle::B128))) return rc;
+        } else if (a->c == nullptr || a->c_rows < 1) {
+            return fail(TDIST_EINVAL, "the scattering epilogue needs C and its row count");
         }
     }
     p.a_own = static_cast<const char*>(a->a);
@@ -1018,6 +1232,20 @@ extern "C" int tdist_gemm_run(const TdistGemmArgs* a) {
     p.src_epoch = a->src_epoch;
     p.src_rank = a->src_rank;
     p.src_world = a->src_world;
+    p.gather_dst = static_cast<char*>(a->gather_dst);
+    p.block_ready = static_cast<uint32_t*>(a->block_ready);
+    p.gather_counter = static_cast<uint32_t*>(a->gather_counter);
+    {
+        // the first wave of tiles: one tile per GEMM CTA, rows of tiles GROUP_M blocks deep
+        const int gm = a->group_m > 0 ? a->group_m : DEFAULT_GROUP_M;
+        const int n_tiles = (a->n + BN - 1) / BN;
+        const int first_wave = (plan.grid - plan.num_comm + n_tiles - 1) / n_tiles;
+        p.gather_pro_blocks = a->gather_counter != nullptr ? (first_wave + gm - 1) / gm * gm : 0;
+    }
+    p.block_rot = static_cast<const int*>(a->block_rot);
+    p.c_scatter = static_cast<const int*>(a->c_scatter);
+    p.c_out = static_cast<char*>(a->c);
+    p.c_rows = a->c_rows;
     p.stage_local = static_cast<const char*>(a->c_stage_peer[a->rank]);
     p.a_ws_mc = (a->mode == TDIST_GEMM_AG && a->world > 1) ? static_cast<char*>(a->a_ws_mc) : nullptr;
     p.rs_out = a->rs_out;
@@ -1061,7 +1289,7 @@ extern "C" int tdist_gemm_run(const TdistGemmArgs* a) {
     cudaStream_t stream = static_cast<cudaStream_t>(a->stream);
     const void* fn = kernel_of(ctas, plan.wide, a->mode);  // smem opt-in done by resident_ctas()
     int block_threads = THREADS;
-    if (a->a_gather != nullptr) {
+    if (a->a_gather != nullptr && a->gather_dst == nullptr) {
         fn = reinterpret_cast<const void*>(&gemm_sm100_kernel<TDIST_GEMM_PLAIN, 1, true>);
         block_threads = GATHER_THREADS;
         static bool attr_set[64] = {};

@@ -88,17 +88,100 @@ __global__ void prim_kernel(const PrimParams p) {
             }
             if ((p.phase & 2) && t0) p.result[0] = signal_wait_until(p.sig + 3, kCmpGe, p.value, p.wctx, prev, 4) ? 1 : 0;
             break;
-        case TDIST_PRIM_GET:  // getmem_block: pull prev's source slot into my slot `prev`
-            if ((p.phase & 2) && blockIdx.x == 0) getmem_block(p.win, slot(p, prev), slot(p, world), p.nbytes, prev);
+        case TDIST_PRIM_GET:  // getmem at the requested scope: pull prev's source slot into my slot `prev`
+            if ((p.phase & 2) && blockIdx.x == 0) {
+                if (p.scope == 0) {
+                    if (threadIdx.x == 0) getmem_nbi(p.win, slot(p, prev), slot(p, world), p.nbytes, prev);
+                } else if (p.scope == 1) {
+                    if (threadIdx.x < 32) getmem_nbi_warp(p.win, slot(p, prev), slot(p, world), p.nbytes, prev);
+                } else {
+                    getmem_block(p.win, slot(p, prev), slot(p, world), p.nbytes, prev);
+                }
+            }
             break;
-        case TDIST_PRIM_BROADCAST:  // root 0's source slot lands in everybody's slot 0, then a barrier
-            if ((p.phase & 1) && blockIdx.x == 0) broadcast_block(p.win, slot(p, 0), slot(p, world), p.nbytes, 0);
-            if ((p.phase & 2) && blockIdx.x == 0 && p.phase == 3) p.result[0] = barrier_all_block(p.sigwin, p.barrier, p.wctx) ? 1 : 0;
+        case TDIST_PRIM_BROADCAST:  // root 0's source slot lands in everybody's slot 0, then a barrier of the same scope
+            if ((p.phase & 1) && blockIdx.x == 0) {
+                if (p.scope == 0) {
+                    if (threadIdx.x == 0) broadcast(p.win, slot(p, 0), slot(p, world), p.nbytes, 0);
+                } else if (p.scope == 1) {
+                    if (threadIdx.x < 32) broadcast_warp(p.win, slot(p, 0), slot(p, world), p.nbytes, 0);
+                } else {
+                    broadcast_block(p.win, slot(p, 0), slot(p, world), p.nbytes, 0);
+                }
+            }
+            if (p.phase == 3 && blockIdx.x == 0) {
+                if (p.scope == 0) {
+                    if (threadIdx.x == 0) p.result[0] = barrier_all(p.sigwin, p.barrier, p.wctx) ? 1 : 0;
+                } else if (p.scope == 1) {
+                    if (threadIdx.x < 32) {
+                        const bool ok = sync_all_warp(p.sigwin, p.barrier, p.wctx);
+                        if (threadIdx.x == 0) p.result[0] = ok ? 1 : 0;
+                    }
+                } else {
+                    p.result[0] = barrier_all_block(p.sigwin, p.barrier, p.wctx) ? 1 : 0;
+                }
+            }
             break;
         case TDIST_PRIM_FCOLLECT:  // everybody's source slot lands in slot `rank` of everybody
-            if ((p.phase & 1) && blockIdx.x == 0) fcollect_block(p.win, slot(p, 0), slot(p, world), p.nbytes);
-            if ((p.phase & 2) && blockIdx.x == 0 && p.phase == 3) p.result[0] = barrier_all_block(p.sigwin, p.barrier, p.wctx) ? 1 : 0;
+            if ((p.phase & 1) && blockIdx.x == 0) {
+                if (p.scope == 0) {
+                    if (threadIdx.x == 0) fcollect(p.win, slot(p, 0), slot(p, world), p.nbytes);
+                } else if (p.scope == 1) {
+                    if (threadIdx.x < 32) fcollect_warp(p.win, slot(p, 0), slot(p, world), p.nbytes);
+                } else {
+                    fcollect_block(p.win, slot(p, 0), slot(p, world), p.nbytes);
+                }
+            }
+            if (p.phase == 3 && blockIdx.x == 0) {
+                if (p.scope == 0) {
+                    if (threadIdx.x == 0) p.result[0] = sync_all(p.sigwin, p.barrier, p.wctx) ? 1 : 0;
+                } else if (p.scope == 1) {
+                    if (threadIdx.x < 32) {
+                        const bool ok = barrier_all_warp(p.sigwin, p.barrier, p.wctx);
+                        if (threadIdx.x == 0) p.result[0] = ok ? 1 : 0;
+                    }
+                } else {
+                    p.result[0] = barrier_all_block(p.sigwin, p.barrier, p.wctx) ? 1 : 0;
+                }
+            }
             break;
+        case TDIST_PRIM_BARRIER:  // barrier_all at the requested scope, `value` rounds back to back
+            if (p.phase == 3 && blockIdx.x == 0) {
+                int fails = 0;
+                for (uint64_t it = 0; it < p.value; ++it) {
+                    bool ok = true;
+                    if (p.scope == 0) {
+                        if (threadIdx.x == 0) ok = barrier_all(p.sigwin, p.barrier, p.wctx);
+                    } else if (p.scope == 1) {
+                        if (threadIdx.x < 32) ok = barrier_all_warp(p.sigwin, p.barrier, p.wctx);
+                    } else {
+                        ok = barrier_all_block(p.sigwin, p.barrier, p.wctx);
+                    }
+                    fails += ok ? 0 : 1;
+                }
+                if (threadIdx.x == 0) p.result[0] = fails;
+            }
+            break;
+#ifdef TDIST_BOUNDS_CHECK
+        case TDIST_PRIM_BOUNDS_PROBE:
+            // Three accesses that leave the symmetric object or name a rank that does not exist. The checked
+            // translation records the first and skips all of them; result[1] counts what was skipped.
+            if (t0) {
+                int skipped = 0;
+                // (a) a put whose span runs 16 bytes past the end of the object
+                char* last = slot(p, world + 1);
+                if (symm_span(p.win, last, static_cast<size_t>(p.nbytes) + 16, next, 1) == nullptr) ++skipped;
+                putmem(p.win, last, slot(p, world), static_cast<size_t>(p.nbytes) + 16, next);
+                // (b) a single-element put to rank `world`
+                if (symm_at(p.win, reinterpret_cast<int*>(slot(p, 0)), world) == nullptr) ++skipped;
+                int_p(p.win, reinterpret_cast<int*>(slot(p, 0)), 12345, world);
+                // (c) a signal on a word past the signal array
+                if (symm_at(p.sigwin, p.sig + 16, next) == nullptr) ++skipped;
+                signal_op(p.sigwin, p.sig + 16, 1, kSignalSet, next);
+                p.result[1] = skipped;
+            }
+            break;
+#endif
         case TDIST_PRIM_GRID_BARRIER: {  // every CTA publishes, all meet, every CTA reads its neighbour
             int* buf = reinterpret_cast<int*>(slot(p, 0));
             if (threadIdx.x == 0) buf[blockIdx.x] = static_cast<int>(blockIdx.x) + static_cast<int>(p.value);
@@ -181,10 +264,22 @@ __global__ void shmem_scopes_compile_check(SymmWindow win, BarrierState st, char
 
 using namespace tdist;
 
+extern "C" int tdist_bounds_checked(void) {
+#ifdef TDIST_BOUNDS_CHECK
+    return 1;
+#else
+    return 0;
+#endif
+}
+
 extern "C" int tdist_primitive(const TdistPrimArgs* a) {
     if (a->world < 1 || a->world > TDIST_MAX_RANKS || a->rank < 0 || a->rank >= a->world)
         return tdist_host::fail(TDIST_EINVAL, "primitive: world/rank out of range");
-    if (a->op < 0 || a->op > TDIST_PRIM_SCOPED_OPS) return tdist_host::fail(TDIST_EINVAL, "primitive: unknown op");
+    if (a->op < 0 || a->op > TDIST_PRIM_BOUNDS_PROBE) return tdist_host::fail(TDIST_EINVAL, "primitive: unknown op");
+#ifndef TDIST_BOUNDS_CHECK
+    if (a->op == TDIST_PRIM_BOUNDS_PROBE)
+        return tdist_host::fail(TDIST_EINVAL, "primitive: the bounds probe only exists in the bounds-checked build (TDIST_BOUNDS_CHECK=1)");
+#endif
     PrimParams p;
     memset(&p, 0, sizeof(p));
     for (int r = 0; r < a->world; ++r) {
@@ -194,6 +289,9 @@ extern "C" int tdist_primitive(const TdistPrimArgs* a) {
     }
     p.win.rank = p.sigwin.rank = a->rank;
     p.win.world = p.sigwin.world = a->world;
+    p.win.bytes = static_cast<size_t>(a->world + 2) * static_cast<size_t>(a->nbytes > 0 ? a->nbytes : 0);
+    p.sigwin.bytes = 16 * sizeof(uint64_t);
+    p.win.dbg = p.sigwin.dbg = static_cast<Status*>(a->status);
     p.data = p.win.base[a->rank];
     p.sig = reinterpret_cast<uint64_t*>(p.sigwin.base[a->rank]);
     p.result = static_cast<int*>(a->result);

@@ -19,6 +19,7 @@ from __future__ import annotations
 
 import ctypes as C
 import math
+import os
 from dataclasses import dataclass
 from typing import Optional
 
@@ -102,7 +103,7 @@ class _Workspace:
 
 def _launch(q, k_cache, v_cache, kv_lens, block_table, scale, soft_cap, out, mode, splits, max_kv=None,
             ll_ptrs=None, world=1, rank=0, epoch=0, workspace=None, stream=None, push_only=False,
-            ll_ptrs_odd=None, epoch_dev=None):
+            ll_ptrs_odd=None, epoch_dev=None, ll_mc=None, ll_mc_odd=None):
     global launch_count
     B, Hq, D = q.shape
     blocks, page, Hkv, Dk = k_cache.shape
@@ -133,6 +134,9 @@ def _launch(q, k_cache, v_cache, kv_lens, block_table, scale, soft_cap, out, mod
     a.push_only = int(push_only)
     if ll_ptrs is not None:
         a.ll_peer = ll_ptrs
+    if ll_mc is not None:
+        a.ll_mc = ll_mc
+        a.ll_mc_alt = ll_mc_odd
     if epoch_dev is not None:       # call number kept on the device: the launch can be captured and replayed
         a.ll_peer_alt = ll_ptrs_odd
         a.epoch_ptr = epoch_dev.data_ptr()
@@ -220,6 +224,11 @@ class SpDecodeContext:
     epoch_dev: Optional[torch.Tensor] = None
 
 
+# the sequence-parallel exchange through the NVSwitch multicast alias when the heap has one (TDIST_NVLS=1);
+# TDIST_SP_DECODE_NVLS=0 keeps the per-rank stores
+SP_DECODE_NVLS = os.environ.get("TDIST_SP_DECODE_NVLS", "1") == "1"
+
+
 def create_sp_decode_context(rank: int, world: int, max_batch: int, Hq: int, head_dim: int, heap=None, group=None,
                              device=None, device_epoch: bool = False) -> SpDecodeContext:
     ctx = SpDecodeContext(rank, world, max_batch, Hq, head_dim, group=group)
@@ -256,11 +265,14 @@ def sp_gqa_fwd_batch_decode(ctx: SpDecodeContext, q, k_cache, v_cache, global_kv
     if B > ctx.max_batch or Hq != ctx.Hq or D != ctx.head_dim:
         raise ValueError("shape exceeds the sequence-parallel context")
     o = out if out is not None else torch.empty_like(q)
+    # with a heap bound to an NVSwitch multicast object (TDIST_NVLS=1) the exchange stores every packet once
+    mc = ctx.gather.mc if (ctx.gather.mc is not None and ctx.world > 1 and SP_DECODE_NVLS) else None
     if ctx.epoch_dev is not None:
         halves = ctx.gather.half_ptr_arrays()
         return _launch(q, k_cache, v_cache, global_kv_lens[ctx.rank], block_table, scale, soft_cap, o, 2, kv_split,
                        max_kv=int(block_table.shape[1]) * k_cache.shape[1], ll_ptrs=halves[0], ll_ptrs_odd=halves[1],
-                       world=ctx.world, rank=ctx.rank, epoch=0, push_only=(phase == 1), epoch_dev=ctx.epoch_dev)
+                       world=ctx.world, rank=ctx.rank, epoch=0, push_only=(phase == 1), epoch_dev=ctx.epoch_dev,
+                       ll_mc=None if mc is None else mc[0].data_ptr(), ll_mc_odd=None if mc is None else mc[1].data_ptr())
     if phase != 2:
         ctx.epoch += 1  # phase 1 = compute and send only, phase 2 = redo with the same epoch and gather
     half = ctx.epoch & 1
@@ -269,7 +281,7 @@ def sp_gqa_fwd_batch_decode(ctx: SpDecodeContext, q, k_cache, v_cache, global_kv
     return _launch(q, k_cache, v_cache, global_kv_lens[ctx.rank], block_table, scale, soft_cap, o, 2, kv_split,
                    max_kv=int(block_table.shape[1]) * k_cache.shape[1],
                    ll_ptrs=ctx.gather.half_ptr_arrays()[half], world=ctx.world, rank=ctx.rank, epoch=ctx.epoch,
-                   push_only=(phase == 1))
+                   push_only=(phase == 1), ll_mc=None if mc is None else mc[half].data_ptr())
 
 
 kernel_inter_rank_gqa_fwd_batch_decode_combine_kv = inter_rank_combine   # the reference's name of the cross-rank merge

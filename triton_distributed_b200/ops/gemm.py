@@ -37,7 +37,7 @@ _DTYPES = {torch.bfloat16: _lib.DT_BF16, torch.float16: _lib.DT_F16}
 # number of native launches since import (bench.py reports it)
 launch_count = 0
 # tiling choice handed to the kernel: -1 = automatic, 0 = one CTA per 128x256 tile,
-# 1 = CTA pair (cta_group::2) per 256x256 tile
+# 1 = CTA pair (cta_group::2) per 256x256 tile, 2 = CTA pair per 256x512 tile; a context's `cta_pair` >= 0 overrides it
 CTA_PAIR = int(os.environ.get("TDIST_GEMM_CTA_PAIR", "-1"))
 # AG-GEMM pushers and multimem.st, when the heap has a multicast alias (TDIST_NVLS=1): 0 = never (default: on
 # 8 x B200 the multicast pusher measured 1.18 ms against 0.98 ms for the unicast one on m8192 n49152 k12288),
@@ -61,7 +61,7 @@ def _check_operands(a: torch.Tensor, b: torch.Tensor) -> None:
         raise ValueError("K and N must be multiples of 8")
 
 
-def _base_args(a, b, world, rank, mode, stream=None) -> "_lib.GemmArgs":
+def _base_args(a, b, world, rank, mode, stream=None, cta_pair: int = -1) -> "_lib.GemmArgs":
     g = _lib.GemmArgs()
     g.a = a.data_ptr()
     g.b = b.data_ptr()
@@ -74,7 +74,7 @@ def _base_args(a, b, world, rank, mode, stream=None) -> "_lib.GemmArgs":
     st = global_status()
     g.status = st.device_ptr if st is not None else None
     g.timeout_ns = default_timeout_ns()
-    g.cta_pair = CTA_PAIR
+    g.cta_pair = cta_pair if cta_pair >= 0 else CTA_PAIR
     g.group_m = GROUP_M
     g.stream = (stream or torch.cuda.current_stream(a.device)).cuda_stream
     return g
@@ -131,6 +131,7 @@ class AllGatherGEMMTensorParallelContext:
     epoch: int = 0
     num_comm_sms: int = 0   # 0 = sized per call from the bytes to push and the expected GEMM time
     num_sms: int = 0
+    cta_pair: int = -1      # >= 0 overrides the module-wide tiling choice for this context
     for_correctness: bool = False
     debug_delay_ns: int = 0
     trace: Optional[torch.Tensor] = None  # int64[2048] timeline buffer, filled by the kernel when set
@@ -178,7 +179,7 @@ def ag_gemm_intra_node(a: torch.Tensor, b: torch.Tensor, ctx: Optional[AllGather
     if mpr > ctx.max_m_per_rank or K != ctx.k:
         raise ValueError(f"shard {tuple(a.shape)} exceeds the context (max rows {ctx.max_m_per_rank}, K {ctx.k})")
     c = out if out is not None else torch.empty((ctx.world * mpr, N), dtype=a.dtype, device=a.device)
-    g = _base_args(a, b, ctx.world, ctx.rank, _lib.GEMM_AG)
+    g = _base_args(a, b, ctx.world, ctx.rank, _lib.GEMM_AG, cta_pair=ctx.cta_pair)
     g.c = c.data_ptr()
     g.m_per_rank = mpr
     ctx.epoch += 1
@@ -227,6 +228,7 @@ class GEMMReduceScatterTensorParallelContext:
     flags: Optional[SymmTensor] = None
     epoch: int = 0
     num_sms: int = 0
+    cta_pair: int = -1      # >= 0 overrides the module-wide tiling choice for this context
 
 
 def create_gemm_rs_context(max_M: int, N: int, rank: int, world_size: int, local_world_size: Optional[int] = None,
@@ -267,7 +269,7 @@ def gemm_rs(a: torch.Tensor, b: torch.Tensor, ctx: GEMMReduceScatterTensorParall
     o = out if out is not None else torch.empty((mpr, N), dtype=a.dtype, device=a.device)
     if ctx.world == 1:
         return gemm_persistent(a, b, out=o, num_sms=ctx.num_sms)  # nothing to scatter or reduce: skip the staging pass
-    g = _base_args(a, b, ctx.world, ctx.rank, _lib.GEMM_RS)
+    g = _base_args(a, b, ctx.world, ctx.rank, _lib.GEMM_RS, cta_pair=ctx.cta_pair)
     g.m_per_rank = mpr
     ctx.epoch += 1
     g.epoch = ctx.epoch

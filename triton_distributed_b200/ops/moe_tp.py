@@ -35,10 +35,17 @@ from . import gemm as G
 from . import moe_utils as MU
 
 GROUP_BLOCK_M = 128
-# True: the all-gather only sends and the grouped GEMM gathers its A rows itself (four cp.async producer warps),
-# waiting per 128-row block for the source rank's flag. False (default): all-gather, row-gather kernel, TMA-fed grouped
-# GEMM. The fused form measured 2.2x slower: sixteen-byte copies saturate the L2 request rate long before TMA does.
-FUSED_AG_GROUP_GEMM = False
+# How AllGather + GroupGEMM (and the A side of GroupGEMM + reduce-scatter) run:
+#   "staged"   all-gather kernel, row-gather kernel, TMA-fed grouped GEMM, un-sort kernel (four launches, no overlap);
+#   "fused"    (default) the all-gather only sends; ONE grouped-GEMM launch whose first CTAs copy the rows of each
+#              128-row block into the sorted staging matrix as the source rank's segment arrives (a flag per block),
+#              whose other CTAs feed on that matrix with TMA block by block, starting at this rank's own tokens, and
+#              whose epilogue stores every row straight to its (token, k) position: gather, all-gather wait and
+#              un-sort overlap the MMAs;
+#   "cp_async" the grouped GEMM's producer warps gather the rows themselves with 16-byte cp.async copies (kept for
+#              comparison: 2.2x slower than "staged", the L2 request rate saturates long before TMA does).
+AG_GROUP_GEMM_MODE = "fused"
+FUSED_AG_GROUP_GEMM = False   # legacy switch: True selects "cp_async"
 FUSED_TOPK_RS = True   # False: separate top-k reduce kernel, then the plain reduce-scatter (for A/B checks)
 launch_count = 0
 
@@ -132,32 +139,63 @@ def group_gemm(a_sorted: torch.Tensor, b: torch.Tensor, expert_ids: torch.Tensor
 def group_gemm_gather(a: torch.Tensor, row_index: torch.Tensor, b: torch.Tensor, expert_ids: torch.Tensor,
                       num_blocks: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None,
                       block_src: Optional[torch.Tensor] = None, src_flags: Optional[torch.Tensor] = None, src_epoch: int = 0,
-                      src_rank: int = 0, src_world: int = 1) -> torch.Tensor:
+                      src_rank: int = 0, src_world: int = 1, staging: Optional[torch.Tensor] = None,
+                      block_ready: Optional[torch.Tensor] = None, epoch: int = 1, block_rot: Optional[torch.Tensor] = None,
+                      c_scatter: Optional[torch.Tensor] = None, c_rows: int = 0, num_gather_ctas: int = 0) -> torch.Tensor:
     """Grouped GEMM whose A rows are gathered inside the kernel: ``out[r] = a[row_index[r]] @ b[expert_ids[r // 128]].T``
-    (rows with ``row_index >= a.shape[0]`` are padding and read as zeros). With ``block_src`` the rows of 128-row
+    (rows with ``row_index >= a.shape[0]`` are padding). With ``block_src`` the rows of 128-row
     block ``i`` come from rank ``block_src[i]``'s segment of an all-gather that may still be in flight: the kernel
     waits for that rank's arrival flag (``src_flags[rank] >= src_epoch``) before loading them, so blocks of ranks
-    that have arrived compute while later segments are still on the wire."""
+    that have arrived compute while later segments are still on the wire.
+
+    With ``staging`` (``[rows, K]`` workspace) and ``block_ready`` (int32 per 128-row block plus one trailing word, zero
+    before the first call; ``epoch`` strictly increasing per call) the gather is done by dedicated CTAs of the same launch into
+    ``staging`` and the GEMM is fed by TMA; without them the producer warps copy the rows with cp.async.
+    ``block_rot`` (device int32 scalar): block the schedule starts at. ``c_scatter`` (int32 per sorted row): the
+    epilogue stores row ``r`` of the product at row ``c_scatter[r]`` of ``out`` (``[c_rows, N]``), dropping rows whose
+    index is not below ``c_rows``."""
     rows = row_index.shape[0]
     E, N, K = b.shape
     if rows % GROUP_BLOCK_M:
         raise ValueError("grouped GEMM rows must be a multiple of 128")
     if a.device.type != "cuda":
         padded = torch.cat([a, a.new_zeros((1, K))])
-        return group_gemm(padded[row_index.long().clamp(max=a.shape[0])], b, expert_ids, num_blocks, out)
+        prod = group_gemm(padded[row_index.long().clamp(max=a.shape[0])], b, expert_ids, num_blocks)
+        if c_scatter is None:
+            return prod
+        o = out if out is not None else torch.zeros((c_rows, N), dtype=a.dtype)
+        live = c_scatter.long() < c_rows
+        o[c_scatter.long()[live]] = prod[live]
+        return o
     G._check_operands(a, b.view(E * N, K))
-    c = out if out is not None else torch.empty((rows, N), dtype=a.dtype, device=a.device)
+    if c_scatter is not None:
+        c = out if out is not None else torch.empty((c_rows, N), dtype=a.dtype, device=a.device)
+    else:
+        c = out if out is not None else torch.empty((rows, N), dtype=a.dtype, device=a.device)
     g = G._base_args(a, b.view(E * N, K), 1, 0, _lib.GEMM_PLAIN)
     g.n = N
     g.c = c.data_ptr()
     g.m_per_rank = rows
-    g.epoch = 1
+    g.epoch = epoch
     g.expert_ids = expert_ids.data_ptr()
     g.num_m_blocks = num_blocks.data_ptr() if num_blocks is not None else None
     g.num_experts = E
     g.cta_pair = 0
     g.a_gather = row_index.data_ptr()
     g.a_gather_rows = a.shape[0]
+    if staging is not None:
+        if block_ready is None or staging.shape[0] < rows or staging.shape[1] != K or staging.dtype != a.dtype:
+            raise ValueError("staging must be [rows, K] of a's dtype, with block_ready")
+        # block_ready carries one extra word at its end: the arrival counter of the all-CTA prologue
+        if block_ready.numel() < rows // GROUP_BLOCK_M + 1:
+            raise ValueError("block_ready needs one int32 per 128-row block plus one")
+        g.gather_dst, g.block_ready = staging.data_ptr(), block_ready.data_ptr()
+        g.gather_counter = block_ready.data_ptr() + 4 * (block_ready.numel() - 1)
+        g.num_comm_sms = num_gather_ctas
+    if block_rot is not None:
+        g.block_rot = block_rot.data_ptr()
+    if c_scatter is not None:
+        g.c_scatter, g.c_rows = c_scatter.data_ptr(), c_rows
     if block_src is not None:
         g.block_src = block_src.data_ptr()
         g.src_flags = src_flags.data_ptr()
@@ -188,6 +226,10 @@ class MoEAllGatherGroupGEMMTensorParallelContext:
     b_nk: Optional[torch.Tensor] = None          # [E, N, K] copy of the weights (K contiguous)
     row_index: Optional[torch.Tensor] = None     # int32 [sorted rows]: token of every sorted row (padding = M)
     pos_of: Optional[torch.Tensor] = None        # int32 [M * topk]: sorted row of every (token, k) pair
+    staging: Optional[torch.Tensor] = None       # [sorted rows, K]: the rows in sorted order, filled inside the GEMM launch
+    block_ready: Optional[torch.Tensor] = None   # int32 per 128-row block: call number at which its rows were staged
+    block_rot: Optional[torch.Tensor] = None     # int32 [1]: first block of this rank's own tokens
+    gemm_calls: int = 0
     calls: int = 0
 
 
@@ -222,6 +264,11 @@ def create_ag_group_gemm_intra_node_context(tp_pg, A: torch.Tensor, B: torch.Ten
     valid = ctx.sorted_ids < numel
     ctx.pos_of = torch.zeros(numel, dtype=torch.int32, device=ctx.sorted_ids.device)
     ctx.pos_of[ctx.sorted_ids[valid].long()] = torch.arange(ctx.sorted_ids.numel(), dtype=torch.int32, device=ctx.sorted_ids.device)[valid]
+    if A.device.type == "cuda":
+        ctx.staging = torch.empty((ctx.sorted_ids.numel(), K), dtype=A.dtype, device=A.device)
+        ctx.block_ready = torch.zeros(ctx.sorted_ids.numel() // GROUP_BLOCK_M + 1, dtype=torch.int32, device=A.device)
+        before = torch.cumsum(ctx.rank_block_num, 0) - ctx.rank_block_num
+        ctx.block_rot = before[rank:rank + 1].to(torch.int32).contiguous()
     if A.device.type == "cuda" and world > 1:
         heap = heap or symm_heap(tp_pg)
         # two gather buffers, alternated per call: a rank that is one call ahead pushes into the other one
@@ -258,16 +305,19 @@ def ag_group_gemm_intra_node(a: torch.Tensor, b: torch.Tensor, ctx: MoEAllGather
         buf = ctx.gather_buf.view_as((M, K), a.dtype, offset_bytes=half * ctx.max_M * K * a.element_size())
         if phase != 2:
             buf.local[ctx.rank * mpr:(ctx.rank + 1) * mpr].copy_(a)
-        if FUSED_AG_GROUP_GEMM:
-            # send half of the all-gather only; the grouped GEMM gathers its A rows itself and waits, block by
+        mode = "cp_async" if FUSED_AG_GROUP_GEMM else AG_GROUP_GEMM_MODE
+        if mode != "staged":
+            # send half of the all-gather only; the grouped GEMM launch gathers its A rows itself and waits, block by
             # block, for the arrival flag of the rank the block's tokens come from
             if phase != 2:
                 CO.fast_allgather(buf, ctx.ag_ctx, mode="push", phase=1)
             if phase == 1:
                 return None
-            c_sorted = group_gemm_gather(buf.local, ctx.row_index, b_nk, ctx.expert_ids, ctx.num_blocks,
-                                         block_src=ctx.block_barrier_ids, src_flags=ctx.ag_ctx.signal.local,
-                                         src_epoch=ctx.ag_ctx.epoch, src_rank=ctx.rank, src_world=ctx.world)
+            src = dict(block_src=ctx.block_barrier_ids, src_flags=ctx.ag_ctx.signal.local, src_epoch=ctx.ag_ctx.epoch,
+                       src_rank=ctx.rank, src_world=ctx.world)
+            if mode == "fused":
+                return _fused_group_gemm(ctx, buf.local, b_nk, numel, **src)
+            c_sorted = group_gemm_gather(buf.local, ctx.row_index, b_nk, ctx.expert_ids, ctx.num_blocks, **src)
             out, _ = gather_rows(c_sorted, ctx.pos_of, 1, c_sorted.shape[0])
             return out
         CO.fast_allgather(buf, ctx.ag_ctx, mode="push", phase=phase)
@@ -276,7 +326,10 @@ def ag_group_gemm_intra_node(a: torch.Tensor, b: torch.Tensor, ctx: MoEAllGather
         full = buf.local
     else:
         full = a
-    if FUSED_AG_GROUP_GEMM:
+    mode = "cp_async" if FUSED_AG_GROUP_GEMM else AG_GROUP_GEMM_MODE
+    if mode == "fused":
+        return _fused_group_gemm(ctx, full, b_nk, numel)
+    if mode == "cp_async":
         c_sorted = group_gemm_gather(full, ctx.row_index, b_nk, ctx.expert_ids, ctx.num_blocks)
         out, _ = gather_rows(c_sorted, ctx.pos_of, 1, c_sorted.shape[0])
         return out
@@ -284,6 +337,15 @@ def ag_group_gemm_intra_node(a: torch.Tensor, b: torch.Tensor, ctx: MoEAllGather
     c_sorted = group_gemm(a_sorted, b_nk, ctx.expert_ids, ctx.num_blocks)
     out, _ = gather_rows(c_sorted, pos_of, 1, c_sorted.shape[0])
     return out
+
+
+def _fused_group_gemm(ctx: MoEAllGatherGroupGEMMTensorParallelContext, full: torch.Tensor, b_nk: torch.Tensor, numel: int, **src):
+    """One launch: gatherer CTAs stage the rows block by block, TMA-fed MMAs start at this rank's own blocks, the
+    epilogue stores every row at its (token, k) position."""
+    ctx.gemm_calls += 1
+    return group_gemm_gather(full, ctx.row_index, b_nk, ctx.expert_ids, ctx.num_blocks, staging=ctx.staging,
+                             block_ready=ctx.block_ready, epoch=ctx.gemm_calls, block_rot=ctx.block_rot,
+                             c_scatter=ctx.sorted_ids, c_rows=numel, **src)
 
 
 # ---------------------------------------------------------------------------- GroupGEMM + reduce + RS
@@ -303,6 +365,10 @@ class MoEReduceRSContext:
     num_blocks: Optional[torch.Tensor] = None
     rs_ctx: Optional[CO.ReduceScatter2DContext] = None
     b_nk: Optional[torch.Tensor] = None   # [E, N, K/ws] copy of the weights, made on first use
+    pos_of: Optional[torch.Tensor] = None        # int32 [M * topk]: sorted row of every (token, k) pair
+    staging: Optional[torch.Tensor] = None       # [sorted rows, K/ws], allocated on first use
+    block_ready: Optional[torch.Tensor] = None
+    gemm_calls: int = 0
     _partial: Optional[torch.Tensor] = None
 
 
@@ -322,6 +388,10 @@ def create_moe_rs_context(pg, local_rank: int, world_size: int, local_world_size
         ctx.full_topk_ids, num_experts, 1, M, GROUP_BLOCK_M)
     ctx.sorted_ids = sorted_ids[: int(post_pad)].contiguous()
     ctx.num_blocks = (post_pad // GROUP_BLOCK_M).to(torch.int32)
+    numel = M * topk
+    valid = ctx.sorted_ids < numel
+    ctx.pos_of = torch.zeros(numel, dtype=torch.int32, device=ctx.sorted_ids.device)
+    ctx.pos_of[ctx.sorted_ids[valid].long()] = torch.arange(ctx.sorted_ids.numel(), dtype=torch.int32, device=ctx.sorted_ids.device)[valid]
     ctx.rs_ctx = CO.create_reduce_scater_2d_ctx(ctx.max_token_num, hidden_dim, local_rank, world_size, dtype=output_dtype,
                                                 heap=heap, group=pg, device=device)
     return ctx
@@ -345,10 +415,21 @@ def moe_reduce_rs(rank: int, world_size: int, local_world_size: int, a: torch.Te
         part = (y.view(M, ctx.topk, N) * ctx.full_topk_weight.view(M, ctx.topk, 1)).sum(1).to(a.dtype)
         return CO.reduce_scatter_2d_op(part, ctx.rs_ctx)
     if phase != 2:
-        a_sorted, pos_of = gather_rows(a, ctx.sorted_ids, 1, numel, want_inverse=True)
         if ctx.b_nk is None:
             ctx.b_nk = b.transpose(1, 2).contiguous()
-        ctx._partial = (group_gemm(a_sorted, ctx.b_nk, ctx.expert_ids, ctx.num_blocks), pos_of)
+        if AG_GROUP_GEMM_MODE == "fused":
+            # the sort of the rows by expert happens inside the grouped-GEMM launch (gatherer CTAs + TMA-fed MMAs)
+            if ctx.staging is None or ctx.staging.shape[1] != a.shape[1] or ctx.staging.dtype != a.dtype:
+                ctx.staging = torch.empty((ctx.sorted_ids.numel(), a.shape[1]), dtype=a.dtype, device=a.device)
+                ctx.block_ready = torch.zeros(ctx.sorted_ids.numel() // GROUP_BLOCK_M + 1, dtype=torch.int32, device=a.device)
+                ctx.gemm_calls = 0
+            ctx.gemm_calls += 1
+            y = group_gemm_gather(a, ctx.sorted_ids, ctx.b_nk, ctx.expert_ids, ctx.num_blocks, staging=ctx.staging,
+                                  block_ready=ctx.block_ready, epoch=ctx.gemm_calls)
+            ctx._partial = (y, ctx.pos_of)
+        else:
+            a_sorted, pos_of = gather_rows(a, ctx.sorted_ids, 1, numel, want_inverse=True)
+            ctx._partial = (group_gemm(a_sorted, ctx.b_nk, ctx.expert_ids, ctx.num_blocks), pos_of)
     y_sorted, pos_of = ctx._partial
     if FUSED_TOPK_RS and y_sorted.dtype == torch.bfloat16 and M % world_size == 0:
         # top-k weighted reduce and reduce-scatter in one kernel: the [M, N] partial is never written

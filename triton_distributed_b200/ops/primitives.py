@@ -22,6 +22,8 @@ OPS = {
     "ring_put": _lib.PRIM_RING_PUT, "notify_wait": _lib.PRIM_NOTIFY_WAIT, "notify_add": _lib.PRIM_NOTIFY_ADD,
     "put_signal": _lib.PRIM_PUT_SIGNAL, "put_quiet_signal": _lib.PRIM_PUT_QUIET_SIGNAL, "get": _lib.PRIM_GET,
     "broadcast": _lib.PRIM_BROADCAST, "fcollect": _lib.PRIM_FCOLLECT, "grid_barrier": _lib.PRIM_GRID_BARRIER, "scoped_ops": _lib.PRIM_SCOPED_OPS,
+    "barrier": _lib.PRIM_BARRIER,            # `value` rounds of barrier_all at the requested scope
+    "bounds_probe": _lib.PRIM_BOUNDS_PROBE,  # bounds-checked build only: out-of-range accesses that must be recorded and skipped
 }
 SCOPES = {"thread": 0, "warp": 1, "block": 2}
 

@@ -14,7 +14,7 @@ import torch
 from .. import _lib
 
 _CODES = {0: "ok", 1: "flag wait timed out", 2: "mbarrier wait timed out", 3: "bad argument"}
-_KERNELS = {1: "gemm_sm100", 2: "collectives", 3: "a2a", 4: "flash_decode", 5: "primitives", 6: "moe"}
+_KERNELS = {1: "gemm_sm100", 2: "collectives", 3: "a2a", 4: "flash_decode", 5: "primitives", 6: "moe", 7: "moe_ep", 8: "bounds check"}
 
 
 _TIMEOUT_CACHE = [None, 0]

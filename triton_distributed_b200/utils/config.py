@@ -23,13 +23,14 @@ class Config:
     ag_gemm_nvls: int = 0                # TDIST_AG_GEMM_NVLS: AG-GEMM pushers use multimem.st (0 never, 1 from 4 ranks, 2 always)
     gemm_cta_pair: int = -1              # TDIST_GEMM_CTA_PAIR: -1 automatic, 0 one CTA per 128x256 tile, 1 CTA pair per 256x256, 2 CTA pair per 256x512
     gemm_group_m: int = 0                # TDIST_GEMM_GROUP_M: row-tiles per raster group, 0 = kernel default (8)
+    bounds_check: bool = False           # TDIST_BOUNDS_CHECK: load the library built with checked symmetric-address translation
     nvtx: bool = False                   # TDIST_NVTX: wrap the ops in NVTX ranges (timelines of external profilers)
     nvcc: str = ""                       # TDIST_NVCC: compiler used by the build, empty = search PATH and /usr/local/cuda
 
     _ENV = {
         "wait_timeout_ms": "TDIST_WAIT_TIMEOUT_MS", "symm_heap_bytes": "TDIST_SYMM_HEAP_BYTES", "heap_backend": "TDIST_HEAP_BACKEND",
         "nvls": "TDIST_NVLS", "ag_gemm_nvls": "TDIST_AG_GEMM_NVLS", "gemm_cta_pair": "TDIST_GEMM_CTA_PAIR",
-        "gemm_group_m": "TDIST_GEMM_GROUP_M", "nvtx": "TDIST_NVTX", "nvcc": "TDIST_NVCC",
+        "gemm_group_m": "TDIST_GEMM_GROUP_M", "bounds_check": "TDIST_BOUNDS_CHECK", "nvtx": "TDIST_NVTX", "nvcc": "TDIST_NVCC",
     }
 
     @classmethod

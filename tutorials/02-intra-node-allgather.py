@@ -11,8 +11,16 @@ all segments.
 * ``push2d_ll_multimem`` one ``multimem.st`` per 16 bytes stores into ALL copies through the NVSwitch
                  (needs ``TDIST_NVLS=1`` so that the heap binds a multicast object; else it runs as LL).
 
+The last part of the script does the push variant once more with a kernel written against the OpenSHMEM-style device
+API of ``csrc/device/shmem.cuh`` (``tutorials/kernels/allgather_putmem_signal.cu``: ``putmem_signal_block`` into every
+peer, then ``signal_wait_until`` on this rank's own signal words), compiled here with
+``triton_distributed_b200.utils.user_kernels``: what a user of the primitives writes.
+
 (reference tutorials/02-intra-node-allgather.py; kernels/nvidia/low_latency_allgather.py)
 """
+import ctypes as C
+import os
+
 import torch
 
 from _common import dist_print, launch
@@ -42,7 +50,36 @@ def run(group, rank, world, dev):
                 CO.barrier_all_on_stream()
             _, ms = perf_func(step, 20, 5)
             dist_print(f"{mode:>20}: {ms * 1e3:7.1f} us per all-gather + barrier ({n * 4} bytes)")
+    if dev.type == "cuda":
+        user_kernel_allgather(heap, rank, world, dev)
     dist_print("all-gather ok in every mode")
+
+
+def user_kernel_allgather(heap, rank, world, dev):
+    """The push all-gather as a user kernel on the shmem.cuh API: three calls on the same buffers, no reset between them
+    (the signal words carry the call number)."""
+    from triton_distributed_b200.runtime import check_status, default_timeout_ns, global_status
+    from triton_distributed_b200.utils.user_kernels import load_user_library
+
+    lib = load_user_library(os.path.join(os.path.dirname(os.path.abspath(__file__)), "kernels", "allgather_putmem_signal.cu"))
+    lib.tutorial_allgather_launch.argtypes = [C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_ulonglong, C.c_ulonglong, C.c_void_p,
+                                              C.c_ulonglong, C.c_void_p]
+    seg = 64 * 1024
+    buf = heap.empty((world, seg), torch.uint8)
+    sig = heap.zeros((world,), torch.int64)
+    for call in range(1, 4):
+        buf.local.fill_(255)
+        buf.local[rank].fill_((rank * 7 + call) % 251)
+        heap.barrier()                    # demo only: nobody's segment is overwritten by the fill above after it was pushed
+        rc = lib.tutorial_allgather_launch(buf.ptr_array(), sig.ptr_array(), rank, world, seg, call, global_status().device_ptr,
+                                           default_timeout_ns(), torch.cuda.current_stream().cuda_stream)
+        assert rc == 0
+        torch.cuda.synchronize()
+        check_status()
+        want = torch.tensor([(r * 7 + call) % 251 for r in range(world)], dtype=torch.uint8, device=dev)
+        assert torch.equal(buf.local, want.view(world, 1).expand(world, seg)), f"user-kernel all-gather, call {call}"
+        heap.barrier()
+    dist_print("putmem_signal_block / signal_wait_until all-gather (user kernel) ok")
 
 
 if __name__ == "__main__":
