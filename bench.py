@@ -295,8 +295,12 @@ def main():
                 torch.matmul(gathered, b.t(), out=c)
             else:
                 torch.matmul(a, b.t(), out=c)
-        tb_ms, tb_spread = timed(torch_step, K_STEPS, W)
+        tb_sampler = ClockSampler(torch.cuda.current_device()) if rank == 0 else None
+        tb_ms, tb_spread = timed(torch_step, K_STEPS, W, tb_sampler)
         extra["torch_nccl_cublas_ag_gemm"] = {"ms_per_step": tb_ms, "tflops": flops / (tb_ms * 1e-3) / 1e12, **tb_spread}
+        if tb_sampler is not None:
+            tb_clk = tb_sampler.summary()    # the baseline's clock under the same power cap, for a like-for-like reading
+            extra["torch_nccl_cublas_ag_gemm"]["clocks"] = {k: tb_clk.get(k) for k in ("sm_mhz", "sm_mhz_min", "power_w_max", "samples", "reasons")}
         extra["ag_gemm_speedup_vs_torch"] = tb_ms / ms
         extra["reference_published_speedup_vs_torch_h800"] = REFERENCE_PUBLISHED_SPEEDUP
         del gathered

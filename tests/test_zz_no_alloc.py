@@ -77,6 +77,8 @@ def test_static_scratch_entry_point_matches_the_regular_one_twice(cuda_device):
         assert rc == 0, _lib.lib().tdist_last_error()
         check_status()
         torch.testing.assert_close(got.float(), expect.float(), atol=1e-2, rtol=1e-2)
+        # and against the plain PyTorch fp32 statement of paged attention, not only against the other entry point
+        torch.testing.assert_close(got.float(), FD.ref_paged_attn(q, k, v, lens, table, scale), atol=2e-2, rtol=2e-2)
         # and the O || LSE form
         expect1 = FD.gqa_fwd_batch_decode_intra_rank(q, k, v, None, None, lens, table, scale, kv_split=splits)
         got1 = torch.full_like(expect1, float("nan"))

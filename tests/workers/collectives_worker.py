@@ -22,7 +22,7 @@ def main():
     # ---- barrier: a rank that is late must hold everybody back (GPU only; CPU uses dist.barrier)
     if cuda:
         t = heap.zeros((world,), torch.int64)
-        for it in range(20):
+        for it in range(200):       # soak: jittered rounds (the reference runs 1000, test/nvidia/test_common_ops.py:54-92)
             if rng.random() < 0.5:
                 torch.cuda._sleep(int(rng.random() * 2e6))
             t.local[rank] = it + 1
@@ -39,11 +39,12 @@ def main():
         for seg in ([512, 4096 + 8, 1 << 20] if cuda else [4096]):
             buf = heap.empty((world * seg,), torch.uint8)
             ctx = CO.create_fast_allgather_context(rank, 0, world, 1, max_buffer_size=world * seg, group=group, device=dev)
-            for it in range(4):
+            for it in range(25 if (cuda and seg <= 8192) else 4):
                 mine = torch.randint(0, 256, (seg,), dtype=torch.uint8, device=dev)
                 heap.barrier()  # nobody is still reading the previous result
                 buf.local.fill_(0xEE)
                 buf.local[rank * seg:(rank + 1) * seg].copy_(mine)
+                heap.barrier()  # every rank's buffer is prepared: a late fill must not wipe out a segment a peer already pushed
                 if cuda and rng.random() < 0.5:
                     torch.cuda._sleep(int(rng.random() * 1e6))
                 CO.fast_allgather(buf, ctx, mode=mode)
@@ -60,7 +61,7 @@ def main():
         mpr, N = 96, 512
         M = world * mpr
         ctx = CO.create_reduce_scater_2d_ctx(M, N, rank, world, dtype=dtype, group=group, device=dev)
-        for it in range(4):
+        for it in range(12 if cuda else 2):
             x = torch.randint(-100, 100, (M, N), device=dev).to(dtype)
             out = CO.reduce_scatter_2d_op(x, ctx)
             full = x.to(torch.float32)

@@ -237,6 +237,28 @@ __device__ __forceinline__ void umma_bf16(uint32_t d_tmem, uint64_t adesc, uint6
             "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
             : "memory");
 }
+// cta_group::2 bf16/f16 MMA with a hint for the A-operand collector: FILL keeps the A fragment this MMA reads from
+// shared memory in the collector buffer, LASTUSE takes A from that buffer instead of shared memory and releases it.
+// For two back-to-back MMAs that multiply the SAME A fragment with different B (the two 256-column halves of a wide
+// tile): A crosses the shared-memory port once instead of twice.
+enum : int { kCollectorFill = 1, kCollectorLastUse = 2 };
+template <int USAGE>
+__device__ __forceinline__ void umma_bf16_pair_collect(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
+                                                       uint32_t accumulate) {
+    if constexpr (USAGE == kCollectorFill)
+        asm volatile(
+            "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+            "tcgen05.mma.cta_group::2.kind::f16.collector::a::fill [%0], %1, %2, %3, p;\n\t}" ::"r"(d_tmem),
+            "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+            : "memory");
+    else
+        asm volatile(
+            "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+            "tcgen05.mma.cta_group::2.kind::f16.collector::a::lastuse [%0], %1, %2, %3, p;\n\t}" ::"r"(d_tmem),
+            "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+            : "memory");
+}
+
 template <int CTAS>
 __device__ __forceinline__ void umma_fp8(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc,
                                          uint32_t idesc, uint32_t accumulate) {

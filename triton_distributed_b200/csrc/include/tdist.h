@@ -69,7 +69,9 @@ typedef struct TdistGemmArgs {
     void* stream;
     /* Optional timeline, 2048 uint64 %globaltimer stamps (NULL = off). Pusher CTA b < 16 writes at
      * [40b]: begin, end, then (start, end) of its first 19 blocks. GEMM CTA c < 64 writes at
-     * [1024 + 4c]: producer begin, producer end, ns spent waiting on flags, waits longer than 2 us. */
+     * [1024 + 4c]: producer begin, producer end, ns spent waiting on flags, waits longer than 2 us. The MMA-issuing
+     * thread of tile unit u < 64 writes at [1536 + 4u]: SM cycles in all, cycles waiting for operands (full
+     * barriers), cycles waiting for a TMEM slot (epilogue not done), tiles computed. */
     void* trace;
     /* Grouped GEMM (PLAIN mode, world 1): B is [num_experts, N, K]; 128-row block i of A and C uses
      * B[expert_ids[i]]; blocks at or past *num_m_blocks (device int32, may be NULL) are skipped. */

@@ -780,15 +780,22 @@ __global__ void __launch_bounds__(GATHER ? GATHER_THREADS : THREADS, 1) gemm_sm1
             uint32_t it = 0;
             uint32_t uses0 = 0, uses1 = 0, next_narrow = 0;   // per-slot use counts give the barrier phases
             const int live_blocks = p.num_m_blocks ? *p.num_m_blocks : 0x7fffffff;
+            // optional timeline of the issuing thread: cycles in all, cycles waiting for operands, cycles waiting for the
+            // epilogue to hand a TMEM slot back, tiles
+            unsigned long long* mtr = (p.trace != nullptr && unit < 64) ? p.trace + 1536 + unit * 4 : nullptr;
+            long long t_begin = mtr ? clock64() : 0, t_full = 0, t_tempty = 0, n_tiles_done = 0;
             Work tc;
             for (int round = 0; get_work<WIDE>(p, unit, num_units, round, first_seg, tc); ++round) {
                 if (tc.m_in_seg * CTAS >= live_blocks) continue;
+                ++n_tiles_done;
                 // the four MMAs of one 256-column half over one K block (stage `s`, K block `kb` of the tile)
                 auto issue_half = [&](int h, int kb, uint32_t s) {
                     const uint32_t slot = slot_of_half(tc, h, next_narrow);
                     if (kb == 0) {
                         // the epilogue has drained this slot's previous accumulator
+                        const long long w0 = mtr ? clock64() : 0;
                         mbar_wait(bar_tempty(slot), ((slot ? uses1 : uses0) & 1u) ^ 1u, p.wctx, 3);
+                        if (mtr) t_tempty += clock64() - w0;
                         tc_fence_after();
                     }
                     const uint32_t sa = smem_u32(smem + s * STAGE_BYTES);
@@ -808,9 +815,27 @@ __global__ void __launch_bounds__(GATHER ? GATHER_THREADS : THREADS, 1) gemm_sm1
                 };
                 for (int kb = 0; kb < p.k_blocks; ++kb, ++it) {
                     const uint32_t s = it % STAGES;
+                    const long long w0 = mtr ? clock64() : 0;
                     mbar_wait(bar_full(s), (it / STAGES) & 1u, p.wctx, 4);
+                    if (mtr) t_full += clock64() - w0;
                     tc_fence_after();
-                    for (int h = 0; h < tc.halves; ++h) issue_half(h, kb, s);
+                    if (WIDE && CTAS == 2 && tc.halves == 2 && kb > 0) {
+                        // Both halves multiply the same A rows: issue them pairwise per 16-wide K step, the first
+                        // filling the A collector, the second reading A from it, so that A crosses the shared-memory
+                        // port once per step. (The first K block of a tile keeps the half-by-half order: its second
+                        // half may still have to wait for the epilogue.)
+                        const uint32_t sa = smem_u32(smem + s * STAGE_BYTES);
+                        const uint64_t adesc = umma_desc_k_sw128(sa);
+                        const uint64_t bdesc0 = umma_desc_k_sw128(sa + A_BYTES);
+                        const uint64_t bdesc1 = umma_desc_k_sw128(sa + A_BYTES + T::B_BYTES);
+#pragma unroll
+                        for (int k = 0; k < BK / UMMA_K; ++k) {
+                            umma_bf16_pair_collect<kCollectorFill>(tmem_base, adesc + 2 * k, bdesc0 + 2 * k, idesc, 1u);
+                            umma_bf16_pair_collect<kCollectorLastUse>(tmem_base + BN, adesc + 2 * k, bdesc1 + 2 * k, idesc, 1u);
+                        }
+                    } else {
+                        for (int h = 0; h < tc.halves; ++h) issue_half(h, kb, s);
+                    }
                     release_stage(s);
                 }
                 for (int h = 0; h < tc.halves; ++h) {
@@ -821,6 +846,12 @@ __global__ void __launch_bounds__(GATHER ? GATHER_THREADS : THREADS, 1) gemm_sm1
                     else ++uses0;
                 }
                 if (tc.halves == 1) next_narrow ^= 1u;
+            }
+            if (mtr) {
+                mtr[0] = static_cast<unsigned long long>(clock64() - t_begin);
+                mtr[1] = static_cast<unsigned long long>(t_full);
+                mtr[2] = static_cast<unsigned long long>(t_tempty);
+                mtr[3] = static_cast<unsigned long long>(n_tiles_done);
             }
         }
         __syncwarp();

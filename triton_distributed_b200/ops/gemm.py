@@ -44,6 +44,7 @@ CTA_PAIR = int(os.environ.get("TDIST_GEMM_CTA_PAIR", "-1"))
 # 1 = from 4 ranks up, 2 = always
 AG_NVLS = int(os.environ.get("TDIST_AG_GEMM_NVLS", "0"))
 GROUP_M = int(os.environ.get("TDIST_GEMM_GROUP_M", "0"))  # row-tiles per raster group, 0 = kernel default
+TRACE = None  # optional int64[2048] device tensor: every launch writes its timeline there (layout: TdistGemmArgs.trace)
 
 
 def _cdiv(a: int, b: int) -> int:
@@ -76,6 +77,8 @@ def _base_args(a, b, world, rank, mode, stream=None, cta_pair: int = -1) -> "_li
     g.timeout_ns = default_timeout_ns()
     g.cta_pair = cta_pair if cta_pair >= 0 else CTA_PAIR
     g.group_m = GROUP_M
+    if TRACE is not None:
+        g.trace = TRACE.data_ptr()
     g.stream = (stream or torch.cuda.current_stream(a.device)).cuda_stream
     return g
 
