@@ -74,3 +74,33 @@ def test_fp8_ops_through_the_dispatcher_on_cpu():
         out = torch.ops.tdist.gemm_fp8(fa, torch.empty(16, 2), fb, torch.empty(1, 2))
         assert out.shape == (16, 24) and out.dtype == torch.bfloat16
     T.release_context(h)
+
+
+def test_expert_parallel_ops_through_the_dispatcher_on_cpu():
+    from triton_distributed_b200.ops import all_to_all as A
+    from triton_distributed_b200.ops import moe_ep as EP
+
+    torch.manual_seed(3)
+    T_, H, E, K = 12, 256, 4, 2
+    x = torch.randn(T_, H).to(torch.bfloat16)
+    w, ids = torch.softmax(torch.randn(T_, E), -1).topk(K, dim=-1)
+    # expert-major bf16 exchange, plain sum on the way back
+    h = T.register_context(EP.create_ep_context(T_, H, K, E, 0, 1, compact=True, align=4, device="cpu"))
+    rows, splits, num = torch.ops.tdist.ep_dispatch(x, ids.int(), h)
+    assert int(num) == T_ * K and splits.shape == (1, E)
+    torch.testing.assert_close(torch.ops.tdist.ep_combine(rows, h).float(), x.float() * K, atol=2e-2, rtol=2e-2)
+    with FakeTensorMode():
+        r, s, n = torch.ops.tdist.ep_dispatch(torch.empty(T_, H, dtype=torch.bfloat16), torch.empty(T_, K, dtype=torch.int32), h)
+        assert r.shape[1] == H and s.shape == (1, E) and n.shape == (1,)
+    T.release_context(h)
+    # the quantising pair
+    h2 = T.register_context(A.create_moe_dispatch_context(T_, H, K, E, 0, 1, device="cpu"))
+    rx, rs, sp = torch.ops.tdist.moe_dispatch(x, ids.int(), w, h2)
+    out = torch.ops.tdist.moe_combine(A.dequant_fp8(rx, rs), sp, h2)
+    q, sc = A.quant_fp8_reference(x)
+    torch.testing.assert_close(out.float(), A.dequant_fp8(q, sc).float() * w.sum(-1, keepdim=True), atol=3e-2, rtol=3e-2)
+    with FakeTensorMode():
+        frx, frs, fsp = torch.ops.tdist.moe_dispatch(torch.empty(T_, H, dtype=torch.bfloat16), torch.empty(T_, K, dtype=torch.int32),
+                                                     torch.empty(T_, K), h2)
+        assert frx.dtype == torch.float8_e4m3fn and frs.shape[1] == H // 128 and fsp.shape == (1, E)
+    T.release_context(h2)

@@ -10,7 +10,7 @@ from . import models, ops, parallel, runtime, utils  # noqa: F401
 from .models import AllGatherLayer, EPAll2AllLayer, EPMoE, SpGQAFlashDecodeAttention, TPMLP  # noqa: F401
 from .ops.all_to_all import (all_to_all_post_process, create_all_to_all_context, create_moe_dispatch_context,  # noqa: F401
                              fast_all_to_all, get_ag_splits_and_recv_offset_for_dispatch,
-                             get_dispatch_send_reqs_for_target_node, moe_combine, moe_dispatch)
+                             get_dispatch_send_reqs_for_target_node, moe_combine, moe_dispatch, moe_expert_out_buffer)
 from .ops.collectives import (AllGatherMethod, barrier_all_on_stream, cp_engine_producer_all_gather_intra_node,  # noqa: F401
                               create_fast_allgather_context, create_reduce_scater_2d_ctx, fast_allgather,
                               get_auto_all_gather_method, inter_node_allgather, reduce_scatter_2d_op, ring_reduce, set_signal,
@@ -22,6 +22,7 @@ from .ops.gemm import (ag_gemm_inter_node, ag_gemm_intra_node, create_ag_gemm_in
                        gemm_rs_op)
 from .ops.gemm_fp8 import (ag_gemm_fp8, create_ag_gemm_fp8_context, gemm_fp8_blockscaled, quantize_fp8_blockwise,  # noqa: F401
                            quantize_fp8_rowwise)
+from .ops.moe_ep import create_ep_context, ep_combine, ep_dispatch, expert_out_buffer  # noqa: F401
 from .ops.moe_tp import (ag_group_gemm_intra_node, create_ag_group_gemm_intra_node_context, create_moe_rs_context,  # noqa: F401
                          group_gemm, moe_reduce_rs, select_experts, sort_topk_ids_align_block_size)
 from .ops.nvls import create_nvls_context, nvls_allgather, nvls_allreduce, nvls_reduce_scatter  # noqa: F401

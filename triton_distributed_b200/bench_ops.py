@@ -345,6 +345,54 @@ def _bench_nvls(args, world, rank, group, dev, dtype, pk, row):
         row.update({"nccl_us": round(base, 2), "speedup_vs_nccl": round(base / us, 3)})
 
 
+def _bench_local_collectives(args, world, rank, group, dev, dtype, pk, row):
+    """The collective kernels of four emulated ranks on ONE GPU (send halves of every rank, then the receive halves, so
+    no launch waits for a launch that has not run): LL all-gather, push all-gather, reduce-scatter with the fused
+    top-k reduce. For single-GPU profiles of these kernels; the times include no link."""
+    from .ops import collectives as CO
+    from .runtime import LocalWorld
+    W = 4
+    lw = LocalWorld(W, dev)
+    seg = max(16, args.bytes // W // 16 * 16)
+    row.update({"emulated_ranks": W, "segment_bytes": seg})
+    for mode in ("push2d_ll", "push2d"):
+        ctxs = [CO.create_fast_allgather_context(r, 0, W, 1, max_buffer_size=W * seg, heap=lw.heap(r), device=dev) for r in range(W)]
+        bufs = [lw.heap(r).empty((W * seg,), torch.uint8) for r in range(W)]
+
+        def step():
+            for r in range(W):
+                CO.fast_allgather(bufs[r], ctxs[r], mode=mode, phase=1)
+            for r in range(W):
+                CO.fast_allgather(bufs[r], ctxs[r], mode=mode, phase=2)
+        row[f"allgather_{mode}_us_per_rank"] = round(timed_us(step, args.iters, args.warmup, 1) / W, 2)
+    M, N, topk = args.tokens * W, args.hidden, args.topk
+    ctxs = [CO.create_reduce_scater_2d_ctx(M, N, r, W, dtype=torch.bfloat16, heap=lw.heap(r), device=dev) for r in range(W)]
+    y = torch.randn(M * topk, N, device=dev).to(torch.bfloat16)
+    pos = torch.randperm(M * topk, device=dev).to(torch.int32)
+    w = torch.rand(M, topk, device=dev)
+
+    def rs_step():
+        for r in range(W):
+            CO.topk_reduce_scatter(y, pos, w, M, topk, ctxs[r], phase=1)
+        for r in range(W):
+            CO.topk_reduce_scatter(y, pos, w, M, topk, ctxs[r], phase=2)
+    row["topk_reduce_scatter_us_per_rank"] = round(timed_us(rs_step, args.iters, args.warmup, 1) / W, 2)
+
+
+def _bench_moe_route(args, world, rank, group, dev, dtype, pk, row):
+    """The MoE routing kernels on one GPU: softmax + top-k, stable expert sort, block-aligned rank-major sort."""
+    from .ops import moe_utils as MU
+    T, E, K = args.tokens, args.experts, args.topk
+    logits = torch.randn(T, E, device=dev)
+    ids, _ = MU.topk_softmax(logits, K)
+    row.update({"tokens": T, "experts": E, "topk": K})
+    row["topk_softmax_us"] = round(timed_us(lambda: MU.topk_softmax(logits, K), args.iters, args.warmup, 1), 2)
+    row["route_us"] = round(timed_us(lambda: MU.route(ids, E), args.iters, args.warmup, 1), 2)
+    ranks = 8 if T % 8 == 0 else 1
+    row["align_block_size_us"] = round(timed_us(lambda: MU.sort_topk_ids_align_block_size(ids, E, ranks, T // ranks, 128),
+                                                args.iters, args.warmup, 1), 2)
+
+
 def _bench_moe_tp(args, world, rank, group, dev, dtype, pk, row):
     """Tensor-parallel MoE (Mixtral-like by default: 8192 tokens, hidden 4096, intermediate 14336, 8 experts, top-2):
     AllGather + GroupGEMM and GroupGEMM + top-k reduce + ReduceScatter, fused against staged."""
@@ -488,7 +536,7 @@ def _run_suite(args, world, rank, group, dev, dtype, pk):
 
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser()
-    ap.add_argument("--op", required=True, choices=["gemm", "ag_gemm", "gemm_rs", "gemm_fp8", "ag_gemm_fp8", "decode", "sp_decode", "a2a", "allgather", "nvls", "nvls_suite", "moe_tp", "fused_local", "suite"])
+    ap.add_argument("--op", required=True, choices=["gemm", "ag_gemm", "gemm_rs", "gemm_fp8", "ag_gemm_fp8", "decode", "sp_decode", "a2a", "allgather", "nvls", "nvls_suite", "moe_tp", "fused_local", "local_collectives", "moe_route", "suite"])
     ap.add_argument("--shape", default="", help="MxNxK in one argument (torchrun swallows a bare --m)")
     ap.add_argument("--m", type=int, default=8192)
     ap.add_argument("--n", type=int, default=6144)
@@ -569,6 +617,10 @@ def main(argv=None) -> int:
         if args.experts == 256 and args.topk == 8 and args.n == 6144 and args.k == 12288:   # untouched defaults: Mixtral-like
             args.n, args.k, args.experts, args.topk = 14336, 4096, 8, 2
         _bench_moe_tp(args, world, rank, group, dev, dtype, pk, row)
+    elif args.op == "local_collectives":
+        _bench_local_collectives(args, world, rank, group, dev, dtype, pk, row)
+    elif args.op == "moe_route":
+        _bench_moe_route(args, world, rank, group, dev, dtype, pk, row)
     else:
         _bench_allgather(args, world, rank, group, dev, dtype, pk, row)
     check_status()

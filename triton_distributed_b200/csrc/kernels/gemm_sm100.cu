@@ -415,23 +415,30 @@ __device__ void gather_prologue(const GemmParams& p, int pro, int live, int rot)
 __device__ void local_gatherer(const GemmParams& p, uint8_t* smem, uint64_t* bars, int pro, int live, int rot) {
     if (threadIdx.x != 0) return;
     const size_t row_bytes = static_cast<size_t>(p.k) * 2;
-    const int cpr = static_cast<int>((row_bytes + PUSH_CHUNK - 1) / PUSH_CHUNK);   // chunks per row
+    // A chunk of the ring is PUSH_CHUNK bytes of rows: several whole rows when they are short (so that the bytes in
+    // flight do not shrink with K), or a piece of one long row.
+    const int rpc = row_bytes >= PUSH_CHUNK ? 1 : static_cast<int>(PUSH_CHUNK / row_bytes);            // rows per chunk
+    const int cpr = row_bytes > PUSH_CHUNK ? static_cast<int>((row_bytes + PUSH_CHUNK - 1) / PUSH_CHUNK) : 1;  // chunks per row
+    const int nchunks = cpr > 1 ? BM * cpr : (BM + rpc - 1) / rpc;
     uint32_t it_load = 0, it_store = 0;
-    // chunk j of block b: false when its row is padding
-    auto chunk = [&](int b, int j, const char** src, char** dst, uint32_t* sz) -> bool {
-        const int r = j / cpr, c = j - r * cpr;
+    // piece i of chunk j of block b: source, destination, size, offset inside the chunk's buffer; false = padding row
+    auto piece = [&](int b, int j, int i, const char** src, char** dst, uint32_t* sz, uint32_t* at) -> bool {
+        const int r = cpr > 1 ? j / cpr : j * rpc + i;
+        const int c = cpr > 1 ? j - r * cpr : 0;
         const int row = b * BM + r;
-        if (row >= p.m_per_rank) return false;
+        if (r >= BM || row >= p.m_per_rank) return false;
         const int idx = p.a_gather[row];
         if (idx < 0 || idx >= p.a_gather_rows) return false;
         const size_t off = static_cast<size_t>(c) * PUSH_CHUNK;
         *src = p.a_raw + static_cast<size_t>(idx) * row_bytes + off;
         *dst = p.gather_dst + static_cast<size_t>(row) * row_bytes + off;
         *sz = static_cast<uint32_t>(min(static_cast<size_t>(PUSH_CHUNK), row_bytes - off));
+        *at = cpr > 1 ? 0u : static_cast<uint32_t>(i) * static_cast<uint32_t>(row_bytes);
         return true;
     };
-    for (int i = pro + static_cast<int>(blockIdx.x); i < live; i += p.num_comm) {
-        const int b = rotate_block(i, rot, live);
+    const int pieces = cpr > 1 ? 1 : rpc;
+    for (int i0 = pro + static_cast<int>(blockIdx.x); i0 < live; i0 += p.num_comm) {
+        const int b = rotate_block(i0, rot, live);
         if (p.block_src != nullptr) {
             const int srcr = p.block_src[b];
             if (srcr != p.src_rank && srcr >= 0 && srcr < p.src_world) {
@@ -440,25 +447,38 @@ __device__ void local_gatherer(const GemmParams& p, uint8_t* smem, uint64_t* bar
             }
         }
         if (p.debug_delay_ns > 0) __nanosleep(p.debug_delay_ns);
-        const int nchunks = BM * cpr;
         for (int j = 0; j < nchunks + PUSH_AHEAD; ++j) {
             const char* src;
             char* dst;
-            uint32_t sz;
-            if (j < nchunks && chunk(b, j, &src, &dst, &sz)) {
-                const uint32_t s = it_load % PUSH_STAGES;
-                // the store that last used this buffer was issued at least PUSH_STAGES - PUSH_AHEAD chunks ago
-                if (it_load >= PUSH_STAGES) bulk_wait_read<PUSH_STAGES - PUSH_AHEAD - 1>();
-                mbar_expect_tx(smem_u32(&bars[s]), sz);
-                bulk_load(smem_u32(smem + s * PUSH_CHUNK), src, sz, smem_u32(&bars[s]));
-                ++it_load;
+            uint32_t sz, at;
+            if (j < nchunks) {
+                // total bytes of the chunk first (one expect_tx), then its loads
+                uint32_t total = 0;
+                for (int i = 0; i < pieces; ++i)
+                    if (piece(b, j, i, &src, &dst, &sz, &at)) total += sz;
+                if (total > 0) {
+                    const uint32_t s = it_load % PUSH_STAGES;
+                    // the stores that last used this buffer were issued at least PUSH_STAGES - PUSH_AHEAD chunks ago
+                    if (it_load >= PUSH_STAGES) bulk_wait_read<PUSH_STAGES - PUSH_AHEAD - 1>();
+                    mbar_expect_tx(smem_u32(&bars[s]), total);
+                    for (int i = 0; i < pieces; ++i)
+                        if (piece(b, j, i, &src, &dst, &sz, &at))
+                            bulk_load(smem_u32(smem + s * PUSH_CHUNK) + at, src, sz, smem_u32(&bars[s]));
+                    ++it_load;
+                }
             }
-            if (j >= PUSH_AHEAD && chunk(b, j - PUSH_AHEAD, &src, &dst, &sz)) {
-                const uint32_t s = it_store % PUSH_STAGES;
-                mbar_wait(smem_u32(&bars[s]), (it_store / PUSH_STAGES) & 1u, p.wctx, 12);
-                bulk_store(dst, smem_u32(smem + s * PUSH_CHUNK), sz);
-                bulk_commit();
-                ++it_store;
+            if (j >= PUSH_AHEAD) {
+                bool any = false;
+                for (int i = 0; i < pieces; ++i) any = piece(b, j - PUSH_AHEAD, i, &src, &dst, &sz, &at) || any;
+                if (any) {
+                    const uint32_t s = it_store % PUSH_STAGES;
+                    mbar_wait(smem_u32(&bars[s]), (it_store / PUSH_STAGES) & 1u, p.wctx, 12);
+                    for (int i = 0; i < pieces; ++i)
+                        if (piece(b, j - PUSH_AHEAD, i, &src, &dst, &sz, &at))
+                            bulk_store(dst, smem_u32(smem + s * PUSH_CHUNK) + at, sz);
+                    bulk_commit();   // one group per chunk: the wait_group.read above counts chunks
+                    ++it_store;
+                }
             }
         }
         // the rows are complete in the staging matrix before the flag: wait for the writes themselves, then order
@@ -1054,7 +1074,9 @@ static bool use_wide(const TdistGemmArgs* a) {
     if (!use_pair(a)) return false;
     if (a->cta_pair == 2) return true;
     if (a->cta_pair == 1) return false;
-    return a->k >= 4096 && a->n > BN;
+    // RS: the epilogue of a wide tile stores 128 KB per CTA over NVLink with the MMAs of the next tile held up, so the
+    // main loop has to be longer still before the wide tile wins
+    return a->k >= (a->mode == TDIST_GEMM_RS && a->world > 1 ? 8192 : 4096) && a->n > BN;
 }
 
 struct GridPlan {
@@ -1137,14 +1159,16 @@ static GridPlan plan_grid(const TdistGemmArgs* a) {
         if (g.num_comm <= 0) {
             // Peers consume this rank's rows one segment-time after another (the rank that needs them first
             // gets them first), so the pushers must sustain shard_bytes per segment time, i.e. all pushes within
-            // (world-1)/world of the run. One unicast pusher CTA sustains ~40 GB/s over NVLink. A multicast pusher
-            // stores the shard once instead of world-1 times but was measured at ~33 GB/s per CTA, and every peer
-            // needs the whole shard when it reaches this rank's segment: a quarter of the run.
+            // (world-1)/world of the run. One unicast pusher CTA moves 36-40 GB/s over NVLink in isolation and less
+            // beside a running GEMM: sized at 30 GB/s (m8192 n49152 k12288 at tp8: 8 pushers 0.97 ms, 6 pushers
+            // 1.19 ms, 10 pushers 1.02 ms). A multicast pusher stores the shard once instead of world-1 times but
+            // was measured at ~33 GB/s per CTA, and every peer needs the whole shard when it reaches this rank's
+            // segment: a quarter of the run.
             const bool nvls = a->a_ws_mc != nullptr;
             const double push_bytes = static_cast<double>(nvls ? 1 : a->world - 1) * a->m_per_rank * a->k * 2.0;
             const double gemm_s = 2.0 * a->world * a->m_per_rank * static_cast<double>(a->n) * a->k / 1.4e15;
             const double window = nvls ? gemm_s * 0.25 : gemm_s * (a->world - 1) / a->world;
-            int need = static_cast<int>(push_bytes / (window > 1e-6 ? window : 1e-6) / (nvls ? 33e9 : 40e9)) + 1;
+            int need = static_cast<int>(push_bytes / (window > 1e-6 ? window : 1e-6) / (nvls ? 33e9 : 30e9)) + 1;
             need = (need + 1) & ~1;
             if (need < 2) need = 2;
             if (need > 18) need = 18;

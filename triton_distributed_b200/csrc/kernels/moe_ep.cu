@@ -88,16 +88,30 @@ struct QuantSeg {
     float scale[kEpSegLoads];
 };
 
-__device__ __forceinline__ void quantise_segment(const char* src, int hidden, int seg, int lane, QuantSeg& out) {
-    const int groups = hidden / 128;
-    const int half = lane >> 4, sub = lane & 15;
-    const int g0 = seg * (kEpSegLoads * 2);
-    uint4 raw[kEpSegLoads];
+// The raw 16-byte loads of one (token, segment) item: issued early (before the routing, which does not need them) and
+// consumed by quantise_segment / the plain copy afterwards.
+__device__ __forceinline__ void load_segment(const char* src, int hidden, int seg, int lane, bool quant, uint4 (&raw)[kEpSegLoads]) {
+    if (quant) {
+        const int groups = hidden / 128;
+        const int half = lane >> 4, sub = lane & 15;
+        const int g0 = seg * (kEpSegLoads * 2);
 #pragma unroll
-    for (int u = 0; u < kEpSegLoads; ++u) {
-        const int g = g0 + 2 * u + half;
-        raw[u] = g < groups ? ld_nc_v4(src + (static_cast<size_t>(g) * 128 + sub * 8) * 2) : make_uint4(0, 0, 0, 0);
+        for (int u = 0; u < kEpSegLoads; ++u) {
+            const int g = g0 + 2 * u + half;
+            raw[u] = g < groups ? ld_nc_v4(src + (static_cast<size_t>(g) * 128 + sub * 8) * 2) : make_uint4(0, 0, 0, 0);
+        }
+    } else {
+        const int b0 = seg * kEpSegValues * 2;
+        const int b1 = min(hidden * 2, b0 + kEpSegValues * 2);
+#pragma unroll
+        for (int u = 0; u < kEpSegLoads; ++u) {
+            const int off = b0 + u * 512 + lane * 16;
+            raw[u] = off < b1 ? ld_nc_v4(src + off) : make_uint4(0, 0, 0, 0);
+        }
     }
+}
+
+__device__ __forceinline__ void quantise_segment(const uint4 (&raw)[kEpSegLoads], QuantSeg& out) {
 #pragma unroll
     for (int u = 0; u < kEpSegLoads; ++u) {
         const uint32_t w[4] = {raw[u].x, raw[u].y, raw[u].z, raw[u].w};
@@ -141,6 +155,15 @@ __global__ void __launch_bounds__(kMoeThreads, 1) moe_dispatch_kernel(const __gr
     const int tid = static_cast<int>(threadIdx.x);
     const int warp = tid >> 5, lane = tid & 31;
     const bool first_cta = blockIdx.x == 0;
+
+    // The rows do not depend on the routing: this warp's first (token, segment) item is loaded now, so that its
+    // memory round trip runs under the sort below.
+    const int segs = (p.hidden + kEpSegValues - 1) / kEpSegValues;
+    const int gw = static_cast<int>(blockIdx.x) * kMoeWarps + warp;
+    const int nw = static_cast<int>(gridDim.x) * kMoeWarps;
+    uint4 raw[kEpSegLoads];
+    if ((p.phase & 2) && gw < p.ntok * segs)
+        load_segment(p.x + static_cast<size_t>(gw / segs) * p.hidden * 2, p.hidden, gw % segs, lane, p.quant != 0, raw);
 
     if (p.phase & 3) {
         // ---------------------------------------------------------------- per-expert counts of this rank
@@ -274,31 +297,30 @@ __global__ void __launch_bounds__(kMoeThreads, 1) moe_dispatch_kernel(const __gr
         __syncthreads();
 
         // ---------------------------------------------------------------- rows: load once, store to every owner
-        const int segs = (p.hidden + kEpSegValues - 1) / kEpSegValues;
-        const int gw = static_cast<int>(blockIdx.x) * kMoeWarps + warp;
-        const int nw = static_cast<int>(gridDim.x) * kMoeWarps;
         const int row_bytes_out = p.quant ? p.hidden : p.hidden * 2;
         const int scale_cols = p.hidden / 128;
         for (int item = gw; item < p.ntok * segs; item += nw) {
             const int t = item / segs, seg = item - t * segs;
-            const char* src = p.x + static_cast<size_t>(t) * p.hidden * 2;
-            if (p.quant) {
-                QuantSeg qs;
-                quantise_segment(src, p.hidden, seg, lane, qs);
-                const int half = lane >> 4, sub = lane & 15;
-                for (int k = 0; k < p.topk; ++k) {
-                    const int i = t * p.topk + k;
-                    int r;
-                    if (in_place) {
-                        r = row_s[i];
-                    } else {
-                        const int e = p.topk_ids[i];
-                        r = expert_in_range(e, E) && p.slot_in[i] >= 0 ? base[e] + p.slot_in[i] - cum[e] : -1;
-                        if (r >= row_limit) r = -1;
-                    }
-                    if (r < 0) continue;
-                    const int d = p.topk_ids[i] / p.epr;
-                    char* dst = p.recv_peer[d] + static_cast<size_t>(r) * row_bytes_out;
+            if (item != gw) load_segment(p.x + static_cast<size_t>(t) * p.hidden * 2, p.hidden, seg, lane, p.quant != 0, raw);
+            QuantSeg qs;
+            if (p.quant) quantise_segment(raw, qs);
+            const int half = lane >> 4, sub = lane & 15;
+            const int b0 = seg * kEpSegValues * 2;
+            const int b1 = min(p.hidden * 2, b0 + kEpSegValues * 2);
+            for (int k = 0; k < p.topk; ++k) {
+                const int i = t * p.topk + k;
+                int r;
+                if (in_place) {
+                    r = row_s[i];
+                } else {
+                    const int e = p.topk_ids[i];
+                    r = expert_in_range(e, E) && p.slot_in[i] >= 0 ? base[e] + p.slot_in[i] - cum[e] : -1;
+                    if (r >= row_limit) r = -1;
+                }
+                if (r < 0) continue;
+                const int d = p.topk_ids[i] / p.epr;
+                char* dst = p.recv_peer[d] + static_cast<size_t>(r) * row_bytes_out;
+                if (p.quant) {
                     float* dsc = p.scale_peer[d] + static_cast<size_t>(r) * scale_cols;
 #pragma unroll
                     for (int u = 0; u < kEpSegLoads; ++u) {
@@ -308,32 +330,11 @@ __global__ void __launch_bounds__(kMoeThreads, 1) moe_dispatch_kernel(const __gr
                             if (sub == 0) dsc[g] = qs.scale[u];
                         }
                     }
-                }
-            } else {
-                const int b0 = seg * kEpSegValues * 2;
-                const int b1 = min(p.hidden * 2, b0 + kEpSegValues * 2);
-                uint4 q[kEpSegLoads];
-#pragma unroll
-                for (int u = 0; u < kEpSegLoads; ++u) {
-                    const int off = b0 + u * 512 + lane * 16;
-                    if (off < b1) q[u] = ld_nc_v4(src + off);
-                }
-                for (int k = 0; k < p.topk; ++k) {
-                    const int i = t * p.topk + k;
-                    int r;
-                    if (in_place) {
-                        r = row_s[i];
-                    } else {
-                        const int e = p.topk_ids[i];
-                        r = expert_in_range(e, E) && p.slot_in[i] >= 0 ? base[e] + p.slot_in[i] - cum[e] : -1;
-                        if (r >= row_limit) r = -1;
-                    }
-                    if (r < 0) continue;
-                    char* dst = p.recv_peer[p.topk_ids[i] / p.epr] + static_cast<size_t>(r) * row_bytes_out;
+                } else {
 #pragma unroll
                     for (int u = 0; u < kEpSegLoads; ++u) {
                         const int off = b0 + u * 512 + lane * 16;
-                        if (off < b1) st_v4(dst + off, q[u]);
+                        if (off < b1) st_v4(dst + off, raw[u]);
                     }
                 }
             }

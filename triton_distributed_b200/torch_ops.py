@@ -184,10 +184,9 @@ def moe_dispatch(x: torch.Tensor, topk_ids: torch.Tensor, topk_weights: torch.Te
 
 @moe_dispatch.register_fake
 def _(x, topk_ids, topk_weights, ctx):
-    c = _CONTEXTS[ctx].dispatch
-    rows = c.WORLD_SIZE * c.max_m
-    return (x.new_empty((rows, c.hidden), dtype=torch.float8_e4m3fn), x.new_empty((rows, c.hidden // 128), dtype=torch.float32),
-            x.new_empty((c.WORLD_SIZE, c.experts_per_rank), dtype=torch.int32))
+    c = _CONTEXTS[ctx].ep
+    return (x.new_empty((c.rows, c.hidden), dtype=torch.float8_e4m3fn), x.new_empty((c.rows, c.hidden // 128), dtype=torch.float32),
+            x.new_empty((c.world, c.experts_per_rank), dtype=torch.int32))
 
 
 @_op("tdist::moe_combine", mutates_args=())
@@ -197,6 +196,35 @@ def moe_combine(expert_out: torch.Tensor, recv_splits: torch.Tensor, ctx: int) -
 
 @moe_combine.register_fake
 def _(expert_out, recv_splits, ctx):
+    c = _CONTEXTS[ctx]
+    return expert_out.new_empty((c.ntok, c.hidden))
+
+
+@_op("tdist::ep_dispatch", mutates_args=())
+def ep_dispatch(x: torch.Tensor, topk_ids: torch.Tensor, ctx: int) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
+    """Expert-parallel dispatch into the expert-major layout: ``(rows [capacity, hidden] bf16, recv_splits
+    [world, experts_per_rank] int32, num_recv [1] int32)``, cloned so that the op owns its outputs."""
+    from .ops import moe_ep as EP
+    rows, _, splits, num = EP.ep_dispatch(_CONTEXTS[ctx], x, topk_ids, None)
+    return rows.clone(), splits.clone(), num.clone()
+
+
+@ep_dispatch.register_fake
+def _(x, topk_ids, ctx):
+    c = _CONTEXTS[ctx]
+    return (x.new_empty((c.rows, c.hidden)), x.new_empty((c.world, c.experts_per_rank), dtype=torch.int32),
+            x.new_empty((1,), dtype=torch.int32))
+
+
+@_op("tdist::ep_combine", mutates_args=())
+def ep_combine(expert_out: torch.Tensor, ctx: int) -> torch.Tensor:
+    """Plain sum of each token's ``topk`` processed rows, read from their owners."""
+    from .ops import moe_ep as EP
+    return EP.ep_combine(_CONTEXTS[ctx], expert_out, weighted=False)
+
+
+@ep_combine.register_fake
+def _(expert_out, ctx):
     c = _CONTEXTS[ctx]
     return expert_out.new_empty((c.ntok, c.hidden))
 
@@ -247,5 +275,5 @@ def _(partials):
 
 
 OP_NAMES = ["gemm", "ag_gemm", "gemm_rs", "gemm_fp8", "ag_gemm_fp8", "group_gemm", "reduce_scatter", "barrier_all", "moe_topk_softmax",
-            "moe_ag_scatter_align_block_size", "moe_dispatch", "moe_combine", "gqa_fwd_batch_decode",
+            "moe_ag_scatter_align_block_size", "moe_dispatch", "moe_combine", "ep_dispatch", "ep_combine", "gqa_fwd_batch_decode",
             "gqa_fwd_batch_decode_intra_rank", "sp_gqa_fwd_batch_decode", "lse_combine"]
