@@ -118,7 +118,7 @@ def test_group_gemm_gathers_rows_in_kernel(cuda_device, T, E, K, N, topk):
 
 @pytest.mark.parametrize("T,E,K,N,topk,rot", [(300, 8, 264, 520, 2, 0), (1500, 16, 512, 776, 3, 7), (128, 4, 64, 256, 1, 1)])
 def test_group_gemm_staged_gather_rotation_and_scatter(cuda_device, T, E, K, N, topk, rot):
-    """Gatherer CTAs + TMA-fed MMAs + scattering epilogue in one launch against the four-launch path, over several
+    """In-launch row staging (all-thread prologue + epilogue warps) + TMA-fed MMAs + scattering epilogue in one launch against the four-launch path, over several
     calls with fresh data (the per-block flags carry the call number), starting the schedule at block `rot`."""
     torch.manual_seed(T + K)
     b = (torch.randn(E, N, K, device=cuda_device) * K ** -0.5).to(torch.bfloat16)
@@ -129,7 +129,7 @@ def test_group_gemm_staged_gather_rotation_and_scatter(cuda_device, T, E, K, N, 
     nb = (post_pad // 128).to(torch.int32)
     row_index = torch.div(sid, topk, rounding_mode="floor").to(torch.int32)
     staging = torch.full((n, K), float("nan"), device=cuda_device, dtype=torch.bfloat16)
-    ready = torch.zeros(n // 128 + 1, dtype=torch.int32, device=cuda_device)   # per-block flags + the prologue's counter
+    ready = MT.staging_flags(n, cuda_device)
     rot_t = torch.tensor([min(rot, n // 128 - 1)], dtype=torch.int32, device=cuda_device)
     for call in range(1, 4):
         x = torch.randn(T, K, device=cuda_device).to(torch.bfloat16)
@@ -137,7 +137,7 @@ def test_group_gemm_staged_gather_rotation_and_scatter(cuda_device, T, E, K, N, 
         want_sorted = MT.group_gemm(a_sorted, b, expert_ids, nb)
         want, _ = MT.gather_rows(want_sorted, pos_of, 1, n)
         got_sorted = MT.group_gemm_gather(x, row_index, b, expert_ids, nb, staging=staging, block_ready=ready, epoch=2 * call - 1,
-                                          block_rot=rot_t, num_gather_ctas=3 + call)
+                                          block_rot=rot_t)
         staging.fill_(float("nan"))    # the second launch must stage the rows again, not reuse what is there
         got = MT.group_gemm_gather(x, row_index, b, expert_ids, nb, staging=staging, block_ready=ready, epoch=2 * call,
                                    block_rot=rot_t, c_scatter=sid, c_rows=T * topk)
@@ -145,3 +145,4 @@ def test_group_gemm_staged_gather_rotation_and_scatter(cuda_device, T, E, K, N, 
         live = sid < T * topk
         assert torch.equal(got_sorted[live], want_sorted[live])
         assert torch.equal(got, want)
+        assert int(ready[n // 128:].abs().sum()) == 0      # the kernel leaves its counters at zero for the next launch

@@ -19,4 +19,4 @@ def test_multimem_collectives_on_gpus(world):
     assert res["ranks_ok"] == world, out[-3000:]
     if not res["multicast"]:
         pytest.skip("this system offers no NVLS multicast objects")
-    assert res["checked"] and res["fast_allgather_used_nvls"]
+    assert res["checked"] and res["fast_allgather_used_nvls"] and res["sp_decode_multicast"]

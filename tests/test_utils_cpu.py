@@ -193,3 +193,48 @@ def test_bench_reference_arm_reports_unavailable():
     assert r.returncode == 0, r.stderr[-1000:]
     line = json.loads(r.stdout.strip().splitlines()[-1])
     assert line["impl"] == "reference" and "unavailable" in line and len(line["unavailable"]) > 10
+
+
+@pytest.mark.parametrize("wide", [0, 1])
+def test_gemm_static_schedule_gives_every_tile_to_one_unit(wide):
+    """The kernel's tile schedule replayed on the host (the same function the device runs): every 256-column tile exactly
+    once, for even and odd tile counts, full and partial last rounds, with and without the split first round."""
+    import ctypes as C
+    import random
+
+    from triton_distributed_b200 import _lib
+    lib = _lib.lib()
+    rng = random.Random(3)
+    span, first = C.c_int(0), C.c_int(0)
+    cases = [(70, 8, 4, 24, 22), (70, 8, 4, 24, 0), (74, 1, 32, 24, 0), (69, 4, 8, 23, 0), (69, 4, 8, 23, 5)]
+    for _ in range(300):
+        units, world = rng.randint(1, 74), rng.randint(1, 8)
+        seg_m, n_tiles = rng.randint(1, 9), rng.randint(1, 25)
+        own = seg_m * ((n_tiles + 1) // 2)
+        split = units - own if (wide and world > 1 and own < units and units - own <= own and rng.random() < 0.7) else 0
+        cases.append((units, world, seg_m, n_tiles, split))
+    for (units, world, seg_m, n_tiles, split) in cases:
+        if not wide:
+            split = 0
+        for rank in {0, world - 1}:
+            rc = lib.tdist_gemm_schedule_check(wide, units, world, rank, seg_m, n_tiles, rng.choice([0, 1, 4, 8]), split,
+                                               C.byref(span), C.byref(first))
+            assert rc == 0, (wide, units, world, rank, seg_m, n_tiles, split, rc)
+            total = world * seg_m * n_tiles
+            assert span.value * units >= total
+            if split and n_tiles % 2 == 0:
+                assert first.value >= 1     # nobody starts on a peer's segment (an odd last tile has no second half to give)
+
+
+def test_gemm_split_first_round_balances_the_headline_problem():
+    """m8192 n49152 k12288 at tp8 with 8 pusher CTAs: 70 CTA pairs, 48 own wide items, 384 in all. Cutting 22 own items in
+    two keeps every unit busy with local rows for the first half item and all units end after 5.5 items."""
+    import ctypes as C
+
+    from triton_distributed_b200 import _lib
+    lib = _lib.lib()
+    span, first = C.c_int(0), C.c_int(0)
+    assert lib.tdist_gemm_schedule_check(1, 70, 8, 3, 4, 24, 0, 22, C.byref(span), C.byref(first)) == 0
+    assert span.value == 11 and first.value == 1
+    assert lib.tdist_gemm_schedule_check(1, 70, 8, 3, 4, 24, 0, 0, C.byref(span), C.byref(first)) == 0
+    assert span.value == 11 and first.value == 0

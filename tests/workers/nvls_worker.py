@@ -72,6 +72,30 @@ def body(group, rank, world, dev, cuda, res):
         assert torch.equal(buf.local, want)
         res["fast_allgather_used_nvls"] = bool(ag.nvls is not None and ag.nvls.epoch > 0)
         heap.barrier()
+    # the sequence-parallel decode exchanges its partial results as LL packets stored once through the multicast alias
+    if cuda:
+        import math
+
+        from triton_distributed_b200.ops import flash_decode as FD
+        B, Hq, Hkv, D, page = 4, 32, 8, 128, 16
+        sctx = FD.create_sp_decode_context(rank, world, B, Hq, D, group=group, device=dev)
+        res["sp_decode_multicast"] = bool(sctx.gather.mc is not None and FD.SP_DECODE_NVLS)
+        for it in range(6):
+            gen = torch.Generator().manual_seed(55 + it)  # identical on every rank
+            q = torch.randn(B, Hq, D, generator=gen).to(dev, torch.bfloat16)
+            glens = torch.randint(1, 600, (world, B), generator=gen, dtype=torch.int32).to(dev)
+            max_blocks = (int(glens[rank].max()) + page - 1) // page
+            k = torch.randn(B * max_blocks, page, Hkv, D, device=dev).to(torch.bfloat16)
+            v = torch.randn(B * max_blocks, page, Hkv, D, device=dev).to(torch.bfloat16)
+            table = torch.randperm(B * max_blocks, device=dev).view(B, max_blocks).to(torch.int32)
+            out = FD.sp_gqa_fwd_batch_decode(sctx, q, k, v, glens, table)
+            check_status()
+            o, l = FD.ref_paged_attn(q, k, v, glens[rank], table, 1.0 / math.sqrt(D), return_lse=True)
+            mine = torch.cat([o, l.unsqueeze(-1)], -1).contiguous()
+            parts = [torch.empty_like(mine) for _ in range(world)]
+            dist.all_gather(parts, mine, group=group)
+            ref = FD.ref_lse_merge(torch.stack(parts))
+            torch.testing.assert_close(out.float(), ref, atol=5e-2, rtol=5e-2)
     res["checked"] = True
 
 

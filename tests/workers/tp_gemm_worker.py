@@ -39,10 +39,11 @@ def main():
 
     # ---------------- AG-GEMM ----------------
     # on GPUs: tile-aligned, ragged (8-column partial tile, rows no multiple of 128), and two K >= 4096 problems that the
-    # launcher runs with the wide (256 x 512) pair tiling, one of them with a 200-column partial tile
+    # launcher runs with the wide (256 x 512) pair tiling, one of them with a 200-column partial tile; the last one has
+    # 44 wide items per segment (21 tiles per row: an odd one out) for ~70 CTA pairs, so its first round is split in halves
     shapes = [(128, 256, 256), (999, 264, 520)] if cuda else [(128, 256, 256)]
     if cuda:
-        shapes += [(1024, 1024, 2048), (520, 1224, 4096), (256, 2048, 4160)]
+        shapes += [(1024, 1024, 2048), (520, 1224, 4096), (256, 2048, 4160), (1000, 5128, 4096)]
     ag_err = 0.0
     for (mpr, n_per, K) in shapes:
         gen = torch.Generator(device="cpu").manual_seed(0)

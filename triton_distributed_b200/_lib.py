@@ -54,7 +54,7 @@ class GemmArgs(C.Structure):
         ("stream", C.c_void_p),
         ("trace", C.c_void_p),
         ("expert_ids", C.c_void_p), ("num_m_blocks", C.c_void_p), ("num_experts", C.c_int),
-        ("a_ws_mc", C.c_void_p),
+        ("a_ws_mc", C.c_void_p), ("push_count", C.c_void_p),
         ("a_gather", C.c_void_p), ("a_gather_rows", C.c_int), ("block_src", C.c_void_p), ("src_flags", C.c_void_p),
         ("src_epoch", C.c_uint64), ("src_rank", C.c_int), ("src_world", C.c_int),
         ("gather_dst", C.c_void_p), ("block_ready", C.c_void_p), ("gather_counter", C.c_void_p), ("block_rot", C.c_void_p),
@@ -222,6 +222,8 @@ def _declare(lib):
     lib.tdist_status_destroy.argtypes = [C.c_void_p]
     lib.tdist_gemm_run.argtypes = [C.POINTER(GemmArgs)]
     lib.tdist_gemm_grid.argtypes = [C.POINTER(GemmArgs)]
+    lib.tdist_gemm_schedule_check.argtypes = [C.c_int] * 8 + [C.POINTER(C.c_int), C.POINTER(C.c_int)]
+    lib.tdist_gemm_schedule_check.restype = C.c_int
     lib.tdist_gemm_fp8_run.argtypes = [C.POINTER(GemmFp8Args)]
     lib.tdist_allgather.argtypes = [C.POINTER(CollArgs)]
     lib.tdist_nvls.argtypes = [C.POINTER(NvlsArgs)]

@@ -1,7 +1,7 @@
 """Per-op micro-benchmarks: device-timed, max over ranks, one JSON row per measurement.
 
     python -m triton_distributed_b200.bench_ops --op gemm --m 8192 --n 6144 --k 12288
-    torchrun --nproc-per-node 8 -m triton_distributed_b200.bench_ops --op ag_gemm --m 8192 --n 49152 --k 12288
+    torchrun --nproc-per-node 8 -m triton_distributed_b200.bench_ops --op ag_gemm --shape 8192x49152x12288
 
 Rows carry {op, shape, world, us (max over ranks), tflops or gbps, roofline fraction}. The
 roofline denominators are read from MEASURED_PEAKS.json at the repository root when present
@@ -412,7 +412,7 @@ def _bench_moe_tp(args, world, rank, group, dev, dtype, pk, row):
     b2 = (torch.randn(E, I // world, H, device=dev) * I ** -0.5).to(dtype)
     ctx2 = MT.create_moe_rs_context(group, rank, world, world, M, H, E, topk, dtype, dtype, dev, full_topk_ids=ids, full_topk_weight=w)
     flops1 = 2.0 * M * topk * (I // world) * H
-    # fused: one grouped-GEMM launch that stages its rows block by block (gatherer CTAs), waits per block for the
+    # fused: one grouped-GEMM launch that stages its rows block by block (its own warps), waits per block for the
     # all-gather, stores every row at its final position; top-k reduce inside the reduce-scatter.
     # staged: all-gather, row-gather, grouped GEMM, un-sort, top-k reduce, reduce-scatter as separate launches.
     for name, mode, flag in (("fused", "fused", True), ("staged", "staged", False)):
@@ -518,6 +518,9 @@ def _run_suite(args, world, rank, group, dev, dtype, pk):
         run("ag_gemm", _bench_gemm_family, m=8192, n=n, k=k)
     for (n, k) in ((4096, 11008), (4096, 14336), (3584, 14336), (4608, 36864), (8192, 28672), (8192, 29568)):
         run("gemm_rs", _bench_gemm_family, m=8192, n=n, k=k)
+    # tensor-parallel MoE (8 experts, top-2, hidden 4096, intermediate 14336 split over the ranks): one-launch against staged
+    run("moe_tp", _bench_moe_tp, m=8192, n=14336, k=4096, experts=8, topk=2, iters=10)
+    run("moe_tp", _bench_moe_tp, m=2048, n=14336, k=4096, experts=8, topk=2, iters=20)
     PRESLEEP_CYCLES = int(30 * 1.9e6)
     if world > 1 or True:
         run("a2a", _bench_a2a, tokens=128, hidden=7168, experts=256, topk=8, iters=50)

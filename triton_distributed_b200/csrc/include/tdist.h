@@ -81,6 +81,10 @@ typedef struct TdistGemmArgs {
     /* AG, optional: multicast alias of `a_ws` (a heap bound to an NVSwitch multicast object). When set, the
      * pushers store every block once with multimem.st instead of once per peer. */
     void* a_ws_mc;
+    /* AG, optional: device uint32[(world - 1) * blocks per segment], zero before the first call (the kernel leaves it
+     * zero). With it the unicast pushers send every 128-row block as up to eight row slices in parallel and meet on
+     * these counters; the pusher that completes a block raises its flag. Without it a block is one pusher's work. */
+    void* push_count;
     /* PLAIN, optional row-gathering A: row r of the logical A [m_per_rank, K] is row a_gather[r] (device int32) of
      * the matrix at `a` ([a_gather_rows, K]); indices outside [0, a_gather_rows) read as zeros. One CTA per tile;
      * the producer warp copies the rows with cp.async. With block_src (device int32 per 128-row block) the rows of
@@ -94,15 +98,16 @@ typedef struct TdistGemmArgs {
     uint64_t src_epoch;
     int src_rank, src_world;
     /* Row-gathering A through a staging matrix (preferred form of the above): with gather_dst set ([m_per_rank, K]
-     * workspace), `num_comm_sms` CTAs of the grid (default 8) copy the rows block by block into gather_dst, in the
-     * order the GEMM consumes them, and raise block_ready[b] = epoch (device uint32 per 128-row block, zero before
-     * the first call, epochs strictly increasing); the GEMM CTAs feed on gather_dst with TMA and wait per block. The
-     * copy of one block overlaps the MMAs of the blocks before it, and with block_src the all-gather in flight. */
+     * workspace) the kernel itself copies the rows block by block into gather_dst, in the order the GEMM consumes
+     * them, and raises block_ready[b] = epoch (device uint32 per 128-row block, zero before the first call, epochs
+     * strictly increasing); the TMA producers feed on gather_dst and wait per block. All threads of the grid stage
+     * the blocks of the first wave of tiles before the roles split; the epilogue warps stage the rest, 16 rows per
+     * claim, while they wait for accumulators. The copy of one block overlaps the MMAs of the blocks before it, and
+     * with block_src the all-gather in flight. */
     void* gather_dst;
     void* block_ready;
-    /* device uint32, zero before the first call, may be NULL: with it, ALL CTAs of the grid first stage the blocks
-     * the first wave of tiles needs (ld/st copies, a warp per row) so the MMAs do not wait for the few gatherer CTAs
-     * to get ahead; without it the gatherer CTAs stage every block */
+    /* device uint32[4 + blocks], zero before the first call (the kernel leaves it zero): grid-wide arrival counters
+     * and the claim cursor of the staging */
     void* gather_counter;
     /* device int32, may be NULL: 128-row block the schedule starts at (blocks are visited cyclically from there),
      * e.g. the first block of this rank's own tokens */
@@ -116,6 +121,13 @@ typedef struct TdistGemmArgs {
 int tdist_gemm_run(const TdistGemmArgs* args);
 /* Number of CTAs a call with these arguments launches (for occupancy planning and tests). */
 int tdist_gemm_grid(const TdistGemmArgs* args);
+/* Host-side replay of the kernel's static tile schedule (no GPU needed): `num_units` CTAs or CTA pairs over a problem
+ * of `world` segments of seg_m_tiles x n_tiles 256-column tiles, wide (items of two neighbouring tiles) or narrow,
+ * with `split_first` own items cut in two in round 0. Returns 0 when every tile is given out exactly once;
+ * *makespan_halves = the longest unit in half items (a wide item counts 2), *first_remote_half = how many half items
+ * the earliest unit has done before it first needs another rank's rows. */
+int tdist_gemm_schedule_check(int wide, int num_units, int world, int rank, int seg_m_tiles, int n_tiles, int group_m,
+                              int split_first, int* makespan_halves, int* first_remote_half);
 
 /* Block-scaled fp8 (e4m3) GEMM, plain or fused AllGather-GEMM (csrc/kernels/gemm_fp8_sm100.cu).
  * C[m, n] = sum_kb sa[m, kb] * sb[n / 128, kb] * dot(A[m, 128kb : 128kb+128], B[n, same]); C is bf16. */

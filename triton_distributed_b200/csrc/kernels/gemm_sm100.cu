@@ -38,6 +38,7 @@
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
 
+#include <cstdlib>
 #include <string>
 
 #include "../device/ptx.cuh"
@@ -99,8 +100,12 @@ struct GemmParams {
     int seg_m_tiles, n_tiles, k_blocks;
     int seg_blocks;  // 128-row blocks per segment (flag granularity)
     int num_tiles;   // work items of the schedule: 256-column tiles, or 512-column tiles (wide tiling)
+    int split_first; // wide tiling, AG: own items cut into halves in round 0 (see get_work)
     int n_pairs;     // wide tiling: 512-column tiles per row of tiles = ceil(n_tiles / 2)
     int num_comm;
+    int push_ahead;             // chunks the pusher's loads run ahead of its stores (1..PUSH_AHEAD)
+    int push_parts;             // row slices a 128-row block is pushed in (AG, unicast pushers)
+    uint32_t* push_count;       // [(world - 1) * seg_blocks] slice arrivals per (hop, block), zero between launches
     int group_m;
     int is_f16;
     uint32_t epoch;
@@ -119,11 +124,11 @@ struct GemmParams {
     const uint64_t* src_flags;
     uint64_t src_epoch;
     int src_rank, src_world;    // this rank and the size of the all-gather's group
-    // Staged row gather (PLAIN): the first num_comm CTAs copy the rows of block b into gather_dst (the matrix tm_a
-    // describes) and raise block_ready[b] = epoch; the TMA producers wait per block.
+    // Staged row gather (PLAIN): the rows of block b are copied into gather_dst (the matrix tm_a describes) by the
+    // CTAs' own warps, block_ready[b] = epoch says they are complete; the TMA producers wait per block.
     char* gather_dst;
     uint32_t* block_ready;
-    uint32_t* gather_counter;   // arrival counter of the all-CTA prologue (zero between launches)
+    uint32_t* gather_counter;   // 4 + blocks words, zero between launches: prologue arrivals, claim cursor, exits, per-block arrivals
     int gather_pro_blocks;      // blocks the prologue stages
     const int* block_rot;       // device scalar: block the schedule starts at (cyclic), nullptr = 0
     // Scattering epilogue (PLAIN, one CTA per tile): row r of the product goes to row c_scatter[r] of c_out.
@@ -155,7 +160,7 @@ struct TileCoord {
 // Tiles are ordered segment by segment (a segment = the rows one rank owns), starting at
 // `first_seg`; inside a segment, groups of GROUP_M row-tiles sweep all column-tiles so that
 // concurrently running CTAs share A rows and B columns in L2.
-__device__ __forceinline__ TileCoord decode_tile(int t, int first_seg, int world, int seg_m_tiles,
+__host__ __device__ __forceinline__ TileCoord decode_tile(int t, int first_seg, int world, int seg_m_tiles,
                                                  int n_tiles, int GROUP_M) {
     const int per_seg = seg_m_tiles * n_tiles;
     const int si = t / per_seg;
@@ -179,11 +184,16 @@ struct Work {
 };
 
 // Static schedule: unit u of num_units takes item u + round * num_units. Narrow tilings: an item is one 256-column
-// tile. Wide tiling: an item is a pair of neighbouring 256-column tiles (the odd last tile of a row stands alone);
-// when the last, partial round holds at most num_units / 2 items, each of them is split into its halves, which go to
-// two units, so that the round takes half as long. Returns false once the unit has nothing left.
+// tile. Wide tiling: an item is a pair of neighbouring 256-column tiles (the odd last tile of a row stands alone), and
+// two rounds may be cut into halves (single 256-column tiles, half as long):
+//  * the last, partial round, when that shortens it (the units that are free first take whole items, the others halves);
+//  * the first round of the AG mode when this rank's own segment has fewer items than there are units (`split_first` of
+//    them, S = units - own items): instead of sending S units to a peer's segment, whose rows have not arrived yet, the
+//    last S own items are cut in two, so that 2 S "early" units finish round 0 in half the time, by when the first
+//    remote segment is here. From then on the early units come first in every round.
+// Returns false once the unit has nothing left; an item with halves == 0 means "nothing in this round".
 template <bool WIDE>
-__device__ __forceinline__ bool get_work(const GemmParams& p, int unit, int num_units, int round, int first_seg, Work& w) {
+__host__ __device__ __forceinline__ bool get_work(const GemmParams& p, int unit, int num_units, int round, int first_seg, Work& w) {
     if (!WIDE) {
         const int t = unit + round * num_units;
         if (t >= p.num_tiles) return false;
@@ -194,20 +204,47 @@ __device__ __forceinline__ bool get_work(const GemmParams& p, int unit, int num_
         w.halves = 1;
         return true;
     }
-    const int full_rounds = p.num_tiles / num_units;
-    const int rem = p.num_tiles - full_rounds * num_units;
+    const int S = p.split_first;             // own items cut in two in round 0
+    const int E = 2 * S, L = num_units - E;  // early units (a half in round 0) and late units (a whole item)
     int t, half = -1;
-    if (round < full_rounds) {
-        t = unit + round * num_units;
-    } else if (round > full_rounds || rem == 0) {
-        return false;
-    } else if (2 * rem <= num_units) {
-        if (unit >= 2 * rem) return false;
-        t = full_rounds * num_units + (unit >> 1);
-        half = unit & 1;
+    if (S > 0 && round == 0) {
+        if (unit < L) {
+            t = unit;
+        } else {
+            t = L + ((unit - L) >> 1);
+            half = (unit - L) & 1;
+        }
     } else {
-        if (unit >= rem) return false;
-        t = full_rounds * num_units + unit;
+        const int base = S > 0 ? L + S : 0;                                  // items taken by round 0
+        const int r = S > 0 ? round - 1 : round;
+        const int pos = S > 0 ? (unit >= L ? unit - L : E + unit) : unit;    // early units first
+        const int rest = p.num_tiles - base;
+        const int full_rounds = rest / num_units;
+        const int rem = rest - full_rounds * num_units;
+        if (r < full_rounds) {
+            t = base + r * num_units + pos;
+        } else if (r > full_rounds || rem == 0) {
+            return false;
+        } else if (2 * rem <= E) {
+            // the early units alone finish the rest as halves
+            if (pos >= 2 * rem) return false;
+            t = base + full_rounds * num_units + (pos >> 1);
+            half = pos & 1;
+        } else if (2 * (rem - E) <= L) {
+            // early units take whole items, late units (half an item behind) halves: both end together
+            if (pos < E) {
+                if (pos >= rem) return false;
+                t = base + full_rounds * num_units + pos;
+            } else {
+                const int j = pos - E;
+                if (j >= 2 * (rem - E)) return false;
+                t = base + full_rounds * num_units + E + (j >> 1);
+                half = j & 1;
+            }
+        } else {
+            if (pos >= rem) return false;
+            t = base + full_rounds * num_units + pos;
+        }
     }
     const TileCoord tc = decode_tile(t, first_seg, p.world, p.seg_m_tiles, p.n_pairs, p.group_m);
     w.seg = tc.seg;
@@ -215,7 +252,10 @@ __device__ __forceinline__ bool get_work(const GemmParams& p, int unit, int num_
     w.n_tile = 2 * tc.n_tile;
     w.halves = (w.n_tile + 1 < p.n_tiles) ? 2 : 1;
     if (half >= 0) {
-        if (half >= w.halves) return false;
+        if (half >= w.halves) {
+            w.halves = 0;   // the second half of a row's odd last tile: nothing to do in this round
+            return true;
+        }
         w.n_tile += half;
         w.halves = 1;
     }
@@ -229,67 +269,172 @@ __device__ __forceinline__ uint32_t slot_of_half(const Work& w, int h, uint32_t 
 
 // ------------------------------------------------------------------------------------------
 // AG pusher: one thread per pusher CTA streams this rank's shard to the peers.
-// Work items are (destination, 128-row block) pairs ordered by how soon the destination's
-// MMA side reaches this rank's rows (rank-1 first), dealt round-robin to the pusher CTAs.
+// Work items are (destination, 128-row block, part) triples ordered by how soon the destination's MMA side reaches
+// this rank's rows (rank-1 first), dealt round-robin to the pusher CTAs. A block is cut into `push_parts` row slices
+// that different pushers send at the same time, so that the first blocks of a segment reach their destination a
+// pusher-count sooner than whole blocks would (the GEMM CTAs that have no local tile in the first wave wait for
+// exactly those); the pusher whose slice completes a block raises the block's flag at the destination.
+// The chunks of consecutive items form ONE stream through the ring (loads PUSH_AHEAD chunks ahead of the stores): an
+// item's flag is raised a few chunks into the next item, when waiting for its stores costs nothing.
 // ------------------------------------------------------------------------------------------
+struct PushItem {
+    const char* src;
+    char* dst;
+    size_t bytes;
+    int nchunks;
+    int dest, mb, hop;
+};
+// Item `j` of this pusher (items blockIdx.x + j * num_comm of the global order). False past the end.
+__device__ __forceinline__ bool push_item(const GemmParams& p, int j, PushItem& it) {
+    const int parts = p.push_parts;
+    const int item = static_cast<int>(blockIdx.x) + j * p.num_comm;
+    if (item >= (p.world - 1) * p.seg_blocks * parts) return false;
+    const int part = item % parts;
+    const int mb = (item / parts) % p.seg_blocks;
+    const int hop = item / (parts * p.seg_blocks) + 1;
+    int dst = p.rank - hop;
+    if (dst < 0) dst += p.world;
+    const size_t row_bytes = static_cast<size_t>(p.k) * 2;
+    const int rows = min(BM, p.m_per_rank - mb * BM);
+    const int per = BM / parts;
+    const int r0 = min(part * per, rows), r1 = min(r0 + per, rows);
+    it.bytes = static_cast<size_t>(r1 - r0) * row_bytes;
+    it.src = p.a_own + (static_cast<size_t>(mb) * BM + r0) * row_bytes;
+    it.dst = p.a_ws_peer[dst] + (static_cast<size_t>(p.rank) * p.m_per_rank + static_cast<size_t>(mb) * BM + r0) * row_bytes;
+    it.nchunks = static_cast<int>((it.bytes + PUSH_CHUNK - 1) / PUSH_CHUNK);
+    it.dest = dst;
+    it.mb = mb;
+    it.hop = hop;
+    return true;
+}
+// The item's rows are complete at the destination (the caller has waited for the stores): order them (async proxy)
+// before the release of the flag (generic proxy). With several parts per block the pushers meet on a local counter
+// and the last one raises the flag.
+__device__ __forceinline__ void push_publish(const GemmParams& p, const PushItem& it) {
+    fence_proxy_async();
+    uint32_t* flag = p.flags_peer[it.dest] + p.rank * p.seg_blocks + it.mb;
+    if (p.push_parts == 1) {
+        fence_acq_rel_sys();
+        st_release_sys_u32(flag, p.epoch);
+        return;
+    }
+    // gpu scope is enough between the pushers of this GPU (the release half of the add orders this slice's completed
+    // writes before it); the pusher that completes the block then releases at system scope on behalf of all of them
+    uint32_t* cnt = p.push_count + (it.hop - 1) * p.seg_blocks + it.mb;
+    if (atom_add_acq_rel_gpu_u32(cnt, 1) == static_cast<uint32_t>(p.push_parts - 1)) {
+        *cnt = 0;   // for the next launch
+        fence_acq_rel_sys();
+        st_release_sys_u32(flag, p.epoch);
+    }
+}
 __device__ void ag_pusher(const GemmParams& p, uint8_t* smem, uint64_t* bars) {
     if (threadIdx.x != 0) return;
-    const int nitems = (p.world - 1) * p.seg_blocks;
-    const size_t row_bytes = static_cast<size_t>(p.k) * 2;
+    // An item's flag is raised once FLAG_LAG younger chunks have been stored: a remote bulk store takes several
+    // microseconds to complete, and waiting for it any sooner stalls the stream (8 slices per block with a lag of 4
+    // chunks ran at 19 GB/s per pusher instead of 36). Up to PENDING finished items wait for their flags.
+    constexpr int FLAG_LAG = 12;
+    constexpr int PENDING = 4;
     uint32_t full[PUSH_STAGES];
     for (int s = 0; s < PUSH_STAGES; ++s) full[s] = smem_u32(&bars[s]);
     uint32_t it_load = 0, it_store = 0;  // running chunk counters (stage = counter % PUSH_STAGES)
     unsigned long long* tr = (p.trace != nullptr && blockIdx.x < 16) ? p.trace + blockIdx.x * 40 : nullptr;
     int tr_item = 0;
+    unsigned long long t_wait = 0, t_publish = 0;   // timeline only: time in completion waits and in flag publication
     if (tr) tr[0] = globaltimer_ns();
+    if (p.debug_delay_ns > 0) __nanosleep(p.debug_delay_ns);
 
-    for (int item = static_cast<int>(blockIdx.x); item < nitems; item += p.num_comm) {
-        const int hop = item / p.seg_blocks + 1;
-        const int mb = item - (hop - 1) * p.seg_blocks;
-        int dst = p.rank - hop;
-        if (dst < 0) dst += p.world;
-        const int rows = min(BM, p.m_per_rank - mb * BM);
-        const size_t bytes = static_cast<size_t>(rows) * row_bytes;
-        const char* src = p.a_own + static_cast<size_t>(mb) * BM * row_bytes;
-        char* out = p.a_ws_peer[dst] +
-                    (static_cast<size_t>(p.rank) * p.m_per_rank + static_cast<size_t>(mb) * BM) * row_bytes;
-        const int nchunks = static_cast<int>((bytes + PUSH_CHUNK - 1) / PUSH_CHUNK);
-        if (p.debug_delay_ns > 0) __nanosleep(p.debug_delay_ns);
-        if (tr && tr_item < 19) tr[2 + 2 * tr_item] = globaltimer_ns();
-
-        for (int c = 0; c < nchunks + PUSH_AHEAD; ++c) {
-            if (c < nchunks) {
-                const uint32_t s = it_load % PUSH_STAGES;
-                // The store that last used this buffer was issued PUSH_STAGES chunks ago; at most
-                // PUSH_STAGES - PUSH_AHEAD - 1 younger stores may still be reading smem.
-                if (it_load >= PUSH_STAGES) bulk_wait_read<PUSH_STAGES - PUSH_AHEAD - 1>();
-                const size_t off = static_cast<size_t>(c) * PUSH_CHUNK;
-                const uint32_t sz = static_cast<uint32_t>(min(static_cast<size_t>(PUSH_CHUNK), bytes - off));
-                mbar_expect_tx(full[s], sz);
-                bulk_load(smem_u32(smem + s * PUSH_CHUNK), src + off, sz, full[s]);
-                ++it_load;
+    PushItem ld, st;
+    PushItem pend[PENDING];       // ring of finished items, oldest at pend_head
+    uint32_t pend_at[PENDING];    // it_store right after the item's last store
+    int pend_head = 0, pend_n = 0;
+    int ld_j = 0, ld_c = 0, st_j = 0, st_c = 0;
+    bool ld_ok = push_item(p, 0, ld), st_ok = push_item(p, 0, st);
+    while (st_ok) {
+        // loads: up to push_ahead chunks ahead of the stores, across item boundaries
+        while (ld_ok && it_load - it_store < static_cast<uint32_t>(p.push_ahead)) {
+            if (ld_c >= ld.nchunks) {
+                ld_ok = push_item(p, ++ld_j, ld);
+                ld_c = 0;
+                continue;
             }
-            if (c >= PUSH_AHEAD) {
-                const int cs = c - PUSH_AHEAD;
-                const uint32_t s = it_store % PUSH_STAGES;
-                mbar_wait(full[s], (it_store / PUSH_STAGES) & 1u, p.wctx, 10);
-                const size_t off = static_cast<size_t>(cs) * PUSH_CHUNK;
-                const uint32_t sz = static_cast<uint32_t>(min(static_cast<size_t>(PUSH_CHUNK), bytes - off));
-                bulk_store(out + off, smem_u32(smem + s * PUSH_CHUNK), sz);
-                bulk_commit();
-                ++it_store;
+            const uint32_t s = it_load % PUSH_STAGES;
+            // The store that last used this buffer was issued PUSH_STAGES chunks ago; at most
+            // PUSH_STAGES - push_ahead - 1 younger stores may still be reading smem.
+            if (it_load >= PUSH_STAGES) {
+                switch (p.push_ahead) {
+                    case 1: bulk_wait_read<PUSH_STAGES - 2>(); break;
+                    case 2: bulk_wait_read<PUSH_STAGES - 3>(); break;
+                    case 3: bulk_wait_read<PUSH_STAGES - 4>(); break;
+                    case 4: bulk_wait_read<PUSH_STAGES - 5>(); break;
+                    default: bulk_wait_read<PUSH_STAGES - PUSH_AHEAD - 1>(); break;
+                }
+            }
+            const size_t off = static_cast<size_t>(ld_c) * PUSH_CHUNK;
+            const uint32_t sz = static_cast<uint32_t>(min(static_cast<size_t>(PUSH_CHUNK), ld.bytes - off));
+            mbar_expect_tx(full[s], sz);
+            bulk_load(smem_u32(smem + s * PUSH_CHUNK), ld.src + off, sz, full[s]);
+            ++it_load;
+            ++ld_c;
+        }
+        if (st_c < st.nchunks) {
+            if (tr && st_c == 0 && tr_item < 19) tr[2 + 2 * tr_item] = globaltimer_ns();
+            const uint32_t s = it_store % PUSH_STAGES;
+            mbar_wait(full[s], (it_store / PUSH_STAGES) & 1u, p.wctx, 10);
+            const size_t off = static_cast<size_t>(st_c) * PUSH_CHUNK;
+            const uint32_t sz = static_cast<uint32_t>(min(static_cast<size_t>(PUSH_CHUNK), st.bytes - off));
+            bulk_store(st.dst + off, smem_u32(smem + s * PUSH_CHUNK), sz);
+            bulk_commit();
+            ++it_store;
+            ++st_c;
+        }
+        if (pend_n > 0 && it_store - pend_at[pend_head] >= static_cast<uint32_t>(FLAG_LAG)) {
+            // everything but the newest FLAG_LAG groups is complete: so are the stores of every pending item that old
+            const unsigned long long w0 = tr ? globaltimer_ns() : 0;
+            bulk_wait<FLAG_LAG>();
+            const unsigned long long w1 = tr ? globaltimer_ns() : 0;
+            while (pend_n > 0 && it_store - pend_at[pend_head] >= static_cast<uint32_t>(FLAG_LAG)) {
+                push_publish(p, pend[pend_head]);
+                pend_head = (pend_head + 1) % PENDING;
+                --pend_n;
+            }
+            if (tr) {
+                t_wait += w1 - w0;
+                t_publish += globaltimer_ns() - w1;
             }
         }
-        // Block complete at the destination before its flag: wait for the writes themselves,
-        // then order them (async proxy) before the system-scope release store (generic proxy).
-        bulk_wait<0>();
-        fence_proxy_async();
-        fence_acq_rel_sys();
-        st_release_sys_u32(p.flags_peer[dst] + p.rank * p.seg_blocks + mb, p.epoch);
-        if (tr && tr_item < 19) tr[3 + 2 * tr_item] = globaltimer_ns();
-        ++tr_item;
+        if (st_c >= st.nchunks) {
+            // the item's last store is issued (or it had none: a slice past the end of a ragged block)
+            if (pend_n == PENDING) {
+                bulk_wait<0>();
+                while (pend_n > 0) {
+                    push_publish(p, pend[pend_head]);
+                    pend_head = (pend_head + 1) % PENDING;
+                    --pend_n;
+                }
+            }
+            if (tr && tr_item < 19) tr[3 + 2 * tr_item] = globaltimer_ns();
+            ++tr_item;
+            const int slot = (pend_head + pend_n) % PENDING;
+            pend[slot] = st;
+            pend_at[slot] = it_store;
+            ++pend_n;
+            st_ok = push_item(p, ++st_j, st);
+            st_c = 0;
+        }
     }
-    if (tr) tr[1] = globaltimer_ns();
+    if (pend_n > 0) {
+        bulk_wait<0>();
+        while (pend_n > 0) {
+            push_publish(p, pend[pend_head]);
+            pend_head = (pend_head + 1) % PENDING;
+            --pend_n;
+        }
+    }
+    if (tr) {
+        tr[1] = globaltimer_ns();
+        tr[38] = t_wait;
+        tr[39] = t_publish;
+    }
 }
 
 // ------------------------------------------------------------------------------------------
@@ -351,14 +496,17 @@ __device__ void ag_pusher_nvls(const GemmParams& p, uint8_t* smem, uint64_t* bar
 }
 
 // ------------------------------------------------------------------------------------------
-// Local gatherer (grouped GEMM over rows picked by index): the comm CTAs copy the rows of one 128-row block after
-// the other into the staging matrix the TMA producers read, in the order the GEMM visits the blocks, and publish
-// one flag per block. With block_src the rows of a block come from another rank's segment of an all-gather that may
-// still be in flight: the gatherer waits for that rank's arrival flag first, so the MMAs of the blocks that are
-// already here run while the later segments are still on the wire. Plays the role of the reference's
-// `kernel_consumer_m_parallel_scatter_group_gemm` gathering A rows by `sorted_token_ids` behind a per-rank barrier
-// (kernels/nvidia/allgather_group_gemm.py:229-314).
+// Staged row gather (grouped GEMM over rows picked by index): the rows of one 128-row block after the other are copied
+// into the staging matrix the TMA producers read, in the order the GEMM visits the blocks, with one flag per block.
+// The first wave's blocks are copied by all threads of the grid before the roles split; the others by the epilogue
+// warps while they wait for accumulators. With block_src the rows of a block come from another rank's segment of an
+// all-gather that may still be in flight: a group is copied only once that rank's arrival flag is up, so the MMAs of
+// the blocks that are already here run while the later segments are still on the wire. Plays the role of the
+// reference's `kernel_consumer_m_parallel_scatter_group_gemm` gathering A rows by `sorted_token_ids` behind a per-rank
+// barrier (kernels/nvidia/allgather_group_gemm.py:229-314).
 // ------------------------------------------------------------------------------------------
+// words of the gather_counter array
+enum : int { kGatherPrologue = 0, kGatherCursor = 1, kGatherExits = 2, kGatherArrive = 4 };
 // Blocks (in schedule order) that every CTA of the grid helps to stage before the MMAs start: what the first wave of
 // tiles touches, cut short at the first block whose rows belong to another rank's segment (those may not be here yet).
 __device__ __forceinline__ int gather_prologue_blocks(const GemmParams& p, int live, int rot) {
@@ -400,93 +548,114 @@ __device__ void gather_prologue(const GemmParams& p, int pro, int live, int rot)
     // arrive has every CTA's rows behind it when it raises the flags
     __syncthreads();
     if (tid == 0) {
-        const uint32_t old = atom_add_acq_rel_gpu_u32(p.gather_counter, 1);
+        const uint32_t old = atom_add_acq_rel_gpu_u32(p.gather_counter + kGatherPrologue, 1);
         if (old == gridDim.x - 1) {
-            *p.gather_counter = 0;
+            p.gather_counter[kGatherPrologue] = 0;
             fence_acq_rel_gpu();
             for (int i = 0; i < pro; ++i) st_release_gpu_u32(p.block_ready + rotate_block(i, rot, live), p.epoch);
         }
     }
 }
 
-// The remaining blocks: one thread per gatherer CTA streams the rows through shared memory with bulk-async copies
-// (the same ring as the AG pusher: loads run PUSH_AHEAD chunks ahead of the stores), a row (or a 32 KB piece of a
-// longer row) per chunk, and raises the block's flag once its stores have completed.
-__device__ void local_gatherer(const GemmParams& p, uint8_t* smem, uint64_t* bars, int pro, int live, int rot) {
-    if (threadIdx.x != 0) return;
-    const size_t row_bytes = static_cast<size_t>(p.k) * 2;
-    // A chunk of the ring is PUSH_CHUNK bytes of rows: several whole rows when they are short (so that the bytes in
-    // flight do not shrink with K), or a piece of one long row.
-    const int rpc = row_bytes >= PUSH_CHUNK ? 1 : static_cast<int>(PUSH_CHUNK / row_bytes);            // rows per chunk
-    const int cpr = row_bytes > PUSH_CHUNK ? static_cast<int>((row_bytes + PUSH_CHUNK - 1) / PUSH_CHUNK) : 1;  // chunks per row
-    const int nchunks = cpr > 1 ? BM * cpr : (BM + rpc - 1) / rpc;
-    uint32_t it_load = 0, it_store = 0;
-    // piece i of chunk j of block b: source, destination, size, offset inside the chunk's buffer; false = padding row
-    auto piece = [&](int b, int j, int i, const char** src, char** dst, uint32_t* sz, uint32_t* at) -> bool {
-        const int r = cpr > 1 ? j / cpr : j * rpc + i;
-        const int c = cpr > 1 ? j - r * cpr : 0;
-        const int row = b * BM + r;
-        if (r >= BM || row >= p.m_per_rank) return false;
+// The remaining blocks are staged by the epilogue warps of the GEMM CTAs in the time they would otherwise spend waiting
+// for an accumulator: a warp claims the next 16-row group (in the order the GEMM visits the blocks) from a grid-wide
+// cursor, copies it one row per step, looking at its accumulator barrier between rows, and the warp that completes a
+// block's last group raises the block's flag. No CTA is taken away from the MMAs and the copy bandwidth grows with the
+// grid (4 warps x 148 CTAs).
+constexpr int GATHER_SUB = 16;              // rows per claimed item
+constexpr int GATHER_SUBS = BM / GATHER_SUB;
+struct GatherCursor {
+    int item;   // claimed group in schedule order (-1: none claimed yet)
+    int row;    // next row of the group
+};
+
+// One step of a warp's share: claim a group if it holds none, then copy at most one row. False once the cursor has run
+// past the last block (nothing left for this warp). A group whose rows belong to an all-gather segment that has not
+// arrived yet is kept and retried on the next step.
+__device__ __forceinline__ bool gather_step(const GemmParams& p, GatherCursor& g, int pro, int live, int rot, int lane) {
+    if (g.item < 0) {
+        int it = 0;
+        if (lane == 0) it = static_cast<int>(atomicAdd(p.gather_counter + kGatherCursor, 1u)) + pro * GATHER_SUBS;
+        g.item = __shfl_sync(0xffffffffu, it, 0);
+        g.row = 0;
+    }
+    if (g.item >= live * GATHER_SUBS) return false;
+    const int b = rotate_block(g.item / GATHER_SUBS, rot, live);
+    if (g.row == 0 && p.block_src != nullptr) {
+        const int srcr = p.block_src[b];
+        if (srcr != p.src_rank && srcr >= 0 && srcr < p.src_world) {
+            // every lane acquires: its own loads below are ordered after the segment's arrival
+            const bool here = static_cast<long long>(ld_acquire_sys_u64(p.src_flags + srcr)) >= static_cast<long long>(p.src_epoch);
+            if (!__all_sync(0xffffffffu, here)) return true;
+        }
+    }
+    const int row = b * BM + (g.item % GATHER_SUBS) * GATHER_SUB + g.row;
+    if (row < p.m_per_rank) {
         const int idx = p.a_gather[row];
-        if (idx < 0 || idx >= p.a_gather_rows) return false;
-        const size_t off = static_cast<size_t>(c) * PUSH_CHUNK;
-        *src = p.a_raw + static_cast<size_t>(idx) * row_bytes + off;
-        *dst = p.gather_dst + static_cast<size_t>(row) * row_bytes + off;
-        *sz = static_cast<uint32_t>(min(static_cast<size_t>(PUSH_CHUNK), row_bytes - off));
-        *at = cpr > 1 ? 0u : static_cast<uint32_t>(i) * static_cast<uint32_t>(row_bytes);
-        return true;
-    };
-    const int pieces = cpr > 1 ? 1 : rpc;
-    for (int i0 = pro + static_cast<int>(blockIdx.x); i0 < live; i0 += p.num_comm) {
-        const int b = rotate_block(i0, rot, live);
-        if (p.block_src != nullptr) {
-            const int srcr = p.block_src[b];
-            if (srcr != p.src_rank && srcr >= 0 && srcr < p.src_world) {
-                signal_wait_until(p.src_flags + srcr, kCmpGe, p.src_epoch, p.wctx, srcr, 8);
-                fence_proxy_async();   // the segment was written by a peer's stores, the bulk loads below read it
+        if (idx >= 0 && idx < p.a_gather_rows) {   // else a padding row: its product is never used
+            const size_t row_bytes = static_cast<size_t>(p.k) * 2;
+            const char* src = p.a_raw + static_cast<size_t>(idx) * row_bytes;
+            char* dst = p.gather_dst + static_cast<size_t>(row) * row_bytes;
+            for (size_t off = static_cast<size_t>(lane) * 16; off < row_bytes; off += 8 * 512) {
+                uint4 q[8];
+#pragma unroll
+                for (int u = 0; u < 8; ++u)
+                    if (off + u * 512 < row_bytes) q[u] = *reinterpret_cast<const uint4*>(src + off + u * 512);
+#pragma unroll
+                for (int u = 0; u < 8; ++u)
+                    if (off + u * 512 < row_bytes) *reinterpret_cast<uint4*>(dst + off + u * 512) = q[u];
             }
         }
-        if (p.debug_delay_ns > 0) __nanosleep(p.debug_delay_ns);
-        for (int j = 0; j < nchunks + PUSH_AHEAD; ++j) {
-            const char* src;
-            char* dst;
-            uint32_t sz, at;
-            if (j < nchunks) {
-                // total bytes of the chunk first (one expect_tx), then its loads
-                uint32_t total = 0;
-                for (int i = 0; i < pieces; ++i)
-                    if (piece(b, j, i, &src, &dst, &sz, &at)) total += sz;
-                if (total > 0) {
-                    const uint32_t s = it_load % PUSH_STAGES;
-                    // the stores that last used this buffer were issued at least PUSH_STAGES - PUSH_AHEAD chunks ago
-                    if (it_load >= PUSH_STAGES) bulk_wait_read<PUSH_STAGES - PUSH_AHEAD - 1>();
-                    mbar_expect_tx(smem_u32(&bars[s]), total);
-                    for (int i = 0; i < pieces; ++i)
-                        if (piece(b, j, i, &src, &dst, &sz, &at))
-                            bulk_load(smem_u32(smem + s * PUSH_CHUNK) + at, src, sz, smem_u32(&bars[s]));
-                    ++it_load;
-                }
-            }
-            if (j >= PUSH_AHEAD) {
-                bool any = false;
-                for (int i = 0; i < pieces; ++i) any = piece(b, j - PUSH_AHEAD, i, &src, &dst, &sz, &at) || any;
-                if (any) {
-                    const uint32_t s = it_store % PUSH_STAGES;
-                    mbar_wait(smem_u32(&bars[s]), (it_store / PUSH_STAGES) & 1u, p.wctx, 12);
-                    for (int i = 0; i < pieces; ++i)
-                        if (piece(b, j - PUSH_AHEAD, i, &src, &dst, &sz, &at))
-                            bulk_store(dst, smem_u32(smem + s * PUSH_CHUNK) + at, sz);
-                    bulk_commit();   // one group per chunk: the wait_group.read above counts chunks
-                    ++it_store;
-                }
+    }
+    if (++g.row == GATHER_SUB) {
+        // the warp barrier orders every lane's stores before lane 0's arrival (gpu scope, acq_rel); the warp that brings
+        // the block's count to GATHER_SUBS therefore has all of the block's rows behind it when it raises the flag
+        __syncwarp();
+        if (lane == 0) {
+            fence_acq_rel_gpu();
+            const uint32_t old = atom_add_acq_rel_gpu_u32(p.gather_counter + kGatherArrive + b, 1);
+            if (old == GATHER_SUBS - 1) {
+                p.gather_counter[kGatherArrive + b] = 0;
+                st_release_gpu_u32(p.block_ready + b, p.epoch);
             }
         }
-        // the rows are complete in the staging matrix before the flag: wait for the writes themselves, then order
-        // them (async proxy) before the release store (generic proxy)
-        bulk_wait<0>();
-        fence_proxy_async();
-        fence_acq_rel_gpu();
-        st_release_gpu_u32(p.block_ready + b, p.epoch);
+        g.item = -1;
+    }
+    return true;
+}
+
+// The epilogue's wait for an accumulator, spent on the row staging while there is any.
+__device__ __forceinline__ void gather_while_waiting(const GemmParams& p, GatherCursor& g, int pro, int live, int rot, int lane,
+                                                     uint32_t bar, uint32_t parity, int where) {
+    uint64_t t0 = 0;
+    uint32_t spins = 0;
+    const uint64_t limit = p.wctx.timeout_ns ? p.wctx.timeout_ns : kDefaultTimeoutNs;
+    while (true) {
+        // all lanes take the same branch: the barrier's state is read by lane 0 only
+        const bool done = __shfl_sync(0xffffffffu, lane == 0 ? mbar_test_wait(bar, parity) : false, 0);
+        if (done) break;
+        if (!gather_step(p, g, pro, live, rot, lane)) break;
+        if ((++spins & 63u) == 0) {
+            const uint64_t now = globaltimer_ns();
+            if (t0 == 0) t0 = now;
+            else if (now - t0 > limit || aborted(p.wctx)) break;   // the bounded wait below reports it
+        }
+    }
+    mbar_wait(bar, parity, p.wctx, where);
+}
+
+// A warp leaves the tile loop: the group it still holds is finished first (a producer may be waiting for it).
+__device__ __forceinline__ void gather_finish(const GemmParams& p, GatherCursor& g, int pro, int live, int rot, int lane) {
+    if (g.item < 0) return;
+    const uint64_t limit = p.wctx.timeout_ns ? p.wctx.timeout_ns : kDefaultTimeoutNs;
+    const uint64_t t0 = globaltimer_ns();
+    uint32_t spins = 0;
+    while (g.item >= 0 && g.item < live * GATHER_SUBS) {
+        gather_step(p, g, pro, live, rot, lane);
+        if ((++spins & 63u) == 0 && (aborted(p.wctx) || globaltimer_ns() - t0 > limit)) {
+            if (lane == 0) report_timeout(p.wctx, kStatusFlagTimeout, -1, g.item, p.src_epoch, -1, 8);
+            return;
+        }
     }
 }
 
@@ -575,21 +744,14 @@ __global__ void __launch_bounds__(GATHER ? GATHER_THREADS : THREADS, 1) gemm_sm1
         return;
     }
 
-    // ---------------- gatherer CTAs (grouped GEMM with a staged row gather) ----------------
-    if (MODE == TDIST_GEMM_PLAIN && CTAS == 1 && !GATHER && p.gather_dst != nullptr) {
-        const int live = min(p.seg_blocks, p.num_m_blocks ? *p.num_m_blocks : p.seg_blocks);
-        const int rot = p.block_rot ? min(max(*p.block_rot, 0), max(live - 1, 0)) : 0;
-        const int pro = gather_prologue_blocks(p, live, rot);
-        if (pro > 0) gather_prologue(p, pro, live, rot);
-        if (static_cast<int>(blockIdx.x) < p.num_comm) {
-            if (threadIdx.x == 0) {
-                for (int s = 0; s < PUSH_STAGES; ++s) mbar_init(smem_u32(&bars[s]), 1);
-                fence_mbar_init();
-            }
-            __syncthreads();
-            local_gatherer(p, smem, bars, pro, live, rot);
-            return;
-        }
+    // ---------------- staged row gather (grouped GEMM): every CTA copies its share of the first wave's rows ----------------
+    constexpr bool STAGED = MODE == TDIST_GEMM_PLAIN && CTAS == 1 && !GATHER;
+    int gather_live = 0, gather_rot = 0, gather_pro = 0;
+    if (STAGED && p.gather_dst != nullptr) {
+        gather_live = min(p.seg_blocks, p.num_m_blocks ? *p.num_m_blocks : p.seg_blocks);
+        gather_rot = p.block_rot ? min(max(*p.block_rot, 0), max(gather_live - 1, 0)) : 0;
+        gather_pro = gather_prologue_blocks(p, gather_live, gather_rot);
+        if (gather_pro > 0) gather_prologue(p, gather_pro, gather_live, gather_rot);
     }
 
     // `unit` = the CTA (CTAS == 1) or the CTA pair (CTAS == 2) that owns a tile.
@@ -737,7 +899,7 @@ __global__ void __launch_bounds__(GATHER ? GATHER_THREADS : THREADS, 1) gemm_sm1
             const int block_rot = p.block_rot ? min(max(*p.block_rot, 0), max(min(live_blocks, p.seg_m_tiles) - 1, 0)) : 0;
             Work tc;
             for (int round = 0; get_work<WIDE>(p, unit, num_units, round, first_seg, tc); ++round) {
-                if (tc.m_in_seg * CTAS >= live_blocks) continue;  // padding tile of a grouped GEMM: every role skips it
+                if (tc.halves == 0 || tc.m_in_seg * CTAS >= live_blocks) continue;  // padding tile of a grouped GEMM: every role skips it
                 int block = tc.m_in_seg * CTAS + cta_rank;  // 128-row block inside the segment
                 if (MODE == TDIST_GEMM_PLAIN && CTAS == 1 && p.block_rot != nullptr)
                     block = rotate_block(block, block_rot, min(live_blocks, p.seg_m_tiles));
@@ -745,7 +907,7 @@ __global__ void __launch_bounds__(GATHER ? GATHER_THREADS : THREADS, 1) gemm_sm1
                 const CUtensorMap* am = &p.tm_a;
                 int az = tc.seg;
                 if (MODE == TDIST_GEMM_PLAIN && CTAS == 1 && p.block_ready != nullptr) {
-                    // the gatherer CTAs have copied this block's rows (generic-proxy stores, read next by TMA)
+                    // this block's rows have been staged (generic-proxy stores, read next by TMA)
                     wait_flag_ge_gpu(p.block_ready + block, p.epoch, p.wctx, -1, block, 7);
                     fence_proxy_async();
                 }
@@ -806,7 +968,7 @@ __global__ void __launch_bounds__(GATHER ? GATHER_THREADS : THREADS, 1) gemm_sm1
             long long t_begin = mtr ? clock64() : 0, t_full = 0, t_tempty = 0, n_tiles_done = 0;
             Work tc;
             for (int round = 0; get_work<WIDE>(p, unit, num_units, round, first_seg, tc); ++round) {
-                if (tc.m_in_seg * CTAS >= live_blocks) continue;
+                if (tc.halves == 0 || tc.m_in_seg * CTAS >= live_blocks) continue;
                 ++n_tiles_done;
                 // the four MMAs of one 256-column half over one K block (stage `s`, K block `kb` of the tile)
                 auto issue_half = [&](int h, int kb, uint32_t s) {
@@ -891,9 +1053,10 @@ __global__ void __launch_bounds__(GATHER ? GATHER_THREADS : THREADS, 1) gemm_sm1
         const int live_blocks = p.num_m_blocks ? *p.num_m_blocks : 0x7fffffff;
         const int block_rot = p.block_rot ? min(max(*p.block_rot, 0), max(min(live_blocks, p.seg_m_tiles) - 1, 0)) : 0;
         const bool scatter = MODE == TDIST_GEMM_PLAIN && CTAS == 1 && p.c_scatter != nullptr;
+        GatherCursor gcur{-1, 0};
         Work tc;
         for (int round = 0; get_work<WIDE>(p, unit, num_units, round, first_seg, tc); ++round) {
-            if (tc.m_in_seg * CTAS >= live_blocks) continue;
+            if (tc.halves == 0 || tc.m_in_seg * CTAS >= live_blocks) continue;
             const CUtensorMap* cm = (MODE == TDIST_GEMM_RS) ? &p.tm_c[tc.seg] : &p.tm_c[0];
             const int cz = (MODE == TDIST_GEMM_RS) ? p.rank : tc.seg;
             int block = tc.m_in_seg * CTAS + cta_rank;
@@ -908,7 +1071,10 @@ __global__ void __launch_bounds__(GATHER ? GATHER_THREADS : THREADS, 1) gemm_sm1
             }
             for (int h = 0; h < tc.halves; ++h) {
                 const uint32_t buf = slot_of_half(tc, h, next_narrow);
-                mbar_wait(bar_tfull(buf), (buf ? uses1 : uses0) & 1u, p.wctx, 5);
+                if (STAGED && p.gather_dst != nullptr)
+                    gather_while_waiting(p, gcur, gather_pro, gather_live, gather_rot, lane, bar_tfull(buf), (buf ? uses1 : uses0) & 1u, 5);
+                else
+                    mbar_wait(bar_tfull(buf), (buf ? uses1 : uses0) & 1u, p.wctx, 5);
                 tc_fence_after();
                 if (buf) ++uses1;
                 else ++uses0;
@@ -1022,6 +1188,7 @@ __global__ void __launch_bounds__(GATHER ? GATHER_THREADS : THREADS, 1) gemm_sm1
         }
         if (issuer) bulk_wait<0>();
         __syncwarp();
+        if (STAGED && p.gather_dst != nullptr) gather_finish(p, gcur, gather_pro, gather_live, gather_rot, lane);
     }
 
     tc_fence_before();
@@ -1033,6 +1200,14 @@ __global__ void __launch_bounds__(GATHER ? GATHER_THREADS : THREADS, 1) gemm_sm1
         __syncthreads();
     }
     if (warp == 1) tmem_dealloc<CTAS>(tmem_base, TMEM_COLS);
+    if (STAGED && p.gather_dst != nullptr && threadIdx.x == 0) {
+        // every warp of this CTA is past its last claim: the last CTA to leave rewinds the cursor for the next launch
+        const uint32_t old = atom_add_acq_rel_gpu_u32(p.gather_counter + kGatherExits, 1);
+        if (old == gridDim.x - 1) {
+            p.gather_counter[kGatherCursor] = 0;
+            p.gather_counter[kGatherExits] = 0;
+        }
+    }
 
     if (MODE == TDIST_GEMM_RS) {
         // ===================== reduce the 128-row blocks this rank owns =====================
@@ -1189,12 +1364,6 @@ static GridPlan plan_grid(const TdistGemmArgs* a) {
         if (g.num_comm > sms - g.ctas_per_tile) g.num_comm = sms - g.ctas_per_tile;
         if (g.num_comm < g.ctas_per_tile) g.num_comm = g.ctas_per_tile;
     }
-    if (a->mode == TDIST_GEMM_PLAIN && a->gather_dst != nullptr) {
-        // gatherer CTAs: a CTA copies ~100 GB/s; the rows have to be in place a block ahead of the MMAs
-        g.num_comm = a->num_comm_sms > 0 ? a->num_comm_sms : 8;
-        if (g.num_comm > sms / 2) g.num_comm = sms / 2;
-        if (g.num_comm < 1) g.num_comm = 1;
-    }
     int units = (sms - g.num_comm) / g.ctas_per_tile;
     // a wide schedule may split its last round in two: allow up to twice the items
     const int most = g.wide ? 2 * g.num_tiles : g.num_tiles;
@@ -1206,6 +1375,55 @@ static GridPlan plan_grid(const TdistGemmArgs* a) {
 
 extern "C" int tdist_gemm_grid(const TdistGemmArgs* a) { return plan_grid(a).grid; }
 
+// Runs the static schedule on the host: every 256-column tile of the problem must be given to exactly one unit, a
+// wide item's halves to the same unit in the same round. Returns 0 and the longest unit's length in half items, or the
+// number of the first check that failed.
+extern "C" int tdist_gemm_schedule_check(int wide, int num_units, int world, int rank, int seg_m_tiles, int n_tiles,
+                                         int group_m, int split_first, int* makespan_halves, int* first_remote_half) {
+    if (num_units < 1 || world < 1 || seg_m_tiles < 1 || n_tiles < 1 || rank < 0 || rank >= world) return -1;
+    GemmParams* p = new GemmParams;
+    memset(p, 0, sizeof(*p));
+    p->world = world;
+    p->rank = rank;
+    p->seg_m_tiles = seg_m_tiles;
+    p->n_tiles = n_tiles;
+    p->n_pairs = (n_tiles + 1) / 2;
+    p->group_m = group_m > 0 ? group_m : DEFAULT_GROUP_M;
+    p->num_tiles = seg_m_tiles * (wide ? p->n_pairs : n_tiles) * world;
+    p->split_first = split_first;
+    std::string seen(static_cast<size_t>(world) * seg_m_tiles * n_tiles, 0);
+    int rc = 0, longest = 0, first_remote = 1 << 30;
+    for (int u = 0; u < num_units && rc == 0; ++u) {
+        Work w;
+        int len = 0;
+        for (int round = 0; rc == 0; ++round) {
+            const bool more = wide ? get_work<true>(*p, u, num_units, round, rank, w) : get_work<false>(*p, u, num_units, round, rank, w);
+            if (!more) break;
+            if (round > 4 * (p->num_tiles / num_units + 2)) rc = 1;   // the schedule must end
+            if (w.halves == 0) continue;
+            if (w.halves < 0 || w.halves > 2 || w.seg < 0 || w.seg >= world || w.m_in_seg < 0 || w.m_in_seg >= seg_m_tiles) rc = 2;
+            for (int h = 0; h < w.halves && rc == 0; ++h) {
+                if (w.n_tile + h >= n_tiles) rc = 3;
+                else {
+                    char& c = seen[(static_cast<size_t>(w.seg) * seg_m_tiles + w.m_in_seg) * n_tiles + w.n_tile + h];
+                    if (c) rc = 4;
+                    c = 1;
+                }
+            }
+            if (w.seg != rank && len < first_remote) first_remote = len;
+            len += w.halves;
+        }
+        if (len > longest) longest = len;
+    }
+    if (rc == 0)
+        for (char c : seen)
+            if (!c) rc = 5;
+    if (makespan_halves) *makespan_halves = longest;
+    if (first_remote_half) *first_remote_half = first_remote;
+    delete p;
+    return rc;
+}
+
 extern "C" int tdist_gemm_run(const TdistGemmArgs* a) {
     if (a == nullptr) return fail(TDIST_EINVAL, "null args");
     if (a->world < 1 || a->world > TDIST_MAX_RANKS || a->rank < 0 || a->rank >= a->world)
@@ -1216,8 +1434,9 @@ extern "C" int tdist_gemm_run(const TdistGemmArgs* a) {
     if (a->mode < TDIST_GEMM_PLAIN || a->mode > TDIST_GEMM_RS) return fail(TDIST_EINVAL, "bad mode");
     if (a->expert_ids != nullptr && (a->mode != TDIST_GEMM_PLAIN || a->world != 1))
         return fail(TDIST_EINVAL, "grouped GEMM (expert_ids) is a single-rank plain-mode feature");
-    if ((a->gather_dst != nullptr) != (a->block_ready != nullptr) || (a->gather_dst != nullptr && a->a_gather == nullptr))
-        return fail(TDIST_EINVAL, "the staged row gather needs a_gather, gather_dst and block_ready together");
+    if ((a->gather_dst != nullptr) != (a->block_ready != nullptr) || (a->gather_dst != nullptr) != (a->gather_counter != nullptr) ||
+        (a->gather_dst != nullptr && a->a_gather == nullptr))
+        return fail(TDIST_EINVAL, "the staged row gather needs a_gather, gather_dst, block_ready and gather_counter together");
     if ((a->c_scatter != nullptr || a->block_rot != nullptr) && (a->mode != TDIST_GEMM_PLAIN || a->world != 1 || a->cta_pair > 0))
         return fail(TDIST_EINVAL, "c_scatter / block_rot are plain-mode, one-CTA-per-tile features");
     if (a->a_gather != nullptr) {
@@ -1238,7 +1457,7 @@ extern "C" int tdist_gemm_run(const TdistGemmArgs* a) {
         // A (or the gather workspace): {K, m_per_rank, world}
         const void* base = a->mode == TDIST_GEMM_AG ? a->a_ws : a->a;
         if (a->mode == TDIST_GEMM_AG && a->world == 1) base = a->a;
-        if (a->gather_dst != nullptr) base = a->gather_dst;   // the gatherer CTAs fill it, TMA reads it
+        if (a->gather_dst != nullptr) base = a->gather_dst;   // the CTAs' own warps fill it, TMA reads it
         if (base == nullptr) return fail(TDIST_EINVAL, "A / workspace pointer is null");
         uint64_t dims[3] = {K, MPR, W};
         uint64_t strides[2] = {K * 2, MPR * K * 2};
@@ -1326,8 +1545,33 @@ extern "C" int tdist_gemm_run(const TdistGemmArgs* a) {
     p.wctx.kernel_id = kKernelGemm;
     p.wctx.rank = a->rank;
     p.num_comm = plan.num_comm;
+    {
+        static const int ahead = [] {
+            const char* e = getenv("TDIST_AG_PUSH_AHEAD");
+            const int v = e ? atoi(e) : PUSH_AHEAD;
+            return v < 1 ? 1 : (v > PUSH_AHEAD ? PUSH_AHEAD : v);
+        }();
+        p.push_ahead = ahead;
+    }
+    p.push_count = static_cast<uint32_t*>(a->push_count);
+    p.push_parts = 1;
+    if (a->mode == TDIST_GEMM_AG && a->world > 1 && a->push_count != nullptr && a->a_ws_mc == nullptr) {
+        // as many slices as pushers (a power of two, at most eight: 16 rows per slice)
+        while (p.push_parts * 2 <= plan.num_comm && p.push_parts < 8) p.push_parts *= 2;
+    }
     p.group_m = a->group_m > 0 ? a->group_m : DEFAULT_GROUP_M;
     p.num_tiles = plan.num_tiles;
+    p.split_first = 0;
+    if (a->mode == TDIST_GEMM_AG && a->world > 1 && plan.wide) {
+        // units that would start on a peer's segment, whose rows are still on the wire: cut that many own items in two
+        static const bool enabled = [] {
+            const char* e = getenv("TDIST_AG_SPLIT_FIRST");
+            return e == nullptr || atoi(e) != 0;
+        }();
+        const int units = (plan.grid - plan.num_comm) / ctas;
+        const int own = plan.num_tiles / a->world;
+        if (enabled && own < units && units - own <= own) p.split_first = units - own;
+    }
 
     if (a->mode == TDIST_GEMM_AG && a->world > 1) {
         if (a->flags == nullptr) return fail(TDIST_EINVAL, "AG needs flags");

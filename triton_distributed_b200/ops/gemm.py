@@ -43,6 +43,10 @@ CTA_PAIR = int(os.environ.get("TDIST_GEMM_CTA_PAIR", "-1"))
 # 8 x B200 the multicast pusher measured 1.18 ms against 0.98 ms for the unicast one on m8192 n49152 k12288),
 # 1 = from 4 ranks up, 2 = always
 AG_NVLS = int(os.environ.get("TDIST_AG_GEMM_NVLS", "0"))
+# 1: the pushers of the fused AG-GEMM send each 128-row block as parallel row slices, so the first blocks land sooner.
+# Off by default: with eight slices a pusher moved 24 GB/s instead of 36-38 (a flag hand-off per 400 KB), which costs
+# more than the earlier first arrival gains now that the first round of tiles is split instead.
+AG_PUSH_SLICES = int(os.environ.get("TDIST_AG_PUSH_SLICES", "0"))
 GROUP_M = int(os.environ.get("TDIST_GEMM_GROUP_M", "0"))  # row-tiles per raster group, 0 = kernel default
 TRACE = None  # optional int64[2048] device tensor: every launch writes its timeline there (layout: TdistGemmArgs.trace)
 
@@ -131,6 +135,7 @@ class AllGatherGEMMTensorParallelContext:
     group: object = None
     workspace: Optional[SymmTensor] = None
     flags: Optional[SymmTensor] = None
+    push_count: Optional[torch.Tensor] = None   # local slice-arrival counters of the pushers, one per (hop, block)
     epoch: int = 0
     num_comm_sms: int = 0   # 0 = sized per call from the bytes to push and the expected GEMM time
     num_sms: int = 0
@@ -160,6 +165,7 @@ def create_ag_gemm_intra_node_context(tensor_A: torch.Tensor, tensor_B: torch.Te
         heap = heap or symm_heap(group)
         ctx.workspace = heap.empty((2, num_ranks * max_mpr * K), tensor_A.dtype)
         ctx.flags = heap.zeros((2, num_ranks * _cdiv(max_mpr, BLOCK_M_TILE)), torch.int32)
+        ctx.push_count = torch.zeros(num_ranks * _cdiv(max_mpr, BLOCK_M_TILE), dtype=torch.int32, device=tensor_A.device)
     return ctx
 
 
@@ -198,6 +204,8 @@ def ag_gemm_intra_node(a: torch.Tensor, b: torch.Tensor, ctx: Optional[AllGather
         g.a_ws_peer = ctx.workspace.half_ptr_arrays()[half]
         g.flags = ctx.flags.local[half].data_ptr()
         g.flags_peer = ctx.flags.half_ptr_arrays()[half]
+        if ctx.push_count is not None and AG_PUSH_SLICES:
+            g.push_count = ctx.push_count.data_ptr()
         if ctx.workspace.mc is not None and (AG_NVLS == 2 or (AG_NVLS == 1 and ctx.world >= 4)):
             g.a_ws_mc = ctx.workspace.mc[half].data_ptr()   # the pushers multicast through the switch
     _launch(g)

@@ -136,21 +136,29 @@ def group_gemm(a_sorted: torch.Tensor, b: torch.Tensor, expert_ids: torch.Tensor
     return c
 
 
+def staging_flags(rows: int, device) -> torch.Tensor:
+    """Flag words of a staged row gather over up to ``rows`` sorted rows: one int32 per 128-row block (the call number at
+    which its rows were staged) followed by the kernel's own counters (4 + one per block). Zero before the first call."""
+    blocks = (rows + GROUP_BLOCK_M - 1) // GROUP_BLOCK_M
+    return torch.zeros(2 * blocks + 4, dtype=torch.int32, device=device)
+
+
 def group_gemm_gather(a: torch.Tensor, row_index: torch.Tensor, b: torch.Tensor, expert_ids: torch.Tensor,
                       num_blocks: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None,
                       block_src: Optional[torch.Tensor] = None, src_flags: Optional[torch.Tensor] = None, src_epoch: int = 0,
                       src_rank: int = 0, src_world: int = 1, staging: Optional[torch.Tensor] = None,
                       block_ready: Optional[torch.Tensor] = None, epoch: int = 1, block_rot: Optional[torch.Tensor] = None,
-                      c_scatter: Optional[torch.Tensor] = None, c_rows: int = 0, num_gather_ctas: int = 0) -> torch.Tensor:
+                      c_scatter: Optional[torch.Tensor] = None, c_rows: int = 0) -> torch.Tensor:
     """Grouped GEMM whose A rows are gathered inside the kernel: ``out[r] = a[row_index[r]] @ b[expert_ids[r // 128]].T``
     (rows with ``row_index >= a.shape[0]`` are padding). With ``block_src`` the rows of 128-row
     block ``i`` come from rank ``block_src[i]``'s segment of an all-gather that may still be in flight: the kernel
     waits for that rank's arrival flag (``src_flags[rank] >= src_epoch``) before loading them, so blocks of ranks
     that have arrived compute while later segments are still on the wire.
 
-    With ``staging`` (``[rows, K]`` workspace) and ``block_ready`` (int32 per 128-row block plus one trailing word, zero
-    before the first call; ``epoch`` strictly increasing per call) the gather is done by dedicated CTAs of the same launch into
-    ``staging`` and the GEMM is fed by TMA; without them the producer warps copy the rows with cp.async.
+    With ``staging`` (``[rows, K]`` workspace) and ``block_ready`` (from :func:`staging_flags`; ``epoch`` strictly increasing
+    per call) the launch copies the rows into ``staging`` itself (all threads for the first wave of tiles, then the
+    epilogue warps while they wait for accumulators) and the GEMM is fed by TMA; without them the producer warps copy
+    the rows with cp.async.
     ``block_rot`` (device int32 scalar): block the schedule starts at. ``c_scatter`` (int32 per sorted row): the
     epilogue stores row ``r`` of the product at row ``c_scatter[r]`` of ``out`` (``[c_rows, N]``), dropping rows whose
     index is not below ``c_rows``."""
@@ -186,12 +194,12 @@ def group_gemm_gather(a: torch.Tensor, row_index: torch.Tensor, b: torch.Tensor,
     if staging is not None:
         if block_ready is None or staging.shape[0] < rows or staging.shape[1] != K or staging.dtype != a.dtype:
             raise ValueError("staging must be [rows, K] of a's dtype, with block_ready")
-        # block_ready carries one extra word at its end: the arrival counter of the all-CTA prologue
-        if block_ready.numel() < rows // GROUP_BLOCK_M + 1:
-            raise ValueError("block_ready needs one int32 per 128-row block plus one")
+        blocks = rows // GROUP_BLOCK_M
+        if block_ready.numel() < 2 * blocks + 4 or block_ready.dtype != torch.int32:
+            raise ValueError("block_ready must come from staging_flags(rows)")
+        # flags first; the kernel's counters (4 + one per block) after the flags of the blocks the buffer was sized for
         g.gather_dst, g.block_ready = staging.data_ptr(), block_ready.data_ptr()
-        g.gather_counter = block_ready.data_ptr() + 4 * (block_ready.numel() - 1)
-        g.num_comm_sms = num_gather_ctas
+        g.gather_counter = block_ready.data_ptr() + 4 * ((block_ready.numel() - 4) // 2)
     if block_rot is not None:
         g.block_rot = block_rot.data_ptr()
     if c_scatter is not None:
@@ -266,7 +274,7 @@ def create_ag_group_gemm_intra_node_context(tp_pg, A: torch.Tensor, B: torch.Ten
     ctx.pos_of[ctx.sorted_ids[valid].long()] = torch.arange(ctx.sorted_ids.numel(), dtype=torch.int32, device=ctx.sorted_ids.device)[valid]
     if A.device.type == "cuda":
         ctx.staging = torch.empty((ctx.sorted_ids.numel(), K), dtype=A.dtype, device=A.device)
-        ctx.block_ready = torch.zeros(ctx.sorted_ids.numel() // GROUP_BLOCK_M + 1, dtype=torch.int32, device=A.device)
+        ctx.block_ready = staging_flags(ctx.sorted_ids.numel(), A.device)
         before = torch.cumsum(ctx.rank_block_num, 0) - ctx.rank_block_num
         ctx.block_rot = before[rank:rank + 1].to(torch.int32).contiguous()
     if A.device.type == "cuda" and world > 1:
@@ -340,8 +348,9 @@ def ag_group_gemm_intra_node(a: torch.Tensor, b: torch.Tensor, ctx: MoEAllGather
 
 
 def _fused_group_gemm(ctx: MoEAllGatherGroupGEMMTensorParallelContext, full: torch.Tensor, b_nk: torch.Tensor, numel: int, **src):
-    """One launch: gatherer CTAs stage the rows block by block, TMA-fed MMAs start at this rank's own blocks, the
-    epilogue stores every row at its (token, k) position."""
+    """One launch: the kernel stages the rows block by block itself (all threads for the first wave, then the epilogue
+    warps between accumulators), TMA-fed MMAs start at this rank's own blocks, the epilogue stores every row at its
+    (token, k) position."""
     ctx.gemm_calls += 1
     return group_gemm_gather(full, ctx.row_index, b_nk, ctx.expert_ids, ctx.num_blocks, staging=ctx.staging,
                              block_ready=ctx.block_ready, epoch=ctx.gemm_calls, block_rot=ctx.block_rot,
@@ -418,10 +427,10 @@ def moe_reduce_rs(rank: int, world_size: int, local_world_size: int, a: torch.Te
         if ctx.b_nk is None:
             ctx.b_nk = b.transpose(1, 2).contiguous()
         if AG_GROUP_GEMM_MODE == "fused":
-            # the sort of the rows by expert happens inside the grouped-GEMM launch (gatherer CTAs + TMA-fed MMAs)
+            # the sort of the rows by expert happens inside the grouped-GEMM launch (in-launch row staging + TMA-fed MMAs)
             if ctx.staging is None or ctx.staging.shape[1] != a.shape[1] or ctx.staging.dtype != a.dtype:
                 ctx.staging = torch.empty((ctx.sorted_ids.numel(), a.shape[1]), dtype=a.dtype, device=a.device)
-                ctx.block_ready = torch.zeros(ctx.sorted_ids.numel() // GROUP_BLOCK_M + 1, dtype=torch.int32, device=a.device)
+                ctx.block_ready = staging_flags(ctx.sorted_ids.numel(), a.device)
                 ctx.gemm_calls = 0
             ctx.gemm_calls += 1
             y = group_gemm_gather(a, ctx.sorted_ids, ctx.b_nk, ctx.expert_ids, ctx.num_blocks, staging=ctx.staging,
