@@ -39,7 +39,7 @@ def test_decode_matches_reference(cuda_device, Hq, Hkv, D, kv_lens, dtype):
     torch.testing.assert_close(out.float(), ref, atol=1e-2, rtol=1e-2)
 
 
-@pytest.mark.parametrize("splits", [1, 3, 32])
+@pytest.mark.parametrize("splits", [1, 3, 8, 16, 32])   # up to 8: one cluster per (batch, kv head), merged through shared memory
 @pytest.mark.parametrize("soft_cap", [0.0, 30.0])
 def test_intra_rank_partials_and_merge(cuda_device, splits, soft_cap):
     torch.manual_seed(splits)

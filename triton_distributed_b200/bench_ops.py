@@ -202,16 +202,17 @@ def _bench_decode(args, world, rank, group, dev, dtype, pk, row):
     q = torch.randn(B, Hq, D, device=dev, dtype=dtype)
     scale = 1.0 / math.sqrt(D)
     out = torch.empty_like(q)
-    row.update({"batch": B, "hq": Hq, "hkv": Hkv, "head_dim": D, "kv_total": args.kv, "kv_per_rank": kv_local})
+    row.update({"batch": B, "hq": Hq, "hkv": Hkv, "head_dim": D, "kv_total": args.kv, "kv_per_rank": kv_local,
+                "kv_split": args.kv_split if args.kv_split > 0 else FD.default_splits(B, Hkv, nblk * page, dev, D)})
     if args.op == "decode":
         lens = torch.full((B,), kv_local, dtype=torch.int32, device=dev)
-        us = timed_us(lambda: FD.gqa_fwd_batch_decode(q, k, v, None, None, lens, table, scale, output_combine=out),
-                      args.iters, args.warmup, 1)
+        us = timed_us(lambda: FD.gqa_fwd_batch_decode(q, k, v, None, None, lens, table, scale, output_combine=out,
+                                                      kv_split=args.kv_split), args.iters, args.warmup, 1)
         base = None
     else:
         glens = torch.full((world, B), kv_local, dtype=torch.int32, device=dev)
         ctx = FD.create_sp_decode_context(rank, world, B, Hq, D, group=group, device=dev)
-        us = timed_us(lambda: FD.sp_gqa_fwd_batch_decode(ctx, q, k, v, glens, table, scale, out=out),
+        us = timed_us(lambda: FD.sp_gqa_fwd_batch_decode(ctx, q, k, v, glens, table, scale, out=out, kv_split=args.kv_split),
                       args.iters, args.warmup, world, group)
         base = None
         if not args.no_baseline:
@@ -550,6 +551,7 @@ def main(argv=None) -> int:
     ap.add_argument("--head-dim", type=int, default=128)
     ap.add_argument("--page-size", type=int, default=16)
     ap.add_argument("--kv", type=int, default=131072, help="total keys per sequence")
+    ap.add_argument("--kv-split", type=int, default=-1, help="decode: CTAs per (batch, kv head); -1 = the launcher's heuristic")
     ap.add_argument("--tokens", type=int, default=128)
     ap.add_argument("--hidden", type=int, default=7168)
     ap.add_argument("--experts", type=int, default=256)

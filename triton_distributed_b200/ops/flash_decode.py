@@ -78,10 +78,12 @@ def ref_lse_merge(parts: torch.Tensor) -> torch.Tensor:
 
 def default_splits(B: int, Hkv: int, max_kv: int, device, head_dim: int = 128) -> int:
     """Enough (batch, kv head, split) CTAs for one wave of the machine (two CTAs fit an SM up to
-    head_dim 128), but at least 64 tokens each."""
+    head_dim 128), but at least 256 tokens each: below that the merge of the splits (a round trip through global
+    memory per eight of them) costs more than the shorter KV loop saves (batch 1, 8 kv heads, 4096 keys: 12.4 us with
+    16 splits, 16.5 us with 37, 21.0 us with 64)."""
     per_sm = 2 if head_dim <= 128 else 1
     want = max(1, per_sm * _sm_count(device) // max(1, B * Hkv))
-    cap = max(1, (max_kv + 63) // 64)
+    cap = max(1, (max_kv + 255) // 256)
     return max(1, min(want, cap, 256))
 
 

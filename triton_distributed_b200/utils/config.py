@@ -21,6 +21,10 @@ class Config:
     heap_backend: str = "auto"           # TDIST_HEAP_BACKEND: auto | vmm (cuMem + fd export) | ipc (cudaIpc) | host
     nvls: bool = False                   # TDIST_NVLS: bind heap segments to an NVSwitch multicast object (multimem ops)
     ag_gemm_nvls: int = 0                # TDIST_AG_GEMM_NVLS: AG-GEMM pushers use multimem.st (0 never, 1 from 4 ranks, 2 always)
+    ag_push_slices: int = 0              # TDIST_AG_PUSH_SLICES: 1 = AG-GEMM pushers send a 128-row block as parallel row slices
+    ag_push_ahead: int = 5               # TDIST_AG_PUSH_AHEAD: chunks a pusher's loads run ahead of its stores (1..5)
+    ag_split_first: int = 1              # TDIST_AG_SPLIT_FIRST: 0 = keep the first round of the wide AG schedule whole
+    decode_cluster_merge: int = 1        # TDIST_DECODE_CLUSTER_MERGE: 0 = the KV splits of flash decode always meet in global memory
     gemm_cta_pair: int = -1              # TDIST_GEMM_CTA_PAIR: -1 automatic, 0 one CTA per 128x256 tile, 1 CTA pair per 256x256, 2 CTA pair per 256x512
     gemm_group_m: int = 0                # TDIST_GEMM_GROUP_M: row-tiles per raster group, 0 = kernel default (8)
     bounds_check: bool = False           # TDIST_BOUNDS_CHECK: load the library built with checked symmetric-address translation
@@ -29,7 +33,8 @@ class Config:
 
     _ENV = {
         "wait_timeout_ms": "TDIST_WAIT_TIMEOUT_MS", "symm_heap_bytes": "TDIST_SYMM_HEAP_BYTES", "heap_backend": "TDIST_HEAP_BACKEND",
-        "nvls": "TDIST_NVLS", "ag_gemm_nvls": "TDIST_AG_GEMM_NVLS", "gemm_cta_pair": "TDIST_GEMM_CTA_PAIR",
+        "nvls": "TDIST_NVLS", "ag_gemm_nvls": "TDIST_AG_GEMM_NVLS", "ag_push_slices": "TDIST_AG_PUSH_SLICES",
+        "ag_push_ahead": "TDIST_AG_PUSH_AHEAD", "ag_split_first": "TDIST_AG_SPLIT_FIRST", "decode_cluster_merge": "TDIST_DECODE_CLUSTER_MERGE", "gemm_cta_pair": "TDIST_GEMM_CTA_PAIR",
         "gemm_group_m": "TDIST_GEMM_GROUP_M", "bounds_check": "TDIST_BOUNDS_CHECK", "nvtx": "TDIST_NVTX", "nvcc": "TDIST_NVCC",
     }
 
