@@ -238,3 +238,31 @@ def test_gemm_split_first_round_balances_the_headline_problem():
     assert span.value == 11 and first.value == 1
     assert lib.tdist_gemm_schedule_check(1, 70, 8, 3, 4, 24, 0, 0, C.byref(span), C.byref(first)) == 0
     assert span.value == 11 and first.value == 0
+
+
+def test_ag_gemm_launch_plan_follows_the_measured_optima():
+    """The pusher-count / tiling model of the fused AG-GEMM, on the shapes it was calibrated with: the long-K headline
+    problem takes the wide tiling with 8 / 4 / 2 pusher CTAs at tp8 / tp4 / tp2 (8 x B200: 8 pushers 0.97 ms, 6 pushers
+    1.19 ms, 10 pushers 1.02 ms); the all-gather-bound short-K problem takes 256 x 256 tiles and many pushers (4 x B200:
+    16 pushers 158 us, 8 pushers 226 us)."""
+    import ctypes as C
+
+    from triton_distributed_b200 import _lib
+    lib = _lib.lib()
+
+    def plan(world, m, n, k):
+        g = _lib.GemmArgs()
+        g.mode, g.world, g.rank, g.m_per_rank, g.n, g.k, g.cta_pair = _lib.GEMM_AG, world, 0, m // world, n // world, k, -1
+        out = (C.c_int * 4)()
+        assert lib.tdist_gemm_plan(C.byref(g), out) == 0
+        return list(out)
+
+    if plan(8, 8192, 49152, 12288)[3] != 148:
+        pytest.skip("calibrated for 148 SMs")
+    assert plan(8, 8192, 49152, 12288)[:3] == [2, 1, 8]
+    assert plan(4, 8192, 49152, 12288)[:3] == [2, 1, 4]
+    assert plan(2, 8192, 49152, 12288)[:3] == [2, 1, 2]
+    ctas, wide, pushers, _ = plan(4, 8192, 11008, 4096)
+    assert (ctas, wide) == (2, 0) and 12 <= pushers <= 18
+    ctas, wide, pushers, _ = plan(8, 8192, 11008, 4096)
+    assert (ctas, wide) == (2, 0) and 14 <= pushers <= 18

@@ -222,6 +222,8 @@ def _declare(lib):
     lib.tdist_status_destroy.argtypes = [C.c_void_p]
     lib.tdist_gemm_run.argtypes = [C.POINTER(GemmArgs)]
     lib.tdist_gemm_grid.argtypes = [C.POINTER(GemmArgs)]
+    lib.tdist_gemm_plan.argtypes = [C.POINTER(GemmArgs), C.POINTER(C.c_int)]
+    lib.tdist_gemm_plan.restype = C.c_int
     lib.tdist_gemm_schedule_check.argtypes = [C.c_int] * 8 + [C.POINTER(C.c_int), C.POINTER(C.c_int)]
     lib.tdist_gemm_schedule_check.restype = C.c_int
     lib.tdist_gemm_fp8_run.argtypes = [C.POINTER(GemmFp8Args)]

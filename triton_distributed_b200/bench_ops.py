@@ -86,7 +86,7 @@ def _bench_gemm_family(args, world, rank, group, dev, dtype, pk, row):
         ctx = G.create_ag_gemm_intra_node_context(a, b, rank, world, max_M=M, group=group)
         if getattr(args, "sweep_comm", ""):
             # pusher-CTA count x tiling in one process (one heap and NCCL bring-up): extra rows before the default one
-            for pair in (1, 2):
+            for pair in (0, 1, 2):
                 for nc in (int(x) for x in args.sweep_comm.split(",")):
                     G.CTA_PAIR, ctx.num_comm_sms = pair, nc
                     t = timed_us(lambda: G.ag_gemm_intra_node(a, b, ctx, out=c), args.iters, args.warmup, world, group)

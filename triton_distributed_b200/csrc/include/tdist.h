@@ -121,6 +121,9 @@ typedef struct TdistGemmArgs {
 int tdist_gemm_run(const TdistGemmArgs* args);
 /* Number of CTAs a call with these arguments launches (for occupancy planning and tests). */
 int tdist_gemm_grid(const TdistGemmArgs* args);
+/* The launch plan of a call with these arguments: out4 = {CTAs per tile (1 or 2), wide tiling (0 / 1), pusher CTAs,
+ * grid size}. Launches nothing. */
+int tdist_gemm_plan(const TdistGemmArgs* args, int* out4);
 /* Host-side replay of the kernel's static tile schedule (no GPU needed): `num_units` CTAs or CTA pairs over a problem
  * of `world` segments of seg_m_tiles x n_tiles 256-column tiles, wide (items of two neighbouring tiles) or narrow,
  * with `split_first` own items cut in two in round 0. Returns 0 when every tile is given out exactly once;

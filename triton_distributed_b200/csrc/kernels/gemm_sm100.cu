@@ -1316,6 +1316,57 @@ static int schedule_cost(int items, int units, int wide) {
     return 2 * full + (rem == 0 ? 0 : (2 * rem <= units ? 1 : 2));
 }
 
+// AG mode, several ranks: how many pusher CTAs and which pair tiling. A model of the run, not a table:
+//   the GEMM side needs  t_gemm = (schedule length in 256-column tiles) x (time of such a tile on a CTA pair);
+//   the pushers need     t_push = bytes / min(pushers x 34 GB/s, 600 GB/s)   (one unicast pusher CTA moves 36-40 GB/s
+//                        alone and a little less beside a running GEMM; NVLink saturates near 600 GB/s of payload);
+//   after the last rows arrive the tiles of one segment are still to do: t_tail = their rounds x tile time;
+//   the run takes max(t_gemm, t_push + t_tail).
+// Long-K problems are bound by t_gemm and want few pushers and the wide tiling (3 % faster per FLOP at K = 12288);
+// short-K problems are bound by the all-gather and want many pushers and small tiles, which shorten the tail.
+// Measured on 8 x B200, m8192 n49152 k12288: wide 4/6/8/10 pushers 1.72/1.19/0.97/1.02 ms (model 8), 256 x 256 tiles
+// 1.29/1.09/1.00/1.24 ms; on 4 x B200, m8192 n11008 k4096: 16 pushers 158 (256 x 256) / 171 us (wide), 8 pushers
+// 226 / 223 us, 24 pushers 190 / 206 us.
+static void plan_ag(const TdistGemmArgs* a, int sms, int n_tiles, GridPlan& g) {
+    const bool nvls = a->a_ws_mc != nullptr;
+    const double push_bytes = static_cast<double>(nvls ? 1 : a->world - 1) * a->m_per_rank * a->k * 2.0;
+    const double per_pusher = nvls ? 33e9 : 34e9, link_cap = 600e9;
+    const int step = g.ctas_per_tile;
+    const int seg_m_tiles = (a->m_per_rank + BM * g.ctas_per_tile - 1) / (BM * g.ctas_per_tile);
+    const int nc_lo = a->num_comm_sms > 0 ? a->num_comm_sms : step;
+    const int nc_hi = a->num_comm_sms > 0 ? a->num_comm_sms : 18;
+    const bool may_wide = g.ctas_per_tile == 2 && a->cta_pair != 1 && a->k >= 4096 && a->n > BN;
+    const bool may_narrow = !(g.ctas_per_tile == 2 && a->cta_pair == 2 && may_wide);
+    double best_t = 1e30;
+    int best_nc = nc_lo, best_wide = may_narrow ? 0 : 1;
+    for (int wide = 0; wide <= 1; ++wide) {
+        if ((wide && !may_wide) || (!wide && !may_narrow)) continue;
+        const int seg_items = seg_m_tiles * (wide ? (n_tiles + 1) / 2 : n_tiles);
+        // a 256-column tile (or half of a wide item) on one CTA pair / CTA: the wide tiling runs ~4 % more FLOP/s but
+        // pays ~1.5 us more per half for an epilogue that overlaps the next main loop only half by half
+        const double rows = BM * g.ctas_per_tile;
+        const double tile_s = 2.0 * rows * BN * a->k / ((wide ? 19.0e12 : 18.2e12) * g.ctas_per_tile / 2.0) + (wide ? 1.5e-6 : 0.5e-6);
+        for (int nc = nc_lo; nc <= nc_hi; nc += step) {
+            const int units = (sms - nc) / g.ctas_per_tile;
+            if (units < 1) break;
+            const double t_gemm = schedule_cost(seg_items * a->world, units, wide) * tile_s;
+            const double rate = nc * per_pusher < link_cap ? nc * per_pusher : link_cap;
+            const double t_push = push_bytes / rate;
+            const double t_tail = schedule_cost(seg_items, units, wide) * tile_s;
+            double t = t_gemm > t_push + t_tail ? t_gemm : t_push + t_tail;
+            if (!wide) t *= 0.98;   // on a tie the smaller tiles: their tail is finer
+            if (t < best_t * 0.999) {
+                best_t = t;
+                best_nc = nc;
+                best_wide = wide;
+            }
+        }
+    }
+    g.num_comm = best_nc;
+    g.wide = best_wide;
+    g.num_tiles = seg_m_tiles * (g.wide ? (n_tiles + 1) / 2 : n_tiles) * a->world;
+}
+
 static GridPlan plan_grid(const TdistGemmArgs* a) {
     GridPlan g;
     g.ctas_per_tile = use_pair(a) ? 2 : 1;
@@ -1323,43 +1374,19 @@ static GridPlan plan_grid(const TdistGemmArgs* a) {
     const int seg_m_tiles = (a->m_per_rank + BM * g.ctas_per_tile - 1) / (BM * g.ctas_per_tile);
     const int n_tiles = (a->n + BN - 1) / BN;
     g.num_tiles = seg_m_tiles * (g.wide ? (n_tiles + 1) / 2 : n_tiles) * a->world;
-    const int capacity = resident_ctas(g.ctas_per_tile, g.wide, a->mode);
+    int capacity = resident_ctas(g.ctas_per_tile, g.wide, a->mode);
+    if (a->mode == TDIST_GEMM_AG && a->world > 1 && g.ctas_per_tile == 2) {
+        // either pair tiling may be chosen below: the grid has to fit both
+        const int other = resident_ctas(2, g.wide ? 0 : 1, a->mode);
+        if (other < capacity) capacity = other;
+    }
     int sms = a->num_sms > 0 ? a->num_sms : capacity;
     if (sms > capacity) sms = capacity;
     if (g.ctas_per_tile == 2) sms &= ~1;
     if (sms < g.ctas_per_tile) sms = g.ctas_per_tile;
     g.num_comm = 0;
     if (a->mode == TDIST_GEMM_AG && a->world > 1) {
-        g.num_comm = a->num_comm_sms;
-        if (g.num_comm <= 0) {
-            // Peers consume this rank's rows one segment-time after another (the rank that needs them first
-            // gets them first), so the pushers must sustain shard_bytes per segment time, i.e. all pushes within
-            // (world-1)/world of the run. One unicast pusher CTA moves 36-40 GB/s over NVLink in isolation and less
-            // beside a running GEMM: sized at 30 GB/s (m8192 n49152 k12288 at tp8: 8 pushers 0.97 ms, 6 pushers
-            // 1.19 ms, 10 pushers 1.02 ms). A multicast pusher stores the shard once instead of world-1 times but
-            // was measured at ~33 GB/s per CTA, and every peer needs the whole shard when it reaches this rank's
-            // segment: a quarter of the run.
-            const bool nvls = a->a_ws_mc != nullptr;
-            const double push_bytes = static_cast<double>(nvls ? 1 : a->world - 1) * a->m_per_rank * a->k * 2.0;
-            const double gemm_s = 2.0 * a->world * a->m_per_rank * static_cast<double>(a->n) * a->k / 1.4e15;
-            const double window = nvls ? gemm_s * 0.25 : gemm_s * (a->world - 1) / a->world;
-            int need = static_cast<int>(push_bytes / (window > 1e-6 ? window : 1e-6) / (nvls ? 33e9 : 30e9)) + 1;
-            need = (need + 1) & ~1;
-            if (need < 2) need = 2;
-            if (need > 18) need = 18;
-            // then the count in [need, need + 8] that leaves the GEMM side the shortest schedule (the smallest such)
-            int best = need, best_cost = 1 << 30;
-            for (int c = need; c <= need + 8; c += 2) {
-                const int units = (sms - c) / g.ctas_per_tile;
-                if (units < 1) break;
-                const int cost = schedule_cost(g.num_tiles, units, g.wide);
-                if (cost < best_cost) {
-                    best_cost = cost;
-                    best = c;
-                }
-            }
-            g.num_comm = best;
-        }
+        plan_ag(a, sms, n_tiles, g);
         if (g.ctas_per_tile == 2) g.num_comm = (g.num_comm + 1) & ~1;
         if (g.num_comm > sms - g.ctas_per_tile) g.num_comm = sms - g.ctas_per_tile;
         if (g.num_comm < g.ctas_per_tile) g.num_comm = g.ctas_per_tile;
@@ -1374,6 +1401,16 @@ static GridPlan plan_grid(const TdistGemmArgs* a) {
 }
 
 extern "C" int tdist_gemm_grid(const TdistGemmArgs* a) { return plan_grid(a).grid; }
+
+extern "C" int tdist_gemm_plan(const TdistGemmArgs* a, int* out4) {
+    if (a == nullptr || out4 == nullptr) return fail(TDIST_EINVAL, "null args");
+    const GridPlan g = plan_grid(a);
+    out4[0] = g.ctas_per_tile;
+    out4[1] = g.wide;
+    out4[2] = g.num_comm;
+    out4[3] = g.grid;
+    return 0;
+}
 
 // Runs the static schedule on the host: every 256-column tile of the problem must be given to exactly one unit, a
 // wide item's halves to the same unit in the same round. Returns 0 and the longest unit's length in half items, or the
