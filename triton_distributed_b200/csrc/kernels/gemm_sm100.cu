@@ -93,6 +93,7 @@ struct GemmParams {
     const char* stage_local;      // RS reduce source [world][m_per_rank][N]
     char* a_ws_mc;                // AG: multicast alias of the gather workspace (NVLS pusher), or nullptr
     void* rs_out;
+    int rs_fused;                 // RS: the epilogue of this rank's own tiles adds the peers' partials and writes rs_out itself
     uint32_t* flags;
     uint32_t* flags_peer[kMaxRanks];
     int m_per_rank, n, k;
@@ -1079,6 +1080,22 @@ __global__ void __launch_bounds__(GATHER ? GATHER_THREADS : THREADS, 1) gemm_sm1
                 if (buf) ++uses1;
                 else ++uses0;
                 const int col = (tc.n_tile + h) * BN;
+                // RS, this rank's own rows: the other ranks' partials of this tile are added here, so wait for them first
+                // (they were computed one segment-time ago or earlier; only the MMAs of the next tile run meanwhile)
+                const bool reduce_here = MODE == TDIST_GEMM_RS && p.rs_fused && tc.seg == p.rank;
+                if (reduce_here && issuer && (pend0 != nullptr || pend1 != nullptr)) {
+                    // the last remote tiles' flags must not wait for this rank's own tiles (which store nothing over
+                    // NVLink): their owners are about to add them
+                    bulk_wait<0>();
+                    fence_proxy_async();
+                    fence_acq_rel_sys();
+                    if (pend0 != nullptr) st_release_sys_u32(pend0, p.epoch);
+                    if (pend1 != nullptr) st_release_sys_u32(pend1, p.epoch);
+                    pend0 = pend1 = nullptr;
+                }
+                if (reduce_here && lane < p.world && lane != p.rank && block < p.seg_blocks)
+                    wait_flag_ge_sys(p.flags + (block * p.n_tiles + tc.n_tile + h) * p.world + lane, p.epoch, p.wctx, lane, block, 6);
+                if (reduce_here) __syncwarp();
 #pragma unroll 1
                 for (int c = 0; c < BN / EPI_COLS; ++c) {
                     uint32_t r0[32], r1[32];
@@ -1094,6 +1111,64 @@ __global__ void __launch_bounds__(GATHER ? GATHER_THREADS : THREADS, 1) gemm_sm1
                             if (CTAS == 1) mbar_arrive(bar_tempty(buf));
                             else mbar_arrive_cluster(bar_tempty(buf), 0);
                         }
+                    }
+                    if (reduce_here) {
+                        // every thread owns one row of the tile: add the 64 columns of every other rank's partial (fp32)
+                        // and store the finished 128 bytes of the output row
+                        const int grow = row + row_in_tile;
+                        if (grow < p.m_per_rank) {
+                            const size_t slot_elems = static_cast<size_t>(p.m_per_rank) * p.n;
+                            const size_t off = static_cast<size_t>(grow) * p.n + col + c * EPI_COLS;
+                            for (int src = 0; src < p.world; ++src) {
+                                if (src == p.rank) continue;
+                                const char* sp = p.stage_local + (src * slot_elems + off) * 2;
+                                uint4 q[8];
+#pragma unroll
+                                for (int j = 0; j < 8; ++j)
+                                    if (col + c * EPI_COLS + j * 8 < p.n) q[j] = *reinterpret_cast<const uint4*>(sp + j * 16);
+#pragma unroll
+                                for (int j = 0; j < 8; ++j) {
+                                    if (col + c * EPI_COLS + j * 8 >= p.n) continue;
+                                    uint32_t* r = j < 4 ? r0 + 8 * j : r1 + 8 * (j - 4);
+                                    const uint32_t w[4] = {q[j].x, q[j].y, q[j].z, q[j].w};
+#pragma unroll
+                                    for (int i = 0; i < 4; ++i) {
+                                        float lo, hi;
+                                        if (p.is_f16) {
+                                            const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&w[i]));
+                                            lo = f.x;
+                                            hi = f.y;
+                                        } else {
+                                            lo = __uint_as_float(w[i] << 16);
+                                            hi = __uint_as_float(w[i] & 0xffff0000u);
+                                        }
+                                        r[2 * i] = __float_as_uint(__uint_as_float(r[2 * i]) + lo);
+                                        r[2 * i + 1] = __float_as_uint(__uint_as_float(r[2 * i + 1]) + hi);
+                                    }
+                                }
+                            }
+                            char* orow = static_cast<char*>(p.rs_out) + off * 2;
+#pragma unroll
+                            for (int j = 0; j < 8; ++j) {
+                                const uint32_t* r = j < 4 ? r0 + 8 * j : r1 + 8 * (j - 4);
+                                if (col + c * EPI_COLS + j * 8 < p.n) {
+                                    uint4 v;
+                                    if (p.is_f16) {
+                                        v.x = pack_f16x2(__uint_as_float(r[0]), __uint_as_float(r[1]));
+                                        v.y = pack_f16x2(__uint_as_float(r[2]), __uint_as_float(r[3]));
+                                        v.z = pack_f16x2(__uint_as_float(r[4]), __uint_as_float(r[5]));
+                                        v.w = pack_f16x2(__uint_as_float(r[6]), __uint_as_float(r[7]));
+                                    } else {
+                                        v.x = pack_bf16x2(__uint_as_float(r[0]), __uint_as_float(r[1]));
+                                        v.y = pack_bf16x2(__uint_as_float(r[2]), __uint_as_float(r[3]));
+                                        v.z = pack_bf16x2(__uint_as_float(r[4]), __uint_as_float(r[5]));
+                                        v.w = pack_bf16x2(__uint_as_float(r[6]), __uint_as_float(r[7]));
+                                    }
+                                    *reinterpret_cast<uint4*>(orow + j * 16) = v;
+                                }
+                            }
+                        }
+                        continue;
                     }
                     if (scatter) {
                         // every thread owns one row of the tile: 64 columns = 128 contiguous bytes of its output row
@@ -1164,7 +1239,7 @@ __global__ void __launch_bounds__(GATHER ? GATHER_THREADS : THREADS, 1) gemm_sm1
                         bulk_wait_read<1>();
                     }
                 }
-                if (MODE == TDIST_GEMM_RS && issuer) {
+                if (MODE == TDIST_GEMM_RS && issuer && !reduce_here) {
                     if (pend0 != nullptr) {
                         // the tile two back is complete at its owner: order its (async-proxy) writes before the
                         // system-scope release store of its flag
@@ -1209,7 +1284,7 @@ __global__ void __launch_bounds__(GATHER ? GATHER_THREADS : THREADS, 1) gemm_sm1
         }
     }
 
-    if (MODE == TDIST_GEMM_RS) {
+    if (MODE == TDIST_GEMM_RS && !p.rs_fused) {
         // ===================== reduce the 128-row blocks this rank owns =====================
         const int own_units = p.seg_blocks * p.n_tiles;
         for (int u = cta; u < own_units; u += num_cta) {
@@ -1560,6 +1635,13 @@ extern "C" int tdist_gemm_run(const TdistGemmArgs* a) {
     p.stage_local = static_cast<const char*>(a->c_stage_peer[a->rank]);
     p.a_ws_mc = (a->mode == TDIST_GEMM_AG && a->world > 1) ? static_cast<char*>(a->a_ws_mc) : nullptr;
     p.rs_out = a->rs_out;
+    {
+        static const bool fused = [] {
+            const char* e = getenv("TDIST_RS_FUSED_REDUCE");
+            return e == nullptr || atoi(e) != 0;
+        }();
+        p.rs_fused = (a->mode == TDIST_GEMM_RS && fused) ? 1 : 0;
+    }
     p.flags = a->flags;
     p.m_per_rank = a->m_per_rank;
     p.n = a->n;
