@@ -10,8 +10,9 @@
 //          835-882), where the gather is a copy-engine stream and the wait is per rank.
 //   RS     GEMM-ReduceScatter (row-parallel linear). The epilogue TMA-stores each partial tile
 //          straight into the owning rank's staging slot over NVLink and raises that tile's flag;
-//          once a CTA has finished its GEMM tiles it reduces the tiles this rank owns in fp32 as
-//          their eight partials land. Plays the role of the reference's `gemm_rs`
+//          this rank's own rows come last, and the epilogue of such a tile adds the other ranks'
+//          partials of it (in fp32) and stores the finished rows, so no reduce pass follows the
+//          GEMM. Plays the role of the reference's `gemm_rs`
 //          (python/triton_dist/kernels/nvidia/gemm_reduce_scatter.py:104-232,482-538 and
 //          reduce_scatter.py:527-685), where scatter and reduction are separate streams.
 //

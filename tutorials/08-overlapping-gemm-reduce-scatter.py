@@ -3,9 +3,9 @@
 Row-parallel linear: rank r holds ``X_r [M, K/ws]`` and ``W_r [N, K/ws]``; the sum over ranks of
 ``X_r @ W_r^T`` leaves row-scattered. The fused kernel computes tiles in the order *peers' row blocks first,
 own block last*; the epilogue of a tile stores it (TMA) straight into the owner's staging and raises the
-tile's flag there; the tail of the same kernel waits for the world-1 senders of each of this rank's tiles and
-adds them in fp32. The scatter of tile i overlaps the MMAs of tile i+1; only the last tile's transfer is
-exposed.
+tile's flag there; the epilogue of one of this rank's OWN tiles instead waits for the world-1 senders of that tile,
+adds their partials to the accumulator in fp32 and writes the finished rows. The scatter of tile i overlaps the MMAs
+of tile i+1; only the last tile's transfer is exposed, and there is no reduce pass after the GEMM.
 
 The script first runs the GEMM-RS half of ``tutorials/kernels/overlap_gemm.cu``: the same structure (tiles in
 "remote owners first" order, epilogue stores into the owner's staging, one flag per (tile, source), reduce tail) with a
