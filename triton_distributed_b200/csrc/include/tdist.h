@@ -68,7 +68,8 @@ typedef struct TdistGemmArgs {
     uint64_t timeout_ns;
     void* stream;
     /* Optional timeline, 2048 uint64 %globaltimer stamps (NULL = off). Pusher CTA b < 16 writes at
-     * [40b]: begin, end, then (start, end) of its first 19 blocks. GEMM CTA c < 64 writes at
+     * [40b]: begin, end, then (start, end) of its first 18 items, at [40b + 38] / [40b + 39] the ns it spent waiting for
+     * store completion / publishing flags. GEMM CTA c < 64 writes at
      * [1024 + 4c]: producer begin, producer end, ns spent waiting on flags, waits longer than 2 us. The MMA-issuing
      * thread of tile unit u < 64 writes at [1536 + 4u]: SM cycles in all, cycles waiting for operands (full
      * barriers), cycles waiting for a TMEM slot (epilogue not done), tiles computed. */

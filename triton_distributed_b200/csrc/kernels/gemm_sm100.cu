@@ -379,7 +379,7 @@ __device__ void ag_pusher(const GemmParams& p, uint8_t* smem, uint64_t* bars) {
             ++ld_c;
         }
         if (st_c < st.nchunks) {
-            if (tr && st_c == 0 && tr_item < 19) tr[2 + 2 * tr_item] = globaltimer_ns();
+            if (tr && st_c == 0 && tr_item < 18) tr[2 + 2 * tr_item] = globaltimer_ns();
             const uint32_t s = it_store % PUSH_STAGES;
             mbar_wait(full[s], (it_store / PUSH_STAGES) & 1u, p.wctx, 10);
             const size_t off = static_cast<size_t>(st_c) * PUSH_CHUNK;
@@ -414,7 +414,7 @@ __device__ void ag_pusher(const GemmParams& p, uint8_t* smem, uint64_t* bars) {
                     --pend_n;
                 }
             }
-            if (tr && tr_item < 19) tr[3 + 2 * tr_item] = globaltimer_ns();
+            if (tr && tr_item < 18) tr[3 + 2 * tr_item] = globaltimer_ns();
             ++tr_item;
             const int slot = (pend_head + pend_n) % PENDING;
             pend[slot] = st;
