@@ -25,7 +25,7 @@ from . import gemm as G
 from . import moe_ep as EP
 
 # 0 / -1 = the launcher's own choice; the other points bracket it
-AG_GEMM_SPACE = [{"num_comm_sms": c, "cta_pair": p} for p in (-1, 1, 2) for c in (0, 4, 8, 12)]
+AG_GEMM_SPACE = [{"num_comm_sms": c, "cta_pair": p} for p in (-1, 1, 2) for c in (0, 4, 8, 12, 16, 24)]
 GEMM_RS_SPACE = [{"cta_pair": p} for p in (-1, 1, 2)]
 DECODE_SPACE = [{"kv_split": s} for s in (-1, 4, 8, 16, 32, 64)]
 MOE_DISPATCH_SPACE = [{"num_ctas": c} for c in (0, 32, 64, 148)]
