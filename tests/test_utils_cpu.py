@@ -266,3 +266,24 @@ def test_ag_gemm_launch_plan_follows_the_measured_optima():
     assert (ctas, wide) == (2, 0) and 12 <= pushers <= 18
     ctas, wide, pushers, _ = plan(8, 8192, 11008, 4096)
     assert (ctas, wide) == (2, 0) and 14 <= pushers <= 18
+
+
+def test_counters_are_cleared_once_after_a_reported_abort(monkeypatch):
+    """Kernels that keep arrival counters in device memory leave them at zero; after a wait was reported (the launch
+    was cut short) the next use of the buffer clears them again, and only that one."""
+    from triton_distributed_b200.runtime import status as S
+
+    class FakeStatus:
+        aborts = 0
+
+    fake = FakeStatus()
+    monkeypatch.setattr(S, "global_status", lambda: fake)
+    t = torch.arange(12, dtype=torch.int32)
+    S.counters_clean(t, 8)
+    assert t[8:].tolist() == [8, 9, 10, 11]          # nothing was reported: untouched
+    fake.aborts = 1
+    S.counters_clean(t, 8)
+    assert t[:8].tolist() == list(range(8)) and t[8:].tolist() == [0, 0, 0, 0]
+    t[8:] = 5
+    S.counters_clean(t, 8)
+    assert t[8:].tolist() == [5, 5, 5, 5]            # same generation: not again

@@ -25,7 +25,7 @@ import torch.distributed as dist
 
 from .. import _lib
 from ..utils.profile import nvtx_range
-from ..runtime import SymmTensor, default_timeout_ns, global_status, symm_heap
+from ..runtime import SymmTensor, counters_clean, default_timeout_ns, global_status, symm_heap
 
 BLOCK_M = 128
 BLOCK_N = 256
@@ -205,6 +205,7 @@ def ag_gemm_intra_node(a: torch.Tensor, b: torch.Tensor, ctx: Optional[AllGather
         g.flags = ctx.flags.local[half].data_ptr()
         g.flags_peer = ctx.flags.half_ptr_arrays()[half]
         if ctx.push_count is not None and AG_PUSH_SLICES:
+            counters_clean(ctx.push_count)
             g.push_count = ctx.push_count.data_ptr()
         if ctx.workspace.mc is not None and (AG_NVLS == 2 or (AG_NVLS == 1 and ctx.world >= 4)):
             g.a_ws_mc = ctx.workspace.mc[half].data_ptr()   # the pushers multicast through the switch

@@ -29,7 +29,7 @@ import torch
 import torch.distributed as dist
 
 from .. import _lib
-from ..runtime import symm_heap
+from ..runtime import counters_clean, symm_heap
 from . import collectives as CO
 from . import gemm as G
 from . import moe_utils as MU
@@ -200,6 +200,7 @@ def group_gemm_gather(a: torch.Tensor, row_index: torch.Tensor, b: torch.Tensor,
         # flags first; the kernel's counters (4 + one per block) after the flags of the blocks the buffer was sized for
         g.gather_dst, g.block_ready = staging.data_ptr(), block_ready.data_ptr()
         g.gather_counter = block_ready.data_ptr() + 4 * ((block_ready.numel() - 4) // 2)
+        counters_clean(block_ready, (block_ready.numel() - 4) // 2)
     if block_rot is not None:
         g.block_rot = block_rot.data_ptr()
     if c_scatter is not None:

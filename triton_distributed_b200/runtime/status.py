@@ -39,6 +39,7 @@ class StatusBlock:
         dptr = C.c_void_p()
         _lib.check(_lib.lib().tdist_status_create(C.byref(dptr)), "tdist_status_create")
         self.device_ptr = dptr.value
+        self.aborts = 0   # reports raised so far: kernels cut short may have left in-kernel counters mid-count
 
     @property
     def record(self) -> "_lib.Status":
@@ -64,12 +65,24 @@ class StatusBlock:
     def check(self, reset: bool = True) -> None:
         rec = self.record
         if rec.abort_flag != 0:
+            self.aborts += 1
             if reset:
                 self.reset()
             raise _lib.TdistTimeoutError(self._describe(rec))
 
 
 _GLOBAL: Optional[StatusBlock] = None
+
+
+def counters_clean(t: torch.Tensor, start: int = 0) -> None:
+    """Some kernels keep arrival counters in device memory and leave them at zero when they finish. A launch that was
+    cut short by a reported wait may have left them mid-count: the first use of ``t`` after such a report zeroes
+    ``t[start:]`` again (an integer comparison on every other call)."""
+    st = global_status()
+    gen = st.aborts if st is not None else 0
+    if getattr(t, "_tdist_abort_gen", gen) != gen:
+        t[start:].zero_()
+    t._tdist_abort_gen = gen
 
 
 def global_status() -> Optional[StatusBlock]:
