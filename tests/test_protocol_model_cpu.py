@@ -1,8 +1,9 @@
 """The flag protocols of the fused kernels, modelled with CPU threads and C++ atomics (ranks = threads,
 st.release / ld.acquire = std::memory_order_release / acquire): epoch flags with two buffer halves and no barrier
 between calls, a peer that stops notifying (every waiter gives up within its limit and reports), LL packets whose
-flag must EQUAL the call number (so no rank may ever run two calls ahead), and the
-top-bit-flip grid barrier with a changing number of participants. No GPU involved."""
+flag must EQUAL the call number (so no rank may ever run two calls ahead), the
+top-bit-flip grid barrier with a changing number of participants, and the claim / copy / arrive scheme in which the
+last arriver of a block publishes its flag (row staging of the grouped GEMM, sliced AG pushers). No GPU involved."""
 import shutil
 import subprocess
 from pathlib import Path

@@ -13,6 +13,9 @@
 //      buffer halves and no barrier: the exchange of the sequence-parallel decode and of the LL all-gather. Here a
 //      writer that ran two calls ahead would make the reader wait forever for a flag value that was overwritten,
 //      so the model also proves that no rank can get two calls ahead.
+//   5. claim / copy / arrive with the last arriver publishing (the in-launch row staging of the grouped GEMM and the
+//      sliced pushers of the AG-GEMM): a consumer that sees a block's flag sees every row of it, and the cursor and the
+//      arrival counters are back at zero when the call ends.
 //
 // Build and run: g++ -O2 -std=c++17 -pthread flag_protocol_model.cc -o model && ./model [ranks] [calls] [seed]
 // Prints "OK ..." and exits 0, or the first violation and exits 1.
@@ -188,6 +191,70 @@ void run_ll_rank(int rank, int world, int calls, unsigned seed, std::vector<LLRa
     }
 }
 
+// ---- claim, copy, arrive; the last arriver publishes (row staging of the grouped GEMM, sliced AG pushers)
+// Workers (the epilogue warps of all CTAs / the pusher CTAs) claim groups of a block from one cursor, write the group's
+// rows with plain stores, then add to the block's arrival counter (acq_rel). The worker whose add completes the block
+// resets the counter for the next call and release-stores the block's flag = call number. Consumers (the TMA producers
+// / the peer's MMA side) acquire-wait for flag >= call and must then see this call's value in EVERY row of the block.
+// The cursor is rewound by the last worker to leave the call (an exit counter), as the kernel does.
+bool staging_model(unsigned seed, int calls) {
+    constexpr int kBlocks = 12, kGroups = 4, kRows = 3, kWorkers = 6, kConsumers = 3;
+    std::vector<std::atomic<uint32_t>> rows(kBlocks * kGroups * kRows), flag(kBlocks), arrive(kBlocks);
+    for (auto& r : rows) r.store(0, std::memory_order_relaxed);
+    for (auto& f : flag) f.store(0, std::memory_order_relaxed);
+    for (auto& a : arrive) a.store(0, std::memory_order_relaxed);
+    std::atomic<uint32_t> cursor{0}, exits{0}, start{0};
+    std::atomic<int> bad{0};
+    auto worker = [&](int id) {
+        std::mt19937 rng(seed * 7919u + id);
+        for (uint32_t e = 1; e <= static_cast<uint32_t>(calls); ++e) {
+            while (start.load(std::memory_order_acquire) < e) std::this_thread::yield();   // the launch of call e
+            while (true) {
+                const uint32_t item = cursor.fetch_add(1, std::memory_order_relaxed);
+                if (item >= kBlocks * kGroups) break;
+                const int b = item / kGroups, g = item % kGroups;
+                if (rng() % 4 == 0) std::this_thread::yield();
+                for (int r = 0; r < kRows; ++r) rows[(b * kGroups + g) * kRows + r].store(e * 1000u + b, std::memory_order_relaxed);
+                if (arrive[b].fetch_add(1, std::memory_order_acq_rel) == kGroups - 1) {
+                    arrive[b].store(0, std::memory_order_relaxed);
+                    flag[b].store(e, std::memory_order_release);
+                }
+            }
+            if (exits.fetch_add(1, std::memory_order_acq_rel) == kWorkers + kConsumers - 1) {
+                cursor.store(0, std::memory_order_relaxed);
+                exits.store(0, std::memory_order_relaxed);
+                start.store(e + 1, std::memory_order_release);   // the next launch starts after this one has ended
+            }
+        }
+    };
+    auto consumer = [&](int id) {
+        for (uint32_t e = 1; e <= static_cast<uint32_t>(calls); ++e) {
+            while (start.load(std::memory_order_acquire) < e) std::this_thread::yield();
+            for (int b = id; b < kBlocks; b += kConsumers) {
+                uint32_t spins = 0;
+                while (static_cast<int32_t>(flag[b].load(std::memory_order_acquire) - e) < 0)
+                    if ((++spins & 255u) == 0) std::this_thread::yield();
+                for (int i = 0; i < kGroups * kRows; ++i)
+                    if (rows[b * kGroups * kRows + i].load(std::memory_order_relaxed) != e * 1000u + b) bad.store(1);
+            }
+            if (exits.fetch_add(1, std::memory_order_acq_rel) == kWorkers + kConsumers - 1) {
+                cursor.store(0, std::memory_order_relaxed);
+                exits.store(0, std::memory_order_relaxed);
+                start.store(e + 1, std::memory_order_release);
+            }
+        }
+    };
+    start.store(1, std::memory_order_release);
+    std::vector<std::thread> th;
+    for (int i = 0; i < kWorkers; ++i) th.emplace_back(worker, i);
+    for (int i = 0; i < kConsumers; ++i) th.emplace_back(consumer, i);
+    for (auto& t : th) t.join();
+    bool ok = bad.load() == 0 && cursor.load() == 0;
+    for (auto& a : arrive) ok = ok && a.load() == 0;
+    if (!ok) std::fprintf(stderr, "VIOLATION staging: a consumer saw a row of another call, or a counter was left non-zero\n");
+    return ok;
+}
+
 }  // namespace
 
 int main(int argc, char** argv) {
@@ -256,6 +323,8 @@ int main(int argc, char** argv) {
             return 1;
         }
     }
+    // 5. claim / copy / arrive, last arriver publishes; counters return to zero for the next call
+    if (!staging_model(seed + 3, calls)) return 1;
     std::printf("OK world=%d calls=%d seed=%u\n", world, calls, seed);
     return 0;
 }
