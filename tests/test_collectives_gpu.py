@@ -11,7 +11,7 @@ from triton_distributed_b200.runtime import LocalWorld, check_status
 pytestmark = pytest.mark.gpu
 
 
-@pytest.mark.parametrize("mode", ["pull", "push2d", "push2d_ll"])
+@pytest.mark.parametrize("mode", ["pull", "push2d", "push_ordered", "push2d_ll"])
 @pytest.mark.parametrize("world,seg", [(2, 4096), (4, 40), (8, 1 << 20), (4, 33 * 16 + 8)])
 def test_fast_allgather_modes(cuda_device, mode, world, seg):
     torch.manual_seed(seg)

@@ -35,7 +35,7 @@ def main():
 
     # ---- all-gather, every mode, several sizes, byte-exact
     ag = {}
-    for mode in (["pull", "push2d", "push2d_ll"] if cuda else ["pull"]):
+    for mode in (["pull", "push2d", "push_ordered", "push2d_ll"] if cuda else ["pull"]):
         for seg in ([512, 4096 + 8, 1 << 20] if cuda else [4096]):
             buf = heap.empty((world * seg,), torch.uint8)
             ctx = CO.create_fast_allgather_context(rank, 0, world, 1, max_buffer_size=world * seg, group=group, device=dev)

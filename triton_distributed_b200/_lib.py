@@ -196,7 +196,7 @@ class PrimArgs(C.Structure):
 GEMM_PLAIN, GEMM_AG, GEMM_RS = 0, 1, 2
 A2A_DISPATCH, A2A_COMBINE = 0, 1
 DT_BF16, DT_F16, DT_F32, DT_I32 = 0, 1, 2, 3
-AG_PULL, AG_PUSH, AG_LL = 0, 1, 2
+AG_PULL, AG_PUSH, AG_LL, AG_PUSH_ORDERED = 0, 1, 2, 3
 
 
 def bounds_checked() -> bool:

@@ -529,7 +529,7 @@ def _run_suite(args, world, rank, group, dev, dtype, pk):
         for kv in (32768, 131072, 1048576):
             run("sp_decode", _bench_decode, batch=batch, kv=kv, hq=32, hkv=8, head_dim=128, iters=30)
     if world > 1:
-        for mode in ("pull", "push2d", "push2d_ll"):
+        for mode in ("pull", "push2d", "push_ordered", "push2d_ll"):
             for nbytes in (65536, 16 << 20):
                 run("allgather", _bench_allgather, mode=mode, bytes=nbytes, iters=30)
         if os.environ.get("TDIST_NVLS", "0") == "1":

@@ -163,7 +163,9 @@ typedef struct TdistGemmFp8Args {
 int tdist_gemm_fp8_run(const TdistGemmFp8Args* args);
 
 /* ------------------------------------------------------------------ standalone collectives */
-enum { TDIST_AG_PULL = 0, TDIST_AG_PUSH = 1, TDIST_AG_LL = 2 };
+/* PUSH_ORDERED: like PUSH, but all copy CTAs serve one destination after the other, rank - 1 first (the order in which the
+ * consumers of a rotated schedule need this rank's segment), so that segments arrive one by one instead of all at the end */
+enum { TDIST_AG_PULL = 0, TDIST_AG_PUSH = 1, TDIST_AG_LL = 2, TDIST_AG_PUSH_ORDERED = 3 };
 
 typedef struct TdistCollArgs {
     /* all-gather: the in-place symmetric buffer [world * seg_bytes] of every rank as mapped here.

@@ -58,13 +58,13 @@ __device__ __forceinline__ void slice_range(size_t bytes, int i, int n, size_t* 
     *end = min(bytes, per * (i + 1) * 16);
 }
 
-// Last CTA of the group (all its stores fenced) publishes this rank's flag on `peer`.
-__device__ __forceinline__ void group_signal(const CollParams& p, int peer) {
+// Last CTA of the group of `ctas` (all its stores fenced) publishes this rank's flag on `peer`.
+__device__ __forceinline__ void group_signal(const CollParams& p, int peer, int ctas) {
     // one fencing thread per CTA: the barrier orders the CTA's stores before thread 0's release
     __syncthreads();
     if (threadIdx.x == 0) {
         const uint32_t old = atom_add_acq_rel_gpu_u32(p.counters + peer, 1);
-        if (old == static_cast<uint32_t>(p.ctas_per_peer - 1)) {
+        if (old == static_cast<uint32_t>(ctas - 1)) {
             p.counters[peer] = 0;
             fence_acq_rel_sys();
             st_release_sys_u64(p.sig_peer[peer] + p.rank, p.epoch);
@@ -89,7 +89,27 @@ __global__ void __launch_bounds__(kCollThreads) allgather_kernel(const CollParam
         }
         if (p.phase & 1) {
             copy_coop(p.buf_peer[peer] + p.rank * seg + b0, local + p.rank * seg + b0, b1 - b0, threadIdx.x, blockDim.x);
-            group_signal(p, peer);
+            group_signal(p, peer, p.ctas_per_peer);
+        }
+    } else if (p.mode == TDIST_AG_PUSH_ORDERED) {
+        if (g == 0) {
+            if ((p.phase & 2) && static_cast<int>(threadIdx.x) < p.world && static_cast<int>(threadIdx.x) != p.rank)
+                signal_wait_until(p.sig_peer[p.rank] + threadIdx.x, kCmpGe, p.epoch, p.wctx, threadIdx.x, 1);
+            return;
+        }
+        if (p.phase & 1) {
+            // every copy CTA sends its slice of the segment to one destination after the other, the rank before this
+            // one first: a consumer that starts at its own rows and goes on with rank + 1, rank + 2, ... finds each
+            // segment complete about when it gets there, instead of all of them at the end
+            const int ctas = (p.world - 1) * p.ctas_per_peer;
+            size_t s0, s1;
+            slice_range(seg, static_cast<int>(blockIdx.x) - 1, ctas, &s0, &s1);
+            for (int h = 1; h < p.world; ++h) {
+                int dest = p.rank - h;
+                if (dest < 0) dest += p.world;
+                copy_coop(p.buf_peer[dest] + p.rank * seg + s0, local + p.rank * seg + s0, s1 - s0, threadIdx.x, blockDim.x);
+                group_signal(p, dest, ctas);
+            }
         }
     } else if (p.mode == TDIST_AG_PULL) {
         if (g == 0) {
@@ -224,7 +244,7 @@ __global__ void __launch_bounds__(kCollThreads) reduce_scatter_kernel(const Coll
         } else {
             copy_coop(dst + b0, p.input + static_cast<size_t>(peer) * seg + b0, b1 - b0, threadIdx.x, blockDim.x);
         }
-        group_signal(p, peer);
+        group_signal(p, peer, p.ctas_per_peer);
     }
     if (!(p.phase & 2)) return;
     // every CTA waits for all sources, then takes its share of the reduction
@@ -323,7 +343,7 @@ extern "C" int tdist_allgather(const TdistCollArgs* a) {
     CollParams p;
     int rc = fill_params(a, &p);
     if (rc) return rc;
-    if (a->mode < TDIST_AG_PULL || a->mode > TDIST_AG_LL) return fail(TDIST_EINVAL, "allgather: bad mode");
+    if (a->mode < TDIST_AG_PULL || a->mode > TDIST_AG_PUSH_ORDERED) return fail(TDIST_EINVAL, "allgather: bad mode");
     if (a->mode == TDIST_AG_LL) {
         if (a->seg_bytes % 8 != 0) return fail(TDIST_EINVAL, "LL all-gather needs a segment size that is a multiple of 8 bytes");
         for (int r = 0; r < a->world; ++r)

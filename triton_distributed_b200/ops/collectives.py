@@ -33,6 +33,7 @@ launch_count = 0
 
 _AG_MODES = {
     "pull": _lib.AG_PULL,
+    "push_ordered": _lib.AG_PUSH_ORDERED,   # all copy CTAs serve rank - 1 first, then rank - 2, ...: segments land one by one
     "push": _lib.AG_PUSH, "push2d": _lib.AG_PUSH, "push3d": _lib.AG_PUSH, "push_numa_2d": _lib.AG_PUSH,
     "ll": _lib.AG_LL, "push2d_ll": _lib.AG_LL, "push3d_ll": _lib.AG_LL, "push_numa_2d_ll": _lib.AG_LL,
     "push_numa_2d_ll_multinode": _lib.AG_LL, "push2d_ll_multimem": _lib.AG_LL, "nvls": _lib.AG_LL,

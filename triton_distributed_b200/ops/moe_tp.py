@@ -22,6 +22,7 @@ test/nvidia/test_ag_moe.py:24-39).
 """
 from __future__ import annotations
 
+import os
 from dataclasses import dataclass
 from typing import Optional, Tuple
 
@@ -45,6 +46,19 @@ GROUP_BLOCK_M = 128
 #   "cp_async" the grouped GEMM's producer warps gather the rows themselves with 16-byte cp.async copies (kept for
 #              comparison: 2.2x slower than "staged", the L2 request rate saturates long before TMA does).
 AG_GROUP_GEMM_MODE = "fused"
+# All-gather feeding the one-launch forms. "push" sends to all peers at once: every segment lands at the end of the
+# all-gather. "push_ordered" sends the segments in the order the grouped GEMM of each peer reaches them (rank + 1's
+# first), one fence per destination more. "auto": ordered above four ranks. Measured at tp4 (8192 tokens, hidden 4096,
+# 3584 columns per rank), where the GEMM of a rank's own blocks (~110 us) outlasts the whole all-gather (~100 us): 602 us
+# ordered, 585 us at once. At tp8 the own blocks take ~35 us of a ~145 us all-gather, which is what the ordered form is
+# for; that case has not been timed.
+AG_PUSH_MODE = os.environ.get("TDIST_MOE_AG_PUSH_MODE", "auto")
+
+
+def _ag_push_mode(world: int) -> str:
+    if AG_PUSH_MODE != "auto":
+        return AG_PUSH_MODE
+    return "push_ordered" if world > 4 else "push"
 FUSED_AG_GROUP_GEMM = False   # legacy switch: True selects "cp_async"
 FUSED_TOPK_RS = True   # False: separate top-k reduce kernel, then the plain reduce-scatter (for A/B checks)
 launch_count = 0
@@ -319,7 +333,7 @@ def ag_group_gemm_intra_node(a: torch.Tensor, b: torch.Tensor, ctx: MoEAllGather
             # send half of the all-gather only; the grouped GEMM launch gathers its A rows itself and waits, block by
             # block, for the arrival flag of the rank the block's tokens come from
             if phase != 2:
-                CO.fast_allgather(buf, ctx.ag_ctx, mode="push", phase=1)
+                CO.fast_allgather(buf, ctx.ag_ctx, mode=_ag_push_mode(ctx.world), phase=1)
             if phase == 1:
                 return None
             src = dict(block_src=ctx.block_barrier_ids, src_flags=ctx.ag_ctx.signal.local, src_epoch=ctx.ag_ctx.epoch,

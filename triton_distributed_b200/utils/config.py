@@ -24,6 +24,7 @@ class Config:
     ag_push_slices: int = 0              # TDIST_AG_PUSH_SLICES: 1 = AG-GEMM pushers send a 128-row block as parallel row slices
     ag_push_ahead: int = 5               # TDIST_AG_PUSH_AHEAD: chunks a pusher's loads run ahead of its stores (1..5)
     ag_split_first: int = 1              # TDIST_AG_SPLIT_FIRST: 0 = keep the first round of the wide AG schedule whole
+    moe_ag_push_mode: str = "auto"       # TDIST_MOE_AG_PUSH_MODE: all-gather of the one-launch AG + GroupGEMM: auto | push | push_ordered
     rs_fused_reduce: int = 1             # TDIST_RS_FUSED_REDUCE: 0 = GEMM-RS reduces the owned tiles in a pass after the GEMM
     decode_cluster_merge: int = 1        # TDIST_DECODE_CLUSTER_MERGE: 0 = the KV splits of flash decode always meet in global memory
     gemm_cta_pair: int = -1              # TDIST_GEMM_CTA_PAIR: -1 automatic, 0 one CTA per 128x256 tile, 1 CTA pair per 256x256, 2 CTA pair per 256x512
@@ -35,7 +36,7 @@ class Config:
     _ENV = {
         "wait_timeout_ms": "TDIST_WAIT_TIMEOUT_MS", "symm_heap_bytes": "TDIST_SYMM_HEAP_BYTES", "heap_backend": "TDIST_HEAP_BACKEND",
         "nvls": "TDIST_NVLS", "ag_gemm_nvls": "TDIST_AG_GEMM_NVLS", "ag_push_slices": "TDIST_AG_PUSH_SLICES",
-        "ag_push_ahead": "TDIST_AG_PUSH_AHEAD", "ag_split_first": "TDIST_AG_SPLIT_FIRST", "decode_cluster_merge": "TDIST_DECODE_CLUSTER_MERGE", "rs_fused_reduce": "TDIST_RS_FUSED_REDUCE",
+        "ag_push_ahead": "TDIST_AG_PUSH_AHEAD", "ag_split_first": "TDIST_AG_SPLIT_FIRST", "decode_cluster_merge": "TDIST_DECODE_CLUSTER_MERGE", "rs_fused_reduce": "TDIST_RS_FUSED_REDUCE", "moe_ag_push_mode": "TDIST_MOE_AG_PUSH_MODE",
         "gemm_cta_pair": "TDIST_GEMM_CTA_PAIR",
         "gemm_group_m": "TDIST_GEMM_GROUP_M", "bounds_check": "TDIST_BOUNDS_CHECK", "nvtx": "TDIST_NVTX", "nvcc": "TDIST_NVCC",
     }
