@@ -287,3 +287,19 @@ def test_counters_are_cleared_once_after_a_reported_abort(monkeypatch):
     t[8:] = 5
     S.counters_clean(t, 8)
     assert t[8:].tolist() == [5, 5, 5, 5]            # same generation: not again
+
+
+def test_launch_heuristics_on_the_host():
+    """Host-side choices that need no GPU: KV splits of flash decode (at least 256 keys per split, one wave of the machine
+    at most), the flag words of a staged row gather, the push order of the MoE all-gather."""
+    from triton_distributed_b200.ops import flash_decode as FD
+    from triton_distributed_b200.ops import moe_tp as MT
+
+    dev = torch.device("cpu")
+    assert FD.default_splits(1, 8, 4096, dev) == 16          # 4096 keys -> 16 splits of 256
+    assert FD.default_splits(1, 8, 100, dev) == 1
+    assert FD.default_splits(8, 8, 131072, dev) <= 8         # 64 (batch, head) pairs already fill the machine
+    assert 16 <= FD.default_splits(1, 8, 1 << 20, dev) <= 256
+    flags = MT.staging_flags(1000, dev)                      # 8 blocks: 8 flags + 4 + 8 counters
+    assert flags.dtype == torch.int32 and flags.numel() == 2 * 8 + 4 and int(flags.abs().sum()) == 0
+    assert MT._ag_push_mode(2) == "push" and MT._ag_push_mode(4) == "push" and MT._ag_push_mode(8) == "push_ordered"

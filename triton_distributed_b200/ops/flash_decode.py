@@ -36,6 +36,8 @@ _SM_COUNT = {}
 
 
 def _sm_count(device) -> int:
+    if getattr(device, "type", "cuda") != "cuda":
+        return 148   # planning on a host without a GPU: the B200's SM count
     idx = device.index if device.index is not None else torch.cuda.current_device()
     if idx not in _SM_COUNT:
         _SM_COUNT[idx] = torch.cuda.get_device_properties(idx).multi_processor_count
