@@ -115,7 +115,7 @@ def test_reference_names_resolve_on_cpu():
     assert CO.ring_reduce(x, out, 1, 4).allclose(x.view(4, 2, 4).sum(0))
     assert CO.inter_node_allgather is CO.cp_engine_producer_all_gather_intra_node
     assert G.ag_gemm_inter_node is G.ag_gemm_intra_node and MT.ag_group_gemm_inter_node is MT.ag_group_gemm_intra_node
-    assert FD.gqa_fwd_batch_decode_aot is FD.gqa_fwd_batch_decode
+    assert callable(FD.gqa_fwd_batch_decode_aot) and FD.gqa_fwd_batch_decode_persistent is FD.gqa_fwd_batch_decode
     padded = G.padded_to_BLOCK_M(torch.arange(12.0).view(6, 2), 2, 4)
     assert padded.shape == (8, 2) and padded[3].abs().sum() == 0 and padded[4].tolist() == [6.0, 7.0]
     ids = torch.tensor([[0, 3], [3, 1]], dtype=torch.int32)
@@ -303,3 +303,46 @@ def test_launch_heuristics_on_the_host():
     flags = MT.staging_flags(1000, dev)                      # 8 blocks: 8 flags + 4 + 8 counters
     assert flags.dtype == torch.int32 and flags.numel() == 2 * 8 + 4 and int(flags.abs().sum()) == 0
     assert MT._ag_push_mode(2) == "push" and MT._ag_push_mode(4) == "push" and MT._ag_push_mode(8) == "push_ordered"
+
+
+def test_every_name_of_the_reference_api_sheet_is_in_the_top_level_namespace():
+    """A user of the reference finds its public Python names on ``import triton_distributed_b200 as tdist``: runtime and
+    pynvshmem-style host calls, utilities, op contexts and ops, layers, decorators."""
+    import math
+
+    import triton_distributed_b200 as tdist
+    names = """initialize_distributed TP_GROUP nvshmem_create_tensor nvshmem_create_tensor_list_intra_node symm_tensor
+    nvshmem_barrier_all nvshmemx_barrier_all_on_stream nvshmem_my_pe nvshmem_n_pes nvshmem_team_my_pe nvshmem_team_n_pes
+    nvshmem_ptr nvshmemx_mc_ptr nvshmemx_putmem_on_stream nvshmemx_putmem_signal_on_stream nvshmem_putmem nvshmem_getmem
+    nvshmem_int_p wait_eq set_signal barrier_all_on_stream perf_func dist_print group_profile generate_data assert_allclose
+    init_seed get_has_nvlink get_numa_world_size check_p2p_native_atomic_supported p2p_native_atomic_required
+    create_ag_gemm_intra_node_context ag_gemm_intra_node gemm_persistent gemm_non_persistent create_ag_gemm_inter_node_context
+    ag_gemm_inter_node create_gemm_rs_context gemm_rs create_reduce_scater_2d_ctx reduce_scatter_2d_op ring_reduce
+    reduce_scatter_ring_push_1d_intra_node_ce reduce_scatter_ring_push_1d_intra_node_sm
+    cp_engine_producer_all_gather_intra_node inter_node_allgather AllGatherMethod get_auto_all_gather_method
+    create_fast_allgather_context fast_allgather AllGatherLayer create_all_to_all_context fast_all_to_all
+    all_to_all_post_process EPAll2AllLayer bincount get_dispatch_send_reqs_for_target_node
+    get_ag_splits_and_recv_offset_for_dispatch gqa_fwd_batch_decode gqa_fwd_batch_decode_intra_rank
+    gqa_fwd_batch_decode_persistent gqa_fwd_batch_decode_aot gqa_fwd_batch_decode_intra_rank_aot
+    gqa_fwd_batch_decode_persistent_aot get_triton_combine_kv_algo_info kernel_inter_rank_gqa_fwd_batch_decode_combine_kv
+    SpGQAFlashDecodeAttention sort_topk_ids_align_block_size create_ag_group_gemm_intra_node_context
+    ag_group_gemm_intra_node create_ag_group_gemm_inter_node_context select_experts create_moe_rs_context moe_reduce_rs
+    contextual_autotune aot_compile_spaces""".split()
+    missing = [n for n in names if not hasattr(tdist, n)]
+    assert not missing, missing
+
+    # the *_aot variants are the same calls with the stream in front (None = current stream)
+    torch.manual_seed(0)
+    B, Hq, Hkv, D, page = 2, 4, 2, 64, 4
+    q = torch.randn(B, Hq, D)
+    k = torch.randn(6, page, Hkv, D)
+    v = torch.randn(6, page, Hkv, D)
+    lens = torch.tensor([5, 9], dtype=torch.int32)
+    table = torch.tensor([[0, 1, 2], [3, 4, 5]], dtype=torch.int32)
+    scale = 1.0 / math.sqrt(D)
+    want = tdist.gqa_fwd_batch_decode(q, k, v, None, None, lens, table, scale)
+    got = tdist.gqa_fwd_batch_decode_aot(None, q, k, v, None, None, lens, table, scale)
+    assert torch.equal(got, want)
+    part = tdist.gqa_fwd_batch_decode_intra_rank_aot(None, q, k, v, None, None, lens, table, scale)
+    assert part.shape == (B, Hq, D + 1) and torch.allclose(part[..., :D], want, atol=1e-5)
+    assert tdist.bincount(torch.tensor([[0, 2], [2, 1]], dtype=torch.int32), 4).tolist() == [1, 1, 2, 0]

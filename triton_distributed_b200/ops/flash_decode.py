@@ -175,9 +175,30 @@ def gqa_fwd_batch_decode(q, k_cache, v_cache, workspace=None, q_lens=None, kv_le
 
 
 gqa_fwd_batch_decode_persistent = gqa_fwd_batch_decode
-# The reference's AOT-compiled entry points (flash_decode.py `*_aot`): kernels here are always compiled ahead of time.
-gqa_fwd_batch_decode_aot = gqa_fwd_batch_decode
-gqa_fwd_batch_decode_persistent_aot = gqa_fwd_batch_decode
+
+
+def _on_stream(stream, fn, *args, **kwargs):
+    """Run ``fn`` with ``stream`` (a torch stream, a raw ``cudaStream_t`` value, or None) as the current stream."""
+    if stream is None or not torch.cuda.is_available():
+        return fn(*args, **kwargs)
+    if isinstance(stream, int):
+        stream = torch.cuda.ExternalStream(stream)
+    with torch.cuda.stream(stream):
+        return fn(*args, **kwargs)
+
+
+# The reference's AOT-compiled entry points (kernels/nvidia/flash_decode.py `*_aot`): the same calls with the stream as
+# the leading argument. Kernels here are always compiled ahead of time, so they are thin wrappers.
+def gqa_fwd_batch_decode_aot(stream, q, k_cache, v_cache, *args, **kwargs):
+    return _on_stream(stream, gqa_fwd_batch_decode, q, k_cache, v_cache, *args, **kwargs)
+
+
+def gqa_fwd_batch_decode_persistent_aot(stream, q, k_cache, v_cache, *args, **kwargs):
+    return _on_stream(stream, gqa_fwd_batch_decode, q, k_cache, v_cache, *args, **kwargs)
+
+
+def gqa_fwd_batch_decode_intra_rank_aot(stream, q, k_cache, v_cache, *args, **kwargs):
+    return _on_stream(stream, gqa_fwd_batch_decode_intra_rank, q, k_cache, v_cache, *args, **kwargs)
 
 
 def gqa_fwd_batch_decode_intra_rank(q, k_cache, v_cache, workspace=None, q_lens=None, kv_lens=None, block_table=None,

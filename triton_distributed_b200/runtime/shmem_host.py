@@ -190,3 +190,8 @@ def nvshmem_p(t: SymmTensor, index: int, value, pe: int) -> None:
     # a device-to-device memcpy of one element (copy engine): no library kernel is handed the peer's memory
     src = torch.tensor([value], dtype=t.local.dtype, device=t.local.device)
     t.peers[pe].reshape(-1)[index:index + 1].copy_(src)
+
+
+# nvshmem_<type>_p of the reference's host binding (pynvshmem.cc:107-215): the element type comes from the tensor
+nvshmem_int_p = nvshmem_int32_p = nvshmem_int64_p = nvshmem_long_p = nvshmem_uint64_p = nvshmem_float_p = nvshmem_p
+nvshmem_half_p = nvshmem_bfloat16_p = nvshmem_double_p = nvshmem_p
