@@ -70,6 +70,13 @@ __device__ __forceinline__ bool wait_eq(const uint64_t* p, uint64_t value, const
     return signal_wait_until(p, kCmpEq, value, w, -1, 50);
 }
 
+// warp intrinsics over 32-bit values (reference `__shfl_sync_i32`, `__shfl_up_sync_i32`, `__shfl_down_sync_i32`,
+// `__ballot_sync`; spelled without the leading underscores, which C++ reserves)
+__device__ __forceinline__ int shfl_sync_i32(unsigned mask, int value, int src_lane) { return __shfl_sync(mask, value, src_lane); }
+__device__ __forceinline__ int shfl_up_sync_i32(unsigned mask, int value, unsigned delta) { return __shfl_up_sync(mask, value, delta); }
+__device__ __forceinline__ int shfl_down_sync_i32(unsigned mask, int value, unsigned delta) { return __shfl_down_sync(mask, value, delta); }
+__device__ __forceinline__ unsigned ballot_sync(unsigned mask, bool predicate) { return __ballot_sync(mask, predicate); }
+
 // vector loads / stores used by the LL protocol
 __device__ __forceinline__ uint4 load_v4_u32(const void* p) {
     uint4 v;

@@ -215,12 +215,15 @@ __global__ void prim_kernel(const PrimParams p) {
                     atomicAdd(p.result, 1);  // lock never obtained
                 }
             }
-            const unsigned ballot = __ballot_sync(0xffffffffu, (threadIdx.x & 1) != 0);
-            int sum = static_cast<int>(threadIdx.x & 31);
+            const int ln = static_cast<int>(threadIdx.x & 31);
+            const unsigned ballot = language_extra::ballot_sync(0xffffffffu, (threadIdx.x & 1) != 0);
+            int sum = ln;
 #pragma unroll
             for (int o = 16; o >= 1; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
-            const int up = __shfl_up_sync(0xffffffffu, static_cast<int>(threadIdx.x & 31), 1);
-            const bool warp_ok = ballot == 0xaaaaaaaau && sum == 496 && ((threadIdx.x & 31) == 0 || up == static_cast<int>(threadIdx.x & 31) - 1);
+            const int up = language_extra::shfl_up_sync_i32(0xffffffffu, ln, 1);
+            const int down = language_extra::shfl_down_sync_i32(0xffffffffu, ln, 2);
+            const int from7 = language_extra::shfl_sync_i32(0xffffffffu, ln * 3, 7);
+            const bool warp_ok = ballot == 0xaaaaaaaau && sum == 496 && (ln == 0 || up == ln - 1) && (ln >= 30 || down == ln + 2) && from7 == 21;
             if (__all_sync(0xffffffffu, warp_ok) && (threadIdx.x & 31) == 0) red_release_gpu_add_u32(w + 5, 1u);
             break;
         }
