@@ -326,7 +326,7 @@ def test_every_name_of_the_reference_api_sheet_is_in_the_top_level_namespace():
     gqa_fwd_batch_decode_persistent gqa_fwd_batch_decode_aot gqa_fwd_batch_decode_intra_rank_aot
     gqa_fwd_batch_decode_persistent_aot get_triton_combine_kv_algo_info kernel_inter_rank_gqa_fwd_batch_decode_combine_kv
     SpGQAFlashDecodeAttention sort_topk_ids_align_block_size create_ag_group_gemm_intra_node_context
-    ag_group_gemm_intra_node create_ag_group_gemm_inter_node_context select_experts create_moe_rs_context moe_reduce_rs
+    ag_group_gemm_intra_node ag_group_gemm_inter_node create_ag_group_gemm_inter_node_context select_experts create_moe_rs_context moe_reduce_rs
     contextual_autotune aot_compile_spaces""".split()
     missing = [n for n in names if not hasattr(tdist, n)]
     assert not missing, missing

@@ -26,7 +26,7 @@ from .ops.gemm import (ag_gemm_inter_node, ag_gemm_intra_node, create_ag_gemm_in
 from .ops.gemm_fp8 import (ag_gemm_fp8, create_ag_gemm_fp8_context, gemm_fp8_blockscaled, quantize_fp8_blockwise,  # noqa: F401
                            quantize_fp8_rowwise)
 from .ops.moe_ep import create_ep_context, ep_combine, ep_dispatch, expert_out_buffer  # noqa: F401
-from .ops.moe_tp import (ag_group_gemm_intra_node, create_ag_group_gemm_inter_node_context,  # noqa: F401
+from .ops.moe_tp import (ag_group_gemm_inter_node, ag_group_gemm_intra_node, create_ag_group_gemm_inter_node_context,  # noqa: F401
                          create_ag_group_gemm_intra_node_context, create_moe_rs_context, group_gemm, moe_reduce_rs,
                          select_experts, sort_topk_ids_align_block_size)
 from .ops.moe_utils import bincount  # noqa: F401
