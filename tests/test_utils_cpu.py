@@ -346,3 +346,52 @@ def test_every_name_of_the_reference_api_sheet_is_in_the_top_level_namespace():
     part = tdist.gqa_fwd_batch_decode_intra_rank_aot(None, q, k, v, None, None, lens, table, scale)
     assert part.shape == (B, Hq, D + 1) and torch.allclose(part[..., :D], want, atol=1e-5)
     assert tdist.bincount(torch.tensor([[0, 2], [2, 1]], dtype=torch.int32), 4).tolist() == [1, 1, 2, 0]
+
+
+def test_small_utilities_of_the_reference(tmp_path):
+    """is_cuda / is_hip / is_fp8_dtype, the deterministic-mode guard, CUDA_CHECK, the tolerant trace loader and the
+    nvidia-smi / sysfs topology parsers, all without a GPU."""
+    import enum
+    import json
+
+    from triton_distributed_b200 import utils as U
+
+    assert U.is_hip() is False and U.is_cuda() == (torch.cuda.is_available() and torch.version.hip is None)
+    assert U.is_fp8_dtype(torch.float8_e4m3fn) and U.is_fp8_dtype(torch.float8_e5m2)
+    assert not U.is_fp8_dtype(torch.int8) and not U.is_fp8_dtype(torch.bfloat16)
+
+    before = torch.are_deterministic_algorithms_enabled()
+    with pytest.raises(ValueError):
+        with U.with_torch_deterministic(not before):
+            assert torch.are_deterministic_algorithms_enabled() == (not before)
+            raise ValueError("inside")
+    assert torch.are_deterministic_algorithms_enabled() == before
+
+    class Res(enum.IntEnum):
+        OK = 0
+        BAD = 700
+    assert U.CUDA_CHECK(Res.OK) is None and U.CUDA_CHECK((Res.OK, 42)) == 42 and U.CUDA_CHECK((0, 1, 2)) == (1, 2)
+    with pytest.raises(RuntimeError, match="700"):
+        U.CUDA_CHECK((Res.BAD, None))
+
+    good = tmp_path / "trace_rank3.json"
+    good.write_text(json.dumps({"traceEvents": [{"ph": "M", "name": "process_name", "pid": 7, "args": {"name": "python"}},
+                                                {"ph": "X", "name": "k", "pid": 7, "tid": 1, "ts": 0, "dur": 1}]}))
+    ev = U.process_trace_json(str(good))
+    assert ev[1]["pid"] == 7 + 3 * 100_000_000 and ev[0]["args"]["name"].startswith("rank 3")
+    bad = tmp_path / "bad.json"
+    bad.write_text('{"traceEvents": [{"ph": "X", "name": "void f<"a">(int)\x01", "pid": 1}]}')
+    tr = U.load_json(str(bad))
+    assert tr["traceEvents"][0]["pid"] == 1 and '"' not in tr["traceEvents"][0]["name"]
+
+    topo = ("\tGPU0\tGPU1\tGPU2\tNIC0\tCPU Affinity\n"
+            "GPU0\t X \tNV18\tNV18\tSYS\t0-55\n"
+            "GPU1\tNV18\t X \tPIX\tSYS\t0-55\n"
+            "GPU2\tNV18\tPIX\t X \tSYS\t56-111\n"
+            "NIC0\tSYS\tSYS\tSYS\t X \n")
+    assert U.NvidiaSmiUtil.parse_topo_matrix(topo) == [[0, 1, 1], [1, 0, -1], [1, -1, 0]]
+    dev = tmp_path / "0000:17:00.0"
+    dev.mkdir()
+    (dev / "numa_node").write_text("1\n")
+    assert U.NvidiaSmiUtil.numa_node_of_bus_id("00000000:17:00.0\n", str(tmp_path)) == 1
+    assert U.NvidiaSmiUtil.numa_node_of_bus_id("00000000:99:00.0", str(tmp_path)) == -1

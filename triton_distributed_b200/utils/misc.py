@@ -173,3 +173,120 @@ def p2p_native_atomic_required(fn):
             return None
         return fn(*a, **kw)
     return wrapped
+
+
+# ---------------------------------------------------------------------------- small predicates and guards
+def is_cuda() -> bool:
+    """A CUDA (not ROCm) build of torch with a GPU present (reference utils.py:50-52)."""
+    return bool(torch.cuda.is_available() and torch.version.hip is None)
+
+
+def is_hip() -> bool:
+    """Always False here: the library is sm_100a only (reference utils.py:55-57)."""
+    return bool(torch.cuda.is_available() and torch.version.hip is not None)
+
+
+def is_fp8_dtype(dtype: torch.dtype) -> bool:
+    """One-byte floating-point types (e4m3, e5m2 and their variants); reference utils.py:130-131."""
+    return dtype.is_floating_point and torch.empty((), dtype=dtype).element_size() == 1
+
+
+class with_torch_deterministic:
+    """``with with_torch_deterministic(True): ...`` switches torch's deterministic-algorithms mode for the block and
+    puts the previous mode back afterwards, also when the block raises (reference utils.py:121-127). Also usable as a
+    decorator."""
+
+    def __init__(self, mode: bool, warn_only: bool = True):
+        self.mode, self.warn_only = mode, warn_only
+
+    def __enter__(self):
+        self._old = torch.are_deterministic_algorithms_enabled()
+        self._old_warn = torch.is_deterministic_algorithms_warn_only_enabled()
+        torch.use_deterministic_algorithms(self.mode, warn_only=self.warn_only)
+        return self
+
+    def __exit__(self, *exc):
+        torch.use_deterministic_algorithms(self._old, warn_only=self._old_warn)
+        return False
+
+    def __call__(self, fn):
+        import functools
+
+        @functools.wraps(fn)
+        def wrapper(*a, **kw):
+            with with_torch_deterministic(self.mode, self.warn_only):
+                return fn(*a, **kw)
+        return wrapper
+
+
+def CUDA_CHECK(err):
+    """Raise unless ``err`` is a success code. Accepts what cuda-python calls return (a result enum, or a tuple whose
+    first element is one: the rest of the tuple is handed back), a plain integer, or a ``tdist`` return code
+    (reference utils.py:233-241)."""
+    rest = None
+    if isinstance(err, tuple):
+        err, rest = err[0], err[1:]
+    code = int(getattr(err, "value", err))
+    if code != 0:
+        name = getattr(err, "name", None) or str(err)
+        raise RuntimeError(f"CUDA error {code}: {name}")
+    if rest is None:
+        return None
+    return rest[0] if len(rest) == 1 else rest
+
+
+# ---------------------------------------------------------------------------- topology from nvidia-smi / sysfs
+class NvidiaSmiUtil:
+    """Topology facts read from ``nvidia-smi`` text and sysfs, for hosts without NVML bindings (reference
+    utils.py:504-544). The parsers take the text as an argument so that they can be checked without a GPU."""
+
+    @staticmethod
+    def parse_topo_matrix(text: str):
+        """``nvidia-smi topo -m`` output -> square matrix with 1 where two GPUs are linked by NVLink (``NV<n>``), 0 on
+        the diagonal, -1 otherwise."""
+        rows = [ln.split() for ln in text.splitlines() if ln.startswith("GPU") and len(ln.split()) > 1 and ln.split()[0][3:].isdigit()]
+        n = len(rows)
+        out = [[-1] * n for _ in range(n)]
+        for i, cols in enumerate(rows):
+            for j in range(n):
+                cell = cols[1 + j] if 1 + j < len(cols) else ""
+                out[i][j] = 0 if cell == "X" else (1 if cell.startswith("NV") else -1)
+        return out
+
+    @staticmethod
+    def get_nvlink_adjacency_matrix():
+        import subprocess
+        return NvidiaSmiUtil.parse_topo_matrix(subprocess.check_output(["nvidia-smi", "topo", "-m"], text=True, timeout=30))
+
+    @staticmethod
+    def numa_node_of_bus_id(bus_id: str, sysfs_root: str = "/sys/bus/pci/devices") -> int:
+        """NUMA node of the PCI device ``bus_id`` (``00000000:17:00.0`` as nvidia-smi prints it); -1 when unknown."""
+        import os
+        short = bus_id.strip().lower()
+        if short.count(":") == 2 and len(short.split(":")[0]) == 8:
+            short = short[4:]                       # 8-digit domain -> the 4 digits sysfs uses
+        try:
+            with open(os.path.join(sysfs_root, short, "numa_node")) as f:
+                return max(int(f.read().strip()), 0)
+        except (OSError, ValueError):
+            return -1
+
+    @staticmethod
+    def get_gpu_numa_node(gpu_index: int = 0) -> int:
+        import subprocess
+        try:
+            bus = subprocess.check_output(["nvidia-smi", "--query-gpu=pci.bus_id", "--format=csv,noheader,nounits", "-i", str(gpu_index)],
+                                          text=True, timeout=30)
+        except (OSError, subprocess.SubprocessError):
+            return -1
+        return NvidiaSmiUtil.numa_node_of_bus_id(bus)
+
+
+def get_numa_node(gpu_index: int = 0) -> int:
+    """NUMA node the GPU hangs off: NVML when it knows, else nvidia-smi + sysfs, else -1 (reference utils.py:581-586)."""
+    try:
+        import pynvml
+        pynvml.nvmlInit()
+        return int(pynvml.nvmlDeviceGetNumaNodeId(pynvml.nvmlDeviceGetHandleByIndex(gpu_index)))
+    except Exception:  # noqa: BLE001 - no NVML, old driver, no GPU
+        return NvidiaSmiUtil.get_gpu_numa_node(gpu_index)

@@ -111,3 +111,37 @@ class group_profile:
         if world > 1:
             dist.barrier(self.group)
         return False
+
+
+def load_json(json_file: str) -> dict:
+    """Read a Chrome-trace JSON written by the torch profiler. Kernel names can carry raw control characters or
+    unescaped quotes that strict parsers refuse: those are replaced inside every ``"name": "..."`` value before
+    parsing (reference utils.py:254-279)."""
+    import json
+    import re
+    with open(json_file, "r", encoding="utf-8", errors="replace") as f:
+        text = f.read()
+    try:
+        return json.loads(text, strict=False)
+    except json.JSONDecodeError:
+        pass
+
+    def clean(match):
+        body = "".join(c if (32 <= ord(c) < 127 and c not in '"\\{}') else "_" for c in match.group(1))
+        return f'"name": "{body}"'
+
+    return json.loads(re.sub(r'"name": "(.*?)"(?=\s*[,}])', clean, text, flags=re.DOTALL), strict=False)
+
+
+def process_trace_json(json_file: str, rank: Optional[int] = None) -> list:
+    """Events of one rank's trace file with its process ids moved into the rank's own range, ready to be concatenated
+    with the other ranks' (reference utils.py:282-309). The rank comes from the argument, else from the trace's
+    ``distributedInfo``, else from a ``rank<N>`` part of the file name, else 0."""
+    import re
+    trace = load_json(json_file)
+    if rank is None:
+        rank = trace.get("distributedInfo", {}).get("rank")
+    if rank is None:
+        m = re.search(r"rank[_-]?(\d+)", str(json_file))
+        rank = int(m.group(1)) if m else 0
+    return _shift_ids(trace, int(rank))
