@@ -1410,7 +1410,11 @@ static void plan_ag(const TdistGemmArgs* a, int sms, int n_tiles, GridPlan& g) {
     const int step = g.ctas_per_tile;
     const int seg_m_tiles = (a->m_per_rank + BM * g.ctas_per_tile - 1) / (BM * g.ctas_per_tile);
     const int nc_lo = a->num_comm_sms > 0 ? a->num_comm_sms : step;
-    const int nc_hi = a->num_comm_sms > 0 ? a->num_comm_sms : 18;
+    // never more pushers than there are (destination, 128-row block) items to push
+    const int seg_blocks = (a->m_per_rank + BM - 1) / BM;
+    int nc_cap = (a->world - 1) * seg_blocks;
+    nc_cap = (nc_cap + step - 1) / step * step;
+    const int nc_hi = a->num_comm_sms > 0 ? a->num_comm_sms : (nc_cap < 18 ? (nc_cap < step ? step : nc_cap) : 18);
     const bool may_wide = g.ctas_per_tile == 2 && a->cta_pair != 1 && a->k >= 4096 && a->n > BN;
     const bool may_narrow = !(g.ctas_per_tile == 2 && a->cta_pair == 2 && may_wide);
     double best_t = 1e30;
